@@ -1,0 +1,124 @@
+/*
+ * fftopk.h — C ABI of the B200 (sm_100a) per-row top-2048 radix selector.
+ *
+ * This is the native boundary a host binds instead of the reference's pybind11
+ * module `topk_indexer_radix` (jit_kernel/csrc/topk_indexer/topk_indexer_radix.cu:1252-1257),
+ * whose `fast_topk(score, indices, lengths, row_starts)` takes at::Tensor objects.
+ * Here every argument is a plain pointer or integer; no torch / ATen type crosses
+ * the boundary.
+ *
+ * Conventions shared by every entry point that takes a stream:
+ *   - returns 0 (FFTOPK_OK) or a negative FFTOPK_E* code; never throws;
+ *   - enqueues work on `cuda_stream` (a cudaStream_t passed as void*; NULL = the
+ *     legacy default stream) and returns without synchronising;
+ *   - never allocates or frees device memory; every buffer is caller-owned;
+ *   - all device pointers must belong to the device that is current on the
+ *     calling thread;
+ *   - output rows are written completely by the kernel (no -1 pre-fill needed,
+ *     unlike the reference, jit_kernel/topk_indexer.py:68-70).
+ */
+#ifndef FFTOPK_H_
+#define FFTOPK_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FFTOPK_K 2048 /* the only supported k (reference: TopK, topk_indexer_radix.cu:69) */
+
+enum {
+  FFTOPK_OK = 0,
+  FFTOPK_EINVAL = -1,  /* bad argument (null pointer, negative size, bad stride)        */
+  FFTOPK_ECUDA = -2,   /* a CUDA runtime call failed; see fftopk_last_cuda_error()      */
+  FFTOPK_EDEVICE = -3, /* device is not sm_100 class or lacks cluster launch            */
+  FFTOPK_ERANGE = -4,  /* size beyond what the entry point supports                     */
+};
+
+/* Bits the kernels may OR into the optional device status word. */
+enum {
+  FFTOPK_ST_STAGE_TIMEOUT = 1, /* a bounded wait on a bulk-copy barrier ran out; the row was
+                                  re-read with plain loads, results are still correct       */
+  FFTOPK_ST_INTERNAL = 2,      /* an internal count did not add up (should never be seen)  */
+  FFTOPK_ST_PEER_TIMEOUT = 4,  /* merge: a bounded wait on a peer's ready flag ran out      */
+};
+
+/* Library version: major*10000 + minor*100 + patch. */
+int fftopk_version(void);
+
+/* Text for an FFTOPK_E* code. */
+const char* fftopk_strerror(int code);
+
+/* cudaError_t of the most recent failing CUDA call made by this library on the calling
+ * thread (0 if none). */
+int fftopk_last_cuda_error(void);
+
+/*
+ * Per-row top-2048 selection.
+ * Replaces fast_topk_interface (topk_indexer_radix.cu:1051-1158) and topk_kernel (:854-869).
+ *
+ *   score        device, fp32, B rows; row b starts at score + b*row_stride (elements),
+ *                inner stride 1 (reference check: topk_indexer_radix.cu:1003)
+ *   row_stride   elements between consecutive rows (>= 0)
+ *   B, L         rows and padded row length; B == 0 is a no-op
+ *   lengths      device, int32 [B]; valid elements of row b. Values are clamped to
+ *                [0, L - row_start]
+ *   row_starts   device, int32 [B] or NULL; first valid element of row b
+ *                (reference: topk_indexer_radix.cu:858, 541-542)
+ *   out_idx      device, int32 [B, 2048]. Row b receives, in unspecified order, the indices
+ *                (relative to row_starts[b]) of the 2048 largest valid elements; among equal
+ *                values the lower index is selected. -0.0 compares equal to +0.0 and NaN
+ *                above +inf, as torch.topk orders them. A row with len <= 2048 receives
+ *                0..len-1 followed by -1 (reference: naive_topk_cuda, :152-163)
+ *   out_key      device, uint32 [B, 2048] or NULL; when given, slot i receives the
+ *                order-preserving radix key of the element out_idx names (0 where out_idx is
+ *                -1). Used by the context-parallel merge; no reference counterpart
+ *   idx_offset   added to every index written (the global position of this shard's first
+ *                element in context-parallel mode; 0 otherwise)
+ *   status       device, uint32 [1] or NULL; FFTOPK_ST_* bits are OR-ed in, never cleared
+ */
+int fftopk_select2048(const float* score, int64_t row_stride, int32_t B, int64_t L,
+                      const int32_t* lengths, const int32_t* row_starts,
+                      int32_t* out_idx, uint32_t* out_key, int32_t idx_offset,
+                      uint32_t* status, void* cuda_stream);
+
+/*
+ * Merge of per-shard candidates into the global top-2048 (context-parallel mode: every GPU
+ * selected a local top-2048 over its sequence shard, the candidates were all-gathered).
+ * No reference counterpart: the reference has no multi-GPU path.
+ *
+ *   cand_key     device, uint32 [G, B, 2048]   keys written by fftopk_select2048(out_key)
+ *   cand_idx     device, int32  [G, B, 2048]   global indices (idx_offset applied); -1 = empty
+ *   G            number of shards (1..8)
+ *   out_idx      device, int32 [B, 2048]; the 2048 candidates largest by (key, lower index),
+ *                unspecified order; -1 padded when fewer than 2048 candidates are valid
+ *   out_key      device, uint32 [B, 2048] or NULL
+ */
+int fftopk_merge2048(const uint32_t* cand_key, const int32_t* cand_idx, int32_t G, int32_t B,
+                     int32_t* out_idx, uint32_t* out_key, uint32_t* status, void* cuda_stream);
+
+/*
+ * Radix key of one fp32 value, computed on the host with the same function the kernels use
+ * (the order-preserving map the reference defines as convert_to_uint32,
+ * topk_indexer_radix.cu:206-209, plus -0.0 / NaN canonicalisation). For tests and bindings.
+ */
+uint32_t fftopk_key_of(float x);
+
+/*
+ * Launch-plan introspection and overrides (experiments and tests; not needed in production).
+ * fftopk_plan reports what fftopk_select2048 would launch for (B, L) on the current device:
+ * plan[0] = CTAs per cluster (= CTAs per row), plan[1] = threads per CTA,
+ * plan[2] = dynamic shared memory bytes, plan[3] = staged floats per CTA,
+ * plan[4] = candidate capacity, plan[5] = SM count.
+ * fftopk_set_tuning overrides the automatic choice process-wide; pass -1 to restore "auto".
+ * Replaces the reference's compile-time split heuristic (topk_indexer_radix.cu:1081-1111).
+ */
+int fftopk_plan(int32_t B, int64_t L, int32_t plan[6]);
+int fftopk_set_tuning(int32_t cluster_ctas, int32_t threads, int32_t stage_kib, int32_t cand_cap);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FFTOPK_H_ */
