@@ -4,30 +4,41 @@
 // (jit_kernel/csrc/topk_indexer/topk_indexer_radix.cu:456-869) and the host launcher
 // fast_topk_interface (:1051-1158).
 //
-// Shape of the computation for one row of `len` > 2048 valid fp32 logits, C CTAs in the cluster:
-//   1. every CTA owns a contiguous shard; the TMA engine bulk-copies as much of it as fits into
-//      shared memory (16 chunks, one mbarrier each), the rest is streamed with 128-bit loads;
-//   2. round 0 histograms the top 12 bits of the order-preserving key (4096 bins) per CTA;
-//   3. after ONE cluster barrier every CTA reads its peers' 64 super-bin sums, then the 64 fine
-//      bins of the threshold super-bin, over distributed shared memory, and picks the threshold
-//      bin with a warp-shuffle suffix scan (no L2 atomics, no broadcast barrier);
-//   4. a second scan (from shared memory where staged, else from L2) writes the indices of
-//      elements above the threshold bin straight to the output and pushes the threshold-bin
-//      survivors into rank 0's shared memory; after the second cluster barrier rank 0 resolves
-//      them with radix passes over (key, inverted index) composites and a warp
-//      compare-exchange network for the last <= 32;
-//   5. if the threshold bin holds more survivors than rank 0 can take (heavy ties, narrow value
-//      ranges) the cluster keeps refining on the next 12 and 8 key bits, and exact ties that
-//      remain after all 32 bits are taken in index order, shard by shard.
+// Shape of the computation for one row of `len` > 2048 valid fp32 logits, C CTAs in the cluster,
+// each owning a contiguous shard of the row:
+//   1. SAMPLE. Every warp reads one 512-byte slab; the slabs are spread evenly over the shards,
+//      so the cluster samples the row uniformly in position. The top 12 bits of the
+//      order-preserving key are histogrammed per CTA (4096 bins). When the whole shard fits in
+//      registers (<= 4 granules per thread) the "sample" is the shard and step 2 is exact.
+//   2. PICK. After ONE cluster barrier every CTA reads its peers' 64 super-bin sums, then the 64
+//      fine bins of the threshold super-bin, over distributed shared memory, and finds the bin
+//      with a warp-shuffle suffix scan (no L2 atomics, no reduce-then-broadcast). From a sample it
+//      takes the bin whose sample rank is the expected rank of the k-th element plus five standard
+//      deviations: a lower bound of the true threshold with overwhelming probability.
+//   3. FILTER. One streaming pass over the shard (128-bit loads, eight in flight per thread) with
+//      ONE float compare per element against the bin's lower edge; the few thousand elements that
+//      pass go to a per-CTA list in shared memory as (key << 32 | ~index) composites. This is the
+//      only full read of the row.
+//   4. RESOLVE. The lists are histogrammed, a second cluster pick gives the exact threshold bin,
+//      elements above it are written straight to the output, the threshold bin's elements are
+//      pushed into rank 0's shared memory, and after the last cluster barrier rank 0 finishes with
+//      radix passes over the composites and a warp compare-exchange network for the last <= 32.
+//      The inverted index in the composite makes equal values resolve to the lower index.
+//   5. If the guess admitted fewer than k elements, a list overflowed or the threshold bin is
+//      larger than rank 0's buffer (heavy ties, rows of equal values), the cluster falls back to
+//      full histograms over the data: 12 + 12 + 8 key bits, re-reading the shard from L2 each
+//      round, and exact ties left after 32 bits are taken in index order, shard by shard.
 #include <cooperative_groups.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
 #include "../../include/fftopk.h"
+#include "fftopk_trace.cuh"
 #include "fftopk_device.cuh"
 #include "fftopk_key.h"
 
 namespace fftopk {
+
 
 struct SelectParams {
   const float* score;
@@ -40,13 +51,16 @@ struct SelectParams {
   uint32_t* status;
   int32_t B;
   int32_t idx_offset;
-  int32_t stage_floats;  // shared-memory staging capacity per CTA, multiple of 128
-  int32_t cand_cap;      // candidate capacity of rank 0
+  int32_t list_cap;  // per-CTA candidate list capacity (entries), multiple of 16
+  int32_t cand_cap;  // rank 0's gathered-candidate capacity (entries), multiple of 16
+  int32_t force_slow;  // tests: skip the filter path and run the full-histogram path
 };
 
-enum Mode : int { kModeNext = 0, kModeGather = 1, kModeTakeAll = 2, kModeTies = 3, kModeAbort = 4 };
+enum Mode : int { kModeNext = 0, kModeGather = 1, kModeTakeAll = 2, kModeTies = 3, kModeAbort = 4, kModeFallback = 5 };
 
-// digit schedule of the distributed rounds: 12 + 12 + 8 bits
+constexpr int kRegSlabs = 4;  // granules a thread keeps in registers when the whole shard fits
+
+// digit schedule of the full-histogram rounds: 12 + 12 + 8 bits
 __device__ __forceinline__ int round_width(int r) { return r < 2 ? 12 : 8; }
 __device__ __forceinline__ int round_shift(int r) { return r == 0 ? 20 : (r == 1 ? 8 : 0); }
 
@@ -54,83 +68,169 @@ __device__ __forceinline__ int round_shift(int r) { return r == 0 ? 20 : (r == 1
 // elements 4g-a .. 4g-a+3, where a in 0..3 is the row's misalignment in elements.
 struct Shard {
   const float* gbase;  // 16-byte aligned address of granule 0
-  const float4* stage; // shared-memory copy of granules [g0, g0 + n_stage)
-  uint64_t* mbar;
   int g0, g1;          // granule range of this CTA
-  int n_stage;         // staged granules
-  int chunk_g;         // granules per bulk-copy chunk
+  int i0, i1;          // the part of [g0, g1) whose granules lie completely inside the row
   int a;               // misalignment (elements)
   int len;             // valid elements in the row
 };
 
-// One granule from global memory; reads only bytes that belong to the row.
-__device__ __forceinline__ float4 load_granule(const Shard& sh, int g) {
-  const int i0 = 4 * g - sh.a;
-  if (i0 >= 0 && i0 + 3 < sh.len) {
-    return __ldg(reinterpret_cast<const float4*>(sh.gbase) + g);
-  }
-  float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
-  const float* p = sh.gbase + 4 * (int64_t)g;
-  if ((unsigned)(i0 + 0) < (unsigned)sh.len) x.x = __ldg(p + 0);
-  if ((unsigned)(i0 + 1) < (unsigned)sh.len) x.y = __ldg(p + 1);
-  if ((unsigned)(i0 + 2) < (unsigned)sh.len) x.z = __ldg(p + 2);
-  if ((unsigned)(i0 + 3) < (unsigned)sh.len) x.w = __ldg(p + 3);
+// A granule that straddles the start or the end of the row (at most two per row): scalar loads of
+// the elements that belong to the row, `fill` elsewhere. Kept out of line so that the streaming
+// loops stay small enough to unroll with every load in flight.
+__device__ __noinline__ float4 load_granule_partial(const float* gbase, int a, int len, int g, float fill) {
+  const int i0 = 4 * g - a;
+  float4 x = make_float4(fill, fill, fill, fill);
+  const float* p = gbase + 4 * (int64_t)g;
+  if ((unsigned)(i0 + 0) < (unsigned)len) x.x = __ldg(p + 0);
+  if ((unsigned)(i0 + 1) < (unsigned)len) x.y = __ldg(p + 1);
+  if ((unsigned)(i0 + 2) < (unsigned)len) x.z = __ldg(p + 2);
+  if ((unsigned)(i0 + 3) < (unsigned)len) x.w = __ldg(p + 3);
   return x;
 }
 
-__device__ __forceinline__ bool granule_full(const Shard& sh, int g) {
-  const int i0 = 4 * g - sh.a;
-  return i0 >= 0 && i0 + 3 < sh.len;
+// One granule from global memory; reads only bytes that belong to the row.
+__device__ __forceinline__ float4 load_granule(const Shard& sh, int g, float fill) {
+  if (g >= sh.i0 && g < sh.i1) return __ldg(reinterpret_cast<const float4*>(sh.gbase) + g);
+  return load_granule_partial(sh.gbase, sh.a, sh.len, g, fill);
 }
 
-// Visit every element of the shard: op(key, idx, valid) is called by all threads of every warp
-// together (valid = false for padding lanes), so op may use warp-synchronous primitives.
-// WAIT: first visit, the staged chunks are consumed as their bulk copies land.
-template <int NT, bool WAIT, class Op>
-__device__ __forceinline__ void scan_shard(const Shard& sh, Ctrl* ctrl, Op&& op) {
+// The one full read of the shard: every element x with !(x < edge) is appended to a candidate
+// list in shared memory as a (key << 32 | ~idx) composite. Every warp owns a private segment of
+// the list (`wcap` entries) and keeps its fill count in a register, identical in all lanes: per
+// loop trip a thread has U 128-bit loads in flight, compares 4*U elements, and if any lane of
+// the warp found something a shuffle scan hands every lane its slots. No atomics: allocating
+// slots from one shared counter serialised at ~20 cycles per candidate and dominated the pass.
+// Returns the warp's count, which exceeds wcap when the segment overflowed.
+template <int NT, int U>
+__device__ __forceinline__ uint32_t filter_shard(const Shard& sh, float edge, uint64_t* seg, uint32_t wcap) {
   const int tid = threadIdx.x;
-  auto proc = [&](const float4& x, int g, bool in) {
-    const int i0 = 4 * g - sh.a;
-    op(fftopk_key_from_bits(__float_as_uint(x.x)), i0 + 0, in && (unsigned)(i0 + 0) < (unsigned)sh.len);
-    op(fftopk_key_from_bits(__float_as_uint(x.y)), i0 + 1, in && (unsigned)(i0 + 1) < (unsigned)sh.len);
-    op(fftopk_key_from_bits(__float_as_uint(x.z)), i0 + 2, in && (unsigned)(i0 + 2) < (unsigned)sh.len);
-    op(fftopk_key_from_bits(__float_as_uint(x.w)), i0 + 3, in && (unsigned)(i0 + 3) < (unsigned)sh.len);
-  };
-  // ---- staged part -------------------------------------------------------------------------
-  if (sh.n_stage > 0) {
-    const bool use_stage = WAIT ? true : (ctrl->stage_fail == 0u);
-    const int nchunk = WAIT ? (sh.n_stage + sh.chunk_g - 1) / sh.chunk_g : 1;
-    for (int c = 0; c < nchunk; ++c) {
-      bool ok = use_stage;
-      if (WAIT) {
-        ok = mbar_wait_bounded(&sh.mbar[c], 0u);
-        if (!ok) ctrl->stage_fail = 1u;
-      }
-      const int gbeg = WAIT ? c * sh.chunk_g : 0;
-      const int gend = WAIT ? min(gbeg + sh.chunk_g, sh.n_stage) : sh.n_stage;
-      for (int gb = gbeg; gb < gend; gb += NT) {
-        const int gl = gb + tid;
-        const bool in = gl < gend;
-        const int g = sh.g0 + gl;
-        float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (in) x = (ok && granule_full(sh, g)) ? sh.stage[gl] : load_granule(sh, g);
-        proc(x, g, in);
-      }
-    }
-  }
-  // ---- streamed part -----------------------------------------------------------------------
-  constexpr int U = 4;
-  for (int gb = sh.g0 + sh.n_stage; gb < sh.g1; gb += NT * U) {
+  const int lane = tid & 31;
+  const float ninf = __uint_as_float(0xff800000u);
+  const float4* base4 = reinterpret_cast<const float4*>(sh.gbase);
+  const int fa = sh.a, fi1 = sh.i1, len = sh.len;
+  uint32_t wc = 0;
+  for (int gb = sh.i0; gb < fi1; gb += NT * U) {
     float4 x[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int g = gb + u * NT + tid;
-      x[u] = (g < sh.g1) ? load_granule(sh, g) : make_float4(0.f, 0.f, 0.f, 0.f);
+      x[u] = make_float4(ninf, ninf, ninf, ninf);
+      if (g < fi1) x[u] = __ldg(base4 + g);
+    }
+    // common case first: one compare per element, OR-ed per granule; the 16-bit pass mask is only
+    // built by lanes that saw something
+    bool hit[U];
+    bool any = false;
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      hit[u] = !(x[u].x < edge) | !(x[u].y < edge) | !(x[u].z < edge) | !(x[u].w < edge);
+      any |= hit[u];
+    }
+    if (!__any_sync(kFull, any)) continue;
+    uint32_t mask = 0;  // bit 4u+e: element e of granule u passes and lies inside the row
+    if (any) {
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (hit[u] && (gb + u * NT + tid) < fi1) {  // padding lanes hold -inf, which passes an edge of -inf
+          const unsigned e0 = (unsigned)(4 * (gb + u * NT + tid) - fa);
+          mask |= (!(x[u].x < edge) && e0 + 0u < (unsigned)len) ? (1u << (4 * u + 0)) : 0u;
+          mask |= (!(x[u].y < edge) && e0 + 1u < (unsigned)len) ? (1u << (4 * u + 1)) : 0u;
+          mask |= (!(x[u].z < edge) && e0 + 2u < (unsigned)len) ? (1u << (4 * u + 2)) : 0u;
+          mask |= (!(x[u].w < edge) && e0 + 3u < (unsigned)len) ? (1u << (4 * u + 3)) : 0u;
+        }
+      }
+    }
+    {
+      const uint32_t cnt = (uint32_t)__popc(mask);
+      uint32_t incl = cnt;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const uint32_t v = __shfl_up_sync(kFull, incl, off);
+        if (lane >= off) incl += v;
+      }
+      uint32_t pos = wc + incl - cnt;
+      wc += __shfl_sync(kFull, incl, 31);
+      if (mask != 0u) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          if ((mask >> (4 * u)) & 0xfu) {
+            const int e0 = 4 * (gb + u * NT + tid) - fa;
+            const float xv[4] = {x[u].x, x[u].y, x[u].z, x[u].w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              if ((mask >> (4 * u + e)) & 1u) {
+                if (pos < wcap)
+                  seg[pos] = ((uint64_t)fftopk_key_from_bits(__float_as_uint(xv[e])) << 32) |
+                             (uint64_t)(~(uint32_t)(e0 + e));
+                ++pos;
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+  // edge granules [g0, i0) and [i1, g1): at most one each, visited by lane 0 of warps 0 and 1
+  {
+    const int ge = (tid == 0) ? sh.g0 : ((tid == 32) ? sh.i1 : -1);
+    const int ge_end = (tid == 0) ? sh.i0 : sh.g1;
+    if (ge >= 0 && ge < ge_end) {
+      const float4 x = load_granule_partial(sh.gbase, sh.a, len, ge, ninf);
+      const int e0 = 4 * ge - fa;
+      const float xv[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        if ((unsigned)(e0 + e) < (unsigned)len && !(xv[e] < edge)) {
+          if (wc < wcap)
+            seg[wc] = ((uint64_t)fftopk_key_from_bits(__float_as_uint(xv[e])) << 32) | (uint64_t)(~(uint32_t)(e0 + e));
+          ++wc;
+        }
+      }
+    }
+    wc = __shfl_sync(kFull, wc, 0);
+  }
+  return wc;
+}
+
+// Visit every valid element of the shard: op(key, idx). Interior granules are read with
+// unconditional 128-bit loads, four in flight per thread; the at most two granules that straddle
+// the row's ends are visited by one thread each through scalar loads.
+template <int NT, class Op>
+__device__ __forceinline__ void scan_shard(const Shard& sh, Op&& op) {
+  const int tid = threadIdx.x;
+  const float4* base4 = reinterpret_cast<const float4*>(sh.gbase);
+  const int a = sh.a, i1 = sh.i1;
+  constexpr int U = 4;
+  for (int gb = sh.i0; gb < i1; gb += NT * U) {
+    float4 x[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int g = gb + u * NT + tid;
+      x[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (g < i1) x[u] = __ldg(base4 + g);
     }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int g = gb + u * NT + tid;
-      proc(x[u], g, g < sh.g1);
+      if (g < i1) {
+        const int e0 = 4 * g - a;
+        op(fftopk_key_from_bits(__float_as_uint(x[u].x)), e0 + 0);
+        op(fftopk_key_from_bits(__float_as_uint(x[u].y)), e0 + 1);
+        op(fftopk_key_from_bits(__float_as_uint(x[u].z)), e0 + 2);
+        op(fftopk_key_from_bits(__float_as_uint(x[u].w)), e0 + 3);
+      }
+    }
+  }
+  // edge granules of this shard: [g0, i0) and [i1, g1), at most one granule each
+  const int ge = (tid == 0) ? sh.g0 : ((tid == 32) ? sh.i1 : -1);
+  const int ge_end = (tid == 0) ? sh.i0 : sh.g1;
+  if (ge >= 0 && ge < ge_end) {
+    const float4 x = load_granule_partial(sh.gbase, sh.a, sh.len, ge, 0.f);
+    const int e0 = 4 * ge - a;
+    const float xv[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      if ((unsigned)(e0 + e) < (unsigned)sh.len) op(fftopk_key_from_bits(__float_as_uint(xv[e])), e0 + e);
     }
   }
 }
@@ -140,8 +240,8 @@ template <int NT>
 __device__ __forceinline__ void compute_sup(const uint32_t* hist, uint32_t* sup, int nb) {
   const int tid = threadIdx.x;
   if (nb == kMaxBins) {
-    constexpr int PER = kMaxBins / NT;       // bins per thread: 4 (1024 thr), 8 (512), 16 (256)
-    constexpr int TPS = (kMaxBins / kSup) / PER;  // threads per super-bin: 16, 8, 4
+    constexpr int PER = kMaxBins / NT;            // bins per thread: 4 (1024 thr), 8 (512)
+    constexpr int TPS = (kMaxBins / kSup) / PER;  // threads per super-bin: 16, 8
     uint32_t s = 0;
     const uint4* h4 = reinterpret_cast<const uint4*>(hist) + tid * (PER / 4);
 #pragma unroll
@@ -160,143 +260,66 @@ __device__ __forceinline__ void compute_sup(const uint32_t* hist, uint32_t* sup,
   }
 }
 
-template <int NT>
-__global__ void __launch_bounds__(NT, 1) select2048_kernel(const SelectParams p) {
-  cg::cluster_group cluster = cg::this_cluster();
-  const int C = (int)cluster.num_blocks();
-  const int rank = (int)cluster.block_rank();
-  const int row = (int)(blockIdx.x / (unsigned)C);
+// What warp 0 knows after a cluster-wide threshold search.
+struct Picked {
+  bool ok;            // false: the histogram holds fewer than `need` elements
+  int t;              // threshold bin
+  uint32_t need2;     // elements still to take from bin t
+  uint32_t cnt;       // cluster-wide population of bin t
+  uint32_t local_w;   // this CTA's elements in bins above t
+  uint32_t local_c;   // this CTA's elements in bin t
+  uint32_t total;     // cluster-wide number of histogrammed elements
+  uint32_t any_flag;  // OR of the peers' published flags
+  int tf;             // t's position inside its super-bin (index into xch rows)
+};
+
+// Cluster-wide threshold search on per-CTA histograms `h` (nb bins) with super-bin sums `s`,
+// both complete and published by a cluster barrier before the call. Every CTA reads its peers'
+// 64 super-bin sums, then the fine bins of the threshold super-bin, over distributed shared
+// memory; warp 0 picks with shuffle scans. need_of(total) maps the cluster-wide element count
+// to the rank searched for. `post(picked)` runs in warp 0 (all lanes) before the closing
+// barrier; the results it wants every thread to see go through `ctrl`.
+// Replaces parallel_reduce_histogram + radix_prefix_sum of the reference
+// (topk_indexer_radix.cu:80-107, 232-279), which reduce to rank 0 and broadcast back with three
+// cluster barriers and eight block barriers per round.
+template <int NT, class NeedFn, class Post>
+__device__ __forceinline__ void cluster_pick(cg::cluster_group& cluster, int C, const uint32_t* h, const uint32_t* s,
+                                             uint32_t* xch, Ctrl* ctrl, int nb, NeedFn&& need_of, Post&& post) {
   const int tid = threadIdx.x;
   const int lane = tid & 31, warp = tid >> 5;
-
-  int64_t row_start = p.row_starts ? (int64_t)p.row_starts[row] : 0;
-  row_start = row_start < 0 ? 0 : (row_start > p.L ? p.L : row_start);
-  int64_t len64 = (int64_t)p.lengths[row];
-  len64 = len64 < 0 ? 0 : len64;
-  len64 = len64 > p.L - row_start ? p.L - row_start : len64;
-  const int len = (int)len64;
-  const float* rowp = p.score + (int64_t)row * p.row_stride + row_start;
-  int32_t* out_idx = p.out_idx + (int64_t)row * kK;
-  uint32_t* out_key = p.out_key ? p.out_key + (int64_t)row * kK : nullptr;
-
-  // Short rows: 0..len-1 then -1 (reference: naive_topk_cuda, topk_indexer_radix.cu:152-163).
-  if (len <= kK) {
-    if (rank == 0) {
-      for (int i = tid; i < kK; i += NT) {
-        out_idx[i] = i < len ? i + p.idx_offset : -1;
-        if (out_key) out_key[i] = i < len ? fftopk_key_from_bits(__float_as_uint(__ldg(rowp + i))) : 0u;
-      }
-    }
-    return;  // uniform over the cluster; no shared memory of this CTA is ever read by a peer
+  const int fine = nb / kSup;
+  for (int i = tid; i < C * kSup; i += NT) {
+    const uint32_t* rs = cluster.map_shared_rank(s, i / kSup);
+    xch[i] = rs[i % kSup];
   }
-
-  // ---- shared memory carve ---------------------------------------------------------------
-  extern __shared__ __align__(128) unsigned char smem_raw[];
-  uint32_t* hist[2] = {reinterpret_cast<uint32_t*>(smem_raw), reinterpret_cast<uint32_t*>(smem_raw) + kMaxBins};
-  uint32_t* sup[2] = {hist[1] + kMaxBins, hist[1] + kMaxBins + kSup};
-  uint32_t* xch = sup[1] + kSup;                                   // kMaxCluster * 64 words
-  Ctrl* ctrl = reinterpret_cast<Ctrl*>(xch + kMaxCluster * kSup);  // 8-byte aligned
-  uint64_t* cand = reinterpret_cast<uint64_t*>(reinterpret_cast<unsigned char*>(ctrl) + ((sizeof(Ctrl) + 127) & ~127u));
-  float* stage = reinterpret_cast<float*>(cand + p.cand_cap);     // cand_cap is a multiple of 16
-
-  // ---- shard geometry --------------------------------------------------------------------
-  Shard sh;
-  sh.a = (int)((reinterpret_cast<uintptr_t>(rowp) >> 2) & 3u);
-  sh.len = len;
-  sh.gbase = rowp - sh.a;
-  sh.stage = reinterpret_cast<const float4*>(stage);
-  sh.mbar = ctrl->mbar;
-  {
-    const int gn = (sh.a + len + 3) >> 2;
-    const int per = (((gn + C - 1) / C) + 31) & ~31;
-    sh.g0 = min(rank * per, gn);
-    sh.g1 = min(sh.g0 + per, gn);
-    sh.n_stage = min(sh.g1 - sh.g0, p.stage_floats >> 2);
-    sh.chunk_g = max(32, (((sh.n_stage + kChunks - 1) / kChunks) + 31) & ~31);
+  if (tid < C) {
+    const Ctrl* rc = cluster.map_shared_rank(ctrl, tid);
+    ctrl->peer_flag[tid] = rc->pub_flag;
   }
-
-  // ---- prologue: clear round-0 histogram, arm the barriers, start the bulk copies ----------
-  {
-    uint4* h4 = reinterpret_cast<uint4*>(hist[0]);
-    for (int i = tid; i < kMaxBins / 4; i += NT) h4[i] = make_uint4(0u, 0u, 0u, 0u);
-    if (tid == 0) {
-      for (int c = 0; c < kChunks; ++c) mbar_init(&ctrl->mbar[c], 1u);
-      ctrl->win_count = 0u;
-      ctrl->cand_count = 0u;
-      ctrl->wslot = 0u;
-      ctrl->cslot = 0u;
-      ctrl->stage_fail = 0u;
-      mbar_fence_init();
-    }
-    __syncthreads();
-    if (tid == 0 && sh.n_stage > 0) {
-      // bulk copies cover only granules that lie completely inside the row
-      const int gn = (sh.a + len + 3) >> 2;
-      const int full_lo = sh.a > 0 ? 1 : 0;
-      const int full_hi = ((sh.a + len) & 3) ? gn - 1 : gn;
-      const int nchunk = (sh.n_stage + sh.chunk_g - 1) / sh.chunk_g;
-      for (int c = 0; c < nchunk; ++c) {
-        int lo = sh.g0 + c * sh.chunk_g;
-        int hi = min(lo + sh.chunk_g, sh.g0 + sh.n_stage);
-        lo = max(lo, full_lo);
-        hi = min(hi, full_hi);
-        const uint32_t bytes = hi > lo ? (uint32_t)(hi - lo) * 16u : 0u;
-        mbar_arrive_expect_tx(&ctrl->mbar[c], bytes);
-        if (bytes) bulk_g2s(stage + 4 * (lo - sh.g0), sh.gbase + 4 * (int64_t)lo, bytes, &ctrl->mbar[c]);
-      }
-    }
-  }
-
-  // ---- round 0: histogram of the top 12 key bits -----------------------------------------
-  scan_shard<NT, true>(sh, ctrl, [&](uint32_t key, int, bool valid) { hist_add(hist[0], key >> 20, valid); });
   __syncthreads();
-
-  Ctrl* ctrl0 = cluster.map_shared_rank(ctrl, 0);
-  uint64_t* cand0 = cluster.map_shared_rank(cand, 0);
-
-  uint32_t need = kK;
-  uint32_t P = 0;  // threshold digits chosen so far (the key prefix every survivor shares)
-  int mode = kModeAbort;
-  int r = 0;
-  for (;; ++r) {
-    const int w = round_width(r);
-    const int shift = round_shift(r);
-    const int nb = 1 << w;
-    const int fine = nb / kSup;
-    uint32_t* h = hist[r & 1];
-    uint32_t* s = sup[r & 1];
-
-    compute_sup<NT>(h, s, nb);
-    cluster.sync();  // every CTA's histogram and super-bin sums of this round are complete
-
-    // (A) super-bin totals: one remote word per thread
-    for (int i = tid; i < C * kSup; i += NT) {
-      const uint32_t* rs = cluster.map_shared_rank(s, i / kSup);
-      xch[i] = rs[i % kSup];
+  if (warp == 0) {
+    uint32_t lo = 0, hi = 0;
+    for (int q = 0; q < C; ++q) {
+      lo += xch[q * kSup + 2 * lane];
+      hi += xch[q * kSup + 2 * lane + 1];
     }
-    __syncthreads();
-    if (warp == 0) {
-      uint32_t lo = 0, hi = 0;
-      for (int q = 0; q < C; ++q) {
-        lo += xch[q * kSup + 2 * lane];
-        hi += xch[q * kSup + 2 * lane + 1];
-      }
-      int ts = -1;
-      uint32_t above = 0, cnt = 0;
-      const bool ok = warp_pick64(lo, hi, need, ts, above, cnt);
-      if (lane == 0) {
-        ctrl->sup_sel = ok ? ts : -1;
-        ctrl->sup_above = above;
-      }
+    const uint32_t total = warp_sum(lo + hi);
+    const uint32_t flags = warp_sum(lane < C ? ctrl->peer_flag[lane] : 0u);
+    const uint32_t need = need_of(total);
+    int ts = -1;
+    uint32_t above = 0, cnt = 0;
+    const bool ok = need > 0 && warp_pick64(lo, hi, need, ts, above, cnt);
+    if (lane == 0) {
+      ctrl->sup_sel = ok ? ts : -1;
+      ctrl->sup_above = above;
+      ctrl->need = need;
+      ctrl->run_total = total;
+      ctrl->any_flag = flags;
     }
-    __syncthreads();
-    const int ssel = ctrl->sup_sel;
-    if (ssel < 0) {
-      mode = kModeAbort;
-      break;
-    }
-    const uint32_t sup_above = ctrl->sup_above;
-    // (B) fine bins of the threshold super-bin
+  }
+  __syncthreads();
+  const int ssel = ctrl->sup_sel;
+  if (ssel >= 0) {
     for (int i = tid; i < C * kSup; i += NT) {
       const int q = i / kSup, f = i % kSup;
       uint32_t v = 0;
@@ -306,115 +329,228 @@ __global__ void __launch_bounds__(NT, 1) select2048_kernel(const SelectParams p)
       }
       xch[i] = v;
     }
-    __syncthreads();
-    if (warp == 0) {
+  }
+  __syncthreads();
+  if (warp == 0) {
+    Picked pk;
+    pk.ok = false;
+    pk.t = -1;
+    pk.need2 = pk.cnt = pk.local_w = pk.local_c = 0;
+    pk.total = ctrl->run_total;
+    pk.any_flag = ctrl->any_flag;
+    pk.tf = 0;
+    if (ssel >= 0) {
       uint32_t lo = 0, hi = 0;
       for (int q = 0; q < C; ++q) {
         lo += xch[q * kSup + 2 * lane];
         hi += xch[q * kSup + 2 * lane + 1];
       }
+      const uint32_t need = ctrl->need;
+      const uint32_t sup_above = ctrl->sup_above;
       int tf = -1;
       uint32_t above_f = 0, cnt_t = 0;
-      const bool ok = warp_pick64(lo, hi, need - sup_above, tf, above_f, cnt_t);
-      int md = kModeAbort;
-      uint32_t base_w = 0, base_c = 0, tie_prefix = 0, local_c = 0, need2 = 0;
-      if (ok) {
-        need2 = need - sup_above - above_f;
-        // this CTA's own counts above / at the threshold bin
+      if (warp_pick64(lo, hi, need - sup_above, tf, above_f, cnt_t)) {
+        pk.ok = true;
+        pk.tf = tf;
+        pk.t = ssel * fine + tf;
+        pk.need2 = need - sup_above - above_f;
+        pk.cnt = cnt_t;
         uint32_t lw = 0;
         lw += (2 * lane > ssel) ? s[2 * lane] : 0u;
         lw += (2 * lane + 1 > ssel) ? s[2 * lane + 1] : 0u;
         lw += (2 * lane < fine && 2 * lane > tf) ? h[ssel * fine + 2 * lane] : 0u;
         lw += (2 * lane + 1 < fine && 2 * lane + 1 > tf) ? h[ssel * fine + 2 * lane + 1] : 0u;
-        lw = warp_sum(lw);
-        local_c = h[ssel * fine + tf];
-        if (cnt_t == need2) {
-          md = kModeTakeAll;
-          lw += local_c;
-        } else if (cnt_t <= (uint32_t)p.cand_cap) {
-          md = kModeGather;
-        } else if (shift == 0) {
-          md = kModeTies;
-          uint32_t tp = (lane < rank) ? xch[lane * kSup + tf] : 0u;
-          tie_prefix = warp_sum(tp);
-        } else {
-          md = kModeNext;
-        }
-        if (lane == 0) {
-          base_w = atomicAdd(&ctrl0->win_count, lw);
-          if (md == kModeGather) base_c = atomicAdd(&ctrl0->cand_count, local_c);
-        }
-      }
-      if (lane == 0) {
-        ctrl->mode = md;
-        ctrl->t = ssel * fine + tf;
-        ctrl->above = need2;  // remaining need after this round
-        ctrl->cnt = cnt_t;
-        ctrl->base_w = base_w;
-        ctrl->base_c = base_c;
-        ctrl->tie_prefix = tie_prefix;
-        ctrl->local_c = local_c;
-        ctrl->wslot = 0u;
-        ctrl->cslot = 0u;
+        pk.local_w = warp_sum(lw);
+        pk.local_c = h[pk.t];
       }
     }
-    // while warp 0 decides, the others clear the next round's histogram (safe: peers finished
-    // reading that buffer before they arrived at this round's cluster barrier)
+    post(pk);
+  }
+  __syncthreads();
+}
+
+// Everything one CTA needs to know about its row and its shared memory.
+template <int NT>
+struct RowCtx {
+  int C, rank;
+  Shard sh;
+  uint32_t* hist0;  // two histograms of kMaxBins words, back to back
+  uint32_t* sup0;   // two super-bin arrays of kSup words, back to back
+  // (computed addresses instead of pointer arrays: indexing an array member with the round number
+  // would force the whole struct into local memory)
+  __device__ __forceinline__ uint32_t* hist(int i) const { return hist0 + i * kMaxBins; }
+  __device__ __forceinline__ uint32_t* sup(int i) const { return sup0 + i * kSup; }
+  uint32_t* xch;
+  Ctrl* ctrl;
+  Ctrl* ctrl0;
+  uint64_t* list;
+  uint64_t* cand;
+  uint64_t* cand0;
+  int32_t* out_idx;
+  uint32_t* out_key;
+  int32_t idx_offset;
+  int32_t cand_cap;
+  int32_t list_cap;
+  uint32_t* status;
+};
+
+template <int NT>
+__device__ __forceinline__ void emit_winner(const RowCtx<NT>& cx, uint32_t base_w, uint32_t key, int idx) {
+  const uint32_t pos = base_w + warp_alloc(&cx.ctrl->wslot);
+  if (pos < (uint32_t)kK) {
+    cx.out_idx[pos] = idx + cx.idx_offset;
+    if (cx.out_key) cx.out_key[pos] = key;
+  }
+}
+
+// Standard decision after a search with need = what is still missing of k: either the threshold
+// bin is taken whole, or its population fits rank 0's buffer and is gathered there, or
+// `otherwise` (a mode) applies. Output and candidate slots are allocated with one remote atomic
+// each on rank 0's counters.
+template <int NT>
+__device__ __forceinline__ void decide_and_allocate(const RowCtx<NT>& cx, const Picked& pk, int otherwise,
+                                                    bool force_otherwise) {
+  int md = kModeAbort;
+  uint32_t base_w = 0, base_c = 0, lw = pk.local_w;
+  if (pk.ok) {
+    if (force_otherwise) {
+      md = otherwise;
+    } else if (pk.cnt == pk.need2) {
+      md = kModeTakeAll;
+      lw += pk.local_c;
+    } else if (pk.cnt <= (uint32_t)cx.cand_cap) {
+      md = kModeGather;
+    } else {
+      md = otherwise;
+    }
+    if (lane_id() == 0 && md != kModeFallback) {
+      base_w = atomicAdd(&cx.ctrl0->win_count, lw);
+      if (md == kModeGather) base_c = atomicAdd(&cx.ctrl0->cand_count, pk.local_c);
+    }
+  }
+  if (lane_id() == 0) {
+    Ctrl* ctrl = cx.ctrl;
+    ctrl->mode = md;
+    ctrl->t = pk.t;
+    ctrl->above = pk.need2;
+    ctrl->cnt = pk.cnt;
+    ctrl->base_w = base_w;
+    ctrl->base_c = base_c;
+    ctrl->local_c = pk.local_c;
+    ctrl->wslot = 0u;
+    ctrl->cslot = 0u;
+  }
+}
+
+// -----------------------------------------------------------------------------------------
+// Full-histogram path: every round re-reads the shard (from L2) and histograms the next key
+// digit of the elements that still match the threshold prefix. Handles anything: lists that
+// would overflow, threshold bins larger than rank 0's buffer, rows of identical values.
+// Returns the final mode; `need`, `P` and `r` describe where it stopped.
+// -----------------------------------------------------------------------------------------
+template <int NT>
+__device__ __forceinline__ int refine_from_data(RowCtx<NT>& cx, uint32_t& need, uint32_t& P, int& r) {
+  cg::cluster_group cluster = cg::this_cluster();
+  const int tid = threadIdx.x;
+  const int lane = tid & 31, warp = tid >> 5;
+  const int C = cx.C, rank = cx.rank;
+  const Shard& sh = cx.sh;
+  Ctrl* ctrl = cx.ctrl;
+  uint32_t* xch = cx.xch;
+
+  // peers may still be reading this CTA's histograms from the attempt that fell back
+  cluster.sync();
+  {
+    uint4* h4 = reinterpret_cast<uint4*>(cx.hist(0));
+    for (int i = tid; i < kMaxBins / 4; i += NT) h4[i] = make_uint4(0u, 0u, 0u, 0u);
+    if (tid == 0) {
+      ctrl->pub_flag = 0u;
+      ctrl->win_count = 0u;   // rank 0's copies are the cluster-wide counters; nobody touches
+      ctrl->cand_count = 0u;  // them again before the cluster barrier of round 0
+      ctrl->over_flag = 0u;
+    }
+  }
+  __syncthreads();
+  {
+    uint32_t* h0 = cx.hist(0);
+    scan_shard<NT>(sh, [&](uint32_t key, int) { hist_add(h0, key >> 20, true); });
+  }
+  __syncthreads();
+
+  need = kK;
+  P = 0;
+  int mode = kModeAbort;
+  for (r = 0;; ++r) {
+    const int w = round_width(r);
+    const int shift = round_shift(r);
+    const int nb = 1 << w;
+    uint32_t* h = cx.hist(r & 1);
+    uint32_t* s = cx.sup(r & 1);
+    compute_sup<NT>(h, s, nb);
+    cluster.sync();  // every CTA's histogram and super-bin sums of this round are complete
+    const uint32_t need_now = need;
+    cluster_pick<NT>(
+        cluster, C, h, s, xch, ctrl, nb, [&](uint32_t) { return need_now; },
+        [&](Picked& pk) {
+          const bool last = (shift == 0);
+          decide_and_allocate<NT>(cx, pk, last ? kModeTies : kModeNext, false);
+          if (pk.ok && last && pk.cnt > (uint32_t)cx.cand_cap && pk.cnt != pk.need2) {
+            // exact duplicates of the threshold key: ties before this shard, in rank order
+            const uint32_t tp = (lane < rank) ? xch[lane * kSup + pk.tf] : 0u;
+            const uint32_t tie_prefix = warp_sum(tp);
+            if (lane == 0) ctrl->tie_prefix = tie_prefix;
+          }
+        });
+    // clear the next round's histogram (peers finished reading that buffer before they arrived
+    // at this round's cluster barrier)
     {
-      uint4* n4 = reinterpret_cast<uint4*>(hist[(r + 1) & 1]);
+      uint4* n4 = reinterpret_cast<uint4*>(cx.hist((r + 1) & 1));
       for (int i = tid; i < kMaxBins / 4; i += NT) n4[i] = make_uint4(0u, 0u, 0u, 0u);
     }
     __syncthreads();
     mode = ctrl->mode;
     if (mode == kModeAbort) break;
     const uint32_t Pn = (P << w) | (uint32_t)ctrl->t;
-    const uint32_t Pold = P;  // digits of the rounds before this one
+    const uint32_t Pold = P;
     const uint32_t base_w = ctrl->base_w;
     const uint32_t base_c = ctrl->base_c;
     need = ctrl->above;
     P = Pn;
 
-    auto emit_winner = [&](uint32_t key, int idx) {
-      const uint32_t pos = base_w + atomicAdd(&ctrl->wslot, 1u);
-      if (pos < (uint32_t)kK) {
-        out_idx[pos] = idx + p.idx_offset;
-        if (out_key) out_key[pos] = key;
-      }
-    };
-
     if (mode == kModeNext) {
       const int shift2 = round_shift(r + 1);
       const uint32_t mask2 = (1u << round_width(r + 1)) - 1u;
-      uint32_t* h2 = hist[(r + 1) & 1];
-      scan_shard<NT, false>(sh, ctrl, [&](uint32_t key, int idx, bool valid) {
+      uint32_t* h2 = cx.hist((r + 1) & 1);
+      scan_shard<NT>(sh, [&](uint32_t key, int idx) {
         const uint32_t hh = key >> shift;
-        const bool older = valid && ((hh >> w) == Pold);
-        if (older && hh > Pn) emit_winner(key, idx);
-        hist_add(h2, (key >> shift2) & mask2, older && hh == Pn);
+        if ((hh >> w) == Pold) {
+          if (hh > Pn) emit_winner<NT>(cx, base_w, key, idx);
+          hist_add(h2, (key >> shift2) & mask2, hh == Pn);
+        }
       });
       __syncthreads();
       continue;
     }
     if (mode == kModeGather) {
-      scan_shard<NT, false>(sh, ctrl, [&](uint32_t key, int idx, bool valid) {
+      scan_shard<NT>(sh, [&](uint32_t key, int idx) {
         const uint32_t hh = key >> shift;
-        if (valid && ((hh >> w) == Pold)) {
+        if ((hh >> w) == Pold) {
           if (hh > Pn) {
-            emit_winner(key, idx);
+            emit_winner<NT>(cx, base_w, key, idx);
           } else if (hh == Pn) {
-            const uint32_t slot = base_c + atomicAdd(&ctrl->cslot, 1u);
-            if (slot < (uint32_t)p.cand_cap) cand0[slot] = ((uint64_t)key << 32) | (uint64_t)(~(uint32_t)idx);
+            const uint32_t slot = base_c + warp_alloc(&ctrl->cslot);
+            if (slot < (uint32_t)cx.cand_cap) cx.cand0[slot] = ((uint64_t)key << 32) | (uint64_t)(~(uint32_t)idx);
           }
         }
       });
     } else if (mode == kModeTakeAll) {
-      scan_shard<NT, false>(sh, ctrl, [&](uint32_t key, int idx, bool valid) {
+      scan_shard<NT>(sh, [&](uint32_t key, int idx) {
         const uint32_t hh = key >> shift;
-        if (valid && ((hh >> w) == Pold) && hh >= Pn) emit_winner(key, idx);
+        if (((hh >> w) == Pold) && hh >= Pn) emit_winner<NT>(cx, base_w, key, idx);
       });
-    } else {  // kModeTies: all 32 key bits are fixed; P is the threshold key itself
-      scan_shard<NT, false>(sh, ctrl, [&](uint32_t key, int idx, bool valid) {
-        if (valid && key > Pn) emit_winner(key, idx);
+    } else {  // kModeTies: all 32 key bits are fixed; Pn is the threshold key itself
+      scan_shard<NT>(sh, [&](uint32_t key, int idx) {
+        if (key > Pn) emit_winner<NT>(cx, base_w, key, idx);
       });
       // Exact duplicates of the threshold key: the first `need` of them in index order win.
       // Shards are contiguous and ordered by rank, so this CTA takes its first `quota`.
@@ -423,26 +559,21 @@ __global__ void __launch_bounds__(NT, 1) select2048_kernel(const SelectParams p)
       const uint32_t quota = need > tie_prefix ? min(need - tie_prefix, local_c) : 0u;
       const uint32_t obase = (uint32_t)kK - need + tie_prefix;
       uint32_t run = 0;  // ties seen so far in this shard (uniform over the CTA)
-      const bool use_stage = ctrl->stage_fail == 0u;
       for (int gb = sh.g0; gb < sh.g1 && run < quota; gb += NT) {
         const int g = gb + tid;
         const bool in = g < sh.g1;
         float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (in) {
-          const int gl = g - sh.g0;
-          x = (use_stage && gl < sh.n_stage && granule_full(sh, g)) ? sh.stage[gl] : load_granule(sh, g);
-        }
+        if (in) x = load_granule(sh, g, 0.f);
         const int i0 = 4 * g - sh.a;
         const float xv[4] = {x.x, x.y, x.z, x.w};
         bool m[4];
         uint32_t c = 0;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          m[j] = in && (unsigned)(i0 + j) < (unsigned)len && fftopk_key_from_bits(__float_as_uint(xv[j])) == Pn;
+          m[j] = in && (unsigned)(i0 + j) < (unsigned)sh.len && fftopk_key_from_bits(__float_as_uint(xv[j])) == Pn;
           c += m[j] ? 1u : 0u;
         }
-        // block exclusive scan of c in thread order
-        uint32_t incl = c;
+        uint32_t incl = c;  // block exclusive scan of c in thread order
 #pragma unroll
         for (int off = 1; off < 32; off <<= 1) {
           const uint32_t v = __shfl_up_sync(kFull, incl, off);
@@ -458,8 +589,8 @@ __global__ void __launch_bounds__(NT, 1) select2048_kernel(const SelectParams p)
         for (int j = 0; j < 4; ++j) {
           if (m[j]) {
             if (rnk < quota && obase + rnk < (uint32_t)kK) {
-              out_idx[obase + rnk] = i0 + j + p.idx_offset;
-              if (out_key) out_key[obase + rnk] = Pn;
+              cx.out_idx[obase + rnk] = i0 + j + cx.idx_offset;
+              if (cx.out_key) cx.out_key[obase + rnk] = Pn;
             }
             ++rnk;
           }
@@ -470,29 +601,331 @@ __global__ void __launch_bounds__(NT, 1) select2048_kernel(const SelectParams p)
     }
     break;
   }
+  return mode;
+}
 
-  // No CTA may leave while a peer can still read its histograms or write into rank 0's
-  // candidate buffer: one last cluster barrier for every mode.
-  cluster.sync();
+template <int NT>
+__global__ void __launch_bounds__(NT, 1) select2048_kernel(const SelectParams p) {
+  RowCtx<NT> cx;
+  cg::cluster_group cluster = cg::this_cluster();
+  const int C = cx.C = (int)cluster.num_blocks();
+  const int rank = cx.rank = (int)cluster.block_rank();
+  const int row = (int)(blockIdx.x / (unsigned)C);
+  const int tid = threadIdx.x;
+  const int lane = tid & 31, warp = tid >> 5;
+  constexpr int NW = NT / 32;
 
+  int64_t row_start = p.row_starts ? (int64_t)p.row_starts[row] : 0;
+  row_start = row_start < 0 ? 0 : (row_start > p.L ? p.L : row_start);
+  int64_t len64 = (int64_t)p.lengths[row];
+  len64 = len64 < 0 ? 0 : len64;
+  len64 = len64 > p.L - row_start ? p.L - row_start : len64;
+  const int len = (int)len64;
+  const float* rowp = p.score + (int64_t)row * p.row_stride + row_start;
+  int32_t* out_idx = cx.out_idx = p.out_idx + (int64_t)row * kK;
+  uint32_t* out_key = cx.out_key = p.out_key ? p.out_key + (int64_t)row * kK : nullptr;
+  cx.idx_offset = p.idx_offset;
+  cx.cand_cap = p.cand_cap;
+  cx.list_cap = p.list_cap;
+  cx.status = p.status;
+
+  // Short rows: 0..len-1 then -1 (reference: naive_topk_cuda, topk_indexer_radix.cu:152-163).
+  if (len <= kK) {
+    if (rank == 0) {
+      for (int i = tid; i < kK; i += NT) {
+        out_idx[i] = i < len ? i + p.idx_offset : -1;
+        if (out_key) out_key[i] = i < len ? fftopk_key_from_bits(__float_as_uint(__ldg(rowp + i))) : 0u;
+      }
+    }
+    return;  // uniform over the cluster; no shared memory of this CTA is ever read by a peer
+  }
+
+  FFTOPK_MARK(0);
+  // ---- shared memory carve ---------------------------------------------------------------
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  cx.hist0 = reinterpret_cast<uint32_t*>(smem_raw);
+  cx.sup0 = cx.hist0 + 2 * kMaxBins;
+  cx.xch = cx.sup0 + 2 * kSup;                                             // kMaxCluster * 64 words
+  Ctrl* ctrl = cx.ctrl = reinterpret_cast<Ctrl*>(cx.xch + kMaxCluster * kSup);  // 8-byte aligned
+  cx.list = reinterpret_cast<uint64_t*>(reinterpret_cast<unsigned char*>(ctrl) + ((sizeof(Ctrl) + 127) & ~127u));
+  cx.cand = cx.list + p.list_cap;
+  cx.ctrl0 = cluster.map_shared_rank(ctrl, 0);
+  cx.cand0 = cluster.map_shared_rank(cx.cand, 0);
+  uint64_t* list = cx.list;
+
+  // ---- shard geometry --------------------------------------------------------------------
+  Shard& sh = cx.sh;
+  sh.a = (int)((reinterpret_cast<uintptr_t>(rowp) >> 2) & 3u);
+  sh.len = len;
+  sh.gbase = rowp - sh.a;
+  const int gn = (sh.a + len + 3) >> 2;
+  const int per = (((gn + C - 1) / C) + 31) & ~31;
+  sh.g0 = min(rank * per, gn);
+  sh.g1 = min(sh.g0 + per, gn);
+  sh.i0 = max(sh.g0, sh.a > 0 ? 1 : 0);
+  sh.i1 = max(sh.i0, min(sh.g1, ((sh.a + len) & 3) ? gn - 1 : gn));
+  const int n_g = sh.g1 - sh.g0;
+  // Whole shard in registers (same answer in every CTA of the cluster: `per` is rank-independent).
+  const bool exact = per <= NT * kRegSlabs;
+
+  // ---- prologue: clear both histograms and the control block ---------------------------------
+  {
+    uint4* h4 = reinterpret_cast<uint4*>(cx.hist(0));
+    for (int i = tid; i < 2 * kMaxBins / 4; i += NT) h4[i] = make_uint4(0u, 0u, 0u, 0u);
+    if (tid == 0) {
+      ctrl->win_count = 0u;
+      ctrl->cand_count = 0u;
+      ctrl->pub_flag = 0u;
+      ctrl->over_flag = 0u;
+      ctrl->wslot = 0u;
+      ctrl->cslot = 0u;
+      ctrl->lcount = 0u;
+    }
+  }
+
+  // ---- sample (or, for a shard that fits in registers, the whole shard) ------------------------
+  // exact:   thread keeps granules g0 + j*NT + tid, j < kRegSlabs
+  // sampled: warp w reads one 512-byte slab at g0 + w*stride; the slabs are spread evenly over the
+  //          shard, so together the cluster samples the row uniformly in position
+  float4 xr[kRegSlabs];
+  int gr[kRegSlabs];
+#pragma unroll
+  for (int j = 0; j < kRegSlabs; ++j) {
+    gr[j] = sh.g1;  // "none"
+    xr[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  {
+    const float4* base4 = reinterpret_cast<const float4*>(sh.gbase);
+    if (exact) {
+#pragma unroll
+      for (int j = 0; j < kRegSlabs; ++j) {
+        const int g = sh.g0 + j * NT + tid;
+        if (g < sh.g1) gr[j] = g;
+        if (g >= sh.i0 && g < sh.i1) xr[j] = __ldg(base4 + g);
+      }
+    } else {
+      int g;
+      if (n_g >= NT) {
+        const int stride = (n_g / NW) & ~7;
+        g = sh.g0 + warp * stride + lane;
+      } else {
+        g = sh.g0 + tid;
+      }
+      if (g < sh.g1) gr[0] = g;
+      if (g >= sh.i0 && g < sh.i1) xr[0] = __ldg(base4 + g);
+    }
+    // granules straddling the row's ends (at most two per row), after every bulk load is in flight
+#pragma unroll
+    for (int j = 0; j < kRegSlabs; ++j) {
+      if (gr[j] < sh.g1 && (gr[j] < sh.i0 || gr[j] >= sh.i1))
+        xr[j] = load_granule_partial(sh.gbase, sh.a, sh.len, gr[j], 0.f);
+    }
+  }
+  __syncthreads();  // histograms are cleared
+  FFTOPK_MARK(1);
+  {
+    uint32_t* h0 = cx.hist(0);
+#pragma unroll
+    for (int j = 0; j < kRegSlabs; ++j) {
+      if (j == 0 || exact) {  // uniform over the CTA
+        const bool in = gr[j] < sh.g1;
+        const int i0 = 4 * gr[j] - sh.a;
+        const float xv[4] = {xr[j].x, xr[j].y, xr[j].z, xr[j].w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          hist_add(h0, fftopk_key_from_bits(__float_as_uint(xv[e])) >> 20,
+                   in && (unsigned)(i0 + e) < (unsigned)len);
+        }
+      }
+    }
+  }
+  __syncthreads();
+  compute_sup<NT>(cx.hist(0), cx.sup(0), kMaxBins);
+  FFTOPK_MARK(2);
+  cluster.sync();  // #1: sample histograms complete
+  FFTOPK_MARK(3);
+
+  uint32_t need = kK;
+  uint32_t P = 0;
+  int r = 0;
+  int mode = kModeAbort;
+
+  if (p.force_slow) {
+    mode = kModeFallback;
+  } else if (exact) {
+    // ---- the sample is the row: its histogram gives the threshold bin directly -----------------
+    cluster_pick<NT>(
+        cluster, C, cx.hist(0), cx.sup(0), cx.xch, ctrl, kMaxBins, [&](uint32_t) { return (uint32_t)kK; },
+        [&](Picked& pk) { decide_and_allocate<NT>(cx, pk, kModeFallback, false); });
+    mode = ctrl->mode;
+    FFTOPK_MARK(4);
+    if (mode == kModeGather || mode == kModeTakeAll) {
+      const uint32_t t = (uint32_t)ctrl->t;
+      const uint32_t base_w = ctrl->base_w, base_c = ctrl->base_c;
+      const bool take_eq = (mode == kModeTakeAll);
+      need = ctrl->above;
+      P = t;
+#pragma unroll
+      for (int j = 0; j < kRegSlabs; ++j) {
+        const int i0 = 4 * gr[j] - sh.a;
+        const float xv[4] = {xr[j].x, xr[j].y, xr[j].z, xr[j].w};
+        if (gr[j] < sh.g1) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            if ((unsigned)(i0 + e) < (unsigned)len) {
+              const uint32_t key = fftopk_key_from_bits(__float_as_uint(xv[e]));
+              const uint32_t bin = key >> 20;
+              if (bin > t || (take_eq && bin == t)) {
+                emit_winner<NT>(cx, base_w, key, i0 + e);
+              } else if (bin == t) {
+                const uint32_t slot = base_c + warp_alloc(&ctrl->cslot);
+                if (slot < (uint32_t)p.cand_cap)
+                  cx.cand0[slot] = ((uint64_t)key << 32) | (uint64_t)(~(uint32_t)(i0 + e));
+              }
+            }
+          }
+        }
+      }
+    }
+  } else {
+    // ---- sampled: pick a conservative lower bound from the sample, filter the shard once ------
+    // need_of: sample rank whose true rank is >= k with overwhelming probability
+    // (m expected sample elements among the true top k, plus five standard deviations).
+    const float flen = (float)len;
+    cluster_pick<NT>(
+        cluster, C, cx.hist(0), cx.sup(0), cx.xch, ctrl, kMaxBins,
+        [&](uint32_t n_s) {
+          const float m = (float)kK * (float)n_s / flen;
+          const uint32_t rk = (uint32_t)(m + 5.0f * sqrtf(m) + 14.0f);
+          return rk < n_s ? rk : n_s;
+        },
+        [&](Picked& pk) {
+          if (lane == 0) {
+            // A 12-bit bin is coarse where values crowd into few exponents (8 bins per octave):
+            // if the sample says the guessed bin holds more than ~k row elements, a second
+            // sample round on the next 12 key bits sharpens the guess.
+            const float in_bin = (float)pk.cnt * flen / (float)(pk.total ? pk.total : 1u);
+            ctrl->mode = !pk.ok ? kModeFallback : (in_bin > (float)kK ? kModeNext : kModeGather);
+            ctrl->t = pk.t;
+            ctrl->above = pk.need2;
+          }
+        });
+    FFTOPK_MARK(4);
+    int smode = ctrl->mode;
+    uint32_t gkey = (uint32_t)ctrl->t << 20;
+    if (smode == kModeNext) {
+      const uint32_t g1 = (uint32_t)ctrl->t;
+      const uint32_t rem = ctrl->above;
+      {
+        uint32_t* h1 = cx.hist(1);
+        const int e0 = 4 * gr[0] - sh.a;
+        const float xv[4] = {xr[0].x, xr[0].y, xr[0].z, xr[0].w};
+        if (gr[0] < sh.g1) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const uint32_t key = fftopk_key_from_bits(__float_as_uint(xv[e]));
+            hist_add(h1, (key >> 8) & 0xfffu, (unsigned)(e0 + e) < (unsigned)len && (key >> 20) == g1);
+          }
+        }
+      }
+      __syncthreads();
+      compute_sup<NT>(cx.hist(1), cx.sup(1), kMaxBins);
+      cluster.sync();  // #1b
+      cluster_pick<NT>(
+          cluster, C, cx.hist(1), cx.sup(1), cx.xch, ctrl, kMaxBins, [&](uint32_t) { return rem; },
+          [&](Picked& pk) {
+            if (lane == 0) {
+              ctrl->mode = pk.ok ? kModeGather : kModeFallback;
+              ctrl->t = pk.t;
+            }
+          });
+      smode = ctrl->mode;
+      gkey |= (uint32_t)ctrl->t << 8;
+      FFTOPK_MARK(11);
+    }
+    if (smode == kModeGather) {
+      // Lower edge of the guess as a float: key(x) >= gkey  <=>  !(x < edge), NaN included.
+      // Keys outside the range real values map to (below -inf's key / above +inf's) admit
+      // everything instead; that only lengthens the lists.
+      float edge = __uint_as_float(0xff800000u);  // -inf
+      if (gkey > 0x007fffffu && gkey <= 0xff800000u) edge = __uint_as_float(fftopk_bits_from_key(gkey));
+#ifdef FFTOPK_EXPERIMENT_NOPASS
+      edge = __uint_as_float(0x7f800000u);  // experiment: nothing but +inf/NaN passes
+#endif
+      const uint32_t wcap = (uint32_t)p.list_cap / NW;
+      uint64_t* seg = list + (size_t)warp * wcap;
+      const uint32_t wc = filter_shard<NT, (NT >= 1024 ? 4 : 8)>(sh, edge, seg, wcap);  // 64 KiB in flight per SM
+      FFTOPK_MARK(8);
+      // hand the candidates to rank 0: one remote atomic per CTA allocates the range
+      const uint32_t wn = min(wc, wcap);
+      if (lane == 0) {
+        ctrl->wtot[warp] = wn;
+        if (wc > wcap) ctrl->pub_flag = 1u;
+      }
+      __syncthreads();
+      if (warp == 0) {
+        const uint32_t mine = lane < NW ? ctrl->wtot[lane] : 0u;
+        uint32_t incl = mine;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+          const uint32_t v = __shfl_up_sync(kFull, incl, off);
+          if (lane >= off) incl += v;
+        }
+        uint32_t base = 0;
+        if (lane == 31) {
+          base = atomicAdd(&cx.ctrl0->cand_count, incl);
+          if (ctrl->pub_flag) atomicOr(&cx.ctrl0->over_flag, 1u);
+        }
+        base = __shfl_sync(kFull, base, 31);
+        if (lane < NW) ctrl->wtot[lane] = base + incl - mine;
+      }
+      __syncthreads();
+      {
+        const uint32_t wbase = ctrl->wtot[warp];
+        for (uint32_t j = lane; j < wn; j += 32) {
+          if (wbase + j < (uint32_t)p.cand_cap) cx.cand0[wbase + j] = seg[j];
+        }
+      }
+      cluster.sync();  // #2: every candidate has landed in rank 0
+      FFTOPK_MARK(9);
+      if (tid == 0) {
+        const uint32_t total = cx.ctrl0->cand_count;
+        const uint32_t over = cx.ctrl0->over_flag;
+        // fewer than k admitted (the guess was too high), a segment overflowed, or more than
+        // rank 0 can hold: start over with full histograms
+        ctrl->mode = (over == 0u && total >= (uint32_t)kK && total <= (uint32_t)p.cand_cap) ? kModeGather : kModeFallback;
+      }
+      __syncthreads();
+      mode = ctrl->mode;
+      need = kK;
+      P = 0;
+      r = -1;  // "no key prefix known" for the finish
+      FFTOPK_MARK(10);
+    } else {
+      mode = kModeFallback;
+    }
+  }
+
+  if (mode == kModeFallback) mode = refine_from_data<NT>(cx, need, P, r);
+
+  // Candidates that peers pushed into rank 0 are complete after a cluster barrier. The sampled
+  // path has had that barrier already (#2) and only needs one more so that rank 0 outlives the
+  // peers' reads of its counters: it goes after the finish, off the critical path. Every other
+  // path pushes right up to here, so the barrier comes first.
+  const bool finish_first = (r < 0);  // uniform over the cluster
+  FFTOPK_MARK(5);
+  if (!finish_first) cluster.sync();
+  FFTOPK_MARK(6);
   if (mode == kModeGather && rank == 0) {
     const int n = (int)min(ctrl->cand_count, (uint32_t)p.cand_cap);
-    const int shift = round_shift(r);
+    const int hi = r < 0 ? 64 : 32 + round_shift(r);
     int idx_bits = 32 - __clz(len - 1);
-    cta_finish<NT>(cand, n, need, 32 + shift, (uint64_t)P, idx_bits, hist[0], ctrl, out_idx, out_key,
+    cta_finish<NT>(cx.cand, n, need, hi, (uint64_t)P, idx_bits, cx.hist(0), ctrl, out_idx, out_key,
                    (uint32_t)kK - need, p.idx_offset, p.status);
   }
-  if (tid == 0 && p.status) {
-    uint32_t st = 0;
-    if (ctrl->stage_fail) st |= (uint32_t)FFTOPK_ST_STAGE_TIMEOUT;
-    if (mode == kModeAbort) st |= (uint32_t)FFTOPK_ST_INTERNAL;
-    if (st) atomicOr(p.status, st);
-  }
-  if (ctrl->stage_fail && tid == 0) {
-    // a copy that missed its bound may still be in flight: wait for it (bounded) before exit
-    const int nchunk = (sh.n_stage + sh.chunk_g - 1) / sh.chunk_g;
-    for (int c = 0; c < nchunk; ++c) (void)mbar_wait_bounded(&ctrl->mbar[c], 0u);
-  }
+  if (finish_first) cluster.sync();
+  FFTOPK_MARK(7);
+  if (tid == 0 && p.status && mode == kModeAbort) atomicOr(p.status, (uint32_t)FFTOPK_ST_INTERNAL);
 }
 
 // -----------------------------------------------------------------------------------------
@@ -526,7 +959,7 @@ __global__ void __launch_bounds__(NT, 1) merge2048_kernel(const uint32_t* __rest
     nvalid += v ? 1u : 0u;
   }
   nvalid = warp_sum(nvalid);
-  if ((tid & 31) == 0 && nvalid) atomicAdd(&ctrl->run_total, nvalid);
+  if ((tid & 31) == 0 && nvalid) red_shared_add(&ctrl->run_total, nvalid);
   __syncthreads();
   const uint32_t total = ctrl->run_total;
   if (total <= (uint32_t)kK) {
@@ -536,7 +969,7 @@ __global__ void __launch_bounds__(NT, 1) merge2048_kernel(const uint32_t* __rest
     for (int i = tid; i < n; i += NT) {
       const uint64_t c = cand[i];
       if (c != 0ull) {
-        const uint32_t pos = atomicAdd(&ctrl->fslot, 1u);
+        const uint32_t pos = warp_alloc(&ctrl->fslot);
         out_idx[pos] = (int32_t)(~(uint32_t)c);
         if (out_key) out_key[pos] = (uint32_t)(c >> 32);
       }
@@ -562,23 +995,25 @@ using namespace fftopk;
 thread_local int g_last_cuda_error = 0;
 
 struct Tuning {
-  int cluster = -1, threads = -1, stage_kib = -1, cand_cap = -1;
+  int cluster = -1, threads = -1, list_cap = -1, cand_cap = -1, force_slow = 0;
 };
 Tuning g_tuning;
 
 struct DeviceInfo {
   bool ready = false;
-  int err = 0;
   int sm_count = 0;
   int smem_optin = 0;
   int cc_major = 0;
-  int max_cluster_1024 = 0;  // largest cluster size that can be scheduled with the full-smem config
+  int max_cluster = 0;  // largest cluster size that can be scheduled with the latency-mode footprint
 };
 DeviceInfo g_dev[64];
 
 constexpr size_t fixed_smem_bytes() {
   return (size_t)(2 * kMaxBins + 2 * kSup + kMaxCluster * kSup) * 4 + ((sizeof(Ctrl) + 127) & ~(size_t)127);
 }
+
+constexpr int kLatencyListCap = 6144, kLatencyCandCap = 16384;  // one CTA per SM: use the shared memory
+constexpr int kBatchListCap = 4096, kBatchCandCap = 4096;       // several CTAs per SM
 
 int cuda_fail(cudaError_t e) {
   g_last_cuda_error = (int)e;
@@ -614,13 +1049,13 @@ int device_info(DeviceInfo** out) {
     if (rc) return rc;
     e = cudaFuncSetAttribute(merge2048_kernel<1024>, cudaFuncAttributeMaxDynamicSharedMemorySize, d.smem_optin);
     if (e != cudaSuccess) return cuda_fail(e);
-    // can a 16-CTA cluster with the largest shared-memory footprint be co-scheduled?
-    d.max_cluster_1024 = 8;
+    // can a 16-CTA cluster with the latency-mode shared-memory footprint be co-scheduled?
+    d.max_cluster = 8;
     {
       cudaLaunchConfig_t cfg = {};
       cfg.gridDim = dim3(16, 1, 1);
       cfg.blockDim = dim3(1024, 1, 1);
-      cfg.dynamicSmemBytes = (size_t)d.smem_optin;
+      cfg.dynamicSmemBytes = fixed_smem_bytes() + (size_t)(kLatencyListCap + kLatencyCandCap) * 8;
       cudaLaunchAttribute at[1];
       at[0].id = cudaLaunchAttributeClusterDimension;
       at[0].val.clusterDim.x = 16;
@@ -630,7 +1065,7 @@ int device_info(DeviceInfo** out) {
       cfg.numAttrs = 1;
       int nclusters = 0;
       e = cudaOccupancyMaxActiveClusters(&nclusters, select2048_kernel<1024>, &cfg);
-      if (e == cudaSuccess && nclusters >= 1) d.max_cluster_1024 = 16;
+      if (e == cudaSuccess && nclusters >= 1) d.max_cluster = 16;
       (void)cudaGetLastError();
     }
     d.ready = true;
@@ -640,7 +1075,7 @@ int device_info(DeviceInfo** out) {
 }
 
 struct Plan {
-  int cluster, threads, smem_bytes, stage_floats, cand_cap;
+  int cluster, threads, smem_bytes, list_cap, cand_cap;
 };
 
 int floor_pow2(int64_t v) {
@@ -649,33 +1084,27 @@ int floor_pow2(int64_t v) {
   return r;
 }
 
+// Replaces the reference's split heuristic (topk_indexer_radix.cu:1081-1111: at most 8 CTAs per
+// row, a hard-coded SM count of 132).
 Plan make_plan(const DeviceInfo& d, int B, int64_t L) {
   Plan pl;
-  // CTAs per row: as many as keep the whole grid on the device at once (one CTA per SM),
-  // but never so many that a shard drops below ~4K elements.
-  int c = floor_pow2(d.sm_count / (B > 0 ? B : 1) > 0 ? d.sm_count / (B > 0 ? B : 1) : 1);
-  if (c > d.max_cluster_1024) c = d.max_cluster_1024;
-  int by_len = floor_pow2(L / 4096 > 0 ? L / 4096 : 1);
+  const int rows = B > 0 ? B : 1;
+  // CTAs per row: as many as keep the whole grid resident at once with one CTA per SM, but never
+  // so many that a shard drops below ~2K elements.
+  int c = floor_pow2(d.sm_count / rows > 0 ? d.sm_count / rows : 1);
+  if (c > d.max_cluster) c = d.max_cluster;
+  const int by_len = floor_pow2(L / 2048 > 0 ? L / 2048 : 1);
   if (c > by_len) c = by_len;
-  if (c < 1) c = 1;
-  pl.cluster = c;
+  pl.cluster = c < 1 ? 1 : c;
   pl.threads = 1024;
-  pl.cand_cap = 4096;
-  int stage_kib = -1;
+  const bool one_per_sm = (int64_t)rows * pl.cluster <= d.sm_count;
+  pl.list_cap = one_per_sm ? kLatencyListCap : kBatchListCap;
+  pl.cand_cap = one_per_sm ? kLatencyCandCap : kBatchCandCap;
   if (g_tuning.cluster > 0) pl.cluster = g_tuning.cluster;
   if (g_tuning.threads > 0) pl.threads = g_tuning.threads;
+  if (g_tuning.list_cap > 0) pl.list_cap = (g_tuning.list_cap + 15) & ~15;
   if (g_tuning.cand_cap > 0) pl.cand_cap = (g_tuning.cand_cap + 15) & ~15;
-  if (g_tuning.stage_kib >= 0) stage_kib = g_tuning.stage_kib;
-  const size_t fixed = fixed_smem_bytes() + (size_t)pl.cand_cap * 8;
-  size_t avail = (size_t)d.smem_optin > fixed ? (size_t)d.smem_optin - fixed : 0;
-  if (stage_kib >= 0 && (size_t)stage_kib * 1024 < avail) avail = (size_t)stage_kib * 1024;
-  // no point in staging more than the largest shard
-  const int64_t gn = (L + 3 + 3) / 4;
-  const int64_t per = ((((gn + pl.cluster - 1) / pl.cluster) + 31) & ~(int64_t)31) * 16;  // bytes
-  if ((int64_t)avail > per) avail = (size_t)per;
-  avail &= ~(size_t)511;
-  pl.stage_floats = (int)(avail / 4);
-  pl.smem_bytes = (int)(fixed + avail);
+  pl.smem_bytes = (int)(fixed_smem_bytes() + (size_t)(pl.list_cap + pl.cand_cap) * 8);
   return pl;
 }
 
@@ -698,20 +1127,33 @@ const char* fftopk_strerror(int code) {
 
 int fftopk_last_cuda_error(void) { return g_last_cuda_error; }
 
+#ifdef FFTOPK_TRACE
+int fftopk_debug_read_trace(unsigned long long* out32) {
+  return (int)cudaMemcpyFromSymbol(out32, fftopk::g_trace, sizeof(unsigned long long) * 32);
+}
+int fftopk_debug_clear_trace(void) {
+  unsigned long long z[32] = {0};
+  return (int)cudaMemcpyToSymbol(fftopk::g_trace, z, sizeof(z));
+}
+#endif
+
 uint32_t fftopk_key_of(float x) {
   uint32_t bits;
   __builtin_memcpy(&bits, &x, 4);
   return fftopk_key_from_bits(bits);
 }
 
-int fftopk_set_tuning(int32_t cluster_ctas, int32_t threads, int32_t stage_kib, int32_t cand_cap) {
+int fftopk_set_tuning(int32_t cluster_ctas, int32_t threads, int32_t list_cap, int32_t cand_cap,
+                      int32_t force_full_histogram) {
   if (cluster_ctas > 0 && (cluster_ctas > kMaxCluster || (cluster_ctas & (cluster_ctas - 1)))) return FFTOPK_EINVAL;
   if (threads > 0 && threads != 512 && threads != 1024) return FFTOPK_EINVAL;
   if (cand_cap > 0 && (cand_cap < kSmall || cand_cap > 16384)) return FFTOPK_EINVAL;
+  if (list_cap > 0 && (list_cap < kSmall || list_cap > 8192)) return FFTOPK_EINVAL;
   g_tuning.cluster = cluster_ctas;
   g_tuning.threads = threads;
-  g_tuning.stage_kib = stage_kib;
+  g_tuning.list_cap = list_cap;
   g_tuning.cand_cap = cand_cap;
+  g_tuning.force_slow = force_full_histogram > 0 ? 1 : 0;
   return FFTOPK_OK;
 }
 
@@ -724,7 +1166,7 @@ int fftopk_plan(int32_t B, int64_t L, int32_t plan[6]) {
   plan[0] = pl.cluster;
   plan[1] = pl.threads;
   plan[2] = pl.smem_bytes;
-  plan[3] = pl.stage_floats;
+  plan[3] = pl.list_cap;
   plan[4] = pl.cand_cap;
   plan[5] = d->sm_count;
   return FFTOPK_OK;
@@ -754,8 +1196,10 @@ int fftopk_select2048(const float* score, int64_t row_stride, int32_t B, int64_t
   p.status = status;
   p.B = B;
   p.idx_offset = idx_offset;
-  p.stage_floats = pl.stage_floats;
+  p.list_cap = pl.list_cap;
   p.cand_cap = pl.cand_cap;
+  p.force_slow = g_tuning.force_slow;
+  if ((size_t)pl.smem_bytes > (size_t)d->smem_optin) return FFTOPK_ERANGE;
 
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)B * (unsigned)pl.cluster, 1, 1);

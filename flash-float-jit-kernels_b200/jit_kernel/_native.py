@@ -76,7 +76,7 @@ def lib() -> ctypes.CDLL:
     L.fftopk_plan.restype = c.c_int
     L.fftopk_plan.argtypes = [c.c_int32, c.c_int64, c.POINTER(c.c_int32)]
     L.fftopk_set_tuning.restype = c.c_int
-    L.fftopk_set_tuning.argtypes = [c.c_int32, c.c_int32, c.c_int32, c.c_int32]
+    L.fftopk_set_tuning.argtypes = [c.c_int32, c.c_int32, c.c_int32, c.c_int32, c.c_int32]
     return L
 
 
@@ -93,9 +93,11 @@ def plan(B: int, L: int) -> dict:
     """Launch plan fftopk_select2048 would use for (B, L) on the current device."""
     arr = (ctypes.c_int32 * 6)()
     check(lib().fftopk_plan(B, L, arr), "fftopk_plan")
-    keys = ("cluster_ctas", "threads", "smem_bytes", "stage_floats", "cand_cap", "sm_count")
+    keys = ("cluster_ctas", "threads", "smem_bytes", "list_cap", "cand_cap", "sm_count")
     return dict(zip(keys, list(arr)))
 
 
-def set_tuning(cluster_ctas: int = -1, threads: int = -1, stage_kib: int = -1, cand_cap: int = -1) -> None:
-    check(lib().fftopk_set_tuning(cluster_ctas, threads, stage_kib, cand_cap), "fftopk_set_tuning")
+def set_tuning(cluster_ctas: int = -1, threads: int = -1, list_cap: int = -1, cand_cap: int = -1,
+               force_full_histogram: bool = False) -> None:
+    check(lib().fftopk_set_tuning(cluster_ctas, threads, list_cap, cand_cap, int(force_full_histogram)),
+          "fftopk_set_tuning")

@@ -39,8 +39,7 @@ enum {
 
 /* Bits the kernels may OR into the optional device status word. */
 enum {
-  FFTOPK_ST_STAGE_TIMEOUT = 1, /* a bounded wait on a bulk-copy barrier ran out; the row was
-                                  re-read with plain loads, results are still correct       */
+  FFTOPK_ST_STAGE_TIMEOUT = 1, /* reserved                                                  */
   FFTOPK_ST_INTERNAL = 2,      /* an internal count did not add up (should never be seen)  */
   FFTOPK_ST_PEER_TIMEOUT = 4,  /* merge: a bounded wait on a peer's ready flag ran out      */
 };
@@ -110,13 +109,16 @@ uint32_t fftopk_key_of(float x);
  * Launch-plan introspection and overrides (experiments and tests; not needed in production).
  * fftopk_plan reports what fftopk_select2048 would launch for (B, L) on the current device:
  * plan[0] = CTAs per cluster (= CTAs per row), plan[1] = threads per CTA,
- * plan[2] = dynamic shared memory bytes, plan[3] = staged floats per CTA,
- * plan[4] = candidate capacity, plan[5] = SM count.
- * fftopk_set_tuning overrides the automatic choice process-wide; pass -1 to restore "auto".
+ * plan[2] = dynamic shared memory bytes, plan[3] = per-CTA candidate-list capacity,
+ * plan[4] = gathered-candidate capacity of the cluster's first CTA, plan[5] = SM count.
+ * fftopk_set_tuning overrides the automatic choice process-wide; pass -1 (0 for the flag) to
+ * restore "auto". force_full_histogram = 1 skips the sample-and-filter path, so that every row
+ * takes the full-histogram path (tests).
  * Replaces the reference's compile-time split heuristic (topk_indexer_radix.cu:1081-1111).
  */
 int fftopk_plan(int32_t B, int64_t L, int32_t plan[6]);
-int fftopk_set_tuning(int32_t cluster_ctas, int32_t threads, int32_t stage_kib, int32_t cand_cap);
+int fftopk_set_tuning(int32_t cluster_ctas, int32_t threads, int32_t list_cap, int32_t cand_cap,
+                      int32_t force_full_histogram);
 
 #ifdef __cplusplus
 }

@@ -101,13 +101,36 @@ def test_every_cluster_size(cluster, threads):
     check(s, ln, what=f"cluster={cluster} threads={threads}")
 
 
-@pytest.mark.parametrize("stage_kib", [0, 4, 64])
-def test_staging_sizes(stage_kib):
-    """No staging, partial staging (rest streamed) and full staging give the same result."""
-    _native.set_tuning(cluster_ctas=4, stage_kib=stage_kib)
-    check(*workloads.c2(L=131072), what=f"stage={stage_kib}")
+@pytest.mark.parametrize("cluster", [1, 4, 16])
+def test_full_histogram_path(cluster):
+    """The fallback that histograms the data itself (no sampling, no lists) on every config."""
+    _native.set_tuning(cluster_ctas=cluster, force_full_histogram=True)
+    check(*workloads.c2(L=131072), what=f"full-hist c2 C={cluster}")
     s, ln = workloads.c3(B=4, L=50000)
-    check(s, ln, what=f"stage={stage_kib} ragged")
+    check(s, ln, what=f"full-hist ragged C={cluster}")
+    s, ln = workloads.c4(B=2, L=100000)
+    check(s, ln, what=f"full-hist ties C={cluster}")
+
+
+@pytest.mark.parametrize("list_cap", [32, 512])
+def test_list_overflow_falls_back(list_cap):
+    """A candidate list too small for what the filter admits must not lose elements."""
+    _native.set_tuning(cluster_ctas=2, list_cap=list_cap)
+    check(*workloads.c2(L=262144), what=f"list_cap={list_cap}")
+    check(*workloads.c5(B=2, L=300000), what=f"list_cap={list_cap} tail")
+
+
+def test_position_correlated_rows():
+    """Sorted and locally clustered rows: the top k sit in one shard; sampling is by position."""
+    L = 400000
+    asc = torch.arange(L, dtype=torch.float32).unsqueeze(0) * 1e-3
+    desc = asc.flip(1).contiguous()
+    g = torch.Generator().manual_seed(21)
+    bump = torch.randn(1, L, generator=g)
+    bump[0, 123456:123456 + 3000] += 10.0  # all winners inside one 3000-element window
+    saw = (torch.arange(L) % 4099).to(torch.float32).unsqueeze(0)
+    s = torch.cat([asc, desc, bump, saw], dim=0)
+    check(s, torch.full((4,), L, dtype=torch.int32), what="position-correlated")
 
 
 @pytest.mark.parametrize("offset", [0, 1, 2, 3, 5])
