@@ -1,0 +1,94 @@
+"""Multi-GPU modes of the top-2048 selector (one process per GPU, torch.distributed / NCCL).
+
+The reference has no multi-GPU path; both modes here are additions on top of its single-GPU op.
+
+* Row sharding: rows are independent, so every rank simply runs ``fast_topk_v3`` on its rows.
+  ``shard_rows`` gives the row range of a rank; there is no collective on the data path.
+* Context parallel: every rank holds a contiguous slice ``score[:, g*Ls:(g+1)*Ls]`` of the
+  sequence. The global top-k is contained in the union of the local top-k sets (same total order:
+  value descending, global index ascending), so each rank selects locally - emitting the radix
+  key and the GLOBAL index of every pick - the picks are all-gathered over NVLink, and one merge
+  kernel per rank selects the final 2048 of the G*2048 candidates. Ties resolve to the lower
+  global index exactly as on a single device.
+
+``select_fn`` / ``merge_fn`` can be replaced (the CPU tests run the plumbing under gloo with
+stand-ins); by default they are the CUDA kernels behind the C ABI.
+"""
+from __future__ import annotations
+
+from typing import Callable, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from . import _native
+from .topk_indexer import TOPK, _status_word, fast_topk
+
+
+def shard_rows(num_rows: int, world_size: int, rank: int) -> Tuple[int, int]:
+    """Contiguous block of rows [begin, end) owned by `rank` (sizes differ by at most one)."""
+    base, extra = divmod(num_rows, world_size)
+    begin = rank * base + min(rank, extra)
+    return begin, begin + base + (1 if rank < extra else 0)
+
+
+def local_lengths(lengths_global: torch.Tensor, shard_len: int, rank: int) -> torch.Tensor:
+    """Valid elements of every row that fall into this rank's slice [rank*shard_len, +shard_len)."""
+    return torch.clamp(lengths_global.to(torch.int64) - rank * shard_len, 0, shard_len).to(torch.int32)
+
+
+def _cuda_select(score, lengths, idx_offset):
+    B = score.size(0)
+    packed = torch.empty((2, B, TOPK), dtype=torch.int32, device=score.device)  # [0]=index, [1]=key
+    fast_topk(score, packed[0], lengths, None, keys=packed[1], idx_offset=idx_offset)
+    return packed
+
+
+def merge_candidates(cand: torch.Tensor) -> torch.Tensor:
+    """cand: int32 [G, 2, B, 2048] (index plane, key plane per shard) -> int32 [B, 2048]."""
+    G, two, B, k = cand.shape
+    assert two == 2 and k == TOPK and cand.is_contiguous() and cand.is_cuda
+    out = torch.empty((B, TOPK), dtype=torch.int32, device=cand.device)
+    if B == 0:
+        return out
+    # the C ABI takes separate [G, B, 2048] planes: gather them out of the packed layout
+    idx_plane = cand[:, 0].contiguous()
+    key_plane = cand[:, 1].contiguous()
+    lib = _native.lib()
+    with torch.cuda.device(cand.device):
+        rc = lib.fftopk_merge2048(key_plane.data_ptr(), idx_plane.data_ptr(), G, B, out.data_ptr(), None,
+                                  _status_word(cand.device).data_ptr(),
+                                  torch.cuda.current_stream().cuda_stream)
+    _native.check(rc, "fftopk_merge2048")
+    return out
+
+
+def fast_topk_v3_context_parallel(
+    score_shard: torch.Tensor,
+    lengths_global: torch.Tensor,
+    topk: int,
+    group: Optional[dist.ProcessGroup] = None,
+    select_fn: Optional[Callable] = None,
+    merge_fn: Optional[Callable] = None,
+) -> torch.Tensor:
+    """Top-2048 over a sequence that is split evenly across the ranks of `group`.
+
+    score_shard:    [B, Ls] this rank's slice (rank g holds global columns g*Ls .. (g+1)*Ls - 1)
+    lengths_global: [B] int32 valid length of every full row (same on all ranks)
+    Returns [B, 2048] int32 GLOBAL indices on every rank (unordered; -1 padded if the row has
+    fewer than 2048 valid entries).
+    """
+    assert topk == TOPK, "only topk=2048 is supported"
+    assert score_shard.dim() == 2
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    B, Ls = score_shard.shape
+    select = select_fn or _cuda_select
+    merge = merge_fn or merge_candidates
+    lens = local_lengths(lengths_global, Ls, rank).to(score_shard.device)
+    mine = select(score_shard, lens, rank * Ls)  # [2, B, 2048]
+    gathered = torch.empty((world,) + tuple(mine.shape), dtype=mine.dtype, device=mine.device)
+    # concatenation along dim 0 is the layout every backend accepts for all_gather_into_tensor
+    dist.all_gather_into_tensor(gathered.view((world * mine.shape[0],) + tuple(mine.shape[1:])),
+                                mine.contiguous(), group=group)
+    return merge(gathered)
