@@ -40,6 +40,19 @@ __device__ __forceinline__ uint32_t atom_shared_add(uint32_t* p, uint32_t v) {
   return old;
 }
 
+// Reduction into the shared memory of CTA `rank` of this cluster, at the address that
+// `local_ptr` has in the calling CTA (distributed shared memory, no result, relaxed).
+__device__ __forceinline__ void red_cluster_add(uint32_t* local_ptr, unsigned rank, uint32_t v) {
+  uint32_t raddr;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(raddr) : "r"(smem_u32(local_ptr)), "r"(rank));
+  asm volatile("red.relaxed.cluster.shared::cluster.add.u32 [%0], %1;" ::"r"(raddr), "r"(v) : "memory");
+}
+
+// Split cluster barrier (arrive now, wait later): both halves are executed by every thread of
+// every CTA of the cluster, exactly once each, like cluster.sync().
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+
 // Histogram update: a plain shared-memory reduction (no result). Measured on B200 (64K updates
 // per CTA, 1024 threads): 6 to 12 updates per clock per SM whatever the bin distribution,
 // all-equal bins included - the hardware combines same-address updates, and ballot / match.any
@@ -145,7 +158,8 @@ struct Ctrl {
   uint32_t tie_prefix;
   uint32_t local_c;
   uint32_t run_total;
-  uint32_t peer_flag[kMaxCluster];
+  uint32_t tot[kSup];   // cluster-wide super-bin totals (zero between searches)
+  uint32_t tot2[kSup];  // cluster-wide fine-bin totals of the threshold super-bin (same)
   uint32_t wtot[32];
   uint64_t small[kSmall];
 };
@@ -207,49 +221,48 @@ __device__ void cta_finish(const uint64_t* cand, int n, uint32_t need, int hi, u
                            uint32_t* hist /* >= kFinishBins words */, Ctrl* ctrl, int32_t* out_idx, uint32_t* out_key,
                            uint32_t out_base, int32_t idx_offset, uint32_t* status) {
   const int tid = threadIdx.x;
-  if (tid == 0) ctrl->fslot = 0;
-  // (the barrier inside the first round orders this store before any use)
-  auto emit = [&](uint64_t c) {
-    const uint32_t pos = out_base + warp_alloc(&ctrl->fslot);
-    if (pos < (uint32_t)kK) {
-      out_idx[pos] = (int32_t)(~(uint32_t)c) + idx_offset;
-      if (out_key) out_key[pos] = (uint32_t)(c >> 32);
-    }
-  };
+  const int lane = tid & 31, warp = tid >> 5;
   if (hi >= 64) {
     // No prefix known: find the bits all candidates agree on (OR and AND over the list), so that
     // the first digit is spent where the candidates actually differ.
-    uint64_t o = 0ull, a = ~0ull;
+    uint32_t o_hi = 0u, o_lo = 0u, a_hi = ~0u, a_lo = ~0u;
     for (int i = tid; i < n; i += NT) {
       const uint64_t c = cand[i];
       if (c != 0ull) {
-        o |= c;
-        a &= c;
+        o_hi |= (uint32_t)(c >> 32);
+        o_lo |= (uint32_t)c;
+        a_hi &= (uint32_t)(c >> 32);
+        a_lo &= (uint32_t)c;
       }
     }
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) {
-      o |= __shfl_xor_sync(kFull, o, off);
-      a &= __shfl_xor_sync(kFull, a, off);
-    }
-    uint64_t* scratch = reinterpret_cast<uint64_t*>(hist);
-    if ((tid & 31) == 0) {
-      ctrl->small[tid >> 5] = o;
-      scratch[tid >> 5] = a;
+    o_hi = __reduce_or_sync(kFull, o_hi);
+    o_lo = __reduce_or_sync(kFull, o_lo);
+    a_hi = __reduce_and_sync(kFull, a_hi);
+    a_lo = __reduce_and_sync(kFull, a_lo);
+    if (lane == 0) {
+      hist[4 * warp + 0] = o_hi;
+      hist[4 * warp + 1] = o_lo;
+      hist[4 * warp + 2] = a_hi;
+      hist[4 * warp + 3] = a_lo;
     }
     __syncthreads();
-    o = ((tid & 31) < NT / 32) ? ctrl->small[tid & 31] : 0ull;
-    a = ((tid & 31) < NT / 32) ? scratch[tid & 31] : ~0ull;
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) {
-      o |= __shfl_xor_sync(kFull, o, off);
-      a &= __shfl_xor_sync(kFull, a, off);
-    }
-    const uint64_t diff = o ^ a;
+    const bool in = lane < NT / 32;
+    o_hi = __reduce_or_sync(kFull, in ? hist[4 * lane + 0] : 0u);
+    o_lo = __reduce_or_sync(kFull, in ? hist[4 * lane + 1] : 0u);
+    a_hi = __reduce_and_sync(kFull, in ? hist[4 * lane + 2] : ~0u);
+    a_lo = __reduce_and_sync(kFull, in ? hist[4 * lane + 3] : ~0u);
+    const uint64_t o = ((uint64_t)o_hi << 32) | o_lo;
+    const uint64_t diff = o ^ (((uint64_t)a_hi << 32) | a_lo);
     hi = diff ? 64 - __clzll((long long)diff) : 1;
     if (hi < 64) pfx = o >> hi;
-    __syncthreads();  // scratch is about to be cleared as the histogram
+    __syncthreads();  // the scratch words are about to be cleared as the histogram
+    FFTOPK_MARK(31);
   }
+  // ---- radix rounds: only the threshold is determined here; nothing is written yet -----------
+  // Outcome: winners are exactly the candidates with (c >> fs) >= fthr.
+  int fs = 0;
+  uint64_t fthr = ~0ull;
+  bool found = false;
   for (int round = 0; round < 16 && hi > 0; ++round) {
     if (hi <= 32 && hi > idx_bits) {
       // constant run of ones in the inverted index: extend the prefix without a pass
@@ -269,9 +282,9 @@ __device__ void cta_finish(const uint64_t* cand, int n, uint32_t need, int hi, u
       if (act) red_shared_add(&hist[(uint32_t)(c >> sh) & dmask], 1u);
     }
     __syncthreads();
-    FFTOPK_MARK(16 + 3 * round);
+    FFTOPK_MARK(16);
     block_pick<NT>(hist, need, ctrl);
-    FFTOPK_MARK(17 + 3 * round);
+    FFTOPK_MARK(17);
     const int t = ctrl->t;
     if (t < 0) {
       if (tid == 0 && status) atomicOr(status, 2u);
@@ -279,39 +292,73 @@ __device__ void cta_finish(const uint64_t* cand, int n, uint32_t need, int hi, u
     }
     const uint32_t cnt = ctrl->cnt;
     const uint32_t need2 = need - ctrl->above;
-    const bool take_all = (cnt == need2);
-    const bool small = !take_all && cnt <= (uint32_t)kSmall;
-    for (int i = tid; i < n; i += NT) {
-      const uint64_t c = cand[i];
-      const bool act = (c != 0ull) && (hi >= 64 || (c >> hi) == pfx);
-      if (!act) continue;
-      const uint32_t d = (uint32_t)(c >> sh) & dmask;
-      if (d > (uint32_t)t) {
-        emit(c);
-      } else if (d == (uint32_t)t) {
-        if (take_all) {
-          emit(c);
-        } else if (small) {
+    const uint64_t pfx2 = (hi >= 64) ? (uint64_t)t : ((pfx << w) | (uint64_t)t);
+    if (cnt == need2) {  // the whole threshold bin wins
+      fs = sh;
+      fthr = pfx2;
+      found = true;
+      break;
+    }
+    if (cnt <= (uint32_t)kSmall) {
+      // the last <= 32 undecided candidates: one warp sorts them with a compare-exchange network
+      for (int i = tid; i < n; i += NT) {
+        const uint64_t c = cand[i];
+        if (c != 0ull && (c >> sh) == pfx2) {
           const uint32_t s = warp_alloc(&ctrl->small_n);
           if (s < (uint32_t)kSmall) ctrl->small[s] = c;
         }
       }
-    }
-    FFTOPK_MARK(18 + 3 * round);
-    if (take_all) return;
-    if (small) {
       __syncthreads();
-      if (tid < 32) {
-        uint64_t c = (tid < (int)cnt) ? ctrl->small[tid] : 0ull;
+      if (warp == 0) {
+        uint64_t c = (lane < (int)cnt) ? ctrl->small[lane] : 0ull;
         c = warp_sort_desc(c);
-        if ((uint32_t)tid < need2) emit(c);
+        c = __shfl_sync(kFull, c, (int)need2 - 1);  // the need2-th largest is the threshold itself
+        if (lane == 0) ctrl->small[0] = c;
       }
-      return;
+      __syncthreads();
+      fs = 0;
+      fthr = ctrl->small[0];
+      found = true;
+      break;
     }
-    pfx = (hi >= 64) ? (uint64_t)t : ((pfx << w) | (uint64_t)t);
+    pfx = pfx2;
     hi = sh;
     need = need2;
     __syncthreads();  // every thread has read ctrl->t/cnt/above before the next round rewrites them
+  }
+  FFTOPK_MARK(30);
+  if (!found) {
+    if (tid == 0 && status) atomicOr(status, 2u);
+    return;
+  }
+  // ---- one output pass: count per thread, one slot-allocating atomic per warp, then write -----
+  if (tid == 0) ctrl->fslot = 0u;
+  __syncthreads();
+  FFTOPK_MARK(32);
+  uint32_t mine = 0;
+  for (int i = tid; i < n; i += NT) {
+    const uint64_t c = cand[i];
+    mine += (c != 0ull && (c >> fs) >= fthr) ? 1u : 0u;
+  }
+  uint32_t incl = mine;
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    const uint32_t v = __shfl_up_sync(kFull, incl, off);
+    if (lane >= off) incl += v;
+  }
+  uint32_t base = 0;
+  if (lane == 31) base = atom_shared_add(&ctrl->fslot, incl);
+  base = __shfl_sync(kFull, base, 31);
+  uint32_t pos = out_base + base + incl - mine;
+  for (int i = tid; i < n; i += NT) {
+    const uint64_t c = cand[i];
+    if (c != 0ull && (c >> fs) >= fthr) {
+      if (pos < (uint32_t)kK) {
+        out_idx[pos] = (int32_t)(~(uint32_t)c) + idx_offset;
+        if (out_key) out_key[pos] = (uint32_t)(c >> 32);
+      }
+      ++pos;
+    }
   }
 }
 

@@ -94,102 +94,78 @@ __device__ __forceinline__ float4 load_granule(const Shard& sh, int g, float fil
   return load_granule_partial(sh.gbase, sh.a, sh.len, g, fill);
 }
 
-// The one full read of the shard: every element x with !(x < edge) is appended to a candidate
-// list in shared memory as a (key << 32 | ~idx) composite. Every warp owns a private segment of
-// the list (`wcap` entries) and keeps its fill count in a register, identical in all lanes: per
-// loop trip a thread has U 128-bit loads in flight, compares 4*U elements, and if any lane of
-// the warp found something a shuffle scan hands every lane its slots. No atomics: allocating
-// slots from one shared counter serialised at ~20 cycles per candidate and dominated the pass.
-// Returns the warp's count, which exceeds wcap when the segment overflowed.
+// Overflow of a thread's private candidate slots: a shared spill area, slots from one counter
+// (rare, so the serialising atomic does not matter). Out of line to keep the filter loop small.
+__device__ __noinline__ void spill_push(Ctrl* ctrl, uint64_t* spill, uint32_t spill_cap, uint64_t comp) {
+  const uint32_t slot = warp_alloc(&ctrl->lcount);
+  if (slot < spill_cap) {
+    spill[slot] = comp;
+  } else {
+    ctrl->pub_flag = 1u;
+  }
+}
+
+// The one full read of the shard: every element x with !(x < edge) is kept as a
+// (key << 32 | ~idx) composite. Per loop trip a thread has U 128-bit loads in flight and spends
+// ONE compare per element, OR-ed per granule; only a granule with a hit enters the append code.
+// Every THREAD owns `lp` private slots of the shared-memory list and counts in a register, so
+// appending needs no atomic, no vote and no scan (allocating slots from one shared counter
+// serialised at ~20 cycles per candidate and dominated the pass; a per-warp shuffle scan per trip
+// still cost more than the compares). A thread with more than `lp` candidates spills the excess.
+// Returns the thread's candidate count (entries beyond lp went to the spill area).
 template <int NT, int U>
-__device__ __forceinline__ uint32_t filter_shard(const Shard& sh, float edge, uint64_t* seg, uint32_t wcap) {
+__device__ __forceinline__ uint32_t filter_shard(const Shard& sh, float edge, uint64_t* mine, uint32_t lp, Ctrl* ctrl,
+                                                 uint64_t* spill, uint32_t spill_cap) {
   const int tid = threadIdx.x;
-  const int lane = tid & 31;
   const float ninf = __uint_as_float(0xff800000u);
   const float4* base4 = reinterpret_cast<const float4*>(sh.gbase);
   const int fa = sh.a, fi1 = sh.i1, len = sh.len;
-  uint32_t wc = 0;
+  uint32_t cnt = 0;
+  auto keep = [&](float x, int idx) {
+    if ((unsigned)idx < (unsigned)len) {
+      const uint64_t comp = ((uint64_t)fftopk_key_from_bits(__float_as_uint(x)) << 32) | (uint64_t)(~(uint32_t)idx);
+      if (cnt < lp) {
+        mine[cnt] = comp;
+      } else {
+        spill_push(ctrl, spill, spill_cap, comp);
+      }
+      ++cnt;
+    }
+  };
   for (int gb = sh.i0; gb < fi1; gb += NT * U) {
     float4 x[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int g = gb + u * NT + tid;
-      x[u] = make_float4(ninf, ninf, ninf, ninf);
-      if (g < fi1) x[u] = __ldg(base4 + g);
+      x[u] = make_float4(ninf, ninf, ninf, ninf);  // padding: passes only an edge of -inf, and then
+      if (g < fi1) x[u] = __ldg(base4 + g);        // carries an index >= len (see e0 below)
     }
-    // common case first: one compare per element, OR-ed per granule; the 16-bit pass mask is only
-    // built by lanes that saw something
-    bool hit[U];
-    bool any = false;
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      hit[u] = !(x[u].x < edge) | !(x[u].y < edge) | !(x[u].z < edge) | !(x[u].w < edge);
-      any |= hit[u];
-    }
-    if (!__any_sync(kFull, any)) continue;
-    uint32_t mask = 0;  // bit 4u+e: element e of granule u passes and lies inside the row
-    if (any) {
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        if (hit[u] && (gb + u * NT + tid) < fi1) {  // padding lanes hold -inf, which passes an edge of -inf
-          const unsigned e0 = (unsigned)(4 * (gb + u * NT + tid) - fa);
-          mask |= (!(x[u].x < edge) && e0 + 0u < (unsigned)len) ? (1u << (4 * u + 0)) : 0u;
-          mask |= (!(x[u].y < edge) && e0 + 1u < (unsigned)len) ? (1u << (4 * u + 1)) : 0u;
-          mask |= (!(x[u].z < edge) && e0 + 2u < (unsigned)len) ? (1u << (4 * u + 2)) : 0u;
-          mask |= (!(x[u].w < edge) && e0 + 3u < (unsigned)len) ? (1u << (4 * u + 3)) : 0u;
-        }
-      }
-    }
-    {
-      const uint32_t cnt = (uint32_t)__popc(mask);
-      uint32_t incl = cnt;
-#pragma unroll
-      for (int off = 1; off < 32; off <<= 1) {
-        const uint32_t v = __shfl_up_sync(kFull, incl, off);
-        if (lane >= off) incl += v;
-      }
-      uint32_t pos = wc + incl - cnt;
-      wc += __shfl_sync(kFull, incl, 31);
-      if (mask != 0u) {
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-          if ((mask >> (4 * u)) & 0xfu) {
-            const int e0 = 4 * (gb + u * NT + tid) - fa;
-            const float xv[4] = {x[u].x, x[u].y, x[u].z, x[u].w};
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              if ((mask >> (4 * u + e)) & 1u) {
-                if (pos < wcap)
-                  seg[pos] = ((uint64_t)fftopk_key_from_bits(__float_as_uint(xv[e])) << 32) |
-                             (uint64_t)(~(uint32_t)(e0 + e));
-                ++pos;
-              }
-            }
-          }
-        }
+      if (!(x[u].x < edge) | !(x[u].y < edge) | !(x[u].z < edge) | !(x[u].w < edge)) {
+        const int g = gb + u * NT + tid;
+        const int e0 = g < fi1 ? 4 * g - fa : len;
+        if (!(x[u].x < edge)) keep(x[u].x, e0 + 0);
+        if (!(x[u].y < edge)) keep(x[u].y, e0 + 1);
+        if (!(x[u].z < edge)) keep(x[u].z, e0 + 2);
+        if (!(x[u].w < edge)) keep(x[u].w, e0 + 3);
       }
     }
   }
-  // edge granules [g0, i0) and [i1, g1): at most one each, visited by lane 0 of warps 0 and 1
+  // edge granules [g0, i0) and [i1, g1): at most one each, visited by threads 0 and 32
   {
     const int ge = (tid == 0) ? sh.g0 : ((tid == 32) ? sh.i1 : -1);
     const int ge_end = (tid == 0) ? sh.i0 : sh.g1;
     if (ge >= 0 && ge < ge_end) {
       const float4 x = load_granule_partial(sh.gbase, sh.a, len, ge, ninf);
       const int e0 = 4 * ge - fa;
-      const float xv[4] = {x.x, x.y, x.z, x.w};
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        if ((unsigned)(e0 + e) < (unsigned)len && !(xv[e] < edge)) {
-          if (wc < wcap)
-            seg[wc] = ((uint64_t)fftopk_key_from_bits(__float_as_uint(xv[e])) << 32) | (uint64_t)(~(uint32_t)(e0 + e));
-          ++wc;
-        }
-      }
+      if (!(x.x < edge)) keep(x.x, e0 + 0);
+      if (!(x.y < edge)) keep(x.y, e0 + 1);
+      if (!(x.z < edge)) keep(x.z, e0 + 2);
+      if (!(x.w < edge)) keep(x.w, e0 + 3);
     }
-    wc = __shfl_sync(kFull, wc, 0);
   }
-  return wc;
+  return cnt;
 }
 
 // Visit every valid element of the shard: op(key, idx). Interior granules are read with
@@ -235,9 +211,13 @@ __device__ __forceinline__ void scan_shard(const Shard& sh, Op&& op) {
   }
 }
 
-// Sum each group of nb/64 consecutive bins into sup[0..63].
+// Sum each group of nb/64 consecutive bins into sup[0..63]. With push_tot != nullptr the thread
+// that holds a super-bin's sum also adds it into `push_tot[bin]` of EVERY CTA of the cluster
+// (remote shared-memory reductions), so that after the next cluster barrier each CTA finds the
+// cluster-wide totals in its own shared memory.
 template <int NT>
-__device__ __forceinline__ void compute_sup(const uint32_t* hist, uint32_t* sup, int nb) {
+__device__ __forceinline__ void compute_sup(const uint32_t* hist, uint32_t* sup, int nb, uint32_t* push_tot = nullptr,
+                                            int C = 0) {
   const int tid = threadIdx.x;
   if (nb == kMaxBins) {
     constexpr int PER = kMaxBins / NT;            // bins per thread: 4 (1024 thr), 8 (512)
@@ -251,7 +231,12 @@ __device__ __forceinline__ void compute_sup(const uint32_t* hist, uint32_t* sup,
     }
 #pragma unroll
     for (int off = TPS / 2; off > 0; off >>= 1) s += __shfl_xor_sync(kFull, s, off);
-    if ((tid % TPS) == 0) sup[tid / TPS] = s;
+    if ((tid % TPS) == 0) {
+      sup[tid / TPS] = s;
+      if (push_tot != nullptr && s != 0u) {
+        for (int q = 0; q < C; ++q) red_cluster_add(&push_tot[tid / TPS], (unsigned)q, s);
+      }
+    }
   } else {  // 256 bins
     if (tid < kSup) {
       const uint4 v = reinterpret_cast<const uint4*>(hist)[tid];
@@ -282,29 +267,28 @@ struct Picked {
 // Replaces parallel_reduce_histogram + radix_prefix_sum of the reference
 // (topk_indexer_radix.cu:80-107, 232-279), which reduce to rank 0 and broadcast back with three
 // cluster barriers and eight block barriers per round.
-template <int NT, class NeedFn, class Post>
+template <int NT, bool PUSHED, class NeedFn, class Post>
 __device__ __forceinline__ void cluster_pick(cg::cluster_group& cluster, int C, const uint32_t* h, const uint32_t* s,
                                              uint32_t* xch, Ctrl* ctrl, int nb, NeedFn&& need_of, Post&& post) {
   const int tid = threadIdx.x;
   const int lane = tid & 31, warp = tid >> 5;
   const int fine = nb / kSup;
-  for (int i = tid; i < C * kSup; i += NT) {
-    const uint32_t* rs = cluster.map_shared_rank(s, i / kSup);
-    xch[i] = rs[i % kSup];
-  }
-  if (tid < C) {
-    const Ctrl* rc = cluster.map_shared_rank(ctrl, tid);
-    ctrl->peer_flag[tid] = rc->pub_flag;
-  }
-  __syncthreads();
-  if (warp == 0) {
-    uint32_t lo = 0, hi = 0;
-    for (int q = 0; q < C; ++q) {
-      lo += xch[q * kSup + 2 * lane];
-      hi += xch[q * kSup + 2 * lane + 1];
+  // (A) cluster-wide super-bin totals in ctrl->tot. PUSHED: every CTA already added its sums
+  // into every peer's tot before the cluster barrier. Otherwise pull: one remote word per thread,
+  // summed with shared-memory reductions instead of a serial loop over the ranks.
+  if (!PUSHED) {
+    for (int i = tid; i < C * kSup; i += NT) {
+      const uint32_t* rs = cluster.map_shared_rank(s, i / kSup);
+      red_shared_add(&ctrl->tot[i % kSup], rs[i % kSup]);
     }
+    __syncthreads();
+  }
+  FFTOPK_MARK(40);
+  if (warp == 0) {
+    const uint32_t lo = ctrl->tot[2 * lane], hi = ctrl->tot[2 * lane + 1];
+    ctrl->tot[2 * lane] = 0u;  // ready for the next search
+    ctrl->tot[2 * lane + 1] = 0u;
     const uint32_t total = warp_sum(lo + hi);
-    const uint32_t flags = warp_sum(lane < C ? ctrl->peer_flag[lane] : 0u);
     const uint32_t need = need_of(total);
     int ts = -1;
     uint32_t above = 0, cnt = 0;
@@ -314,11 +298,13 @@ __device__ __forceinline__ void cluster_pick(cg::cluster_group& cluster, int C, 
       ctrl->sup_above = above;
       ctrl->need = need;
       ctrl->run_total = total;
-      ctrl->any_flag = flags;
     }
   }
   __syncthreads();
+  FFTOPK_MARK(41);
   const int ssel = ctrl->sup_sel;
+  // (B) fine bins of the threshold super-bin: pulled from every peer, kept per rank in xch (the
+  // tie path wants them) and summed into ctrl->tot2
   if (ssel >= 0) {
     for (int i = tid; i < C * kSup; i += NT) {
       const int q = i / kSup, f = i % kSup;
@@ -326,25 +312,25 @@ __device__ __forceinline__ void cluster_pick(cg::cluster_group& cluster, int C, 
       if (f < fine) {
         const uint32_t* rh = cluster.map_shared_rank(h, q);
         v = rh[ssel * fine + f];
+        red_shared_add(&ctrl->tot2[f], v);
       }
       xch[i] = v;
     }
   }
   __syncthreads();
+  FFTOPK_MARK(42);
   if (warp == 0) {
     Picked pk;
     pk.ok = false;
     pk.t = -1;
     pk.need2 = pk.cnt = pk.local_w = pk.local_c = 0;
     pk.total = ctrl->run_total;
-    pk.any_flag = ctrl->any_flag;
+    pk.any_flag = 0u;
     pk.tf = 0;
     if (ssel >= 0) {
-      uint32_t lo = 0, hi = 0;
-      for (int q = 0; q < C; ++q) {
-        lo += xch[q * kSup + 2 * lane];
-        hi += xch[q * kSup + 2 * lane + 1];
-      }
+      const uint32_t lo = ctrl->tot2[2 * lane], hi = ctrl->tot2[2 * lane + 1];
+      ctrl->tot2[2 * lane] = 0u;
+      ctrl->tot2[2 * lane + 1] = 0u;
       const uint32_t need = ctrl->need;
       const uint32_t sup_above = ctrl->sup_above;
       int tf = -1;
@@ -367,6 +353,7 @@ __device__ __forceinline__ void cluster_pick(cg::cluster_group& cluster, int C, 
     post(pk);
   }
   __syncthreads();
+  FFTOPK_MARK(43);
 }
 
 // Everything one CTA needs to know about its row and its shared memory.
@@ -469,6 +456,10 @@ __device__ __forceinline__ int refine_from_data(RowCtx<NT>& cx, uint32_t& need, 
       ctrl->cand_count = 0u;  // them again before the cluster barrier of round 0
       ctrl->over_flag = 0u;
     }
+    if (tid < kSup) {  // totals pushed for a search that never ran (forced fallback) must not linger
+      ctrl->tot[tid] = 0u;
+      ctrl->tot2[tid] = 0u;
+    }
   }
   __syncthreads();
   {
@@ -489,7 +480,7 @@ __device__ __forceinline__ int refine_from_data(RowCtx<NT>& cx, uint32_t& need, 
     compute_sup<NT>(h, s, nb);
     cluster.sync();  // every CTA's histogram and super-bin sums of this round are complete
     const uint32_t need_now = need;
-    cluster_pick<NT>(
+    cluster_pick<NT, false>(
         cluster, C, h, s, xch, ctrl, nb, [&](uint32_t) { return need_now; },
         [&](Picked& pk) {
           const bool last = (shift == 0);
@@ -605,7 +596,7 @@ __device__ __forceinline__ int refine_from_data(RowCtx<NT>& cx, uint32_t& need, 
 }
 
 template <int NT>
-__global__ void __launch_bounds__(NT, 1) select2048_kernel(const SelectParams p) {
+__global__ void __launch_bounds__(NT, (NT <= 512 ? 2 : 1)) select2048_kernel(const SelectParams p) {
   RowCtx<NT> cx;
   cg::cluster_group cluster = cg::this_cluster();
   const int C = cx.C = (int)cluster.num_blocks();
@@ -681,7 +672,14 @@ __global__ void __launch_bounds__(NT, 1) select2048_kernel(const SelectParams p)
       ctrl->cslot = 0u;
       ctrl->lcount = 0u;
     }
+    if (tid < kSup) {
+      ctrl->tot[tid] = 0u;
+      ctrl->tot2[tid] = 0u;
+    }
   }
+  // first half of a split cluster barrier: "my totals are cleared". The second half sits just
+  // before the peers' first remote additions, a microsecond of useful work later.
+  cluster_arrive();
 
   // ---- sample (or, for a shard that fits in registers, the whole shard) ------------------------
   // exact:   thread keeps granules g0 + j*NT + tid, j < kRegSlabs
@@ -740,9 +738,11 @@ __global__ void __launch_bounds__(NT, 1) select2048_kernel(const SelectParams p)
     }
   }
   __syncthreads();
-  compute_sup<NT>(cx.hist(0), cx.sup(0), kMaxBins);
+  // every CTA of the cluster has cleared its totals (the arrive is at the end of the prologue)
+  cluster_wait();
+  compute_sup<NT>(cx.hist(0), cx.sup(0), kMaxBins, ctrl->tot, C);
   FFTOPK_MARK(2);
-  cluster.sync();  // #1: sample histograms complete
+  cluster.sync();  // #1: sample histograms complete, super-bin sums added into every peer
   FFTOPK_MARK(3);
 
   uint32_t need = kK;
@@ -754,7 +754,7 @@ __global__ void __launch_bounds__(NT, 1) select2048_kernel(const SelectParams p)
     mode = kModeFallback;
   } else if (exact) {
     // ---- the sample is the row: its histogram gives the threshold bin directly -----------------
-    cluster_pick<NT>(
+    cluster_pick<NT, true>(
         cluster, C, cx.hist(0), cx.sup(0), cx.xch, ctrl, kMaxBins, [&](uint32_t) { return (uint32_t)kK; },
         [&](Picked& pk) { decide_and_allocate<NT>(cx, pk, kModeFallback, false); });
     mode = ctrl->mode;
@@ -792,7 +792,7 @@ __global__ void __launch_bounds__(NT, 1) select2048_kernel(const SelectParams p)
     // need_of: sample rank whose true rank is >= k with overwhelming probability
     // (m expected sample elements among the true top k, plus five standard deviations).
     const float flen = (float)len;
-    cluster_pick<NT>(
+    cluster_pick<NT, true>(
         cluster, C, cx.hist(0), cx.sup(0), cx.xch, ctrl, kMaxBins,
         [&](uint32_t n_s) {
           const float m = (float)kK * (float)n_s / flen;
@@ -831,7 +831,7 @@ __global__ void __launch_bounds__(NT, 1) select2048_kernel(const SelectParams p)
       __syncthreads();
       compute_sup<NT>(cx.hist(1), cx.sup(1), kMaxBins);
       cluster.sync();  // #1b
-      cluster_pick<NT>(
+      cluster_pick<NT, false>(
           cluster, C, cx.hist(1), cx.sup(1), cx.xch, ctrl, kMaxBins, [&](uint32_t) { return rem; },
           [&](Picked& pk) {
             if (lane == 0) {
@@ -852,20 +852,27 @@ __global__ void __launch_bounds__(NT, 1) select2048_kernel(const SelectParams p)
 #ifdef FFTOPK_EXPERIMENT_NOPASS
       edge = __uint_as_float(0x7f800000u);  // experiment: nothing but +inf/NaN passes
 #endif
-      const uint32_t wcap = (uint32_t)p.list_cap / NW;
-      uint64_t* seg = list + (size_t)warp * wcap;
-      const uint32_t wc = filter_shard<NT, (NT >= 1024 ? 4 : 8)>(sh, edge, seg, wcap);  // 64 KiB in flight per SM
+      // list layout: NT * lp thread-private slots, then the spill area (an eighth of the list)
+      const uint32_t spill_cap = (uint32_t)p.list_cap / 8u;
+      const uint32_t lp = ((uint32_t)p.list_cap - spill_cap) / NT;
+      uint64_t* mine_l = list + (size_t)tid * lp;
+      uint64_t* spill = list + (size_t)NT * lp;
+      const uint32_t cnt_all = filter_shard<NT, (NT >= 1024 ? 4 : 8)>(sh, edge, mine_l, lp, ctrl, spill, spill_cap);
       FFTOPK_MARK(8);
       // hand the candidates to rank 0: one remote atomic per CTA allocates the range
-      const uint32_t wn = min(wc, wcap);
-      if (lane == 0) {
-        ctrl->wtot[warp] = wn;
-        if (wc > wcap) ctrl->pub_flag = 1u;
+      const uint32_t mycnt = min(cnt_all, lp);
+      uint32_t lincl = mycnt;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const uint32_t v = __shfl_up_sync(kFull, lincl, off);
+        if (lane >= off) lincl += v;
       }
+      if (lane == 31) ctrl->wtot[warp] = lincl;
       __syncthreads();
+      FFTOPK_MARK(44);
       if (warp == 0) {
-        const uint32_t mine = lane < NW ? ctrl->wtot[lane] : 0u;
-        uint32_t incl = mine;
+        const uint32_t wmine = lane < NW ? ctrl->wtot[lane] : 0u;
+        uint32_t incl = wmine;
 #pragma unroll
         for (int off = 1; off < 32; off <<= 1) {
           const uint32_t v = __shfl_up_sync(kFull, incl, off);
@@ -873,19 +880,28 @@ __global__ void __launch_bounds__(NT, 1) select2048_kernel(const SelectParams p)
         }
         uint32_t base = 0;
         if (lane == 31) {
-          base = atomicAdd(&cx.ctrl0->cand_count, incl);
+          const uint32_t spill_n = min(ctrl->lcount, spill_cap);
+          base = atomicAdd(&cx.ctrl0->cand_count, incl + spill_n);
           if (ctrl->pub_flag) atomicOr(&cx.ctrl0->over_flag, 1u);
+          ctrl->base_c = base + incl;  // where the spill entries go
         }
         base = __shfl_sync(kFull, base, 31);
-        if (lane < NW) ctrl->wtot[lane] = base + incl - mine;
+        if (lane < NW) ctrl->wtot[lane] = base + incl - wmine;
       }
       __syncthreads();
+      FFTOPK_MARK(45);
       {
-        const uint32_t wbase = ctrl->wtot[warp];
-        for (uint32_t j = lane; j < wn; j += 32) {
-          if (wbase + j < (uint32_t)p.cand_cap) cx.cand0[wbase + j] = seg[j];
+        const uint32_t dst = ctrl->wtot[warp] + lincl - mycnt;
+        for (uint32_t j = 0; j < mycnt; ++j) {
+          if (dst + j < (uint32_t)p.cand_cap) cx.cand0[dst + j] = mine_l[j];
+        }
+        const uint32_t spill_n = min(ctrl->lcount, spill_cap);
+        const uint32_t sbase = ctrl->base_c;
+        for (uint32_t j = tid; j < spill_n; j += NT) {
+          if (sbase + j < (uint32_t)p.cand_cap) cx.cand0[sbase + j] = spill[j];
         }
       }
+      FFTOPK_MARK(46);
       cluster.sync();  // #2: every candidate has landed in rank 0
       FFTOPK_MARK(9);
       if (tid == 0) {
@@ -1128,12 +1144,15 @@ const char* fftopk_strerror(int code) {
 int fftopk_last_cuda_error(void) { return g_last_cuda_error; }
 
 #ifdef FFTOPK_TRACE
-int fftopk_debug_read_trace(unsigned long long* out32) {
-  return (int)cudaMemcpyFromSymbol(out32, fftopk::g_trace, sizeof(unsigned long long) * 32);
+int fftopk_debug_read_trace(unsigned long long* times, int* ids, int* n) {
+  cudaError_t e = cudaMemcpyFromSymbol(n, fftopk::g_trace_n, sizeof(int));
+  if (e == cudaSuccess) e = cudaMemcpyFromSymbol(times, fftopk::g_trace_t, sizeof(unsigned long long) * fftopk::kTraceCap);
+  if (e == cudaSuccess) e = cudaMemcpyFromSymbol(ids, fftopk::g_trace_id, sizeof(int) * fftopk::kTraceCap);
+  return (int)e;
 }
 int fftopk_debug_clear_trace(void) {
-  unsigned long long z[32] = {0};
-  return (int)cudaMemcpyToSymbol(fftopk::g_trace, z, sizeof(z));
+  const int z = 0;
+  return (int)cudaMemcpyToSymbol(fftopk::g_trace_n, &z, sizeof(int));
 }
 #endif
 

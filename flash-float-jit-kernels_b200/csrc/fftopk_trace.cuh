@@ -1,20 +1,27 @@
 // Phase timestamps for debugging (compiled in only with -DFFTOPK_TRACE; the production build
-// turns every mark into nothing).
+// turns every mark into nothing). Thread 0 of block 0 appends (id, %globaltimer) pairs to a log.
 #pragma once
 #include <stdint.h>
 namespace fftopk {
 #ifdef FFTOPK_TRACE
-// Debug build only: phase timestamps (ns, %globaltimer) of row 0 / rank 0 / thread 0.
-__device__ unsigned long long g_trace[32];
-__device__ __forceinline__ void trace_mark(int slot, bool who) {
+constexpr int kTraceCap = 128;
+__device__ unsigned long long g_trace_t[kTraceCap];
+__device__ int g_trace_id[kTraceCap];
+__device__ int g_trace_n;
+__device__ __forceinline__ void trace_mark(int id, bool who) {
   if (who) {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    g_trace[slot] = t;
+    const int i = g_trace_n;
+    if (i < kTraceCap) {
+      g_trace_t[i] = t;
+      g_trace_id[i] = id;
+      g_trace_n = i + 1;
+    }
   }
 }
-#define FFTOPK_MARK(slot) trace_mark((slot), blockIdx.x == 0 && threadIdx.x == 0)
+#define FFTOPK_MARK(id) trace_mark((id), blockIdx.x == 0 && threadIdx.x == 0)
 #else
-#define FFTOPK_MARK(slot) ((void)0)
+#define FFTOPK_MARK(id) ((void)0)
 #endif
 }  // namespace fftopk
