@@ -40,19 +40,6 @@ __device__ __forceinline__ uint32_t atom_shared_add(uint32_t* p, uint32_t v) {
   return old;
 }
 
-// Reduction into the shared memory of CTA `rank` of this cluster, at the address that
-// `local_ptr` has in the calling CTA (distributed shared memory, no result, relaxed).
-__device__ __forceinline__ void red_cluster_add(uint32_t* local_ptr, unsigned rank, uint32_t v) {
-  uint32_t raddr;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(raddr) : "r"(smem_u32(local_ptr)), "r"(rank));
-  asm volatile("red.relaxed.cluster.shared::cluster.add.u32 [%0], %1;" ::"r"(raddr), "r"(v) : "memory");
-}
-
-// Split cluster barrier (arrive now, wait later): both halves are executed by every thread of
-// every CTA of the cluster, exactly once each, like cluster.sync().
-__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
-__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
-
 // Histogram update: a plain shared-memory reduction (no result). Measured on B200 (64K updates
 // per CTA, 1024 threads): 6 to 12 updates per clock per SM whatever the bin distribution,
 // all-equal bins included - the hardware combines same-address updates, and ballot / match.any
@@ -136,6 +123,7 @@ struct Ctrl {
   uint32_t win_count;
   uint32_t cand_count;
   uint32_t over_flag;  // rank 0 only: some CTA's candidate list overflowed (remote OR)
+  uint32_t max_key;    // rank 0 only: largest key among the gathered candidates (remote max)
   // published to the peers before a cluster barrier
   uint32_t pub_flag;
   // per-pass local slot counters
@@ -161,6 +149,7 @@ struct Ctrl {
   uint32_t tot[kSup];   // cluster-wide super-bin totals (zero between searches)
   uint32_t tot2[kSup];  // cluster-wide fine-bin totals of the threshold super-bin (same)
   uint32_t wtot[32];
+  uint32_t wmax[32];
   uint64_t small[kSmall];
 };
 
@@ -316,8 +305,8 @@ __device__ void cta_finish(const uint64_t* cand, int n, uint32_t need, int hi, u
         if (lane == 0) ctrl->small[0] = c;
       }
       __syncthreads();
-      fs = 0;
       fthr = ctrl->small[0];
+      fs = 0;
       found = true;
       break;
     }

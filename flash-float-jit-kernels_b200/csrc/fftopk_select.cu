@@ -115,15 +115,18 @@ __device__ __noinline__ void spill_push(Ctrl* ctrl, uint64_t* spill, uint32_t sp
 // Returns the thread's candidate count (entries beyond lp went to the spill area).
 template <int NT, int U>
 __device__ __forceinline__ uint32_t filter_shard(const Shard& sh, float edge, uint64_t* mine, uint32_t lp, Ctrl* ctrl,
-                                                 uint64_t* spill, uint32_t spill_cap) {
+                                                 uint64_t* spill, uint32_t spill_cap, uint32_t& kmax) {
   const int tid = threadIdx.x;
   const float ninf = __uint_as_float(0xff800000u);
   const float4* base4 = reinterpret_cast<const float4*>(sh.gbase);
   const int fa = sh.a, fi1 = sh.i1, len = sh.len;
   uint32_t cnt = 0;
+  kmax = 0u;
   auto keep = [&](float x, int idx) {
     if ((unsigned)idx < (unsigned)len) {
-      const uint64_t comp = ((uint64_t)fftopk_key_from_bits(__float_as_uint(x)) << 32) | (uint64_t)(~(uint32_t)idx);
+      const uint32_t key = fftopk_key_from_bits(__float_as_uint(x));
+      kmax = max(kmax, key);
+      const uint64_t comp = ((uint64_t)key << 32) | (uint64_t)(~(uint32_t)idx);
       if (cnt < lp) {
         mine[cnt] = comp;
       } else {
@@ -132,24 +135,37 @@ __device__ __forceinline__ uint32_t filter_shard(const Shard& sh, float edge, ui
       ++cnt;
     }
   };
+  const float* base1 = sh.gbase;
   for (int gb = sh.i0; gb < fi1; gb += NT * U) {
     float4 x[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int g = gb + u * NT + tid;
-      x[u] = make_float4(ninf, ninf, ninf, ninf);  // padding: passes only an edge of -inf, and then
-      if (g < fi1) x[u] = __ldg(base4 + g);        // carries an index >= len (see e0 below)
+      x[u] = make_float4(ninf, ninf, ninf, ninf);  // padding: passes only an edge of -inf
+      if (g < fi1) x[u] = __ldg(base4 + g);
     }
+    // pass mask of this thread's 4*U elements: bit 4u+e. Granules without a hit (almost all of
+    // them) cost one OR-ed compare per element and nothing else.
+    uint32_t mask = 0;
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       if (!(x[u].x < edge) | !(x[u].y < edge) | !(x[u].z < edge) | !(x[u].w < edge)) {
-        const int g = gb + u * NT + tid;
-        const int e0 = g < fi1 ? 4 * g - fa : len;
-        if (!(x[u].x < edge)) keep(x[u].x, e0 + 0);
-        if (!(x[u].y < edge)) keep(x[u].y, e0 + 1);
-        if (!(x[u].z < edge)) keep(x[u].z, e0 + 2);
-        if (!(x[u].w < edge)) keep(x[u].w, e0 + 3);
+        uint32_t m = !(x[u].x < edge) ? 1u : 0u;
+        m |= !(x[u].y < edge) ? 2u : 0u;
+        m |= !(x[u].z < edge) ? 4u : 0u;
+        m |= !(x[u].w < edge) ? 8u : 0u;
+        if (gb + u * NT + tid < fi1) mask |= m << (4 * u);
       }
+    }
+    // One loop for all hits of the trip: the lanes of a warp work on their own hits side by side
+    // (a separate branch per element position would serialise them). The value is fetched again
+    // (an L1 hit) instead of being selected out of the registers by a computed index.
+    while (mask) {
+      const int bit = __ffs(mask) - 1;
+      mask &= mask - 1u;
+      const int g = gb + (bit >> 2) * NT + tid;
+      const int e = bit & 3;
+      keep(__ldg(base1 + 4 * (int64_t)g + e), 4 * g - fa + e);
     }
   }
   // edge granules [g0, i0) and [i1, g1): at most one each, visited by threads 0 and 32
@@ -211,13 +227,9 @@ __device__ __forceinline__ void scan_shard(const Shard& sh, Op&& op) {
   }
 }
 
-// Sum each group of nb/64 consecutive bins into sup[0..63]. With push_tot != nullptr the thread
-// that holds a super-bin's sum also adds it into `push_tot[bin]` of EVERY CTA of the cluster
-// (remote shared-memory reductions), so that after the next cluster barrier each CTA finds the
-// cluster-wide totals in its own shared memory.
+// Sum each group of nb/64 consecutive bins into sup[0..63].
 template <int NT>
-__device__ __forceinline__ void compute_sup(const uint32_t* hist, uint32_t* sup, int nb, uint32_t* push_tot = nullptr,
-                                            int C = 0) {
+__device__ __forceinline__ void compute_sup(const uint32_t* hist, uint32_t* sup, int nb) {
   const int tid = threadIdx.x;
   if (nb == kMaxBins) {
     constexpr int PER = kMaxBins / NT;            // bins per thread: 4 (1024 thr), 8 (512)
@@ -231,12 +243,7 @@ __device__ __forceinline__ void compute_sup(const uint32_t* hist, uint32_t* sup,
     }
 #pragma unroll
     for (int off = TPS / 2; off > 0; off >>= 1) s += __shfl_xor_sync(kFull, s, off);
-    if ((tid % TPS) == 0) {
-      sup[tid / TPS] = s;
-      if (push_tot != nullptr && s != 0u) {
-        for (int q = 0; q < C; ++q) red_cluster_add(&push_tot[tid / TPS], (unsigned)q, s);
-      }
-    }
+    if ((tid % TPS) == 0) sup[tid / TPS] = s;
   } else {  // 256 bins
     if (tid < kSup) {
       const uint4 v = reinterpret_cast<const uint4*>(hist)[tid];
@@ -267,27 +274,28 @@ struct Picked {
 // Replaces parallel_reduce_histogram + radix_prefix_sum of the reference
 // (topk_indexer_radix.cu:80-107, 232-279), which reduce to rank 0 and broadcast back with three
 // cluster barriers and eight block barriers per round.
-template <int NT, bool PUSHED, class NeedFn, class Post>
+template <int NT, class NeedFn, class Post>
 __device__ __forceinline__ void cluster_pick(cg::cluster_group& cluster, int C, const uint32_t* h, const uint32_t* s,
-                                             uint32_t* xch, Ctrl* ctrl, int nb, NeedFn&& need_of, Post&& post) {
+                                             uint32_t* xch, Ctrl* ctrl, uint32_t* tot, int nb, NeedFn&& need_of,
+                                             Post&& post) {
   const int tid = threadIdx.x;
   const int lane = tid & 31, warp = tid >> 5;
   const int fine = nb / kSup;
-  // (A) cluster-wide super-bin totals in ctrl->tot. PUSHED: every CTA already added its sums
-  // into every peer's tot before the cluster barrier. Otherwise pull: one remote word per thread,
-  // summed with shared-memory reductions instead of a serial loop over the ranks.
-  if (!PUSHED) {
-    for (int i = tid; i < C * kSup; i += NT) {
-      const uint32_t* rs = cluster.map_shared_rank(s, i / kSup);
-      red_shared_add(&ctrl->tot[i % kSup], rs[i % kSup]);
-    }
-    __syncthreads();
+  // (A) cluster-wide super-bin totals in `tot`: one remote word per thread, summed with
+  // shared-memory reductions instead of a serial loop over the ranks. (Pushing the sums into the
+  // peers before the cluster barrier instead - remote reductions behind a split arrive / wait
+  // barrier - was measured and was not faster: the release of the extra arrive costs what the
+  // remote loads cost.)
+  for (int i = tid; i < C * kSup; i += NT) {
+    const uint32_t* rs = cluster.map_shared_rank(s, i / kSup);
+    red_shared_add(&tot[i % kSup], rs[i % kSup]);
   }
+  __syncthreads();
   FFTOPK_MARK(40);
   if (warp == 0) {
-    const uint32_t lo = ctrl->tot[2 * lane], hi = ctrl->tot[2 * lane + 1];
-    ctrl->tot[2 * lane] = 0u;  // ready for the next search
-    ctrl->tot[2 * lane + 1] = 0u;
+    const uint32_t lo = tot[2 * lane], hi = tot[2 * lane + 1];
+    tot[2 * lane] = 0u;  // ready for the next search
+    tot[2 * lane + 1] = 0u;
     const uint32_t total = warp_sum(lo + hi);
     const uint32_t need = need_of(total);
     int ts = -1;
@@ -455,6 +463,7 @@ __device__ __forceinline__ int refine_from_data(RowCtx<NT>& cx, uint32_t& need, 
       ctrl->win_count = 0u;   // rank 0's copies are the cluster-wide counters; nobody touches
       ctrl->cand_count = 0u;  // them again before the cluster barrier of round 0
       ctrl->over_flag = 0u;
+      ctrl->max_key = 0u;
     }
     if (tid < kSup) {  // totals pushed for a search that never ran (forced fallback) must not linger
       ctrl->tot[tid] = 0u;
@@ -480,8 +489,8 @@ __device__ __forceinline__ int refine_from_data(RowCtx<NT>& cx, uint32_t& need, 
     compute_sup<NT>(h, s, nb);
     cluster.sync();  // every CTA's histogram and super-bin sums of this round are complete
     const uint32_t need_now = need;
-    cluster_pick<NT, false>(
-        cluster, C, h, s, xch, ctrl, nb, [&](uint32_t) { return need_now; },
+    cluster_pick<NT>(
+        cluster, C, h, s, xch, ctrl, ctrl->tot, nb, [&](uint32_t) { return need_now; },
         [&](Picked& pk) {
           const bool last = (shift == 0);
           decide_and_allocate<NT>(cx, pk, last ? kModeTies : kModeNext, false);
@@ -659,7 +668,11 @@ __global__ void __launch_bounds__(NT, (NT <= 512 ? 2 : 1)) select2048_kernel(con
   // Whole shard in registers (same answer in every CTA of the cluster: `per` is rank-independent).
   const bool exact = per <= NT * kRegSlabs;
 
-  // ---- prologue: clear both histograms and the control block ---------------------------------
+  // ---- prologue: clear the search totals, both histograms and the control block --------------
+  if (tid < kSup) {
+    ctrl->tot[tid] = 0u;
+    ctrl->tot2[tid] = 0u;
+  }
   {
     uint4* h4 = reinterpret_cast<uint4*>(cx.hist(0));
     for (int i = tid; i < 2 * kMaxBins / 4; i += NT) h4[i] = make_uint4(0u, 0u, 0u, 0u);
@@ -668,19 +681,12 @@ __global__ void __launch_bounds__(NT, (NT <= 512 ? 2 : 1)) select2048_kernel(con
       ctrl->cand_count = 0u;
       ctrl->pub_flag = 0u;
       ctrl->over_flag = 0u;
+      ctrl->max_key = 0u;
       ctrl->wslot = 0u;
       ctrl->cslot = 0u;
       ctrl->lcount = 0u;
     }
-    if (tid < kSup) {
-      ctrl->tot[tid] = 0u;
-      ctrl->tot2[tid] = 0u;
-    }
   }
-  // first half of a split cluster barrier: "my totals are cleared". The second half sits just
-  // before the peers' first remote additions, a microsecond of useful work later.
-  cluster_arrive();
-
   // ---- sample (or, for a shard that fits in registers, the whole shard) ------------------------
   // exact:   thread keeps granules g0 + j*NT + tid, j < kRegSlabs
   // sampled: warp w reads one 512-byte slab at g0 + w*stride; the slabs are spread evenly over the
@@ -738,24 +744,24 @@ __global__ void __launch_bounds__(NT, (NT <= 512 ? 2 : 1)) select2048_kernel(con
     }
   }
   __syncthreads();
-  // every CTA of the cluster has cleared its totals (the arrive is at the end of the prologue)
-  cluster_wait();
-  compute_sup<NT>(cx.hist(0), cx.sup(0), kMaxBins, ctrl->tot, C);
+  compute_sup<NT>(cx.hist(0), cx.sup(0), kMaxBins);
   FFTOPK_MARK(2);
-  cluster.sync();  // #1: sample histograms complete, super-bin sums added into every peer
+  cluster.sync();  // #1: sample histograms complete
   FFTOPK_MARK(3);
 
   uint32_t need = kK;
   uint32_t P = 0;
   int r = 0;
   int mode = kModeAbort;
+  int fin_hi = 64;        // where the finish starts when the sampled path gathered (r < 0)
+  uint64_t fin_pfx = 0ull;
 
   if (p.force_slow) {
     mode = kModeFallback;
   } else if (exact) {
     // ---- the sample is the row: its histogram gives the threshold bin directly -----------------
-    cluster_pick<NT, true>(
-        cluster, C, cx.hist(0), cx.sup(0), cx.xch, ctrl, kMaxBins, [&](uint32_t) { return (uint32_t)kK; },
+    cluster_pick<NT>(
+        cluster, C, cx.hist(0), cx.sup(0), cx.xch, ctrl, ctrl->tot, kMaxBins, [&](uint32_t) { return (uint32_t)kK; },
         [&](Picked& pk) { decide_and_allocate<NT>(cx, pk, kModeFallback, false); });
     mode = ctrl->mode;
     FFTOPK_MARK(4);
@@ -792,8 +798,8 @@ __global__ void __launch_bounds__(NT, (NT <= 512 ? 2 : 1)) select2048_kernel(con
     // need_of: sample rank whose true rank is >= k with overwhelming probability
     // (m expected sample elements among the true top k, plus five standard deviations).
     const float flen = (float)len;
-    cluster_pick<NT, true>(
-        cluster, C, cx.hist(0), cx.sup(0), cx.xch, ctrl, kMaxBins,
+    cluster_pick<NT>(
+        cluster, C, cx.hist(0), cx.sup(0), cx.xch, ctrl, ctrl->tot, kMaxBins,
         [&](uint32_t n_s) {
           const float m = (float)kK * (float)n_s / flen;
           const uint32_t rk = (uint32_t)(m + 5.0f * sqrtf(m) + 14.0f);
@@ -831,8 +837,8 @@ __global__ void __launch_bounds__(NT, (NT <= 512 ? 2 : 1)) select2048_kernel(con
       __syncthreads();
       compute_sup<NT>(cx.hist(1), cx.sup(1), kMaxBins);
       cluster.sync();  // #1b
-      cluster_pick<NT, false>(
-          cluster, C, cx.hist(1), cx.sup(1), cx.xch, ctrl, kMaxBins, [&](uint32_t) { return rem; },
+      cluster_pick<NT>(
+          cluster, C, cx.hist(1), cx.sup(1), cx.xch, ctrl, ctrl->tot, kMaxBins, [&](uint32_t) { return rem; },
           [&](Picked& pk) {
             if (lane == 0) {
               ctrl->mode = pk.ok ? kModeGather : kModeFallback;
@@ -857,7 +863,9 @@ __global__ void __launch_bounds__(NT, (NT <= 512 ? 2 : 1)) select2048_kernel(con
       const uint32_t lp = ((uint32_t)p.list_cap - spill_cap) / NT;
       uint64_t* mine_l = list + (size_t)tid * lp;
       uint64_t* spill = list + (size_t)NT * lp;
-      const uint32_t cnt_all = filter_shard<NT, (NT >= 1024 ? 4 : 8)>(sh, edge, mine_l, lp, ctrl, spill, spill_cap);
+      uint32_t kmax = 0u;
+      const uint32_t cnt_all =
+          filter_shard<NT, (NT >= 1024 ? 4 : 8)>(sh, edge, mine_l, lp, ctrl, spill, spill_cap, kmax);
       FFTOPK_MARK(8);
       // hand the candidates to rank 0: one remote atomic per CTA allocates the range
       const uint32_t mycnt = min(cnt_all, lp);
@@ -867,7 +875,11 @@ __global__ void __launch_bounds__(NT, (NT <= 512 ? 2 : 1)) select2048_kernel(con
         const uint32_t v = __shfl_up_sync(kFull, lincl, off);
         if (lane >= off) lincl += v;
       }
-      if (lane == 31) ctrl->wtot[warp] = lincl;
+      kmax = __reduce_max_sync(kFull, kmax);
+      if (lane == 31) {
+        ctrl->wtot[warp] = lincl;
+        ctrl->wmax[warp] = kmax;
+      }
       __syncthreads();
       FFTOPK_MARK(44);
       if (warp == 0) {
@@ -878,10 +890,12 @@ __global__ void __launch_bounds__(NT, (NT <= 512 ? 2 : 1)) select2048_kernel(con
           const uint32_t v = __shfl_up_sync(kFull, incl, off);
           if (lane >= off) incl += v;
         }
+        const uint32_t cmax = __reduce_max_sync(kFull, lane < NW ? ctrl->wmax[lane] : 0u);
         uint32_t base = 0;
         if (lane == 31) {
           const uint32_t spill_n = min(ctrl->lcount, spill_cap);
           base = atomicAdd(&cx.ctrl0->cand_count, incl + spill_n);
+          atomicMax(&cx.ctrl0->max_key, cmax);
           if (ctrl->pub_flag) atomicOr(&cx.ctrl0->over_flag, 1u);
           ctrl->base_c = base + incl;  // where the spill entries go
         }
@@ -904,18 +918,27 @@ __global__ void __launch_bounds__(NT, (NT <= 512 ? 2 : 1)) select2048_kernel(con
       FFTOPK_MARK(46);
       cluster.sync();  // #2: every candidate has landed in rank 0
       FFTOPK_MARK(9);
-      if (tid == 0) {
-        const uint32_t total = cx.ctrl0->cand_count;
-        const uint32_t over = cx.ctrl0->over_flag;
-        // fewer than k admitted (the guess was too high), a segment overflowed, or more than
-        // rank 0 can hold: start over with full histograms
-        ctrl->mode = (over == 0u && total >= (uint32_t)kK && total <= (uint32_t)p.cand_cap) ? kModeGather : kModeFallback;
+      {
+        // every thread reads rank 0's totals itself (no broadcast barrier; for rank 0, whose finish
+        // is the critical path, these are local reads)
+        const Ctrl* c0 = rank == 0 ? ctrl : cx.ctrl0;
+        const uint32_t total = c0->cand_count;
+        const uint32_t over = c0->over_flag;
+        const uint32_t maxkey = c0->max_key;
+        // fewer than k admitted (the guess was too high), a list overflowed, or more than rank 0
+        // can hold: start over with full histograms
+        mode = (over == 0u && total >= (uint32_t)kK && total <= (uint32_t)p.cand_cap) ? kModeGather : kModeFallback;
+        // every candidate's key lies in [lowkey, maxkey]: the bits those two share are a prefix of
+        // all of them, so the finish starts at the first bit where they differ
+        const uint32_t lowkey = (gkey > 0x007fffffu && gkey <= 0xff800000u) ? gkey : 0u;
+        const uint32_t diff = lowkey ^ maxkey;
+        const int kb = diff ? 32 - __clz((int)diff) : 0;
+        fin_hi = 32 + kb;
+        fin_pfx = kb >= 32 ? 0ull : (uint64_t)(maxkey >> kb);
       }
-      __syncthreads();
-      mode = ctrl->mode;
       need = kK;
       P = 0;
-      r = -1;  // "no key prefix known" for the finish
+      r = -1;  // finish first, final barrier afterwards
       FFTOPK_MARK(10);
     } else {
       mode = kModeFallback;
@@ -934,9 +957,10 @@ __global__ void __launch_bounds__(NT, (NT <= 512 ? 2 : 1)) select2048_kernel(con
   FFTOPK_MARK(6);
   if (mode == kModeGather && rank == 0) {
     const int n = (int)min(ctrl->cand_count, (uint32_t)p.cand_cap);
-    const int hi = r < 0 ? 64 : 32 + round_shift(r);
+    const int hi = r < 0 ? fin_hi : 32 + round_shift(r);
+    const uint64_t pfx = r < 0 ? fin_pfx : (uint64_t)P;
     int idx_bits = 32 - __clz(len - 1);
-    cta_finish<NT>(cx.cand, n, need, hi, (uint64_t)P, idx_bits, cx.hist(0), ctrl, out_idx, out_key,
+    cta_finish<NT>(cx.cand, n, need, hi, pfx, idx_bits, cx.hist(0), ctrl, out_idx, out_key,
                    (uint32_t)kK - need, p.idx_offset, p.status);
   }
   if (finish_first) cluster.sync();
