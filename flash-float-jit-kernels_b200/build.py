@@ -18,8 +18,9 @@ ROOT = Path(__file__).resolve().parent
 CSRC = ROOT / "csrc"
 LIB_DIR = ROOT / "lib"
 LIB_PATH = LIB_DIR / "libfftopk.so"
-SOURCES = [CSRC / "fftopk_select.cu"]
-HEADERS = [CSRC / "fftopk_device.cuh", CSRC / "fftopk_key.h", ROOT.parent / "include" / "fftopk.h"]
+SOURCES = [CSRC / "fftopk_select.cu", CSRC / "fftopk_cp.cu"]
+HEADERS = [CSRC / "fftopk_device.cuh", CSRC / "fftopk_key.h", CSRC / "fftopk_host.h", CSRC / "fftopk_trace.cuh",
+           ROOT.parent / "include" / "fftopk.h"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -1,0 +1,289 @@
+// Context-parallel side of the top-2048 selector: the candidate merge, and a fused
+// gather-and-merge over peer memory that needs no collective library call.
+//
+// Every GPU selects a local top-2048 over its slice of the sequence (fftopk_select2048 with keys
+// and a global index offset). The global top-2048 is contained in the union of the local ones, so
+// one CTA per row loads the G*2048 (key, global index) candidates into shared memory and runs the
+// same single-CTA finish the selector uses.
+//
+//  * fftopk_merge2048: candidates already gathered into local memory (NCCL all-gather).
+//  * fftopk_merge2048_cp: every rank published its candidates in a buffer its peers have mapped
+//    (CUDA IPC over NVLink); the merge kernel itself waits - bounded - for each peer's epoch flag
+//    and pulls the peer's candidates with plain loads. Gather and merge are one kernel; there is no
+//    multicast load and no library kernel that touches peer memory.
+//
+// No reference counterpart: the reference has no multi-GPU path.
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <string.h>
+
+#include "../../include/fftopk.h"
+#include "fftopk_trace.cuh"
+#include "fftopk_device.cuh"
+#include "fftopk_host.h"
+#include "fftopk_key.h"
+
+namespace fftopk {
+
+constexpr int kMaxShards = 8;
+constexpr int kCommFlagWords = 32;  // one 128-byte line for the epoch flag
+
+// Where the candidates of each shard live, and (fused mode) the flag that says they are there.
+struct MergeSrc {
+  const int32_t* idx[kMaxShards];
+  const uint32_t* key[kMaxShards];
+  const uint32_t* flag[kMaxShards];  // nullptr: no wait
+  uint32_t epoch;
+  unsigned long long wait_ns;
+};
+
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Publishes "my candidates of this epoch are written": runs after the select kernel in stream
+// order, fences its writes system-wide and releases the flag.
+__global__ void publish_kernel(uint32_t* flag, uint32_t epoch) {
+  __threadfence_system();
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(epoch) : "memory");
+}
+
+template <int NT>
+__global__ void __launch_bounds__(NT, 1) merge2048_kernel(const MergeSrc src, int G, int B,
+                                                         int32_t* __restrict__ out_idx_all,
+                                                         uint32_t* __restrict__ out_key_all, uint32_t* status) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  uint32_t* hist = reinterpret_cast<uint32_t*>(smem_raw);
+  Ctrl* ctrl = reinterpret_cast<Ctrl*>(hist + kFinishBins);
+  uint64_t* cand = reinterpret_cast<uint64_t*>(reinterpret_cast<unsigned char*>(ctrl) + ((sizeof(Ctrl) + 127) & ~127u));
+  const int row = blockIdx.x;
+  const int tid = threadIdx.x;
+  const int n = G * kK;
+  int32_t* out_idx = out_idx_all + (int64_t)row * kK;
+  uint32_t* out_key = out_key_all ? out_key_all + (int64_t)row * kK : nullptr;
+
+  if (tid == 0) {
+    ctrl->run_total = 0u;
+    ctrl->pub_flag = 0u;
+  }
+  __syncthreads();
+  // Fused mode: thread g waits until shard g's owner has published this epoch. The wait is
+  // bounded: when it runs out the row is filled with -1, a status bit is raised and the kernel
+  // returns normally, so a peer that never arrives cannot hang this GPU.
+  if (tid < G && src.flag[tid] != nullptr) {
+    const unsigned long long t0 = global_timer_ns();
+    bool ok = false;
+    for (;;) {
+      if ((int32_t)(ld_acquire_sys(src.flag[tid]) - src.epoch) >= 0) {
+        ok = true;
+        break;
+      }
+      if (global_timer_ns() - t0 > src.wait_ns) break;
+      __nanosleep(200);
+    }
+    if (!ok) ctrl->pub_flag = 1u;
+  }
+  __syncthreads();
+  if (ctrl->pub_flag) {
+    for (int i = tid; i < kK; i += NT) {
+      out_idx[i] = -1;
+      if (out_key) out_key[i] = 0u;
+    }
+    if (tid == 0 && status) atomicOr(status, (uint32_t)FFTOPK_ST_PEER_TIMEOUT);
+    return;
+  }
+  uint32_t nvalid = 0;
+  for (int i = tid; i < n; i += NT) {
+    const int g = i / kK, j = i % kK;
+    const int64_t off = (int64_t)row * kK + j;
+    // L2-coherent loads: the data may have been written by another GPU a moment ago
+    const int32_t idx = __ldcg(src.idx[g] + off);
+    const uint32_t key = __ldcg(src.key[g] + off);
+    const bool v = idx >= 0;
+    cand[i] = v ? (((uint64_t)key << 32) | (uint64_t)(~(uint32_t)idx)) : 0ull;
+    nvalid += v ? 1u : 0u;
+  }
+  nvalid = warp_sum(nvalid);
+  if ((tid & 31) == 0 && nvalid) red_shared_add(&ctrl->run_total, nvalid);
+  __syncthreads();
+  const uint32_t total = ctrl->run_total;
+  if (total <= (uint32_t)kK) {
+    // fewer candidates than k: keep them all (gather order), pad with -1
+    if (tid == 0) ctrl->fslot = 0u;
+    __syncthreads();
+    for (int i = tid; i < n; i += NT) {
+      const uint64_t c = cand[i];
+      if (c != 0ull) {
+        const uint32_t pos = warp_alloc(&ctrl->fslot);
+        out_idx[pos] = (int32_t)(~(uint32_t)c);
+        if (out_key) out_key[pos] = (uint32_t)(c >> 32);
+      }
+    }
+    for (int i = (int)total + tid; i < kK; i += NT) {
+      out_idx[i] = -1;
+      if (out_key) out_key[i] = 0u;
+    }
+    return;
+  }
+  cta_finish<NT>(cand, n, (uint32_t)kK, 64, 0ull, 31, hist, ctrl, out_idx, out_key, 0u, 0, status);
+}
+
+}  // namespace fftopk
+
+namespace {
+using namespace fftopk;
+
+bool g_merge_ready[64];
+
+int merge_setup() {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_fail(e);
+  if (dev < 0 || dev >= 64) return FFTOPK_EDEVICE;
+  if (!g_merge_ready[dev]) {
+    int optin = 0;
+    e = cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+    if (e != cudaSuccess) return cuda_fail(e);
+    e = cudaFuncSetAttribute(merge2048_kernel<1024>, cudaFuncAttributeMaxDynamicSharedMemorySize, optin);
+    if (e != cudaSuccess) return cuda_fail(e);
+    g_merge_ready[dev] = true;
+  }
+  return 0;
+}
+
+size_t merge_smem(int G) {
+  return (size_t)kFinishBins * 4 + ((sizeof(Ctrl) + 127) & ~(size_t)127) + (size_t)G * kK * 8;
+}
+
+// comm buffer layout, in 32-bit words, for a row capacity of b_cap:
+//   [parity 0: index plane b_cap*2048 | key plane b_cap*2048][parity 1: same][flag line: 32 words]
+size_t comm_words(int32_t b_cap) { return (size_t)4 * b_cap * kK + kCommFlagWords; }
+
+}  // namespace
+
+extern "C" {
+
+int fftopk_merge2048(const uint32_t* cand_key, const int32_t* cand_idx, int64_t shard_stride, int32_t G, int32_t B,
+                     int32_t* out_idx, uint32_t* out_key, uint32_t* status, void* cuda_stream) {
+  if (B < 0 || G < 1 || shard_stride < 0) return FFTOPK_EINVAL;
+  if (G > kMaxShards) return FFTOPK_ERANGE;
+  if (B == 0) return FFTOPK_OK;
+  if (!cand_key || !cand_idx || !out_idx) return FFTOPK_EINVAL;
+  if (shard_stride == 0) shard_stride = (int64_t)B * kK;
+  int rc = merge_setup();
+  if (rc) return rc;
+  MergeSrc src;
+  memset(&src, 0, sizeof(src));
+  for (int g = 0; g < G; ++g) {
+    src.idx[g] = cand_idx + (int64_t)g * shard_stride;
+    src.key[g] = cand_key + (int64_t)g * shard_stride;
+  }
+  merge2048_kernel<1024><<<dim3((unsigned)B), dim3(1024), merge_smem(G), static_cast<cudaStream_t>(cuda_stream)>>>(
+      src, G, B, out_idx, out_key, status);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e);
+  return FFTOPK_OK;
+}
+
+int fftopk_comm_bytes(int32_t b_cap, size_t* bytes) {
+  if (b_cap < 1 || !bytes) return FFTOPK_EINVAL;
+  *bytes = comm_words(b_cap) * 4;
+  return FFTOPK_OK;
+}
+
+int fftopk_comm_create(int32_t b_cap, void** comm, unsigned char handle[64]) {
+  if (b_cap < 1 || !comm || !handle) return FFTOPK_EINVAL;
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, comm_words(b_cap) * 4);
+  if (e != cudaSuccess) return cuda_fail(e);
+  e = cudaMemset(p, 0, comm_words(b_cap) * 4);
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  cudaIpcMemHandle_t h;
+  if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, p);
+  if (e != cudaSuccess) {
+    cudaFree(p);
+    return cuda_fail(e);
+  }
+  memcpy(handle, &h, 64);
+  *comm = p;
+  return FFTOPK_OK;
+}
+
+int fftopk_comm_open(const unsigned char handle[64], void** peer_comm) {
+  if (!handle || !peer_comm) return FFTOPK_EINVAL;
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, 64);
+  cudaError_t e = cudaIpcOpenMemHandle(peer_comm, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) return cuda_fail(e);
+  return FFTOPK_OK;
+}
+
+int fftopk_comm_close(void* peer_comm) {
+  if (!peer_comm) return FFTOPK_EINVAL;
+  cudaError_t e = cudaIpcCloseMemHandle(peer_comm);
+  if (e != cudaSuccess) return cuda_fail(e);
+  return FFTOPK_OK;
+}
+
+int fftopk_comm_destroy(void* comm) {
+  if (!comm) return FFTOPK_EINVAL;
+  cudaError_t e = cudaFree(comm);
+  if (e != cudaSuccess) return cuda_fail(e);
+  return FFTOPK_OK;
+}
+
+int fftopk_select2048_cp(const float* score, int64_t row_stride, int32_t B, int64_t L, const int32_t* lengths,
+                         int32_t idx_offset, void* comm, int32_t b_cap, uint32_t epoch, uint32_t* status,
+                         void* cuda_stream) {
+  if (!comm || b_cap < 1 || B < 0 || B > b_cap) return FFTOPK_EINVAL;
+  int32_t* base = static_cast<int32_t*>(comm) + (size_t)(epoch & 1u) * 2 * b_cap * kK;
+  if (B > 0) {
+    int rc = fftopk_select2048(score, row_stride, B, L, lengths, nullptr, base,
+                               reinterpret_cast<uint32_t*>(base + (size_t)b_cap * kK), idx_offset, status,
+                               cuda_stream);
+    if (rc) return rc;
+  }
+  uint32_t* flag = reinterpret_cast<uint32_t*>(static_cast<int32_t*>(comm) + (size_t)4 * b_cap * kK);
+  publish_kernel<<<1, 1, 0, static_cast<cudaStream_t>(cuda_stream)>>>(flag, epoch);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e);
+  return FFTOPK_OK;
+}
+
+int fftopk_merge2048_cp(void* const* comms, int32_t G, int32_t B, int32_t b_cap, uint32_t epoch, int32_t wait_ms,
+                        int32_t* out_idx, uint32_t* out_key, uint32_t* status, void* cuda_stream) {
+  if (!comms || G < 1 || B < 0 || b_cap < 1 || B > b_cap || wait_ms < 0) return FFTOPK_EINVAL;
+  if (G > kMaxShards) return FFTOPK_ERANGE;
+  if (B == 0) return FFTOPK_OK;
+  if (!out_idx) return FFTOPK_EINVAL;
+  int rc = merge_setup();
+  if (rc) return rc;
+  MergeSrc src;
+  memset(&src, 0, sizeof(src));
+  for (int g = 0; g < G; ++g) {
+    if (!comms[g]) return FFTOPK_EINVAL;
+    const int32_t* words = static_cast<const int32_t*>(comms[g]);
+    const int32_t* base = words + (size_t)(epoch & 1u) * 2 * b_cap * kK;
+    src.idx[g] = base;
+    src.key[g] = reinterpret_cast<const uint32_t*>(base + (size_t)b_cap * kK);
+    src.flag[g] = reinterpret_cast<const uint32_t*>(words + (size_t)4 * b_cap * kK);
+  }
+  src.epoch = epoch;
+  src.wait_ns = (unsigned long long)wait_ms * 1000000ull;
+  merge2048_kernel<1024><<<dim3((unsigned)B), dim3(1024), merge_smem(G), static_cast<cudaStream_t>(cuda_stream)>>>(
+      src, G, B, out_idx, out_key, status);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e);
+  return FFTOPK_OK;
+}
+
+}  // extern "C"

@@ -35,6 +35,7 @@
 #include "../../include/fftopk.h"
 #include "fftopk_trace.cuh"
 #include "fftopk_device.cuh"
+#include "fftopk_host.h"
 #include "fftopk_key.h"
 
 namespace fftopk {
@@ -968,61 +969,6 @@ __global__ void __launch_bounds__(NT, (NT <= 512 ? 2 : 1)) select2048_kernel(con
   if (tid == 0 && p.status && mode == kModeAbort) atomicOr(p.status, (uint32_t)FFTOPK_ST_INTERNAL);
 }
 
-// -----------------------------------------------------------------------------------------
-// Merge of all-gathered shard candidates: one CTA per row, candidates held in shared memory.
-// -----------------------------------------------------------------------------------------
-template <int NT>
-__global__ void __launch_bounds__(NT, 1) merge2048_kernel(const uint32_t* __restrict__ cand_key,
-                                                         const int32_t* __restrict__ cand_idx, int G, int B,
-                                                         int32_t* __restrict__ out_idx_all,
-                                                         uint32_t* __restrict__ out_key_all, uint32_t* status) {
-  extern __shared__ __align__(128) unsigned char smem_raw[];
-  uint32_t* hist = reinterpret_cast<uint32_t*>(smem_raw);
-  Ctrl* ctrl = reinterpret_cast<Ctrl*>(hist + kFinishBins);
-  uint64_t* cand = reinterpret_cast<uint64_t*>(reinterpret_cast<unsigned char*>(ctrl) + ((sizeof(Ctrl) + 127) & ~127u));
-  const int row = blockIdx.x;
-  const int tid = threadIdx.x;
-  const int n = G * kK;
-  int32_t* out_idx = out_idx_all + (int64_t)row * kK;
-  uint32_t* out_key = out_key_all ? out_key_all + (int64_t)row * kK : nullptr;
-
-  if (tid == 0) ctrl->run_total = 0u;
-  __syncthreads();
-  uint32_t nvalid = 0;
-  for (int i = tid; i < n; i += NT) {
-    const int g = i / kK, j = i % kK;
-    const int64_t src = ((int64_t)g * B + row) * kK + j;
-    const int32_t idx = __ldg(cand_idx + src);
-    const uint32_t key = __ldg(cand_key + src);
-    const bool v = idx >= 0;
-    cand[i] = v ? (((uint64_t)key << 32) | (uint64_t)(~(uint32_t)idx)) : 0ull;
-    nvalid += v ? 1u : 0u;
-  }
-  nvalid = warp_sum(nvalid);
-  if ((tid & 31) == 0 && nvalid) red_shared_add(&ctrl->run_total, nvalid);
-  __syncthreads();
-  const uint32_t total = ctrl->run_total;
-  if (total <= (uint32_t)kK) {
-    // fewer candidates than k: keep them all (gather order), pad with -1
-    if (tid == 0) ctrl->fslot = 0u;
-    __syncthreads();
-    for (int i = tid; i < n; i += NT) {
-      const uint64_t c = cand[i];
-      if (c != 0ull) {
-        const uint32_t pos = warp_alloc(&ctrl->fslot);
-        out_idx[pos] = (int32_t)(~(uint32_t)c);
-        if (out_key) out_key[pos] = (uint32_t)(c >> 32);
-      }
-    }
-    for (int i = (int)total + tid; i < kK; i += NT) {
-      out_idx[i] = -1;
-      if (out_key) out_key[i] = 0u;
-    }
-    return;
-  }
-  cta_finish<NT>(cand, n, (uint32_t)kK, 64, 0ull, 31, hist, ctrl, out_idx, out_key, 0u, 0, status);
-}
-
 }  // namespace fftopk
 
 // =============================================================================================
@@ -1032,7 +978,6 @@ namespace {
 
 using namespace fftopk;
 
-thread_local int g_last_cuda_error = 0;
 
 struct Tuning {
   int cluster = -1, threads = -1, list_cap = -1, cand_cap = -1, force_slow = 0;
@@ -1055,10 +1000,6 @@ constexpr size_t fixed_smem_bytes() {
 constexpr int kLatencyListCap = 6144, kLatencyCandCap = 16384;  // one CTA per SM: use the shared memory
 constexpr int kBatchListCap = 4096, kBatchCandCap = 4096;       // several CTAs per SM
 
-int cuda_fail(cudaError_t e) {
-  g_last_cuda_error = (int)e;
-  return FFTOPK_ECUDA;
-}
 
 template <int NT>
 int setup_kernel(int smem_optin) {
@@ -1087,8 +1028,6 @@ int device_info(DeviceInfo** out) {
     if (rc) return rc;
     rc = setup_kernel<512>(d.smem_optin);
     if (rc) return rc;
-    e = cudaFuncSetAttribute(merge2048_kernel<1024>, cudaFuncAttributeMaxDynamicSharedMemorySize, d.smem_optin);
-    if (e != cudaSuccess) return cuda_fail(e);
     // can a 16-CTA cluster with the latency-mode shared-memory footprint be co-scheduled?
     d.max_cluster = 8;
     {
@@ -1165,7 +1104,7 @@ const char* fftopk_strerror(int code) {
   }
 }
 
-int fftopk_last_cuda_error(void) { return g_last_cuda_error; }
+int fftopk_last_cuda_error(void) { return fftopk::g_last_cuda_error; }
 
 #ifdef FFTOPK_TRACE
 int fftopk_debug_read_trace(unsigned long long* times, int* ids, int* n) {
@@ -1262,23 +1201,6 @@ int fftopk_select2048(const float* score, int64_t row_stride, int32_t B, int64_t
   } else {
     e = cudaLaunchKernelEx(&cfg, select2048_kernel<512>, p);
   }
-  if (e != cudaSuccess) return cuda_fail(e);
-  return FFTOPK_OK;
-}
-
-int fftopk_merge2048(const uint32_t* cand_key, const int32_t* cand_idx, int32_t G, int32_t B, int32_t* out_idx,
-                     uint32_t* out_key, uint32_t* status, void* cuda_stream) {
-  if (B < 0 || G < 1) return FFTOPK_EINVAL;
-  if (G > 8) return FFTOPK_ERANGE;
-  if (B == 0) return FFTOPK_OK;
-  if (!cand_key || !cand_idx || !out_idx) return FFTOPK_EINVAL;
-  DeviceInfo* d = nullptr;
-  int rc = device_info(&d);
-  if (rc) return rc;
-  const size_t smem = (size_t)kFinishBins * 4 + ((sizeof(Ctrl) + 127) & ~(size_t)127) + (size_t)G * kK * 8;
-  merge2048_kernel<1024><<<dim3((unsigned)B), dim3(1024), smem, static_cast<cudaStream_t>(cuda_stream)>>>(
-      cand_key, cand_idx, G, B, out_idx, out_key, status);
-  cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e);
   return FFTOPK_OK;
 }

@@ -5,9 +5,9 @@
 namespace fftopk {
 #ifdef FFTOPK_TRACE
 constexpr int kTraceCap = 128;
-__device__ unsigned long long g_trace_t[kTraceCap];
-__device__ int g_trace_id[kTraceCap];
-__device__ int g_trace_n;
+static __device__ unsigned long long g_trace_t[kTraceCap];
+static __device__ int g_trace_id[kTraceCap];
+static __device__ int g_trace_n;
 __device__ __forceinline__ void trace_mark(int id, bool who) {
   if (who) {
     unsigned long long t;

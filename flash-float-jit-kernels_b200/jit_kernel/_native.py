@@ -25,6 +25,13 @@ EXPORTS = (
     "fftopk_last_cuda_error",
     "fftopk_select2048",
     "fftopk_merge2048",
+    "fftopk_comm_bytes",
+    "fftopk_comm_create",
+    "fftopk_comm_open",
+    "fftopk_comm_close",
+    "fftopk_comm_destroy",
+    "fftopk_select2048_cp",
+    "fftopk_merge2048_cp",
     "fftopk_key_of",
     "fftopk_plan",
     "fftopk_set_tuning",
@@ -70,7 +77,23 @@ def lib() -> ctypes.CDLL:
         c.c_void_p, c.c_void_p, c.c_int32, c.c_void_p, c.c_void_p]
     L.fftopk_merge2048.restype = c.c_int
     L.fftopk_merge2048.argtypes = [
-        c.c_void_p, c.c_void_p, c.c_int32, c.c_int32, c.c_void_p, c.c_void_p, c.c_void_p, c.c_void_p]
+        c.c_void_p, c.c_void_p, c.c_int64, c.c_int32, c.c_int32, c.c_void_p, c.c_void_p, c.c_void_p, c.c_void_p]
+    L.fftopk_comm_bytes.restype = c.c_int
+    L.fftopk_comm_bytes.argtypes = [c.c_int32, c.POINTER(c.c_size_t)]
+    L.fftopk_comm_create.restype = c.c_int
+    L.fftopk_comm_create.argtypes = [c.c_int32, c.POINTER(c.c_void_p), c.c_char_p]
+    L.fftopk_comm_open.restype = c.c_int
+    L.fftopk_comm_open.argtypes = [c.c_char_p, c.POINTER(c.c_void_p)]
+    L.fftopk_comm_close.restype = c.c_int
+    L.fftopk_comm_close.argtypes = [c.c_void_p]
+    L.fftopk_comm_destroy.restype = c.c_int
+    L.fftopk_comm_destroy.argtypes = [c.c_void_p]
+    L.fftopk_select2048_cp.restype = c.c_int
+    L.fftopk_select2048_cp.argtypes = [c.c_void_p, c.c_int64, c.c_int32, c.c_int64, c.c_void_p, c.c_int32,
+                                       c.c_void_p, c.c_int32, c.c_uint32, c.c_void_p, c.c_void_p]
+    L.fftopk_merge2048_cp.restype = c.c_int
+    L.fftopk_merge2048_cp.argtypes = [c.POINTER(c.c_void_p), c.c_int32, c.c_int32, c.c_int32, c.c_uint32, c.c_int32,
+                                      c.c_void_p, c.c_void_p, c.c_void_p, c.c_void_p]
     L.fftopk_key_of.restype = c.c_uint32
     L.fftopk_key_of.argtypes = [c.c_float]
     L.fftopk_plan.restype = c.c_int

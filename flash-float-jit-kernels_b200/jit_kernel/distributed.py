@@ -51,12 +51,11 @@ def merge_candidates(cand: torch.Tensor) -> torch.Tensor:
     out = torch.empty((B, TOPK), dtype=torch.int32, device=cand.device)
     if B == 0:
         return out
-    # the C ABI takes separate [G, B, 2048] planes: gather them out of the packed layout
-    idx_plane = cand[:, 0].contiguous()
-    key_plane = cand[:, 1].contiguous()
+    # [G, 2, B, 2048]: index plane at the base, key plane B*2048 elements later, shards 2*B*2048 apart
+    plane = B * TOPK
     lib = _native.lib()
     with torch.cuda.device(cand.device):
-        rc = lib.fftopk_merge2048(key_plane.data_ptr(), idx_plane.data_ptr(), G, B, out.data_ptr(), None,
+        rc = lib.fftopk_merge2048(cand.data_ptr() + 4 * plane, cand.data_ptr(), 2 * plane, G, B, out.data_ptr(), None,
                                   _status_word(cand.device).data_ptr(),
                                   torch.cuda.current_stream().cuda_stream)
     _native.check(rc, "fftopk_merge2048")
@@ -92,3 +91,81 @@ def fast_topk_v3_context_parallel(
     dist.all_gather_into_tensor(gathered.view((world * mine.shape[0],) + tuple(mine.shape[1:])),
                                 mine.contiguous(), group=group)
     return merge(gathered)
+
+
+class FusedContextParallelTopk:
+    """Context-parallel top-2048 without a collective call on the data path.
+
+    Every rank keeps one "comm" buffer that all peers map through CUDA IPC. A call is: local
+    selection straight into the rank's own buffer, a flag release, and ONE merge kernel that waits
+    (bounded, `wait_ms`) for every peer's flag and pulls the peers' candidates over NVLink with
+    plain loads. torch.distributed is used once, at construction, to exchange the IPC handles.
+
+    All ranks of `group` must construct the object and call it the same number of times (the
+    epoch counter advances by one per call on every rank).
+    """
+
+    def __init__(self, max_rows: int, group: Optional[dist.ProcessGroup] = None, wait_ms: int = 2000):
+        import ctypes
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.b_cap = int(max_rows)
+        self.wait_ms = int(wait_ms)
+        self.epoch = 0
+        self.device = torch.device("cuda", torch.cuda.current_device())
+        lib = _native.lib()
+        own = ctypes.c_void_p()
+        handle = ctypes.create_string_buffer(64)
+        _native.check(lib.fftopk_comm_create(self.b_cap, ctypes.byref(own), handle), "fftopk_comm_create")
+        self._own = own.value
+        handles = [None] * self.world
+        dist.all_gather_object(handles, bytes(handle.raw), group=group)
+        self._peers = []
+        ptrs = []
+        for r in range(self.world):
+            if r == self.rank:
+                ptrs.append(self._own)
+                continue
+            p = ctypes.c_void_p()
+            _native.check(lib.fftopk_comm_open(handles[r], ctypes.byref(p)), "fftopk_comm_open")
+            self._peers.append(p.value)
+            ptrs.append(p.value)
+        self._comms = (ctypes.c_void_p * self.world)(*ptrs)
+        dist.barrier(group=group)  # every buffer is mapped everywhere before the first call
+
+    def __call__(self, score_shard: torch.Tensor, lengths_global: torch.Tensor, topk: int = TOPK) -> torch.Tensor:
+        assert topk == TOPK and score_shard.dim() == 2
+        B, Ls = score_shard.shape
+        if B > self.b_cap:
+            raise RuntimeError(f"batch of {B} rows exceeds the comm buffer capacity {self.b_cap}")
+        if not score_shard.is_cuda or score_shard.dtype != torch.float32 or (score_shard.stride(1) != 1 and Ls > 1):
+            raise RuntimeError("score_shard must be a CUDA float32 tensor with unit inner stride")
+        lens = local_lengths(lengths_global, Ls, self.rank).to(score_shard.device)
+        out = torch.empty((B, TOPK), dtype=torch.int32, device=score_shard.device)
+        self.epoch += 1
+        lib = _native.lib()
+        status = _status_word(score_shard.device).data_ptr()
+        with torch.cuda.device(score_shard.device):
+            stream = torch.cuda.current_stream().cuda_stream
+            rc = lib.fftopk_select2048_cp(score_shard.data_ptr(), score_shard.stride(0), B, Ls, lens.data_ptr(),
+                                          self.rank * Ls, self._own, self.b_cap, self.epoch, status, stream)
+            _native.check(rc, "fftopk_select2048_cp")
+            rc = lib.fftopk_merge2048_cp(self._comms, self.world, B, self.b_cap, self.epoch, self.wait_ms,
+                                         out.data_ptr(), None, status, stream)
+            _native.check(rc, "fftopk_merge2048_cp")
+        return out
+
+    def close(self) -> None:
+        """Unmap the peers' buffers and free the own one (all ranks, after a barrier)."""
+        if self._own is None:
+            return
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)
+        lib = _native.lib()
+        for p in self._peers:
+            lib.fftopk_comm_close(p)
+        dist.barrier(group=self.group)
+        lib.fftopk_comm_destroy(self._own)
+        self._own = None
+        self._peers = []

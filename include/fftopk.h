@@ -90,13 +90,53 @@ int fftopk_select2048(const float* score, int64_t row_stride, int32_t B, int64_t
  *
  *   cand_key     device, uint32 [G, B, 2048]   keys written by fftopk_select2048(out_key)
  *   cand_idx     device, int32  [G, B, 2048]   global indices (idx_offset applied); -1 = empty
+ *   shard_stride elements between the planes of consecutive shards in BOTH arrays; 0 means
+ *                B*2048 (dense). An all-gathered [G, 2, B, 2048] buffer (index plane, key plane
+ *                per shard) is passed as cand_idx = base, cand_key = base + B*2048,
+ *                shard_stride = 2*B*2048, without any repacking
  *   G            number of shards (1..8)
  *   out_idx      device, int32 [B, 2048]; the 2048 candidates largest by (key, lower index),
  *                unspecified order; -1 padded when fewer than 2048 candidates are valid
  *   out_key      device, uint32 [B, 2048] or NULL
  */
-int fftopk_merge2048(const uint32_t* cand_key, const int32_t* cand_idx, int32_t G, int32_t B,
-                     int32_t* out_idx, uint32_t* out_key, uint32_t* status, void* cuda_stream);
+int fftopk_merge2048(const uint32_t* cand_key, const int32_t* cand_idx, int64_t shard_stride,
+                     int32_t G, int32_t B, int32_t* out_idx, uint32_t* out_key, uint32_t* status,
+                     void* cuda_stream);
+
+/*
+ * Fused gather-and-merge for the context-parallel mode, without a collective library call.
+ * No reference counterpart. Every rank owns one "comm" buffer that its peers map through CUDA
+ * IPC (NVLink peer access); a call with epoch e (1, 2, 3, ... the same on every rank) works in
+ * two enqueue-only steps:
+ *   fftopk_select2048_cp  local selection written into the rank's own comm buffer (half e & 1),
+ *                         then a one-thread kernel fences and releases the buffer's epoch flag;
+ *   fftopk_merge2048_cp   ONE kernel per rank that waits - at most wait_ms milliseconds per
+ *                         shard - until every shard's flag has reached e, pulls the candidates
+ *                         out of the peers' buffers with plain loads and merges them.
+ * A wait that runs out fills the row with -1, raises FFTOPK_ST_PEER_TIMEOUT in *status and lets
+ * the kernel return: a peer that never publishes cannot hang the GPU. The two halves of the
+ * buffer alternate, which is enough because a rank can only start call e+2 after its own merge
+ * e+1 has seen every peer's flag e+1, i.e. after every peer finished reading half e.
+ *
+ * Set-up (these four allocate / map memory and synchronise; call them outside the hot path):
+ *   fftopk_comm_create  cudaMalloc + clear a comm buffer for up to b_cap rows, export its handle
+ *   fftopk_comm_open    map a peer's buffer from the 64-byte handle it exported (other process)
+ *   fftopk_comm_close / fftopk_comm_destroy
+ *
+ *   comms        HOST array of G device pointers, shard order: comms[g] is rank g's comm buffer
+ *                (the rank's own pointer for itself, fftopk_comm_open results for the peers)
+ */
+int fftopk_comm_bytes(int32_t b_cap, size_t* bytes);
+int fftopk_comm_create(int32_t b_cap, void** comm, unsigned char handle[64]);
+int fftopk_comm_open(const unsigned char handle[64], void** peer_comm);
+int fftopk_comm_close(void* peer_comm);
+int fftopk_comm_destroy(void* comm);
+int fftopk_select2048_cp(const float* score, int64_t row_stride, int32_t B, int64_t L,
+                         const int32_t* lengths, int32_t idx_offset, void* comm, int32_t b_cap,
+                         uint32_t epoch, uint32_t* status, void* cuda_stream);
+int fftopk_merge2048_cp(void* const* comms, int32_t G, int32_t B, int32_t b_cap, uint32_t epoch,
+                        int32_t wait_ms, int32_t* out_idx, uint32_t* out_key, uint32_t* status,
+                        void* cuda_stream);
 
 /*
  * Radix key of one fp32 value, computed on the host with the same function the kernels use

@@ -55,7 +55,7 @@ def test_argument_validation_without_a_device():
     assert lib.fftopk_select2048(None, 0, 1, 10, None, None, None, None, 0, None, None) == -1
     assert lib.fftopk_select2048(None, 0, -1, 10, None, None, None, None, 0, None, None) == -1
     assert lib.fftopk_select2048(None, 0, 0, 10, None, None, None, None, 0, None, None) == 0  # B == 0: no-op
-    assert lib.fftopk_merge2048(None, None, 9, 1, None, None, None, None) == -4
+    assert lib.fftopk_merge2048(None, None, 0, 9, 1, None, None, None, None) == -4
     assert lib.fftopk_set_tuning(3, -1, -1, -1, 0) == -1
     assert lib.fftopk_set_tuning(-1, -1, -1, -1, 0) == 0
 

@@ -53,3 +53,79 @@ def test_ragged_global_lengths_and_short_rows():
         assert np.array_equal(np.sort(got[b][got[b] >= 0]), np.sort(exp[b][exp[b] >= 0])), b
         assert (got[b] >= 0).sum() == n
         assert np.all(got[b][n:] == -1)  # -1 padding at the end
+
+
+# ----------------------------------------------------------------------------------------------
+# fused gather-and-merge (fftopk_select2048_cp / fftopk_merge2048_cp) on one device: the G shards
+# publish into G separate comm buffers one after the other (stream order), so the merge kernel's
+# waits are already satisfied when it starts - nothing here waits on a concurrently running kernel.
+# ----------------------------------------------------------------------------------------------
+def _comm_create(b_cap):
+    import ctypes
+    from jit_kernel import _native
+    lib = _native.lib()
+    p = ctypes.c_void_p()
+    h = ctypes.create_string_buffer(64)
+    _native.check(lib.fftopk_comm_create(b_cap, ctypes.byref(p), h), "comm_create")
+    return p.value
+
+
+def _fused_on_one_device(score, lengths, G, epochs=(1,)):
+    import ctypes
+    from jit_kernel import _native
+    lib = _native.lib()
+    dev = torch.device("cuda", 0)
+    B, L = score.shape
+    Ls = L // G
+    comms = [_comm_create(B) for _ in range(G)]
+    arr = (ctypes.c_void_p * G)(*comms)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    out = torch.empty(B, K, dtype=torch.int32, device=dev)
+    shards = [score[:, g * Ls:(g + 1) * Ls].contiguous().to(dev) for g in range(G)]
+    lens = [local_lengths(lengths, Ls, g).to(dev) for g in range(G)]
+    results = []
+    for e in epochs:
+        for g in range(G):
+            rc = lib.fftopk_select2048_cp(shards[g].data_ptr(), Ls, B, Ls, lens[g].data_ptr(), g * Ls, comms[g], B, e,
+                                          status.data_ptr(), None)
+            assert rc == 0
+        rc = lib.fftopk_merge2048_cp(arr, G, B, B, e, 1000, out.data_ptr(), None, status.data_ptr(), None)
+        assert rc == 0
+        torch.cuda.synchronize()
+        results.append(out.cpu().numpy().copy())
+    for c in comms:
+        lib.fftopk_comm_destroy(c)
+    return results, int(status.item())
+
+
+@pytest.mark.parametrize("G", [2, 8])
+def test_fused_gather_merge_matches_oracle(G):
+    score, lengths = workloads.c5(B=2, L=1 << 19)
+    results, status = _fused_on_one_device(score, lengths, G, epochs=(1, 2, 3))  # both buffer halves, reused
+    assert status == 0
+    for got in results:
+        orc.check_result(score.numpy(), lengths.numpy(), got, what=f"fused G={G}")
+
+
+def test_fused_merge_wait_runs_out_without_hanging():
+    """A flag that nothing sets: the bounded wait gives up, the row is -1, the status says so and
+    the context stays usable."""
+    import ctypes
+    from jit_kernel import _native
+    lib = _native.lib()
+    dev = torch.device("cuda", 0)
+    comm = _comm_create(2)
+    arr = (ctypes.c_void_p * 1)(comm)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    out = torch.zeros(2, K, dtype=torch.int32, device=dev)
+    rc = lib.fftopk_merge2048_cp(arr, 1, 2, 2, 5, 20, out.data_ptr(), None, status.data_ptr(), None)  # epoch 5 never published
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert int(status.item()) & _native.ST_PEER_TIMEOUT
+    assert bool((out == -1).all())
+    # the device still works
+    s, ln = workloads.c1()
+    from jit_kernel.topk_indexer import fast_topk_v3
+    got = fast_topk_v3(s.to(dev), ln.to(dev), K).cpu().numpy()
+    orc.check_result(s.numpy(), ln.numpy(), got, what="after timeout")
+    lib.fftopk_comm_destroy(comm)
