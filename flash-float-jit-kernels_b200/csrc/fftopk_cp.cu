@@ -136,6 +136,38 @@ __global__ void __launch_bounds__(NT, 1) merge2048_kernel(const MergeSrc src, in
   cta_finish<NT>(cand, n, (uint32_t)kK, 64, 0ull, 31, hist, ctrl, out_idx, out_key, 0u, 0, status);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Scratch for the allocation-free entry point (fftopk_topk2048_sliced_noalloc): the per-slice
+// candidates and the per-slice lengths live in this file-scope array instead of a buffer from
+// cudaMalloc. Every GPU that loads the library holds these bytes until the process exits.
+// In HOST code the name below is only a stand-in for the symbol, never a device address: the
+// address is fetched once per device with cudaGetSymbolAddress (static_scratch_ptr).
+// ---------------------------------------------------------------------------------------------
+constexpr int kStaticMaxRows = 8;
+constexpr int kStaticMaxSlices = 8;
+constexpr size_t kStaticCandWords = (size_t)kStaticMaxSlices * 2 * kStaticMaxRows * kK;  // 262,144 words = 1 MiB
+constexpr size_t kStaticLenWords = (size_t)kStaticMaxSlices * kStaticMaxRows;            // 64 words
+constexpr size_t kStaticBytes = (kStaticCandWords + kStaticLenWords) * 4;                // 1 MiB + 256 B
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticBytes];
+
+// Valid length of every (slice, row): how much of row b falls into columns [g*ls, g*ls + lg).
+__global__ void slice_lengths_kernel(const int32_t* __restrict__ lengths, int B, int slices, int64_t L, int64_t ls,
+                                     int32_t* __restrict__ out /* [slices][kStaticMaxRows] */) {
+  const int i = threadIdx.x;
+  if (i < slices * kStaticMaxRows) {
+    const int g = i / kStaticMaxRows, b = i % kStaticMaxRows;
+    int64_t v = 0;
+    if (b < B) {
+      const int64_t lg = L - g * ls < ls ? L - g * ls : ls;
+      int64_t len = lengths[b];
+      len = len < 0 ? 0 : (len > L ? L : len);
+      v = len - g * ls;
+      v = v < 0 ? 0 : (v > lg ? lg : v);
+    }
+    out[i] = (int32_t)v;
+  }
+}
+
 }  // namespace fftopk
 
 namespace {
@@ -166,6 +198,25 @@ size_t merge_smem(int G) {
 // comm buffer layout, in 32-bit words, for a row capacity of b_cap:
 //   [parity 0: index plane b_cap*2048 | key plane b_cap*2048][parity 1: same][flag line: 32 words]
 size_t comm_words(int32_t b_cap) { return (size_t)4 * b_cap * kK + kCommFlagWords; }
+
+// Device address of g_static_scratch on the current device, looked up once per device.
+void* g_static_ptr[64];
+
+int static_scratch_ptr(void** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_fail(e);
+  if (dev < 0 || dev >= 64) return FFTOPK_EDEVICE;
+  if (g_static_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_static_scratch);  // with device `dev` current
+    if (e != cudaSuccess) return cuda_fail(e);
+    if (p == nullptr) return FFTOPK_EDEVICE;
+    g_static_ptr[dev] = p;
+  }
+  *out = g_static_ptr[dev];
+  return 0;
+}
 
 }  // namespace
 
@@ -282,6 +333,47 @@ int fftopk_merge2048_cp(void* const* comms, int32_t G, int32_t B, int32_t b_cap,
   merge2048_kernel<1024><<<dim3((unsigned)B), dim3(1024), merge_smem(G), static_cast<cudaStream_t>(cuda_stream)>>>(
       src, G, B, out_idx, out_key, status);
   cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e);
+  return FFTOPK_OK;
+}
+
+int fftopk_topk2048_sliced_noalloc(const float* score, int64_t row_stride, int32_t B, int64_t L,
+                                   const int32_t* lengths, int32_t slices, int32_t* out_idx, uint32_t* status,
+                                   void* cuda_stream) {
+  if (B < 0 || L < 0 || row_stride < 0 || slices < 1) return FFTOPK_EINVAL;
+  if (B > kStaticMaxRows || slices > kStaticMaxSlices) return FFTOPK_ERANGE;  // beyond the built-in scratch
+  if (B == 0) return FFTOPK_OK;
+  if (!score || !lengths || !out_idx) return FFTOPK_EINVAL;
+  if (L > (int64_t)0x7fffffff - 8) return FFTOPK_ERANGE;
+  void* scratch = nullptr;
+  int rc = static_scratch_ptr(&scratch);  // first call on a device: cudaGetSymbolAddress
+  if (rc) return rc;
+  rc = merge_setup();
+  if (rc) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  int32_t* cand = static_cast<int32_t*>(scratch);
+  int32_t* slice_len = cand + kStaticCandWords;
+  const int64_t ls = (L + slices - 1) / slices;  // columns per slice (the last one may be shorter)
+  slice_lengths_kernel<<<1, kStaticMaxSlices * kStaticMaxRows, 0, stream>>>(lengths, B, slices, L, ls, slice_len);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e);
+  MergeSrc src;
+  memset(&src, 0, sizeof(src));
+  for (int g = 0; g < slices; ++g) {
+    int32_t* idx_plane = cand + (size_t)g * 2 * kStaticMaxRows * kK;
+    uint32_t* key_plane = reinterpret_cast<uint32_t*>(idx_plane + (size_t)kStaticMaxRows * kK);
+    const int64_t first = (int64_t)g * ls;
+    const int64_t lg = L - first < ls ? (L - first > 0 ? L - first : 0) : ls;
+    // every slot of the slice's planes is rewritten by this call: nothing has to start at zero
+    rc = fftopk_select2048(score + first, row_stride, B, lg, slice_len + (size_t)g * kStaticMaxRows, nullptr, idx_plane,
+                           key_plane, (int32_t)first, status, cuda_stream);
+    if (rc) return rc;
+    src.idx[g] = idx_plane;
+    src.key[g] = key_plane;
+  }
+  merge2048_kernel<1024><<<dim3((unsigned)B), dim3(1024), merge_smem(slices), stream>>>(src, slices, B, out_idx, nullptr,
+                                                                                      status);
+  e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e);
   return FFTOPK_OK;
 }

@@ -32,6 +32,7 @@ EXPORTS = (
     "fftopk_comm_destroy",
     "fftopk_select2048_cp",
     "fftopk_merge2048_cp",
+    "fftopk_topk2048_sliced_noalloc",
     "fftopk_key_of",
     "fftopk_plan",
     "fftopk_set_tuning",
@@ -94,6 +95,9 @@ def lib() -> ctypes.CDLL:
     L.fftopk_merge2048_cp.restype = c.c_int
     L.fftopk_merge2048_cp.argtypes = [c.POINTER(c.c_void_p), c.c_int32, c.c_int32, c.c_int32, c.c_uint32, c.c_int32,
                                       c.c_void_p, c.c_void_p, c.c_void_p, c.c_void_p]
+    L.fftopk_topk2048_sliced_noalloc.restype = c.c_int
+    L.fftopk_topk2048_sliced_noalloc.argtypes = [c.c_void_p, c.c_int64, c.c_int32, c.c_int64, c.c_void_p, c.c_int32,
+                                                 c.c_void_p, c.c_void_p, c.c_void_p]
     L.fftopk_key_of.restype = c.c_uint32
     L.fftopk_key_of.argtypes = [c.c_float]
     L.fftopk_plan.restype = c.c_int

@@ -139,6 +139,34 @@ int fftopk_merge2048_cp(void* const* comms, int32_t G, int32_t B, int32_t b_cap,
                         void* cuda_stream);
 
 /*
+ * Top-2048 by column slices, with no allocation anywhere. (This entry point has no counterpart in
+ * the reference.)
+ *
+ * For callers that are not allowed to obtain device memory when the call is made: a serving
+ * process that handed every free byte of HBM to its KV-cache pool at start-up, or a real-time loop
+ * in which cudaMalloc - which may block until the whole device is idle - is forbidden. It runs the
+ * same kernels as fftopk_select2048_cp + fftopk_merge2048_cp (each row is cut into `slices`
+ * column ranges, a local top-2048 is selected per range, one merge kernel picks the final 2048),
+ * but the per-slice candidates and lengths sit in a scratch array that is compiled into the
+ * library as a device global, instead of in buffers from fftopk_comm_create. The function calls
+ * neither cudaMalloc nor cudaFree nor any allocating library routine.
+ *
+ *   score, row_stride, B, L, lengths, out_idx, status, cuda_stream: as for fftopk_select2048
+ *   (row_starts is not supported); out_idx receives the same index set fftopk_select2048 gives.
+ *   slices       1..8 column ranges per row
+ * Limits: B <= 8 and slices <= 8 (the built-in scratch is 1 MiB + 256 bytes per GPU, held by
+ * every GPU that loads the library until the process exits); larger values return FFTOPK_ERANGE.
+ * The first call on a device looks up the scratch array's device address (cudaGetSymbolAddress);
+ * make that first call before any stream capture. All calls on a device share the one array, which
+ * keeps the previous call's contents (every slot a call reads is rewritten by that call first,
+ * nothing needs clearing): two calls whose kernels overlap on the GPU - different streams, or one
+ * stream per thread - race on it and return garbage. Serialise them.
+ */
+int fftopk_topk2048_sliced_noalloc(const float* score, int64_t row_stride, int32_t B, int64_t L,
+                                   const int32_t* lengths, int32_t slices, int32_t* out_idx,
+                                   uint32_t* status, void* cuda_stream);
+
+/*
  * Radix key of one fp32 value, computed on the host with the same function the kernels use
  * (the order-preserving map the reference defines as convert_to_uint32,
  * topk_indexer_radix.cu:206-209, plus -0.0 / NaN canonicalisation). For tests and bindings.
