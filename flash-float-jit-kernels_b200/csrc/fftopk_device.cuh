@@ -96,25 +96,6 @@ __device__ __forceinline__ uint32_t warp_sum(uint32_t v) {
   return v;
 }
 
-// Descending bitonic compare-exchange network over one 64-bit value per lane.
-__device__ __forceinline__ uint64_t warp_sort_desc(uint64_t c) {
-  const int lane = lane_id();
-#pragma unroll
-  for (int k = 2; k <= 32; k <<= 1) {
-#pragma unroll
-    for (int j = k >> 1; j > 0; j >>= 1) {
-      const uint64_t other = __shfl_xor_sync(kFull, c, j);
-      const bool lower = (lane & j) == 0;
-      const bool desc_block = (lane & k) == 0;
-      const bool keep_max = (lower == desc_block);
-      const uint64_t mx = c > other ? c : other;
-      const uint64_t mn = c > other ? other : c;
-      c = keep_max ? mx : mn;
-    }
-  }
-  return c;
-}
-
 // ---------------------------------------------------------------------------------------------
 // Shared-memory control block (one per CTA; rank 0's counters are the cluster-wide ones).
 // ---------------------------------------------------------------------------------------------
@@ -146,11 +127,14 @@ struct Ctrl {
   uint32_t tie_prefix;
   uint32_t local_c;
   uint32_t run_total;
-  uint32_t tot[kSup];   // cluster-wide super-bin totals (zero between searches)
-  uint32_t tot2[kSup];  // cluster-wide fine-bin totals of the threshold super-bin (same)
+  // cluster-wide super-bin totals and fine-bin totals of the threshold super-bin, double-buffered
+  // by search number (each search clears the buffers of the next one)
+  uint32_t tot[2][kSup];
+  uint32_t tot2[2][kSup];
   uint32_t wtot[32];
   uint32_t wmax[32];
   uint64_t small[kSmall];
+  uint64_t thr;  // finish: the threshold composite found among the last <= 32 candidates
 };
 
 // Block-wide threshold pick over kFinishBins counts (descending bin order); result in ctrl->t
@@ -204,13 +188,20 @@ __device__ __forceinline__ void block_pick(const uint32_t* hist, uint32_t need, 
 // composite, equal values are resolved towards the lower index by the same radix passes, and
 // the last <= 32 undecided candidates go through a warp compare-exchange network.
 // `idx_bits`: all indices are < 2^idx_bits, so the inverted-index bits above that are all ones.
+// `page`: optional per-row table; the value written is then page[idx] instead of idx + idx_offset
+// (the fused page-table transform of the reference's topk_transform_* kernels, :871-958).
 // ---------------------------------------------------------------------------------------------
 template <int NT>
 __device__ void cta_finish(const uint64_t* cand, int n, uint32_t need, int hi, uint64_t pfx, int idx_bits,
                            uint32_t* hist /* >= kFinishBins words */, Ctrl* ctrl, int32_t* out_idx, uint32_t* out_key,
-                           uint32_t out_base, int32_t idx_offset, uint32_t* status) {
+                           uint32_t out_base, int32_t idx_offset, uint32_t* status,
+                           const int32_t* page = nullptr /* when set: out = page[idx] */) {
   const int tid = threadIdx.x;
   const int lane = tid & 31, warp = tid >> 5;
+  if (tid == 0) {
+    ctrl->fslot = 0u;  // (every path below has a block barrier before these are used)
+    ctrl->small_n = 0u;
+  }
   if (hi >= 64) {
     // No prefix known: find the bits all candidates agree on (OR and AND over the list), so that
     // the first digit is spent where the candidates actually differ.
@@ -263,7 +254,6 @@ __device__ void cta_finish(const uint64_t* cand, int n, uint32_t need, int hi, u
     const int sh = hi - w;
     const uint32_t dmask = (1u << w) - 1u;
     for (int b = tid; b < kFinishBins; b += NT) hist[b] = 0u;
-    if (tid == 0) ctrl->small_n = 0;
     __syncthreads();
     for (int i = tid; i < n; i += NT) {
       const uint64_t c = cand[i];
@@ -298,14 +288,20 @@ __device__ void cta_finish(const uint64_t* cand, int n, uint32_t need, int hi, u
         }
       }
       __syncthreads();
-      if (warp == 0) {
-        uint64_t c = (lane < (int)cnt) ? ctrl->small[lane] : 0ull;
-        c = warp_sort_desc(c);
-        c = __shfl_sync(kFull, c, (int)need2 - 1);  // the need2-th largest is the threshold itself
-        if (lane == 0) ctrl->small[0] = c;
+      {
+        // Rank by vote: warp i takes candidate i, every lane j compares it with candidate j, and
+        // the number of larger ones is candidate i's rank. The candidate of rank need2-1 is the
+        // threshold. (A 15-stage bitonic compare-exchange network over the same 32 values is a
+        // chain of 60 dependent shuffles; this is one ballot.)
+        const uint64_t other = (lane < (int)cnt) ? ctrl->small[lane] : 0ull;
+        for (int i = warp; i < (int)cnt; i += NT / 32) {
+          const uint64_t me = ctrl->small[i];
+          const unsigned larger = __ballot_sync(kFull, other > me);
+          if (lane == 0 && (uint32_t)__popc(larger) == need2 - 1u) ctrl->thr = me;
+        }
       }
       __syncthreads();
-      fthr = ctrl->small[0];
+      fthr = ctrl->thr;
       fs = 0;
       found = true;
       break;
@@ -343,7 +339,8 @@ __device__ void cta_finish(const uint64_t* cand, int n, uint32_t need, int hi, u
     const uint64_t c = cand[i];
     if (c != 0ull && (c >> fs) >= fthr) {
       if (pos < (uint32_t)kK) {
-        out_idx[pos] = (int32_t)(~(uint32_t)c) + idx_offset;
+        const int32_t idx = (int32_t)(~(uint32_t)c);
+        out_idx[pos] = page ? __ldg(page + idx) : idx + idx_offset;
         if (out_key) out_key[pos] = (uint32_t)(c >> 32);
       }
       ++pos;

@@ -55,6 +55,13 @@ struct SelectParams {
   int32_t list_cap;  // per-CTA candidate list capacity (entries), multiple of 16
   int32_t cand_cap;  // rank 0's gathered-candidate capacity (entries), multiple of 16
   int32_t force_slow;  // tests: skip the filter path and run the full-histogram path
+  // fused output transforms (all optional; reference: topk_transform_decode_kernel,
+  // topk_transform_prefill_kernel, topk_transform_prefill_ragged_kernel, radix.cu:871-995)
+  const int32_t* src_page_table;  // [prefill_bs, src_stride]: out = table_row[idx]
+  int64_t src_stride;
+  const int32_t* cu_seqlens_q;    // [prefill_bs + 1] or NULL (then table row = score row)
+  int32_t prefill_bs;
+  const int32_t* row_offsets;     // [B]: out = idx + row_offsets[row]
 };
 
 enum Mode : int { kModeNext = 0, kModeGather = 1, kModeTakeAll = 2, kModeTies = 3, kModeAbort = 4, kModeFallback = 5 };
@@ -277,43 +284,37 @@ struct Picked {
 // cluster barriers and eight block barriers per round.
 template <int NT, class NeedFn, class Post>
 __device__ __forceinline__ void cluster_pick(cg::cluster_group& cluster, int C, const uint32_t* h, const uint32_t* s,
-                                             uint32_t* xch, Ctrl* ctrl, uint32_t* tot, int nb, NeedFn&& need_of,
+                                             uint32_t* xch, Ctrl* ctrl, int& pick_no, int nb, NeedFn&& need_of,
                                              Post&& post) {
   const int tid = threadIdx.x;
-  const int lane = tid & 31, warp = tid >> 5;
+  const int lane = tid & 31;
   const int fine = nb / kSup;
-  // (A) cluster-wide super-bin totals in `tot`: one remote word per thread, summed with
-  // shared-memory reductions instead of a serial loop over the ranks. (Pushing the sums into the
-  // peers before the cluster barrier instead - remote reductions behind a split arrive / wait
-  // barrier - was measured and was not faster: the release of the extra arrive costs what the
-  // remote loads cost.)
+  uint32_t* tot = ctrl->tot[pick_no & 1];
+  uint32_t* tot2 = ctrl->tot2[pick_no & 1];
+  // (A) cluster-wide super-bin totals: one remote word per thread, summed with shared-memory
+  // reductions instead of a serial loop over the ranks. (Pushing the sums into the peers before
+  // the cluster barrier instead - remote reductions behind a split arrive / wait barrier - was
+  // measured and was not faster: the release of the extra arrive costs what the remote loads cost.)
   for (int i = tid; i < C * kSup; i += NT) {
     const uint32_t* rs = cluster.map_shared_rank(s, i / kSup);
     red_shared_add(&tot[i % kSup], rs[i % kSup]);
   }
   __syncthreads();
   FFTOPK_MARK(40);
-  if (warp == 0) {
+  // every warp picks for itself (same inputs, same result): no broadcast, no barrier
+  int ssel = -1;
+  uint32_t sup_above = 0, need = 0, total = 0;
+  {
     const uint32_t lo = tot[2 * lane], hi = tot[2 * lane + 1];
-    tot[2 * lane] = 0u;  // ready for the next search
-    tot[2 * lane + 1] = 0u;
-    const uint32_t total = warp_sum(lo + hi);
-    const uint32_t need = need_of(total);
+    total = warp_sum(lo + hi);
+    need = need_of(total);
+    uint32_t cnt = 0;
     int ts = -1;
-    uint32_t above = 0, cnt = 0;
-    const bool ok = need > 0 && warp_pick64(lo, hi, need, ts, above, cnt);
-    if (lane == 0) {
-      ctrl->sup_sel = ok ? ts : -1;
-      ctrl->sup_above = above;
-      ctrl->need = need;
-      ctrl->run_total = total;
-    }
+    if (need > 0 && warp_pick64(lo, hi, need, ts, sup_above, cnt)) ssel = ts;
   }
-  __syncthreads();
   FFTOPK_MARK(41);
-  const int ssel = ctrl->sup_sel;
   // (B) fine bins of the threshold super-bin: pulled from every peer, kept per rank in xch (the
-  // tie path wants them) and summed into ctrl->tot2
+  // tie path wants them) and summed into tot2
   if (ssel >= 0) {
     for (int i = tid; i < C * kSup; i += NT) {
       const int q = i / kSup, f = i % kSup;
@@ -321,47 +322,46 @@ __device__ __forceinline__ void cluster_pick(cg::cluster_group& cluster, int C, 
       if (f < fine) {
         const uint32_t* rh = cluster.map_shared_rank(h, q);
         v = rh[ssel * fine + f];
-        red_shared_add(&ctrl->tot2[f], v);
+        red_shared_add(&tot2[f], v);
       }
       xch[i] = v;
     }
   }
   __syncthreads();
   FFTOPK_MARK(42);
-  if (warp == 0) {
-    Picked pk;
-    pk.ok = false;
-    pk.t = -1;
-    pk.need2 = pk.cnt = pk.local_w = pk.local_c = 0;
-    pk.total = ctrl->run_total;
-    pk.any_flag = 0u;
-    pk.tf = 0;
-    if (ssel >= 0) {
-      const uint32_t lo = ctrl->tot2[2 * lane], hi = ctrl->tot2[2 * lane + 1];
-      ctrl->tot2[2 * lane] = 0u;
-      ctrl->tot2[2 * lane + 1] = 0u;
-      const uint32_t need = ctrl->need;
-      const uint32_t sup_above = ctrl->sup_above;
-      int tf = -1;
-      uint32_t above_f = 0, cnt_t = 0;
-      if (warp_pick64(lo, hi, need - sup_above, tf, above_f, cnt_t)) {
-        pk.ok = true;
-        pk.tf = tf;
-        pk.t = ssel * fine + tf;
-        pk.need2 = need - sup_above - above_f;
-        pk.cnt = cnt_t;
-        uint32_t lw = 0;
-        lw += (2 * lane > ssel) ? s[2 * lane] : 0u;
-        lw += (2 * lane + 1 > ssel) ? s[2 * lane + 1] : 0u;
-        lw += (2 * lane < fine && 2 * lane > tf) ? h[ssel * fine + 2 * lane] : 0u;
-        lw += (2 * lane + 1 < fine && 2 * lane + 1 > tf) ? h[ssel * fine + 2 * lane + 1] : 0u;
-        pk.local_w = warp_sum(lw);
-        pk.local_c = h[pk.t];
-      }
-    }
-    post(pk);
+  // the buffers of the next search: their last readers passed the barrier above long ago
+  if (tid < kSup) {
+    ctrl->tot[(pick_no + 1) & 1][tid] = 0u;
+    ctrl->tot2[(pick_no + 1) & 1][tid] = 0u;
   }
-  __syncthreads();
+  ++pick_no;
+  Picked pk;
+  pk.ok = false;
+  pk.t = -1;
+  pk.need2 = pk.cnt = pk.local_w = pk.local_c = 0;
+  pk.total = total;
+  pk.any_flag = 0u;
+  pk.tf = 0;
+  if (ssel >= 0) {
+    const uint32_t lo = tot2[2 * lane], hi = tot2[2 * lane + 1];
+    int tf = -1;
+    uint32_t above_f = 0, cnt_t = 0;
+    if (warp_pick64(lo, hi, need - sup_above, tf, above_f, cnt_t)) {
+      pk.ok = true;
+      pk.tf = tf;
+      pk.t = ssel * fine + tf;
+      pk.need2 = need - sup_above - above_f;
+      pk.cnt = cnt_t;
+      uint32_t lw = 0;
+      lw += (2 * lane > ssel) ? s[2 * lane] : 0u;
+      lw += (2 * lane + 1 > ssel) ? s[2 * lane + 1] : 0u;
+      lw += (2 * lane < fine && 2 * lane > tf) ? h[ssel * fine + 2 * lane] : 0u;
+      lw += (2 * lane + 1 < fine && 2 * lane + 1 > tf) ? h[ssel * fine + 2 * lane + 1] : 0u;
+      pk.local_w = warp_sum(lw);
+      pk.local_c = h[pk.t];
+    }
+  }
+  post(pk);  // called by every warp with identical values
   FFTOPK_MARK(43);
 }
 
@@ -385,6 +385,7 @@ struct RowCtx {
   int32_t* out_idx;
   uint32_t* out_key;
   int32_t idx_offset;
+  const int32_t* page;  // fused page-table transform: out = page[idx] (NULL: out = idx + idx_offset)
   int32_t cand_cap;
   int32_t list_cap;
   uint32_t* status;
@@ -394,7 +395,7 @@ template <int NT>
 __device__ __forceinline__ void emit_winner(const RowCtx<NT>& cx, uint32_t base_w, uint32_t key, int idx) {
   const uint32_t pos = base_w + warp_alloc(&cx.ctrl->wslot);
   if (pos < (uint32_t)kK) {
-    cx.out_idx[pos] = idx + cx.idx_offset;
+    cx.out_idx[pos] = cx.page ? __ldg(cx.page + idx) : idx + cx.idx_offset;
     if (cx.out_key) cx.out_key[pos] = key;
   }
 }
@@ -445,7 +446,7 @@ __device__ __forceinline__ void decide_and_allocate(const RowCtx<NT>& cx, const 
 // Returns the final mode; `need`, `P` and `r` describe where it stopped.
 // -----------------------------------------------------------------------------------------
 template <int NT>
-__device__ __forceinline__ int refine_from_data(RowCtx<NT>& cx, uint32_t& need, uint32_t& P, int& r) {
+__device__ __forceinline__ int refine_from_data(RowCtx<NT>& cx, uint32_t& need, uint32_t& P, int& r, int& pick_no) {
   cg::cluster_group cluster = cg::this_cluster();
   const int tid = threadIdx.x;
   const int lane = tid & 31, warp = tid >> 5;
@@ -466,10 +467,11 @@ __device__ __forceinline__ int refine_from_data(RowCtx<NT>& cx, uint32_t& need, 
       ctrl->over_flag = 0u;
       ctrl->max_key = 0u;
     }
-    if (tid < kSup) {  // totals pushed for a search that never ran (forced fallback) must not linger
-      ctrl->tot[tid] = 0u;
-      ctrl->tot2[tid] = 0u;
+    if (tid < kSup) {
+      ctrl->tot[0][tid] = ctrl->tot[1][tid] = 0u;
+      ctrl->tot2[0][tid] = ctrl->tot2[1][tid] = 0u;
     }
+    pick_no = 0;
   }
   __syncthreads();
   {
@@ -491,8 +493,9 @@ __device__ __forceinline__ int refine_from_data(RowCtx<NT>& cx, uint32_t& need, 
     cluster.sync();  // every CTA's histogram and super-bin sums of this round are complete
     const uint32_t need_now = need;
     cluster_pick<NT>(
-        cluster, C, h, s, xch, ctrl, ctrl->tot, nb, [&](uint32_t) { return need_now; },
+        cluster, C, h, s, xch, ctrl, pick_no, nb, [&](uint32_t) { return need_now; },
         [&](Picked& pk) {
+          if (warp != 0) return;  // one warp allocates and publishes; the barrier below broadcasts
           const bool last = (shift == 0);
           decide_and_allocate<NT>(cx, pk, last ? kModeTies : kModeNext, false);
           if (pk.ok && last && pk.cnt > (uint32_t)cx.cand_cap && pk.cnt != pk.need2) {
@@ -590,7 +593,7 @@ __device__ __forceinline__ int refine_from_data(RowCtx<NT>& cx, uint32_t& need, 
         for (int j = 0; j < 4; ++j) {
           if (m[j]) {
             if (rnk < quota && obase + rnk < (uint32_t)kK) {
-              cx.out_idx[obase + rnk] = i0 + j + cx.idx_offset;
+              cx.out_idx[obase + rnk] = cx.page ? __ldg(cx.page + i0 + j) : i0 + j + cx.idx_offset;
               if (cx.out_key) cx.out_key[obase + rnk] = Pn;
             }
             ++rnk;
@@ -625,7 +628,22 @@ __global__ void __launch_bounds__(NT, (NT <= 512 ? 2 : 1)) select2048_kernel(con
   const float* rowp = p.score + (int64_t)row * p.row_stride + row_start;
   int32_t* out_idx = cx.out_idx = p.out_idx + (int64_t)row * kK;
   uint32_t* out_key = cx.out_key = p.out_key ? p.out_key + (int64_t)row * kK : nullptr;
-  cx.idx_offset = p.idx_offset;
+  cx.idx_offset = p.idx_offset + (p.row_offsets ? __ldg(p.row_offsets + row) : 0);
+  cx.page = nullptr;
+  if (p.src_page_table) {
+    // which table row serves this score row: the request i with cu_seqlens_q[i] <= row < cu_seqlens_q[i+1]
+    // (radix.cu:925-939); without cu_seqlens_q, the row itself (decode, :880)
+    int64_t req = row;
+    if (p.cu_seqlens_q) {
+      int lo = 0, hi = p.prefill_bs;  // invariant: cu[lo] <= row, answer in [lo, hi)
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (__ldg(p.cu_seqlens_q + mid) <= row) lo = mid; else hi = mid;
+      }
+      req = lo;
+    }
+    cx.page = p.src_page_table + req * p.src_stride;
+  }
   cx.cand_cap = p.cand_cap;
   cx.list_cap = p.list_cap;
   cx.status = p.status;
@@ -634,7 +652,7 @@ __global__ void __launch_bounds__(NT, (NT <= 512 ? 2 : 1)) select2048_kernel(con
   if (len <= kK) {
     if (rank == 0) {
       for (int i = tid; i < kK; i += NT) {
-        out_idx[i] = i < len ? i + p.idx_offset : -1;
+        out_idx[i] = i < len ? (cx.page ? __ldg(cx.page + i) : i + cx.idx_offset) : -1;
         if (out_key) out_key[i] = i < len ? fftopk_key_from_bits(__float_as_uint(__ldg(rowp + i))) : 0u;
       }
     }
@@ -671,8 +689,8 @@ __global__ void __launch_bounds__(NT, (NT <= 512 ? 2 : 1)) select2048_kernel(con
 
   // ---- prologue: clear the search totals, both histograms and the control block --------------
   if (tid < kSup) {
-    ctrl->tot[tid] = 0u;
-    ctrl->tot2[tid] = 0u;
+    ctrl->tot[0][tid] = 0u;  // (the buffers with index 1 are cleared by the first search)
+    ctrl->tot2[0][tid] = 0u;
   }
   {
     uint4* h4 = reinterpret_cast<uint4*>(cx.hist(0));
@@ -718,6 +736,12 @@ __global__ void __launch_bounds__(NT, (NT <= 512 ? 2 : 1)) select2048_kernel(con
       }
       if (g < sh.g1) gr[0] = g;
       if (g >= sh.i0 && g < sh.i1) xr[0] = __ldg(base4 + g);
+      // The filter pass cannot start before the sample has been histogrammed and searched
+      // (several microseconds); ask L2 for the shard now, one 128-byte line per request, so that
+      // HBM latency and bandwidth are spent while the memory system would otherwise idle.
+      for (int gl = sh.i0 + 8 * tid; gl < sh.i1; gl += 8 * NT) {
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(base4 + gl));
+      }
     }
     // granules straddling the row's ends (at most two per row), after every bulk load is in flight
 #pragma unroll
@@ -754,6 +778,7 @@ __global__ void __launch_bounds__(NT, (NT <= 512 ? 2 : 1)) select2048_kernel(con
   uint32_t P = 0;
   int r = 0;
   int mode = kModeAbort;
+  int pick_no = 0;        // number of cluster-wide searches so far (selects their total buffers)
   int fin_hi = 64;        // where the finish starts when the sampled path gathered (r < 0)
   uint64_t fin_pfx = 0ull;
 
@@ -762,8 +787,11 @@ __global__ void __launch_bounds__(NT, (NT <= 512 ? 2 : 1)) select2048_kernel(con
   } else if (exact) {
     // ---- the sample is the row: its histogram gives the threshold bin directly -----------------
     cluster_pick<NT>(
-        cluster, C, cx.hist(0), cx.sup(0), cx.xch, ctrl, ctrl->tot, kMaxBins, [&](uint32_t) { return (uint32_t)kK; },
-        [&](Picked& pk) { decide_and_allocate<NT>(cx, pk, kModeFallback, false); });
+        cluster, C, cx.hist(0), cx.sup(0), cx.xch, ctrl, pick_no, kMaxBins, [&](uint32_t) { return (uint32_t)kK; },
+        [&](Picked& pk) {
+          if (warp == 0) decide_and_allocate<NT>(cx, pk, kModeFallback, false);
+        });
+    __syncthreads();  // slot bases allocated by warp 0
     mode = ctrl->mode;
     FFTOPK_MARK(4);
     if (mode == kModeGather || mode == kModeTakeAll) {
@@ -799,30 +827,27 @@ __global__ void __launch_bounds__(NT, (NT <= 512 ? 2 : 1)) select2048_kernel(con
     // need_of: sample rank whose true rank is >= k with overwhelming probability
     // (m expected sample elements among the true top k, plus five standard deviations).
     const float flen = (float)len;
+    int smode = kModeFallback;
+    uint32_t g1 = 0, rem = 0;
     cluster_pick<NT>(
-        cluster, C, cx.hist(0), cx.sup(0), cx.xch, ctrl, ctrl->tot, kMaxBins,
+        cluster, C, cx.hist(0), cx.sup(0), cx.xch, ctrl, pick_no, kMaxBins,
         [&](uint32_t n_s) {
           const float m = (float)kK * (float)n_s / flen;
           const uint32_t rk = (uint32_t)(m + 5.0f * sqrtf(m) + 14.0f);
           return rk < n_s ? rk : n_s;
         },
         [&](Picked& pk) {
-          if (lane == 0) {
-            // A 12-bit bin is coarse where values crowd into few exponents (8 bins per octave):
-            // if the sample says the guessed bin holds more than ~k row elements, a second
-            // sample round on the next 12 key bits sharpens the guess.
-            const float in_bin = (float)pk.cnt * flen / (float)(pk.total ? pk.total : 1u);
-            ctrl->mode = !pk.ok ? kModeFallback : (in_bin > (float)kK ? kModeNext : kModeGather);
-            ctrl->t = pk.t;
-            ctrl->above = pk.need2;
-          }
+          // A 12-bit bin is coarse where values crowd into few exponents (8 bins per octave): if
+          // the sample says the guessed bin holds more than ~k row elements, a second sample round
+          // on the next 12 key bits sharpens the guess.
+          const float in_bin = (float)pk.cnt * flen / (float)(pk.total ? pk.total : 1u);
+          smode = !pk.ok ? kModeFallback : (in_bin > (float)kK ? kModeNext : kModeGather);
+          g1 = (uint32_t)pk.t;
+          rem = pk.need2;
         });
     FFTOPK_MARK(4);
-    int smode = ctrl->mode;
-    uint32_t gkey = (uint32_t)ctrl->t << 20;
+    uint32_t gkey = g1 << 20;
     if (smode == kModeNext) {
-      const uint32_t g1 = (uint32_t)ctrl->t;
-      const uint32_t rem = ctrl->above;
       {
         uint32_t* h1 = cx.hist(1);
         const int e0 = 4 * gr[0] - sh.a;
@@ -838,16 +863,14 @@ __global__ void __launch_bounds__(NT, (NT <= 512 ? 2 : 1)) select2048_kernel(con
       __syncthreads();
       compute_sup<NT>(cx.hist(1), cx.sup(1), kMaxBins);
       cluster.sync();  // #1b
+      uint32_t g2 = 0;
       cluster_pick<NT>(
-          cluster, C, cx.hist(1), cx.sup(1), cx.xch, ctrl, ctrl->tot, kMaxBins, [&](uint32_t) { return rem; },
+          cluster, C, cx.hist(1), cx.sup(1), cx.xch, ctrl, pick_no, kMaxBins, [&](uint32_t) { return rem; },
           [&](Picked& pk) {
-            if (lane == 0) {
-              ctrl->mode = pk.ok ? kModeGather : kModeFallback;
-              ctrl->t = pk.t;
-            }
+            smode = pk.ok ? kModeGather : kModeFallback;
+            g2 = (uint32_t)pk.t;
           });
-      smode = ctrl->mode;
-      gkey |= (uint32_t)ctrl->t << 8;
+      gkey |= g2 << 8;
       FFTOPK_MARK(11);
     }
     if (smode == kModeGather) {
@@ -946,7 +969,7 @@ __global__ void __launch_bounds__(NT, (NT <= 512 ? 2 : 1)) select2048_kernel(con
     }
   }
 
-  if (mode == kModeFallback) mode = refine_from_data<NT>(cx, need, P, r);
+  if (mode == kModeFallback) mode = refine_from_data<NT>(cx, need, P, r, pick_no);
 
   // Candidates that peers pushed into rank 0 are complete after a cluster barrier. The sampled
   // path has had that barrier already (#2) and only needs one more so that rank 0 outlives the
@@ -962,7 +985,7 @@ __global__ void __launch_bounds__(NT, (NT <= 512 ? 2 : 1)) select2048_kernel(con
     const uint64_t pfx = r < 0 ? fin_pfx : (uint64_t)P;
     int idx_bits = 32 - __clz(len - 1);
     cta_finish<NT>(cx.cand, n, need, hi, pfx, idx_bits, cx.hist(0), ctrl, out_idx, out_key,
-                   (uint32_t)kK - need, p.idx_offset, p.status);
+                   (uint32_t)kK - need, cx.idx_offset, p.status, cx.page);
   }
   if (finish_first) cluster.sync();
   FFTOPK_MARK(7);
@@ -1154,9 +1177,10 @@ int fftopk_plan(int32_t B, int64_t L, int32_t plan[6]) {
   return FFTOPK_OK;
 }
 
-int fftopk_select2048(const float* score, int64_t row_stride, int32_t B, int64_t L, const int32_t* lengths,
-                      const int32_t* row_starts, int32_t* out_idx, uint32_t* out_key, int32_t idx_offset,
-                      uint32_t* status, void* cuda_stream) {
+static int launch_select(const float* score, int64_t row_stride, int32_t B, int64_t L, const int32_t* lengths,
+                         const int32_t* row_starts, int32_t* out_idx, uint32_t* out_key, int32_t idx_offset,
+                         uint32_t* status, void* cuda_stream, const int32_t* src_page_table, int64_t src_stride,
+                         const int32_t* cu_seqlens_q, int32_t prefill_bs, const int32_t* row_offsets) {
   if (B < 0 || L < 0 || row_stride < 0) return FFTOPK_EINVAL;
   if (B == 0) return FFTOPK_OK;
   if (!score || !lengths || !out_idx) return FFTOPK_EINVAL;
@@ -1181,6 +1205,11 @@ int fftopk_select2048(const float* score, int64_t row_stride, int32_t B, int64_t
   p.list_cap = pl.list_cap;
   p.cand_cap = pl.cand_cap;
   p.force_slow = g_tuning.force_slow;
+  p.src_page_table = src_page_table;
+  p.src_stride = src_stride;
+  p.cu_seqlens_q = cu_seqlens_q;
+  p.prefill_bs = prefill_bs;
+  p.row_offsets = row_offsets;
   if ((size_t)pl.smem_bytes > (size_t)d->smem_optin) return FFTOPK_ERANGE;
 
   cudaLaunchConfig_t cfg = {};
@@ -1203,6 +1232,30 @@ int fftopk_select2048(const float* score, int64_t row_stride, int32_t B, int64_t
   }
   if (e != cudaSuccess) return cuda_fail(e);
   return FFTOPK_OK;
+}
+
+int fftopk_select2048(const float* score, int64_t row_stride, int32_t B, int64_t L, const int32_t* lengths,
+                      const int32_t* row_starts, int32_t* out_idx, uint32_t* out_key, int32_t idx_offset,
+                      uint32_t* status, void* cuda_stream) {
+  return launch_select(score, row_stride, B, L, lengths, row_starts, out_idx, out_key, idx_offset, status, cuda_stream,
+                       nullptr, 0, nullptr, 0, nullptr);
+}
+
+int fftopk_select2048_page_table(const float* score, int64_t row_stride, int32_t B, int64_t L,
+                                 const int32_t* lengths, const int32_t* row_starts, int32_t* dst_page_table,
+                                 const int32_t* src_page_table, int64_t src_stride, const int32_t* cu_seqlens_q,
+                                 int32_t prefill_bs, uint32_t* status, void* cuda_stream) {
+  if (B > 0 && (!src_page_table || src_stride < 0 || prefill_bs < 1 || prefill_bs > B)) return FFTOPK_EINVAL;
+  return launch_select(score, row_stride, B, L, lengths, row_starts, dst_page_table, nullptr, 0, status, cuda_stream,
+                       src_page_table, src_stride, cu_seqlens_q, prefill_bs, nullptr);
+}
+
+int fftopk_select2048_ragged(const float* score, int64_t row_stride, int32_t B, int64_t L, const int32_t* lengths,
+                             const int32_t* row_starts, int32_t* topk_indices_ragged,
+                             const int32_t* topk_indices_offset, uint32_t* status, void* cuda_stream) {
+  if (B > 0 && !topk_indices_offset) return FFTOPK_EINVAL;
+  return launch_select(score, row_stride, B, L, lengths, row_starts, topk_indices_ragged, nullptr, 0, status,
+                       cuda_stream, nullptr, 0, nullptr, 0, topk_indices_offset);
 }
 
 }  // extern "C"

@@ -24,6 +24,8 @@ EXPORTS = (
     "fftopk_strerror",
     "fftopk_last_cuda_error",
     "fftopk_select2048",
+    "fftopk_select2048_page_table",
+    "fftopk_select2048_ragged",
     "fftopk_merge2048",
     "fftopk_comm_bytes",
     "fftopk_comm_create",
@@ -76,6 +78,14 @@ def lib() -> ctypes.CDLL:
     L.fftopk_select2048.argtypes = [
         c.c_void_p, c.c_int64, c.c_int32, c.c_int64, c.c_void_p, c.c_void_p,
         c.c_void_p, c.c_void_p, c.c_int32, c.c_void_p, c.c_void_p]
+    L.fftopk_select2048_page_table.restype = c.c_int
+    L.fftopk_select2048_page_table.argtypes = [
+        c.c_void_p, c.c_int64, c.c_int32, c.c_int64, c.c_void_p, c.c_void_p, c.c_void_p, c.c_void_p, c.c_int64,
+        c.c_void_p, c.c_int32, c.c_void_p, c.c_void_p]
+    L.fftopk_select2048_ragged.restype = c.c_int
+    L.fftopk_select2048_ragged.argtypes = [
+        c.c_void_p, c.c_int64, c.c_int32, c.c_int64, c.c_void_p, c.c_void_p, c.c_void_p, c.c_void_p, c.c_void_p,
+        c.c_void_p]
     L.fftopk_merge2048.restype = c.c_int
     L.fftopk_merge2048.argtypes = [
         c.c_void_p, c.c_void_p, c.c_int64, c.c_int32, c.c_int32, c.c_void_p, c.c_void_p, c.c_void_p, c.c_void_p]

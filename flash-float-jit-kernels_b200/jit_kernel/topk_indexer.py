@@ -116,3 +116,83 @@ def fast_topk_v3(
     topk_indices = torch.empty((score.size(0), topk), dtype=torch.int32, device=score.device)
     fast_topk(score, topk_indices, lengths, row_starts)
     return topk_indices
+
+
+def fast_topk_transform_fused(
+    score: torch.Tensor,
+    lengths: torch.Tensor,
+    page_table_size_1: torch.Tensor,
+    cu_seqlens_q: torch.Tensor,
+    topk: int,
+    row_starts: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """Top-2048 selection fused with the page-table gather that follows it.
+
+    Mirrors the reference's exported ``fast_topk_transform_fused``
+    (topk_indexer_radix.cu:1160-1214, 1255): ``dst[b, j] = page_table_size_1[i, idx_j]`` where
+    ``idx_j`` are the selected indices of row ``b`` and ``i`` is the request that row belongs to
+    (``cu_seqlens_q[i] <= b < cu_seqlens_q[i+1]``; with ``row_starts is None`` and one row per
+    request - decode - simply ``i = b``). Rows with ``lengths[b] <= 2048`` give the first
+    ``lengths[b]`` table entries followed by -1.
+    """
+    assert topk == TOPK, "only topk=2048 is supported"
+    assert score.dim() == 2
+    _check_inputs(score, lengths, row_starts)
+    B = score.size(0)
+    if not page_table_size_1.is_cuda or page_table_size_1.dtype != torch.int32 or page_table_size_1.dim() != 2 \
+            or (page_table_size_1.stride(1) != 1 and page_table_size_1.size(1) > 1):
+        raise RuntimeError("page_table_size_1 must be a 2-D CUDA int32 tensor with unit inner stride")
+    if not cu_seqlens_q.is_cuda or cu_seqlens_q.dtype != torch.int32 or cu_seqlens_q.dim() != 1 \
+            or not cu_seqlens_q.is_contiguous():
+        raise RuntimeError("cu_seqlens_q must be a contiguous 1-D CUDA int32 tensor")
+    prefill_bs = cu_seqlens_q.size(0) - 1
+    if page_table_size_1.size(0) != prefill_bs or prefill_bs > B:
+        raise RuntimeError("page_table_size_1 must have one row per request and prefill_bs <= B")
+    dst = torch.empty((B, TOPK), dtype=torch.int32, device=score.device)
+    if B == 0:
+        return dst
+    is_decode = row_starts is None and prefill_bs == B  # reference: radix.cu:1196
+    lib = _native.lib()
+    with torch.cuda.device(score.device):
+        rc = lib.fftopk_select2048_page_table(
+            score.data_ptr(), score.stride(0), B, score.size(1), lengths.data_ptr(),
+            row_starts.data_ptr() if row_starts is not None else None, dst.data_ptr(),
+            page_table_size_1.data_ptr(), page_table_size_1.stride(0),
+            None if is_decode else cu_seqlens_q.data_ptr(), prefill_bs,
+            _status_word(score.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
+    _native.check(rc, "fftopk_select2048_page_table")
+    return dst
+
+
+def fast_topk_transform_ragged_fused(
+    score: torch.Tensor,
+    lengths: torch.Tensor,
+    topk_indices_offset: torch.Tensor,
+    topk: int,
+    row_starts: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """Top-2048 selection with a per-row offset added to every index (ragged KV layout).
+
+    Mirrors ``fast_topk_transform_ragged_fused`` (topk_indexer_radix.cu:1216-1250, 1256):
+    ``out[b, j] = idx_j + topk_indices_offset[b]``; short rows give ``offset + 0..len-1`` then -1.
+    """
+    assert topk == TOPK, "only topk=2048 is supported"
+    assert score.dim() == 2
+    _check_inputs(score, lengths, row_starts)
+    B = score.size(0)
+    if not topk_indices_offset.is_cuda or topk_indices_offset.dtype != torch.int32 \
+            or topk_indices_offset.dim() != 1 or topk_indices_offset.size(0) != B \
+            or not topk_indices_offset.is_contiguous():
+        raise RuntimeError("topk_indices_offset must be a contiguous CUDA int32 tensor of size B")
+    out = torch.empty((B, TOPK), dtype=torch.int32, device=score.device)
+    if B == 0:
+        return out
+    lib = _native.lib()
+    with torch.cuda.device(score.device):
+        rc = lib.fftopk_select2048_ragged(
+            score.data_ptr(), score.stride(0), B, score.size(1), lengths.data_ptr(),
+            row_starts.data_ptr() if row_starts is not None else None, out.data_ptr(),
+            topk_indices_offset.data_ptr(), _status_word(score.device).data_ptr(),
+            torch.cuda.current_stream().cuda_stream)
+    _native.check(rc, "fftopk_select2048_ragged")
+    return out

@@ -84,6 +84,31 @@ int fftopk_select2048(const float* score, int64_t row_stride, int32_t B, int64_t
                       uint32_t* status, void* cuda_stream);
 
 /*
+ * Selection fused with the step that follows it in a sparse-attention decode / prefill layer.
+ * Replace fast_topk_transform_interface and fast_topk_transform_ragged_interface
+ * (topk_indexer_radix.cu:1160-1250) with their three kernels (:871-995), which the reference
+ * exports as fast_topk_transform_fused / fast_topk_transform_ragged_fused (:1255-1256). All
+ * arguments shared with fftopk_select2048 mean the same.
+ *
+ * fftopk_select2048_page_table: dst_page_table[b, j] = table_row[idx_j], where idx_j runs over
+ *   the selected indices of row b and table_row = src_page_table + i*src_stride for the request i
+ *   with cu_seqlens_q[i] <= b < cu_seqlens_q[i+1] (cu_seqlens_q int32 [prefill_bs + 1], its last
+ *   entry = B). cu_seqlens_q == NULL is the decode case: prefill_bs == B and i = b. Rows with
+ *   len <= 2048 give table_row[0..len-1] followed by -1 (naive_topk_transform, :166-175).
+ * fftopk_select2048_ragged: topk_indices_ragged[b, j] = idx_j + topk_indices_offset[b]; short rows
+ *   give offset + 0..len-1 followed by -1 (naive_topk_transform_ragged, :178-184).
+ */
+int fftopk_select2048_page_table(const float* score, int64_t row_stride, int32_t B, int64_t L,
+                                 const int32_t* lengths, const int32_t* row_starts,
+                                 int32_t* dst_page_table, const int32_t* src_page_table,
+                                 int64_t src_stride, const int32_t* cu_seqlens_q, int32_t prefill_bs,
+                                 uint32_t* status, void* cuda_stream);
+int fftopk_select2048_ragged(const float* score, int64_t row_stride, int32_t B, int64_t L,
+                             const int32_t* lengths, const int32_t* row_starts,
+                             int32_t* topk_indices_ragged, const int32_t* topk_indices_offset,
+                             uint32_t* status, void* cuda_stream);
+
+/*
  * Merge of per-shard candidates into the global top-2048 (context-parallel mode: every GPU
  * selected a local top-2048 over its sequence shard, the candidates were all-gathered).
  * No reference counterpart: the reference has no multi-GPU path.
