@@ -55,6 +55,7 @@ struct SelectParams {
   int32_t list_cap;  // per-CTA candidate list capacity (entries), multiple of 16
   int32_t cand_cap;  // rank 0's gathered-candidate capacity (entries), multiple of 16
   int32_t force_slow;  // tests: skip the filter path and run the full-histogram path
+  int32_t overlap;     // let the next launch on the stream start before this one has finished
   // fused output transforms (all optional; reference: topk_transform_decode_kernel,
   // topk_transform_prefill_kernel, topk_transform_prefill_ragged_kernel, radix.cu:871-995)
   const int32_t* src_page_table;  // [prefill_bs, src_stride]: out = table_row[idx]
@@ -609,7 +610,7 @@ __device__ __forceinline__ int refine_from_data(RowCtx<NT>& cx, uint32_t& need, 
 }
 
 template <int NT>
-__global__ void __launch_bounds__(NT, (NT <= 512 ? 2 : 1)) select2048_kernel(const SelectParams p) {
+__global__ void __launch_bounds__(NT, 1024 / NT) select2048_kernel(const SelectParams p) {
   RowCtx<NT> cx;
   cg::cluster_group cluster = cg::this_cluster();
   const int C = cx.C = (int)cluster.num_blocks();
@@ -618,6 +619,12 @@ __global__ void __launch_bounds__(NT, (NT <= 512 ? 2 : 1)) select2048_kernel(con
   const int tid = threadIdx.x;
   const int lane = tid & 31, warp = tid >> 5;
   constexpr int NW = NT / 32;
+
+  // Opt-in overlap of back-to-back calls (programmatic dependent launch): once every CTA of this
+  // grid has passed this point - or exited - the next kernel on the stream may start filling the
+  // SMs that short rows free early. This kernel never waits on its predecessor, so it is only
+  // enabled when the caller has declared consecutive calls independent (fftopk_set_overlap).
+  if (p.overlap) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   int64_t row_start = p.row_starts ? (int64_t)p.row_starts[row] : 0;
   row_start = row_start < 0 ? 0 : (row_start > p.L ? p.L : row_start);
@@ -667,7 +674,8 @@ __global__ void __launch_bounds__(NT, (NT <= 512 ? 2 : 1)) select2048_kernel(con
   cx.xch = cx.sup0 + 2 * kSup;                                             // kMaxCluster * 64 words
   Ctrl* ctrl = cx.ctrl = reinterpret_cast<Ctrl*>(cx.xch + kMaxCluster * kSup);  // 8-byte aligned
   cx.list = reinterpret_cast<uint64_t*>(reinterpret_cast<unsigned char*>(ctrl) + ((sizeof(Ctrl) + 127) & ~127u));
-  cx.cand = cx.list + p.list_cap;
+  // a cluster of one CTA has nobody to gather from: its candidate buffer IS the list
+  cx.cand = C == 1 ? cx.list : cx.list + p.list_cap;
   cx.ctrl0 = cluster.map_shared_rank(ctrl, 0);
   cx.cand0 = cluster.map_shared_rank(cx.cand, 0);
   uint64_t* list = cx.list;
@@ -686,6 +694,8 @@ __global__ void __launch_bounds__(NT, (NT <= 512 ? 2 : 1)) select2048_kernel(con
   const int n_g = sh.g1 - sh.g0;
   // Whole shard in registers (same answer in every CTA of the cluster: `per` is rank-independent).
   const bool exact = per <= NT * kRegSlabs;
+  // sampled mode: slabs read per warp
+  const int ns = min(kRegSlabs, max(1, 2048 / (C * NT)));
 
   // ---- prologue: clear the search totals, both histograms and the control block --------------
   if (tid < kSup) {
@@ -727,15 +737,23 @@ __global__ void __launch_bounds__(NT, (NT <= 512 ? 2 : 1)) select2048_kernel(con
         if (g >= sh.i0 && g < sh.i1) xr[j] = __ldg(base4 + g);
       }
     } else {
-      int g;
-      if (n_g >= NT) {
-        const int stride = (n_g / NW) & ~7;
-        g = sh.g0 + warp * stride + lane;
-      } else {
-        g = sh.g0 + tid;
+      // ns slabs per warp: small clusters of small CTAs sample more per thread, so that a row
+      // is always sampled at about 8K positions or more (a thin sample needs a wide safety margin,
+      // which means more candidates to carry)
+#pragma unroll
+      for (int j = 0; j < kRegSlabs; ++j) {
+        if (j < ns) {
+          int g;
+          if (n_g >= NT * ns) {
+            const int stride = (n_g / (NW * ns)) & ~7;
+            g = sh.g0 + (warp * ns + j) * stride + lane;
+          } else {
+            g = sh.g0 + j * NT + tid;
+          }
+          if (g < sh.g1) gr[j] = g;
+          if (g >= sh.i0 && g < sh.i1) xr[j] = __ldg(base4 + g);
+        }
       }
-      if (g < sh.g1) gr[0] = g;
-      if (g >= sh.i0 && g < sh.i1) xr[0] = __ldg(base4 + g);
       // The filter pass cannot start before the sample has been histogrammed and searched
       // (several microseconds); ask L2 for the shard now, one 128-byte line per request, so that
       // HBM latency and bandwidth are spent while the memory system would otherwise idle.
@@ -756,7 +774,7 @@ __global__ void __launch_bounds__(NT, (NT <= 512 ? 2 : 1)) select2048_kernel(con
     uint32_t* h0 = cx.hist(0);
 #pragma unroll
     for (int j = 0; j < kRegSlabs; ++j) {
-      if (j == 0 || exact) {  // uniform over the CTA
+      if (j < ns || exact) {  // uniform over the CTA
         const bool in = gr[j] < sh.g1;
         const int i0 = 4 * gr[j] - sh.a;
         const float xv[4] = {xr[j].x, xr[j].y, xr[j].z, xr[j].w};
@@ -850,13 +868,16 @@ __global__ void __launch_bounds__(NT, (NT <= 512 ? 2 : 1)) select2048_kernel(con
     if (smode == kModeNext) {
       {
         uint32_t* h1 = cx.hist(1);
-        const int e0 = 4 * gr[0] - sh.a;
-        const float xv[4] = {xr[0].x, xr[0].y, xr[0].z, xr[0].w};
-        if (gr[0] < sh.g1) {
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const uint32_t key = fftopk_key_from_bits(__float_as_uint(xv[e]));
-            hist_add(h1, (key >> 8) & 0xfffu, (unsigned)(e0 + e) < (unsigned)len && (key >> 20) == g1);
+        for (int j = 0; j < kRegSlabs; ++j) {
+          if (j < ns && gr[j] < sh.g1) {
+            const int e0 = 4 * gr[j] - sh.a;
+            const float xv[4] = {xr[j].x, xr[j].y, xr[j].z, xr[j].w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const uint32_t key = fftopk_key_from_bits(__float_as_uint(xv[e]));
+              hist_add(h1, (key >> 8) & 0xfffu, (unsigned)(e0 + e) < (unsigned)len && (key >> 20) == g1);
+            }
           }
         }
       }
@@ -891,8 +912,12 @@ __global__ void __launch_bounds__(NT, (NT <= 512 ? 2 : 1)) select2048_kernel(con
       const uint32_t cnt_all =
           filter_shard<NT, (NT >= 1024 ? 4 : 8)>(sh, edge, mine_l, lp, ctrl, spill, spill_cap, kmax);
       FFTOPK_MARK(8);
-      // hand the candidates to rank 0: one remote atomic per CTA allocates the range
       const uint32_t mycnt = min(cnt_all, lp);
+      if (C == 1) {
+        // single CTA: the finish reads the list where it lies; unused slots become "empty" (0)
+        for (uint32_t j = mycnt; j < lp; ++j) mine_l[j] = 0ull;
+      }
+      // hand the candidates to rank 0: one remote atomic per CTA allocates the range
       uint32_t lincl = mycnt;
 #pragma unroll
       for (int off = 1; off < 32; off <<= 1) {
@@ -905,6 +930,10 @@ __global__ void __launch_bounds__(NT, (NT <= 512 ? 2 : 1)) select2048_kernel(con
         ctrl->wmax[warp] = kmax;
       }
       __syncthreads();
+      if (C == 1) {  // (the spill count is final only now)
+        const uint32_t spill_n1 = min(ctrl->lcount, spill_cap);
+        for (uint32_t j = spill_n1 + tid; j < spill_cap; j += NT) spill[j] = 0ull;
+      }
       FFTOPK_MARK(44);
       if (warp == 0) {
         const uint32_t wmine = lane < NW ? ctrl->wtot[lane] : 0u;
@@ -928,7 +957,7 @@ __global__ void __launch_bounds__(NT, (NT <= 512 ? 2 : 1)) select2048_kernel(con
       }
       __syncthreads();
       FFTOPK_MARK(45);
-      {
+      if (C > 1) {
         const uint32_t dst = ctrl->wtot[warp] + lincl - mycnt;
         for (uint32_t j = 0; j < mycnt; ++j) {
           if (dst + j < (uint32_t)p.cand_cap) cx.cand0[dst + j] = mine_l[j];
@@ -951,7 +980,8 @@ __global__ void __launch_bounds__(NT, (NT <= 512 ? 2 : 1)) select2048_kernel(con
         const uint32_t maxkey = c0->max_key;
         // fewer than k admitted (the guess was too high), a list overflowed, or more than rank 0
         // can hold: start over with full histograms
-        mode = (over == 0u && total >= (uint32_t)kK && total <= (uint32_t)p.cand_cap) ? kModeGather : kModeFallback;
+        const uint32_t room = C == 1 ? 0xffffffffu : (uint32_t)p.cand_cap;  // (a lone CTA keeps them in the list)
+        mode = (over == 0u && total >= (uint32_t)kK && total <= room) ? kModeGather : kModeFallback;
         // every candidate's key lies in [lowkey, maxkey]: the bits those two share are a prefix of
         // all of them, so the finish starts at the first bit where they differ
         const uint32_t lowkey = (gkey > 0x007fffffu && gkey <= 0xff800000u) ? gkey : 0u;
@@ -980,7 +1010,10 @@ __global__ void __launch_bounds__(NT, (NT <= 512 ? 2 : 1)) select2048_kernel(con
   if (!finish_first) cluster.sync();
   FFTOPK_MARK(6);
   if (mode == kModeGather && rank == 0) {
-    const int n = (int)min(ctrl->cand_count, (uint32_t)p.cand_cap);
+    // sampled path of a lone CTA: the whole list region, empty slots included
+    const int spill_cap1 = p.list_cap / 8;
+    const int n = (r < 0 && C == 1) ? NT * ((p.list_cap - spill_cap1) / NT) + spill_cap1
+                                    : (int)min(ctrl->cand_count, (uint32_t)p.cand_cap);
     const int hi = r < 0 ? fin_hi : 32 + round_shift(r);
     const uint64_t pfx = r < 0 ? fin_pfx : (uint64_t)P;
     int idx_bits = 32 - __clz(len - 1);
@@ -1003,7 +1036,7 @@ using namespace fftopk;
 
 
 struct Tuning {
-  int cluster = -1, threads = -1, list_cap = -1, cand_cap = -1, force_slow = 0;
+  int cluster = -1, threads = -1, list_cap = -1, cand_cap = -1, force_slow = 0, overlap = 0;
 };
 Tuning g_tuning;
 
@@ -1022,6 +1055,8 @@ constexpr size_t fixed_smem_bytes() {
 
 constexpr int kLatencyListCap = 6144, kLatencyCandCap = 16384;  // one CTA per SM: use the shared memory
 constexpr int kBatchListCap = 4096, kBatchCandCap = 4096;       // several CTAs per SM
+constexpr int kOverlapListCap1 = 9216;                          // one CTA per row: list = candidates
+constexpr int kOverlapListCap = 3072, kOverlapCandCap = 6144;   // two CTAs per SM
 
 
 template <int NT>
@@ -1050,6 +1085,8 @@ int device_info(DeviceInfo** out) {
     int rc = setup_kernel<1024>(d.smem_optin);
     if (rc) return rc;
     rc = setup_kernel<512>(d.smem_optin);
+    if (rc) return rc;
+    rc = setup_kernel<256>(d.smem_optin);
     if (rc) return rc;
     // can a 16-CTA cluster with the latency-mode shared-memory footprint be co-scheduled?
     d.max_cluster = 8;
@@ -1102,11 +1139,26 @@ Plan make_plan(const DeviceInfo& d, int B, int64_t L) {
   const bool one_per_sm = (int64_t)rows * pl.cluster <= d.sm_count;
   pl.list_cap = one_per_sm ? kLatencyListCap : kBatchListCap;
   pl.cand_cap = one_per_sm ? kLatencyCandCap : kBatchCandCap;
+  if (g_tuning.overlap) {
+    // Back-to-back calls may overlap: what counts is work per row, not the latency of one call.
+    // Few CTAs per row (less cluster traffic per row), 512 threads and about 110 KB of shared
+    // memory so that two CTAs - of different calls - share an SM, and about four calls in flight.
+    int ct = floor_pow2(d.sm_count / (4 * rows) > 0 ? d.sm_count / (4 * rows) : 1);
+    if (ct < pl.cluster) pl.cluster = ct;
+    pl.threads = 512;
+    if (pl.cluster == 1) {
+      pl.list_cap = kOverlapListCap1;
+    } else {
+      pl.list_cap = kOverlapListCap;
+      pl.cand_cap = kOverlapCandCap;
+    }
+  }
   if (g_tuning.cluster > 0) pl.cluster = g_tuning.cluster;
   if (g_tuning.threads > 0) pl.threads = g_tuning.threads;
   if (g_tuning.list_cap > 0) pl.list_cap = (g_tuning.list_cap + 15) & ~15;
   if (g_tuning.cand_cap > 0) pl.cand_cap = (g_tuning.cand_cap + 15) & ~15;
-  pl.smem_bytes = (int)(fixed_smem_bytes() + (size_t)(pl.list_cap + pl.cand_cap) * 8);
+  if (pl.cluster == 1) pl.cand_cap = pl.list_cap;  // one CTA per row: the two buffers are the same memory
+  pl.smem_bytes = (int)(fixed_smem_bytes() + (size_t)(pl.cluster == 1 ? pl.list_cap : pl.list_cap + pl.cand_cap) * 8);
   return pl;
 }
 
@@ -1151,14 +1203,19 @@ uint32_t fftopk_key_of(float x) {
 int fftopk_set_tuning(int32_t cluster_ctas, int32_t threads, int32_t list_cap, int32_t cand_cap,
                       int32_t force_full_histogram) {
   if (cluster_ctas > 0 && (cluster_ctas > kMaxCluster || (cluster_ctas & (cluster_ctas - 1)))) return FFTOPK_EINVAL;
-  if (threads > 0 && threads != 512 && threads != 1024) return FFTOPK_EINVAL;
+  if (threads > 0 && threads != 256 && threads != 512 && threads != 1024) return FFTOPK_EINVAL;
   if (cand_cap > 0 && (cand_cap < kSmall || cand_cap > 16384)) return FFTOPK_EINVAL;
-  if (list_cap > 0 && (list_cap < kSmall || list_cap > 8192)) return FFTOPK_EINVAL;
+  if (list_cap > 0 && (list_cap < kSmall || list_cap > 16384)) return FFTOPK_EINVAL;
   g_tuning.cluster = cluster_ctas;
   g_tuning.threads = threads;
   g_tuning.list_cap = list_cap;
   g_tuning.cand_cap = cand_cap;
   g_tuning.force_slow = force_full_histogram > 0 ? 1 : 0;
+  return FFTOPK_OK;
+}
+
+int fftopk_set_overlap(int32_t enable) {
+  g_tuning.overlap = enable ? 1 : 0;
   return FFTOPK_OK;
 }
 
@@ -1205,6 +1262,7 @@ static int launch_select(const float* score, int64_t row_stride, int32_t B, int6
   p.list_cap = pl.list_cap;
   p.cand_cap = pl.cand_cap;
   p.force_slow = g_tuning.force_slow;
+  p.overlap = g_tuning.overlap;
   p.src_page_table = src_page_table;
   p.src_stride = src_stride;
   p.cu_seqlens_q = cu_seqlens_q;
@@ -1217,18 +1275,25 @@ static int launch_select(const float* score, int64_t row_stride, int32_t B, int6
   cfg.blockDim = dim3((unsigned)pl.threads, 1, 1);
   cfg.dynamicSmemBytes = (size_t)pl.smem_bytes;
   cfg.stream = static_cast<cudaStream_t>(cuda_stream);
-  cudaLaunchAttribute at[1];
+  cudaLaunchAttribute at[2];
   at[0].id = cudaLaunchAttributeClusterDimension;
   at[0].val.clusterDim.x = (unsigned)pl.cluster;
   at[0].val.clusterDim.y = 1;
   at[0].val.clusterDim.z = 1;
   cfg.attrs = at;
   cfg.numAttrs = 1;
+  if (g_tuning.overlap) {
+    at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.numAttrs = 2;
+  }
   cudaError_t e;
   if (pl.threads == 1024) {
     e = cudaLaunchKernelEx(&cfg, select2048_kernel<1024>, p);
-  } else {
+  } else if (pl.threads == 512) {
     e = cudaLaunchKernelEx(&cfg, select2048_kernel<512>, p);
+  } else {
+    e = cudaLaunchKernelEx(&cfg, select2048_kernel<256>, p);
   }
   if (e != cudaSuccess) return cuda_fail(e);
   return FFTOPK_OK;

@@ -38,6 +38,7 @@ EXPORTS = (
     "fftopk_key_of",
     "fftopk_plan",
     "fftopk_set_tuning",
+    "fftopk_set_overlap",
 )
 
 
@@ -114,6 +115,8 @@ def lib() -> ctypes.CDLL:
     L.fftopk_plan.argtypes = [c.c_int32, c.c_int64, c.POINTER(c.c_int32)]
     L.fftopk_set_tuning.restype = c.c_int
     L.fftopk_set_tuning.argtypes = [c.c_int32, c.c_int32, c.c_int32, c.c_int32, c.c_int32]
+    L.fftopk_set_overlap.restype = c.c_int
+    L.fftopk_set_overlap.argtypes = [c.c_int32]
     return L
 
 
@@ -138,3 +141,8 @@ def set_tuning(cluster_ctas: int = -1, threads: int = -1, list_cap: int = -1, ca
                force_full_histogram: bool = False) -> None:
     check(lib().fftopk_set_tuning(cluster_ctas, threads, list_cap, cand_cap, int(force_full_histogram)),
           "fftopk_set_tuning")
+
+
+def set_overlap(enable: bool) -> None:
+    """Allow back-to-back selection calls on a stream to overlap (see include/fftopk.h)."""
+    check(lib().fftopk_set_overlap(int(bool(enable))), "fftopk_set_overlap")

@@ -210,6 +210,17 @@ uint32_t fftopk_key_of(float x);
  * Replaces the reference's compile-time split heuristic (topk_indexer_radix.cu:1081-1111).
  */
 int fftopk_plan(int32_t B, int64_t L, int32_t plan[6]);
+/*
+ * Overlap of back-to-back calls (off by default; process-wide). With enable = 1 every selection
+ * launch is a programmatic dependent launch AND signals its own dependents at once, so when two
+ * selection kernels follow each other on a stream the second starts filling SMs as soon as CTAs of
+ * the first exit (short rows finish early), instead of waiting for the whole grid. The kernel
+ * never waits on its predecessor. Enable it only if (1) no kernel that precedes a call on the
+ * stream hands over unfinished inputs through programmatic launch completion, and (2) calls that
+ * may overlap do not share an output buffer. Kernels of other libraries around the calls keep
+ * normal stream ordering. No reference counterpart.
+ */
+int fftopk_set_overlap(int32_t enable);
 int fftopk_set_tuning(int32_t cluster_ctas, int32_t threads, int32_t list_cap, int32_t cand_cap,
                       int32_t force_full_histogram);
 

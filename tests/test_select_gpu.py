@@ -92,13 +92,35 @@ def test_reference_benchmark_grid(bs, seq_len, has_row_starts):
 
 
 @pytest.mark.parametrize("cluster", [1, 2, 4, 8, 16])
-@pytest.mark.parametrize("threads", [512, 1024])
+@pytest.mark.parametrize("threads", [256, 512, 1024])
 def test_every_cluster_size(cluster, threads):
     _native.set_tuning(cluster_ctas=cluster, threads=threads)
     g = torch.Generator().manual_seed(cluster * 10 + threads)
     s = torch.randn(3, 70001, generator=g)
     ln = torch.tensor([70001, 33333, 2049], dtype=torch.int32)
     check(s, ln, what=f"cluster={cluster} threads={threads}")
+    if cluster <= 2:  # long rows on few CTAs: the sampled path, single-CTA shortcut included
+        check(*workloads.c5(B=2, L=400000), what=f"cluster={cluster} threads={threads} long")
+
+
+def test_overlapped_back_to_back_calls():
+    """Programmatic dependent launch between consecutive calls (opt-in): same results."""
+    dev = torch.device("cuda", 0)
+    s, ln = workloads.c3(B=32, L=60000)
+    bufs = [torch.roll(s, i, 0).contiguous().to(dev) for i in range(4)]
+    lens = [torch.roll(ln, i, 0).contiguous().to(dev) for i in range(4)]
+    outs = [torch.empty(32, K, dtype=torch.int32, device=dev) for _ in range(4)]
+    _native.set_overlap(True)
+    try:
+        for rep in range(3):
+            for i in range(4):
+                fast_topk(bufs[i], outs[i], lens[i])
+        torch.cuda.synchronize()
+    finally:
+        _native.set_overlap(False)
+    for i in range(4):
+        orc.check_result(torch.roll(s, i, 0).numpy(), torch.roll(ln, i, 0).numpy(), outs[i].cpu().numpy(),
+                         what=f"overlap buffer {i}")
 
 
 @pytest.mark.parametrize("cluster", [1, 4, 16])
