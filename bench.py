@@ -11,7 +11,11 @@ N(0,1) logits, -inf padding, k=2048). With N GPUs every rank processes its own 6
 (rows are independent: no collective on the data path), so `value` = 64*N*K rows / time.
 
   value      rows/s with the inputs resident in HBM, eight 32 MiB input buffers rotated so that no
-             step finds its input in L2 (256 MiB > 126 MB L2)
+             step finds its input in L2 (256 MiB > 126 MB L2). The steps are independent batches
+             and the library's throughput mode is on (fftopk_set_overlap: consecutive calls are
+             programmatic dependent launches, so a call starts filling the SMs that the short rows
+             of the previous call have already left; every step has its own output buffer)
+  serial     the same K steps with the default, strictly serialised launches: us per call
   e2e        the same metric through the public op with HOST buffers: pinned-memory H2D copy of
              the batch, the op, D2H copy of the indices, all inside the timed region
   roofline   algorithmic bytes per launch / measured launch time, against the measured HBM peak
@@ -258,12 +262,28 @@ def ours_arm(args, rank: int, local_rank: int, world: int) -> None:
     for i in range(1, N_ROTATE):  # same lengths, rolled rows: different bytes in every buffer
         bufs.append(torch.roll(bufs[0], shifts=i, dims=0).contiguous())
     lens_rot = [torch.roll(ld, shifts=i, dims=0).contiguous() for i in range(N_ROTATE)]
-    out = torch.empty(B, K, dtype=torch.int32, device=dev)
+    outs = [torch.empty(B, K, dtype=torch.int32, device=dev) for _ in range(N_ROTATE)]
     nbytes = workloads.algorithmic_bytes(lengths, L)
-    plan = _native.plan(B, L)
 
     def step(i):
-        fast_topk(bufs[i % N_ROTATE], out, lens_rot[i % N_ROTATE])
+        fast_topk(bufs[i % N_ROTATE], outs[i % N_ROTATE], lens_rot[i % N_ROTATE])
+
+    # ---- serialised launches first (the default mode of the library): latency of one call --------
+    _native.set_overlap(False)
+    plan_serial = _native.plan(B, L)
+    with torch.cuda.stream(stream):
+        for i in range(warmup):
+            step(i)
+    stream.synchronize()
+    n_serial = min(steps, 200)
+    g_serial = capture_steps(step, n_serial, stream)
+    time_graph(g_serial, stream)
+    serial_sec = min(time_graph(g_serial, stream) for _ in range(3)) / n_serial
+    del g_serial
+
+    # ---- throughput mode for the headline -------------------------------------------------------
+    _native.set_overlap(True)
+    plan = _native.plan(B, L)
 
     # ---- warm-up (also the first call, which sets kernel attributes, outside any capture) -------
     with torch.cuda.stream(stream):
@@ -303,6 +323,7 @@ def ours_arm(args, rank: int, local_rank: int, world: int) -> None:
     sec_per_step = sec / steps
     value = B * world * steps / sec
 
+    _native.set_overlap(False)
     # ---- end to end through the public op with host buffers ------------------------------------
     e2e_steps = max(3, min(steps, 20))
     h_score = score.pin_memory()
@@ -348,7 +369,12 @@ def ours_arm(args, rank: int, local_rank: int, world: int) -> None:
         "dtype": "f32", "data": "synthetic",
         "config": {"workload": WORKLOAD, "rows_per_gpu": B, "l2": f"{N_ROTATE} input buffers of {4 * B * L >> 20} MiB "
                    "rotated (> 126 MB L2)", "timing": "CUDA graph of the steps, CUDA events on its stream",
+                   "mode": "throughput: fftopk_set_overlap(1), consecutive calls are programmatic dependent "
+                           "launches and may overlap; one output buffer per rotated input",
                    "plan": plan},
+        "serial": {"us_per_call": serial_sec * 1e6, "rows_per_s": B * world / serial_sec,
+                   "gbs": nbytes / serial_sec / 1e9, "plan": plan_serial,
+                   "note": "same steps, default serialised launches (fftopk_set_overlap(0)), this rank"},
         "clocks": clk.summary(note),
         "e2e": {"value": e2e_value, "unit": "rows/s", "h2d_bytes_per_step": 4 * B * L + 4 * B,
                 "d2h_bytes_per_step": 4 * B * K, "steps": e2e_steps},
