@@ -112,7 +112,8 @@ struct Ctrl {
   uint32_t cslot;
   uint32_t fslot;
   uint32_t small_n;
-  uint32_t lcount;  // entries pushed to this CTA's candidate list (may exceed its capacity)
+  uint32_t lcount;  // entries pushed to this CTA's spill area (may exceed its capacity)
+  uint32_t spill_kmax;  // largest key among the spilled entries
   // result of the most recent threshold search
   int32_t t;
   uint32_t above;

@@ -103,12 +103,24 @@ __device__ __forceinline__ float4 load_granule(const Shard& sh, int g, float fil
   return load_granule_partial(sh.gbase, sh.a, sh.len, g, fill);
 }
 
+// A kept element on its way into the list: the raw float bits and the row index. It becomes a
+// (key << 32 | ~idx) composite later, in a dense pass - the hit loop is the divergent part of
+// the filter and every instruction in it is paid by a whole warp for one or two lanes.
+__device__ __forceinline__ uint64_t raw_to_composite(uint64_t raw, uint32_t& kmax) {
+  const uint32_t key = fftopk_key_from_bits((uint32_t)(raw >> 32));
+  kmax = max(kmax, key);
+  return ((uint64_t)key << 32) | (uint64_t)(~(uint32_t)raw);
+}
+
 // Overflow of a thread's private candidate slots: a shared spill area, slots from one counter
-// (rare, so the serialising atomic does not matter). Out of line to keep the filter loop small.
-__device__ __noinline__ void spill_push(Ctrl* ctrl, uint64_t* spill, uint32_t spill_cap, uint64_t comp) {
+// (rare, so the serialising atomic does not matter). Converts on the spot. Out of line to keep
+// the filter loop small.
+__device__ __noinline__ void spill_push(Ctrl* ctrl, uint64_t* spill, uint32_t spill_cap, uint64_t raw) {
   const uint32_t slot = warp_alloc(&ctrl->lcount);
   if (slot < spill_cap) {
-    spill[slot] = comp;
+    uint32_t k = 0;
+    spill[slot] = raw_to_composite(raw, k);
+    atomicMax(&ctrl->spill_kmax, k);
   } else {
     ctrl->pub_flag = 1u;
   }
@@ -121,7 +133,8 @@ __device__ __noinline__ void spill_push(Ctrl* ctrl, uint64_t* spill, uint32_t sp
 // appending needs no atomic, no vote and no scan (allocating slots from one shared counter
 // serialised at ~20 cycles per candidate and dominated the pass; a per-warp shuffle scan per trip
 // still cost more than the compares). A thread with more than `lp` candidates spills the excess.
-// Returns the thread's candidate count (entries beyond lp went to the spill area).
+// Returns the thread's candidate count (entries beyond lp went to the spill area); kmax is the
+// largest key among the thread's own entries.
 template <int NT, int U>
 __device__ __forceinline__ uint32_t filter_shard(const Shard& sh, float edge, uint64_t* mine, uint32_t lp, Ctrl* ctrl,
                                                  uint64_t* spill, uint32_t spill_cap, uint32_t& kmax) {
@@ -130,21 +143,16 @@ __device__ __forceinline__ uint32_t filter_shard(const Shard& sh, float edge, ui
   const float4* base4 = reinterpret_cast<const float4*>(sh.gbase);
   const int fa = sh.a, fi1 = sh.i1, len = sh.len;
   uint32_t cnt = 0;
-  kmax = 0u;
-  auto keep = [&](float x, int idx) {
-    if ((unsigned)idx < (unsigned)len) {
-      const uint32_t key = fftopk_key_from_bits(__float_as_uint(x));
-      kmax = max(kmax, key);
-      const uint64_t comp = ((uint64_t)key << 32) | (uint64_t)(~(uint32_t)idx);
-      if (cnt < lp) {
-        mine[cnt] = comp;
-      } else {
-        spill_push(ctrl, spill, spill_cap, comp);
-      }
-      ++cnt;
+  auto keep = [&](uint32_t bits, int idx) {
+    const uint64_t raw = ((uint64_t)bits << 32) | (uint64_t)(uint32_t)idx;
+    if (cnt < lp) {
+      mine[cnt] = raw;
+    } else {
+      spill_push(ctrl, spill, spill_cap, raw);
     }
+    ++cnt;
   };
-  const float* base1 = sh.gbase;
+  const uint32_t* base1 = reinterpret_cast<const uint32_t*>(sh.gbase);
   for (int gb = sh.i0; gb < fi1; gb += NT * U) {
     float4 x[U];
 #pragma unroll
@@ -163,7 +171,7 @@ __device__ __forceinline__ uint32_t filter_shard(const Shard& sh, float edge, ui
         m |= !(x[u].y < edge) ? 2u : 0u;
         m |= !(x[u].z < edge) ? 4u : 0u;
         m |= !(x[u].w < edge) ? 8u : 0u;
-        if (gb + u * NT + tid < fi1) mask |= m << (4 * u);
+        if (gb + u * NT + tid < fi1) mask |= m << (4 * u);  // interior granules only: all four valid
       }
     }
     // One loop for all hits of the trip: the lanes of a warp work on their own hits side by side
@@ -172,9 +180,8 @@ __device__ __forceinline__ uint32_t filter_shard(const Shard& sh, float edge, ui
     while (mask) {
       const int bit = __ffs(mask) - 1;
       mask &= mask - 1u;
-      const int g = gb + (bit >> 2) * NT + tid;
-      const int e = bit & 3;
-      keep(__ldg(base1 + 4 * (int64_t)g + e), 4 * g - fa + e);
+      const int el = 4 * (gb + (bit >> 2) * NT + tid) + (bit & 3);
+      keep(__ldg(base1 + el), el - fa);
     }
   }
   // edge granules [g0, i0) and [i1, g1): at most one each, visited by threads 0 and 32
@@ -184,12 +191,17 @@ __device__ __forceinline__ uint32_t filter_shard(const Shard& sh, float edge, ui
     if (ge >= 0 && ge < ge_end) {
       const float4 x = load_granule_partial(sh.gbase, sh.a, len, ge, ninf);
       const int e0 = 4 * ge - fa;
-      if (!(x.x < edge)) keep(x.x, e0 + 0);
-      if (!(x.y < edge)) keep(x.y, e0 + 1);
-      if (!(x.z < edge)) keep(x.z, e0 + 2);
-      if (!(x.w < edge)) keep(x.w, e0 + 3);
+      const float xv[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        if ((unsigned)(e0 + e) < (unsigned)len && !(xv[e] < edge)) keep(__float_as_uint(xv[e]), e0 + e);
+      }
     }
   }
+  // dense conversion of the thread's own entries
+  kmax = 0u;
+  const uint32_t own = min(cnt, lp);
+  for (uint32_t j = 0; j < own; ++j) mine[j] = raw_to_composite(mine[j], kmax);
   return cnt;
 }
 
@@ -288,7 +300,7 @@ __device__ __forceinline__ void cluster_pick(cg::cluster_group& cluster, int C, 
                                              uint32_t* xch, Ctrl* ctrl, int& pick_no, int nb, NeedFn&& need_of,
                                              Post&& post) {
   const int tid = threadIdx.x;
-  const int lane = tid & 31;
+  const int lane = tid & 31, warp = tid >> 5;
   const int fine = nb / kSup;
   uint32_t* tot = ctrl->tot[pick_no & 1];
   uint32_t* tot2 = ctrl->tot2[pick_no & 1];
@@ -302,18 +314,26 @@ __device__ __forceinline__ void cluster_pick(cg::cluster_group& cluster, int C, 
   }
   __syncthreads();
   FFTOPK_MARK(40);
-  // every warp picks for itself (same inputs, same result): no broadcast, no barrier
-  int ssel = -1;
-  uint32_t sup_above = 0, need = 0, total = 0;
-  {
+  // Warp 0 picks and publishes through the control block. (Letting every warp pick for itself
+  // saves the two broadcast barriers but was measured slower: 32 warps running the same shuffle
+  // scans get in each other's way.)
+  if (warp == 0) {
     const uint32_t lo = tot[2 * lane], hi = tot[2 * lane + 1];
-    total = warp_sum(lo + hi);
-    need = need_of(total);
-    uint32_t cnt = 0;
+    const uint32_t total = warp_sum(lo + hi);
+    const uint32_t need = need_of(total);
+    uint32_t above = 0, cnt = 0;
     int ts = -1;
-    if (need > 0 && warp_pick64(lo, hi, need, ts, sup_above, cnt)) ssel = ts;
+    const bool ok = need > 0 && warp_pick64(lo, hi, need, ts, above, cnt);
+    if (lane == 0) {
+      ctrl->sup_sel = ok ? ts : -1;
+      ctrl->sup_above = above;
+      ctrl->need = need;
+      ctrl->run_total = total;
+    }
   }
+  __syncthreads();
   FFTOPK_MARK(41);
+  const int ssel = ctrl->sup_sel;
   // (B) fine bins of the threshold super-bin: pulled from every peer, kept per rank in xch (the
   // tie path wants them) and summed into tot2
   if (ssel >= 0) {
@@ -336,33 +356,37 @@ __device__ __forceinline__ void cluster_pick(cg::cluster_group& cluster, int C, 
     ctrl->tot2[(pick_no + 1) & 1][tid] = 0u;
   }
   ++pick_no;
-  Picked pk;
-  pk.ok = false;
-  pk.t = -1;
-  pk.need2 = pk.cnt = pk.local_w = pk.local_c = 0;
-  pk.total = total;
-  pk.any_flag = 0u;
-  pk.tf = 0;
-  if (ssel >= 0) {
-    const uint32_t lo = tot2[2 * lane], hi = tot2[2 * lane + 1];
-    int tf = -1;
-    uint32_t above_f = 0, cnt_t = 0;
-    if (warp_pick64(lo, hi, need - sup_above, tf, above_f, cnt_t)) {
-      pk.ok = true;
-      pk.tf = tf;
-      pk.t = ssel * fine + tf;
-      pk.need2 = need - sup_above - above_f;
-      pk.cnt = cnt_t;
-      uint32_t lw = 0;
-      lw += (2 * lane > ssel) ? s[2 * lane] : 0u;
-      lw += (2 * lane + 1 > ssel) ? s[2 * lane + 1] : 0u;
-      lw += (2 * lane < fine && 2 * lane > tf) ? h[ssel * fine + 2 * lane] : 0u;
-      lw += (2 * lane + 1 < fine && 2 * lane + 1 > tf) ? h[ssel * fine + 2 * lane + 1] : 0u;
-      pk.local_w = warp_sum(lw);
-      pk.local_c = h[pk.t];
+  if (warp == 0) {
+    Picked pk;
+    pk.ok = false;
+    pk.t = -1;
+    pk.need2 = pk.cnt = pk.local_w = pk.local_c = 0;
+    pk.total = ctrl->run_total;
+    pk.any_flag = 0u;
+    pk.tf = 0;
+    if (ssel >= 0) {
+      const uint32_t lo = tot2[2 * lane], hi = tot2[2 * lane + 1];
+      const uint32_t need = ctrl->need, sup_above = ctrl->sup_above;
+      int tf = -1;
+      uint32_t above_f = 0, cnt_t = 0;
+      if (warp_pick64(lo, hi, need - sup_above, tf, above_f, cnt_t)) {
+        pk.ok = true;
+        pk.tf = tf;
+        pk.t = ssel * fine + tf;
+        pk.need2 = need - sup_above - above_f;
+        pk.cnt = cnt_t;
+        uint32_t lw = 0;
+        lw += (2 * lane > ssel) ? s[2 * lane] : 0u;
+        lw += (2 * lane + 1 > ssel) ? s[2 * lane + 1] : 0u;
+        lw += (2 * lane < fine && 2 * lane > tf) ? h[ssel * fine + 2 * lane] : 0u;
+        lw += (2 * lane + 1 < fine && 2 * lane + 1 > tf) ? h[ssel * fine + 2 * lane + 1] : 0u;
+        pk.local_w = warp_sum(lw);
+        pk.local_c = h[pk.t];
+      }
     }
+    post(pk);  // warp 0 only; what the other warps need goes through the control block
   }
-  post(pk);  // called by every warp with identical values
+  __syncthreads();
   FFTOPK_MARK(43);
 }
 
@@ -496,7 +520,6 @@ __device__ __forceinline__ int refine_from_data(RowCtx<NT>& cx, uint32_t& need, 
     cluster_pick<NT>(
         cluster, C, h, s, xch, ctrl, pick_no, nb, [&](uint32_t) { return need_now; },
         [&](Picked& pk) {
-          if (warp != 0) return;  // one warp allocates and publishes; the barrier below broadcasts
           const bool last = (shift == 0);
           decide_and_allocate<NT>(cx, pk, last ? kModeTies : kModeNext, false);
           if (pk.ok && last && pk.cnt > (uint32_t)cx.cand_cap && pk.cnt != pk.need2) {
@@ -714,6 +737,7 @@ __global__ void __launch_bounds__(NT, 1024 / NT) select2048_kernel(const SelectP
       ctrl->wslot = 0u;
       ctrl->cslot = 0u;
       ctrl->lcount = 0u;
+      ctrl->spill_kmax = 0u;
     }
   }
   // ---- sample (or, for a shard that fits in registers, the whole shard) ------------------------
@@ -754,12 +778,6 @@ __global__ void __launch_bounds__(NT, 1024 / NT) select2048_kernel(const SelectP
           if (g >= sh.i0 && g < sh.i1) xr[j] = __ldg(base4 + g);
         }
       }
-      // The filter pass cannot start before the sample has been histogrammed and searched
-      // (several microseconds); ask L2 for the shard now, one 128-byte line per request, so that
-      // HBM latency and bandwidth are spent while the memory system would otherwise idle.
-      for (int gl = sh.i0 + 8 * tid; gl < sh.i1; gl += 8 * NT) {
-        asm volatile("prefetch.global.L2 [%0];" ::"l"(base4 + gl));
-      }
     }
     // granules straddling the row's ends (at most two per row), after every bulk load is in flight
 #pragma unroll
@@ -786,6 +804,8 @@ __global__ void __launch_bounds__(NT, 1024 / NT) select2048_kernel(const SelectP
       }
     }
   }
+  // (Asking L2 for the shard here with prefetch.global.L2, to hide HBM latency behind the
+  // cluster-wide search, was measured: issuing the requests cost about as much as it saved.)
   __syncthreads();
   compute_sup<NT>(cx.hist(0), cx.sup(0), kMaxBins);
   FFTOPK_MARK(2);
@@ -806,10 +826,7 @@ __global__ void __launch_bounds__(NT, 1024 / NT) select2048_kernel(const SelectP
     // ---- the sample is the row: its histogram gives the threshold bin directly -----------------
     cluster_pick<NT>(
         cluster, C, cx.hist(0), cx.sup(0), cx.xch, ctrl, pick_no, kMaxBins, [&](uint32_t) { return (uint32_t)kK; },
-        [&](Picked& pk) {
-          if (warp == 0) decide_and_allocate<NT>(cx, pk, kModeFallback, false);
-        });
-    __syncthreads();  // slot bases allocated by warp 0
+        [&](Picked& pk) { decide_and_allocate<NT>(cx, pk, kModeFallback, false); });
     mode = ctrl->mode;
     FFTOPK_MARK(4);
     if (mode == kModeGather || mode == kModeTakeAll) {
@@ -859,10 +876,15 @@ __global__ void __launch_bounds__(NT, 1024 / NT) select2048_kernel(const SelectP
           // the sample says the guessed bin holds more than ~k row elements, a second sample round
           // on the next 12 key bits sharpens the guess.
           const float in_bin = (float)pk.cnt * flen / (float)(pk.total ? pk.total : 1u);
-          smode = !pk.ok ? kModeFallback : (in_bin > (float)kK ? kModeNext : kModeGather);
-          g1 = (uint32_t)pk.t;
-          rem = pk.need2;
+          if (lane == 0) {
+            ctrl->mode = !pk.ok ? kModeFallback : (in_bin > (float)kK ? kModeNext : kModeGather);
+            ctrl->t = pk.t;
+            ctrl->above = pk.need2;
+          }
         });
+    smode = ctrl->mode;
+    g1 = (uint32_t)ctrl->t;
+    rem = ctrl->above;
     FFTOPK_MARK(4);
     uint32_t gkey = g1 << 20;
     if (smode == kModeNext) {
@@ -888,9 +910,13 @@ __global__ void __launch_bounds__(NT, 1024 / NT) select2048_kernel(const SelectP
       cluster_pick<NT>(
           cluster, C, cx.hist(1), cx.sup(1), cx.xch, ctrl, pick_no, kMaxBins, [&](uint32_t) { return rem; },
           [&](Picked& pk) {
-            smode = pk.ok ? kModeGather : kModeFallback;
-            g2 = (uint32_t)pk.t;
+            if (lane == 0) {
+              ctrl->mode = pk.ok ? kModeGather : kModeFallback;
+              ctrl->t = pk.t;
+            }
           });
+      smode = ctrl->mode;
+      g2 = (uint32_t)ctrl->t;
       gkey |= g2 << 8;
       FFTOPK_MARK(11);
     }
@@ -943,7 +969,7 @@ __global__ void __launch_bounds__(NT, 1024 / NT) select2048_kernel(const SelectP
           const uint32_t v = __shfl_up_sync(kFull, incl, off);
           if (lane >= off) incl += v;
         }
-        const uint32_t cmax = __reduce_max_sync(kFull, lane < NW ? ctrl->wmax[lane] : 0u);
+        const uint32_t cmax = max(__reduce_max_sync(kFull, lane < NW ? ctrl->wmax[lane] : 0u), ctrl->spill_kmax);
         uint32_t base = 0;
         if (lane == 31) {
           const uint32_t spill_n = min(ctrl->lcount, spill_cap);
