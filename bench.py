@@ -52,7 +52,7 @@ N_ROTATE = 8
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one select2048 launch on this workload, from the
 # ncu capture summarised in profiles/ (None until a capture exists)
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 16754688  # profiles/select2048_ragged_b64.md
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 16754688  # profiles/select2048_ragged_b64.md (throughput plan)
 
 
 def measured_peak_gbs():
