@@ -632,8 +632,11 @@ __device__ __forceinline__ int refine_from_data(RowCtx<NT>& cx, uint32_t& need, 
   return mode;
 }
 
+#ifndef FFTOPK_CTAS_512
+#define FFTOPK_CTAS_512 2
+#endif
 template <int NT>
-__global__ void __launch_bounds__(NT, 1024 / NT) select2048_kernel(const SelectParams p) {
+__global__ void __launch_bounds__(NT, (NT == 512 ? FFTOPK_CTAS_512 : 1024 / NT)) select2048_kernel(const SelectParams p) {
   RowCtx<NT> cx;
   cg::cluster_group cluster = cg::this_cluster();
   const int C = cx.C = (int)cluster.num_blocks();
@@ -718,7 +721,10 @@ __global__ void __launch_bounds__(NT, 1024 / NT) select2048_kernel(const SelectP
   // Whole shard in registers (same answer in every CTA of the cluster: `per` is rank-independent).
   const bool exact = per <= NT * kRegSlabs;
   // sampled mode: slabs read per warp
-  const int ns = min(kRegSlabs, max(1, 2048 / (C * NT)));
+  #ifndef FFTOPK_SAMPLE_GRANULES
+#define FFTOPK_SAMPLE_GRANULES 2048
+#endif
+  const int ns = min(kRegSlabs, max(1, FFTOPK_SAMPLE_GRANULES / (C * NT)));
 
   // ---- prologue: clear the search totals, both histograms and the control block --------------
   if (tid < kSup) {

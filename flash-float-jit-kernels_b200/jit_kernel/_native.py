@@ -9,8 +9,11 @@ import functools
 import importlib.util
 from pathlib import Path
 
+import os
+
 _PKG_ROOT = Path(__file__).resolve().parent.parent
-LIB_PATH = _PKG_ROOT / "lib" / "libfftopk.so"
+#: the library next to the package, or another build of it named by FFTOPK_LIBRARY
+LIB_PATH = Path(os.environ["FFTOPK_LIBRARY"]) if os.environ.get("FFTOPK_LIBRARY") else _PKG_ROOT / "lib" / "libfftopk.so"
 
 K = 2048
 
@@ -63,7 +66,8 @@ def _build_if_needed() -> None:
 @functools.cache
 def lib() -> ctypes.CDLL:
     """Load (building first if the sources are newer) the native library."""
-    _build_if_needed()
+    if not os.environ.get("FFTOPK_LIBRARY"):
+        _build_if_needed()
     try:
         L = ctypes.CDLL(str(LIB_PATH))
     except OSError as e:  # pragma: no cover - depends on the machine
