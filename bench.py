@@ -239,6 +239,39 @@ def latency_sweep(dev, stream, fast_topk):
     return out
 
 
+def context_parallel_leg(dev, rank: int, world: int):
+    """Config 5: B=4, L=1M split evenly over the ranks; local select, exchange, merge. Two variants:
+    NCCL all-gather + merge kernel, and the fused gather-and-merge over IPC-mapped peer buffers.
+    Eager calls, CUDA events, max over ranks."""
+    import torch.distributed as dist
+
+    from jit_kernel.distributed import FusedContextParallelTopk, fast_topk_v3_context_parallel
+
+    score, lengths = workloads.c5()
+    Ls = score.size(1) // world
+    shard = score[:, rank * Ls:(rank + 1) * Ls].contiguous().to(dev)
+    fused = FusedContextParallelTopk(max_rows=score.size(0))
+    out = {"workload": f"B=4, L=1048576 over {world} GPUs, k=2048"}
+    reps = 50
+    for name, fn in (("nccl_allgather_merge", lambda: fast_topk_v3_context_parallel(shard, lengths, K)),
+                     ("fused_peer_merge", lambda: fused(shard, lengths))):
+        for _ in range(5):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        e1.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / reps * 1e3], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        out[name + "_us_per_call"] = float(t.item())
+    fused.close()
+    return out
+
+
 def ours_arm(args, rank: int, local_rank: int, world: int) -> None:
     import torch.distributed as dist
 
@@ -355,6 +388,14 @@ def ours_arm(args, rank: int, local_rank: int, world: int) -> None:
         e2e_sec = float(t.item())
     e2e_value = B * world * e2e_steps / e2e_sec
 
+    # ---- context-parallel decode (config 5) when there is more than one GPU -----------------------
+    cp = None
+    if world > 1 and not args.no_extras:
+        try:
+            cp = context_parallel_leg(dev, rank, world)
+        except Exception as e:  # an extra: never lose the headline over it
+            cp = {"error": repr(e)[:200]}
+
     status = kernel_status(dev)
     if rank != 0:
         if world > 1:
@@ -385,6 +426,8 @@ def ours_arm(args, rank: int, local_rank: int, world: int) -> None:
                      "frac_of_nominal_8TBs": achieved / 8000.0},
         "kernel_status": status,
     }
+    if cp is not None:
+        line["context_parallel"] = cp
     if not args.no_extras:
         line["latency"] = latency_sweep(dev, stream, fast_topk)
         line["p50_us_B1_L1M"] = line["latency"]["1048576"]["warm"]["p50_us"]
