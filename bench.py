@@ -253,8 +253,23 @@ def context_parallel_leg(dev, rank: int, world: int):
     fused = FusedContextParallelTopk(max_rows=score.size(0))
     out = {"workload": f"B=4, L=1048576 over {world} GPUs, k=2048"}
     reps = 50
+    # the fused path again as a replayed CUDA graph (its epochs live on the device): no Python
+    # between the kernels
+    from jit_kernel.distributed import local_lengths
+    lens_dev = local_lengths(lengths, Ls, rank).to(dev)
+    res = torch.empty(score.size(0), K, dtype=torch.int32, device=dev)
+    fused.run_into(shard, lens_dev, res)
+    torch.cuda.synchronize()
+    dist.barrier()
+    side = torch.cuda.Stream(device=dev)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            fused.run_into(shard, lens_dev, res)
+    dist.barrier()
     for name, fn in (("nccl_allgather_merge", lambda: fast_topk_v3_context_parallel(shard, lengths, K)),
-                     ("fused_peer_merge", lambda: fused(shard, lengths))):
+                     ("fused_peer_merge", lambda: fused(shard, lengths)),
+                     ("fused_peer_merge_graph", graph.replay)):
         for _ in range(5):
             fn()
         torch.cuda.synchronize()

@@ -23,6 +23,12 @@
 #include "fftopk_host.h"
 #include "fftopk_key.h"
 
+// defined in fftopk_select.cu (internal, not part of the public header)
+extern "C" int fftopk_select2048_into_comm(const float* score, int64_t row_stride, int32_t B, int64_t L,
+                                           const int32_t* lengths, int32_t* idx_plane0, uint32_t* key_plane0,
+                                           int32_t idx_offset, const uint32_t* flag, int64_t half_words,
+                                           uint32_t* status, void* cuda_stream);
+
 namespace fftopk {
 
 constexpr int kMaxShards = 8;
@@ -33,7 +39,9 @@ struct MergeSrc {
   const int32_t* idx[kMaxShards];
   const uint32_t* key[kMaxShards];
   const uint32_t* flag[kMaxShards];  // nullptr: no wait
-  uint32_t epoch;
+  uint32_t epoch;                    // epoch to wait for; 0 with own_flag set: read it from own_flag
+  const uint32_t* own_flag;          // this rank's published epoch (device-side epochs)
+  int64_t half_words;                // device-side epochs: idx/key point at half 0, add (e & 1) * half_words
   unsigned long long wait_ns;
 };
 
@@ -52,6 +60,7 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
 // Publishes "my candidates of this epoch are written": runs after the select kernel in stream
 // order, fences its writes system-wide and releases the flag.
 __global__ void publish_kernel(uint32_t* flag, uint32_t epoch) {
+  if (epoch == 0u) epoch = __ldcg(flag) + 1u;  // device-side epochs: the next one
   __threadfence_system();
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(epoch) : "memory");
 }
@@ -74,6 +83,10 @@ __global__ void __launch_bounds__(NT, 1) merge2048_kernel(const MergeSrc src, in
     ctrl->run_total = 0u;
     ctrl->pub_flag = 0u;
   }
+  // device-side epochs: this rank's own flag already holds the epoch of this call (its publish
+  // kernel ran earlier on the same stream)
+  const uint32_t epoch = (src.epoch == 0u && src.own_flag != nullptr) ? __ldcg(src.own_flag) : src.epoch;
+  const int64_t half_shift = src.own_flag != nullptr && src.epoch == 0u ? (int64_t)(epoch & 1u) * src.half_words : 0;
   __syncthreads();
   // Fused mode: thread g waits until shard g's owner has published this epoch. The wait is
   // bounded: when it runs out the row is filled with -1, a status bit is raised and the kernel
@@ -82,7 +95,7 @@ __global__ void __launch_bounds__(NT, 1) merge2048_kernel(const MergeSrc src, in
     const unsigned long long t0 = global_timer_ns();
     bool ok = false;
     for (;;) {
-      if ((int32_t)(ld_acquire_sys(src.flag[tid]) - src.epoch) >= 0) {
+      if ((int32_t)(ld_acquire_sys(src.flag[tid]) - epoch) >= 0) {
         ok = true;
         break;
       }
@@ -105,8 +118,8 @@ __global__ void __launch_bounds__(NT, 1) merge2048_kernel(const MergeSrc src, in
     const int g = i / kK, j = i % kK;
     const int64_t off = (int64_t)row * kK + j;
     // L2-coherent loads: the data may have been written by another GPU a moment ago
-    const int32_t idx = __ldcg(src.idx[g] + off);
-    const uint32_t key = __ldcg(src.key[g] + off);
+    const int32_t idx = __ldcg(src.idx[g] + half_shift + off);
+    const uint32_t key = __ldcg(src.key[g] + half_shift + off);
     const bool v = idx >= 0;
     cand[i] = v ? (((uint64_t)key << 32) | (uint64_t)(~(uint32_t)idx)) : 0ull;
     nvalid += v ? 1u : 0u;
@@ -296,23 +309,31 @@ int fftopk_select2048_cp(const float* score, int64_t row_stride, int32_t B, int6
                          int32_t idx_offset, void* comm, int32_t b_cap, uint32_t epoch, uint32_t* status,
                          void* cuda_stream) {
   if (!comm || b_cap < 1 || B < 0 || B > b_cap) return FFTOPK_EINVAL;
-  int32_t* base = static_cast<int32_t*>(comm) + (size_t)(epoch & 1u) * 2 * b_cap * kK;
+  uint32_t* flag = reinterpret_cast<uint32_t*>(static_cast<int32_t*>(comm) + (size_t)4 * b_cap * kK);
+  const int64_t half = (int64_t)2 * b_cap * kK;
   if (B > 0) {
-    int rc = fftopk_select2048(score, row_stride, B, L, lengths, nullptr, base,
-                               reinterpret_cast<uint32_t*>(base + (size_t)b_cap * kK), idx_offset, status,
-                               cuda_stream);
+    int rc;
+    if (epoch != 0u) {
+      int32_t* base = static_cast<int32_t*>(comm) + (size_t)(epoch & 1u) * half;
+      rc = fftopk_select2048(score, row_stride, B, L, lengths, nullptr, base,
+                             reinterpret_cast<uint32_t*>(base + (size_t)b_cap * kK), idx_offset, status, cuda_stream);
+    } else {  // device-side epoch: the kernel picks the half from the flag it finds
+      int32_t* base = static_cast<int32_t*>(comm);
+      rc = fftopk_select2048_into_comm(score, row_stride, B, L, lengths, base,
+                                       reinterpret_cast<uint32_t*>(base + (size_t)b_cap * kK), idx_offset, flag, half,
+                                       status, cuda_stream);
+    }
     if (rc) return rc;
   }
-  uint32_t* flag = reinterpret_cast<uint32_t*>(static_cast<int32_t*>(comm) + (size_t)4 * b_cap * kK);
   publish_kernel<<<1, 1, 0, static_cast<cudaStream_t>(cuda_stream)>>>(flag, epoch);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e);
   return FFTOPK_OK;
 }
 
-int fftopk_merge2048_cp(void* const* comms, int32_t G, int32_t B, int32_t b_cap, uint32_t epoch, int32_t wait_ms,
-                        int32_t* out_idx, uint32_t* out_key, uint32_t* status, void* cuda_stream) {
-  if (!comms || G < 1 || B < 0 || b_cap < 1 || B > b_cap || wait_ms < 0) return FFTOPK_EINVAL;
+int fftopk_merge2048_cp(void* const* comms, int32_t G, int32_t own, int32_t B, int32_t b_cap, uint32_t epoch,
+                        int32_t wait_ms, int32_t* out_idx, uint32_t* out_key, uint32_t* status, void* cuda_stream) {
+  if (!comms || G < 1 || B < 0 || b_cap < 1 || B > b_cap || wait_ms < 0 || own < 0 || own >= G) return FFTOPK_EINVAL;
   if (G > kMaxShards) return FFTOPK_ERANGE;
   if (B == 0) return FFTOPK_OK;
   if (!out_idx) return FFTOPK_EINVAL;
@@ -323,12 +344,14 @@ int fftopk_merge2048_cp(void* const* comms, int32_t G, int32_t B, int32_t b_cap,
   for (int g = 0; g < G; ++g) {
     if (!comms[g]) return FFTOPK_EINVAL;
     const int32_t* words = static_cast<const int32_t*>(comms[g]);
-    const int32_t* base = words + (size_t)(epoch & 1u) * 2 * b_cap * kK;
+    const int32_t* base = words + (epoch != 0u ? (size_t)(epoch & 1u) * 2 * b_cap * kK : 0);
     src.idx[g] = base;
     src.key[g] = reinterpret_cast<const uint32_t*>(base + (size_t)b_cap * kK);
     src.flag[g] = reinterpret_cast<const uint32_t*>(words + (size_t)4 * b_cap * kK);
   }
   src.epoch = epoch;
+  src.own_flag = src.flag[own];
+  src.half_words = (int64_t)2 * b_cap * kK;
   src.wait_ns = (unsigned long long)wait_ms * 1000000ull;
   merge2048_kernel<1024><<<dim3((unsigned)B), dim3(1024), merge_smem(G), static_cast<cudaStream_t>(cuda_stream)>>>(
       src, G, B, out_idx, out_key, status);

@@ -63,6 +63,11 @@ struct SelectParams {
   const int32_t* cu_seqlens_q;    // [prefill_bs + 1] or NULL (then table row = score row)
   int32_t prefill_bs;
   const int32_t* row_offsets;     // [B]: out = idx + row_offsets[row]
+  // context-parallel publication with a device-side epoch: when cp_flag is set, the output planes
+  // are shifted by ((*cp_flag + 1) & 1) * cp_half_words (the half of the comm buffer that the NEXT
+  // epoch writes), so that a captured CUDA graph can be replayed
+  const uint32_t* cp_flag;
+  int64_t cp_half_words;
 };
 
 enum Mode : int { kModeNext = 0, kModeGather = 1, kModeTakeAll = 2, kModeTies = 3, kModeAbort = 4, kModeFallback = 5 };
@@ -659,8 +664,9 @@ __global__ void __launch_bounds__(NT, (NT == 512 ? FFTOPK_CTAS_512 : 1024 / NT))
   len64 = len64 > p.L - row_start ? p.L - row_start : len64;
   const int len = (int)len64;
   const float* rowp = p.score + (int64_t)row * p.row_stride + row_start;
-  int32_t* out_idx = cx.out_idx = p.out_idx + (int64_t)row * kK;
-  uint32_t* out_key = cx.out_key = p.out_key ? p.out_key + (int64_t)row * kK : nullptr;
+  const int64_t cp_shift = p.cp_flag ? (int64_t)((__ldcg(p.cp_flag) + 1u) & 1u) * p.cp_half_words : 0;
+  int32_t* out_idx = cx.out_idx = p.out_idx + cp_shift + (int64_t)row * kK;
+  uint32_t* out_key = cx.out_key = p.out_key ? p.out_key + cp_shift + (int64_t)row * kK : nullptr;
   cx.idx_offset = p.idx_offset + (p.row_offsets ? __ldg(p.row_offsets + row) : 0);
   cx.page = nullptr;
   if (p.src_page_table) {
@@ -1269,7 +1275,8 @@ int fftopk_plan(int32_t B, int64_t L, int32_t plan[6]) {
 static int launch_select(const float* score, int64_t row_stride, int32_t B, int64_t L, const int32_t* lengths,
                          const int32_t* row_starts, int32_t* out_idx, uint32_t* out_key, int32_t idx_offset,
                          uint32_t* status, void* cuda_stream, const int32_t* src_page_table, int64_t src_stride,
-                         const int32_t* cu_seqlens_q, int32_t prefill_bs, const int32_t* row_offsets) {
+                         const int32_t* cu_seqlens_q, int32_t prefill_bs, const int32_t* row_offsets,
+                         const uint32_t* cp_flag = nullptr, int64_t cp_half_words = 0) {
   if (B < 0 || L < 0 || row_stride < 0) return FFTOPK_EINVAL;
   if (B == 0) return FFTOPK_OK;
   if (!score || !lengths || !out_idx) return FFTOPK_EINVAL;
@@ -1300,6 +1307,8 @@ static int launch_select(const float* score, int64_t row_stride, int32_t B, int6
   p.cu_seqlens_q = cu_seqlens_q;
   p.prefill_bs = prefill_bs;
   p.row_offsets = row_offsets;
+  p.cp_flag = cp_flag;
+  p.cp_half_words = cp_half_words;
   if ((size_t)pl.smem_bytes > (size_t)d->smem_optin) return FFTOPK_ERANGE;
 
   cudaLaunchConfig_t cfg = {};
@@ -1345,6 +1354,14 @@ int fftopk_select2048_page_table(const float* score, int64_t row_stride, int32_t
   if (B > 0 && (!src_page_table || src_stride < 0 || prefill_bs < 1 || prefill_bs > B)) return FFTOPK_EINVAL;
   return launch_select(score, row_stride, B, L, lengths, row_starts, dst_page_table, nullptr, 0, status, cuda_stream,
                        src_page_table, src_stride, cu_seqlens_q, prefill_bs, nullptr);
+}
+
+// internal: selection into the half of a comm buffer that the next device-side epoch owns
+int fftopk_select2048_into_comm(const float* score, int64_t row_stride, int32_t B, int64_t L, const int32_t* lengths,
+                                int32_t* idx_plane0, uint32_t* key_plane0, int32_t idx_offset, const uint32_t* flag,
+                                int64_t half_words, uint32_t* status, void* cuda_stream) {
+  return launch_select(score, row_stride, B, L, lengths, nullptr, idx_plane0, key_plane0, idx_offset, status,
+                       cuda_stream, nullptr, 0, nullptr, 0, nullptr, flag, half_words);
 }
 
 int fftopk_select2048_ragged(const float* score, int64_t row_stride, int32_t B, int64_t L, const int32_t* lengths,

@@ -108,8 +108,8 @@ def lib() -> ctypes.CDLL:
     L.fftopk_select2048_cp.argtypes = [c.c_void_p, c.c_int64, c.c_int32, c.c_int64, c.c_void_p, c.c_int32,
                                        c.c_void_p, c.c_int32, c.c_uint32, c.c_void_p, c.c_void_p]
     L.fftopk_merge2048_cp.restype = c.c_int
-    L.fftopk_merge2048_cp.argtypes = [c.POINTER(c.c_void_p), c.c_int32, c.c_int32, c.c_int32, c.c_uint32, c.c_int32,
-                                      c.c_void_p, c.c_void_p, c.c_void_p, c.c_void_p]
+    L.fftopk_merge2048_cp.argtypes = [c.POINTER(c.c_void_p), c.c_int32, c.c_int32, c.c_int32, c.c_int32, c.c_uint32,
+                                      c.c_int32, c.c_void_p, c.c_void_p, c.c_void_p, c.c_void_p]
     L.fftopk_topk2048_sliced_noalloc.restype = c.c_int
     L.fftopk_topk2048_sliced_noalloc.argtypes = [c.c_void_p, c.c_int64, c.c_int32, c.c_int64, c.c_void_p, c.c_int32,
                                                  c.c_void_p, c.c_void_p, c.c_void_p]

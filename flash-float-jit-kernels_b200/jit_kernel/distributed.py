@@ -143,18 +143,25 @@ class FusedContextParallelTopk:
             raise RuntimeError("score_shard must be a CUDA float32 tensor with unit inner stride")
         lens = local_lengths(lengths_global, Ls, self.rank).to(score_shard.device)
         out = torch.empty((B, TOPK), dtype=torch.int32, device=score_shard.device)
+        self.run_into(score_shard, lens, out)
+        return out
+
+    def run_into(self, score_shard: torch.Tensor, local_lens: torch.Tensor, out: torch.Tensor) -> None:
+        """The enqueue-only core (no allocation, no host-side state: the epoch lives on the device),
+        so this sequence can be captured in a CUDA graph and replayed - every rank the same number
+        of times. `local_lens` = local_lengths(lengths_global, Ls, rank) on the device."""
+        B, Ls = score_shard.shape
         self.epoch += 1
         lib = _native.lib()
         status = _status_word(score_shard.device).data_ptr()
         with torch.cuda.device(score_shard.device):
             stream = torch.cuda.current_stream().cuda_stream
-            rc = lib.fftopk_select2048_cp(score_shard.data_ptr(), score_shard.stride(0), B, Ls, lens.data_ptr(),
-                                          self.rank * Ls, self._own, self.b_cap, self.epoch, status, stream)
+            rc = lib.fftopk_select2048_cp(score_shard.data_ptr(), score_shard.stride(0), B, Ls, local_lens.data_ptr(),
+                                          self.rank * Ls, self._own, self.b_cap, 0, status, stream)
             _native.check(rc, "fftopk_select2048_cp")
-            rc = lib.fftopk_merge2048_cp(self._comms, self.world, B, self.b_cap, self.epoch, self.wait_ms,
+            rc = lib.fftopk_merge2048_cp(self._comms, self.world, self.rank, B, self.b_cap, 0, self.wait_ms,
                                          out.data_ptr(), None, status, stream)
             _native.check(rc, "fftopk_merge2048_cp")
-        return out
 
     def close(self) -> None:
         """Unmap the peers' buffers and free the own one (all ranks, after a barrier)."""

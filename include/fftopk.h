@@ -150,6 +150,11 @@ int fftopk_merge2048(const uint32_t* cand_key, const int32_t* cand_idx, int64_t 
  *
  *   comms        HOST array of G device pointers, shard order: comms[g] is rank g's comm buffer
  *                (the rank's own pointer for itself, fftopk_comm_open results for the peers)
+ *   own          this rank's position in comms
+ *   epoch        1, 2, 3, ... chosen by the host, or 0 in BOTH calls for device-side epochs: the
+ *                publish kernel then increments the buffer's own flag and the kernels derive the
+ *                epoch and the buffer half from it, so the select / publish / merge sequence has no
+ *                per-call host argument and a captured CUDA graph of it can be replayed
  */
 int fftopk_comm_bytes(int32_t b_cap, size_t* bytes);
 int fftopk_comm_create(int32_t b_cap, void** comm, unsigned char handle[64]);
@@ -159,9 +164,9 @@ int fftopk_comm_destroy(void* comm);
 int fftopk_select2048_cp(const float* score, int64_t row_stride, int32_t B, int64_t L,
                          const int32_t* lengths, int32_t idx_offset, void* comm, int32_t b_cap,
                          uint32_t epoch, uint32_t* status, void* cuda_stream);
-int fftopk_merge2048_cp(void* const* comms, int32_t G, int32_t B, int32_t b_cap, uint32_t epoch,
-                        int32_t wait_ms, int32_t* out_idx, uint32_t* out_key, uint32_t* status,
-                        void* cuda_stream);
+int fftopk_merge2048_cp(void* const* comms, int32_t G, int32_t own, int32_t B, int32_t b_cap,
+                        uint32_t epoch, int32_t wait_ms, int32_t* out_idx, uint32_t* out_key,
+                        uint32_t* status, void* cuda_stream);
 
 /*
  * Top-2048 by column slices, with no allocation anywhere. (This entry point has no counterpart in

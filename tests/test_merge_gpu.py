@@ -89,7 +89,7 @@ def _fused_on_one_device(score, lengths, G, epochs=(1,)):
             rc = lib.fftopk_select2048_cp(shards[g].data_ptr(), Ls, B, Ls, lens[g].data_ptr(), g * Ls, comms[g], B, e,
                                           status.data_ptr(), None)
             assert rc == 0
-        rc = lib.fftopk_merge2048_cp(arr, G, B, B, e, 1000, out.data_ptr(), None, status.data_ptr(), None)
+        rc = lib.fftopk_merge2048_cp(arr, G, 0, B, B, e, 1000, out.data_ptr(), None, status.data_ptr(), None)
         assert rc == 0
         torch.cuda.synchronize()
         results.append(out.cpu().numpy().copy())
@@ -118,7 +118,7 @@ def test_fused_merge_wait_runs_out_without_hanging():
     arr = (ctypes.c_void_p * 1)(comm)
     status = torch.zeros(1, dtype=torch.int32, device=dev)
     out = torch.zeros(2, K, dtype=torch.int32, device=dev)
-    rc = lib.fftopk_merge2048_cp(arr, 1, 2, 2, 5, 20, out.data_ptr(), None, status.data_ptr(), None)  # epoch 5 never published
+    rc = lib.fftopk_merge2048_cp(arr, 1, 0, 2, 2, 5, 20, out.data_ptr(), None, status.data_ptr(), None)  # epoch 5 never published
     assert rc == 0
     torch.cuda.synchronize()
     assert int(status.item()) & _native.ST_PEER_TIMEOUT
@@ -129,3 +129,46 @@ def test_fused_merge_wait_runs_out_without_hanging():
     got = fast_topk_v3(s.to(dev), ln.to(dev), K).cpu().numpy()
     orc.check_result(s.numpy(), ln.numpy(), got, what="after timeout")
     lib.fftopk_comm_destroy(comm)
+
+
+def test_fused_device_side_epochs_and_graph_replay():
+    """epoch = 0: the publish kernel counts epochs on the device, so the whole select / publish /
+    merge sequence has no per-call host argument and a captured graph can be replayed."""
+    import ctypes
+    from jit_kernel import _native
+    lib = _native.lib()
+    dev = torch.device("cuda", 0)
+    G = 4
+    score, lengths = workloads.c5(B=2, L=1 << 18)
+    B, L = score.shape
+    Ls = L // G
+    comms = [_comm_create(B) for _ in range(G)]
+    arr = (ctypes.c_void_p * G)(*comms)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    out = torch.empty(B, K, dtype=torch.int32, device=dev)
+    shards = [score[:, g * Ls:(g + 1) * Ls].contiguous().to(dev) for g in range(G)]
+    lens = [local_lengths(lengths, Ls, g).to(dev) for g in range(G)]
+
+    def sequence(stream_ptr):
+        for g in range(G):
+            assert lib.fftopk_select2048_cp(shards[g].data_ptr(), Ls, B, Ls, lens[g].data_ptr(), g * Ls, comms[g], B, 0,
+                                            status.data_ptr(), stream_ptr) == 0
+        assert lib.fftopk_merge2048_cp(arr, G, 0, B, B, 0, 1000, out.data_ptr(), None, status.data_ptr(), stream_ptr) == 0
+
+    for _ in range(2):  # eager: epochs 1 and 2 (both halves)
+        sequence(None)
+        torch.cuda.synchronize()
+        orc.check_result(score.numpy(), lengths.numpy(), out.cpu().numpy(), what="device epochs eager")
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            sequence(side.cuda_stream)
+    for _ in range(3):  # epochs 3, 4, 5
+        out.fill_(-7)
+        graph.replay()
+        torch.cuda.synchronize()
+        orc.check_result(score.numpy(), lengths.numpy(), out.cpu().numpy(), what="device epochs replay")
+    assert int(status.item()) == 0
+    for c in comms:
+        lib.fftopk_comm_destroy(c)

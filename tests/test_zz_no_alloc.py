@@ -46,7 +46,7 @@ def _with_allocated_scratch(lib, dev, score, lengths, G):
         keep += [shard, lens]
         _native.check(lib.fftopk_select2048_cp(shard.data_ptr(), Ls, B, Ls, lens.data_ptr(), g * Ls, comms[g], B, 1,
                                                None, None), "fftopk_select2048_cp")
-    _native.check(lib.fftopk_merge2048_cp(arr, G, B, B, 1, 1000, out.data_ptr(), None, None, None),
+    _native.check(lib.fftopk_merge2048_cp(arr, G, 0, B, B, 1, 1000, out.data_ptr(), None, None, None),
                   "fftopk_merge2048_cp")
     torch.cuda.synchronize()
     for c in comms:
