@@ -493,7 +493,7 @@ __device__ __forceinline__ int refine_from_data(RowCtx<NT>& cx, uint32_t& need, 
     if (tid == 0) {
       ctrl->pub_flag = 0u;
       ctrl->win_count = 0u;   // rank 0's copies are the cluster-wide counters; nobody touches
-      ctrl->cand_count = 0u;  // them again before the cluster barrier of round 0
+      ctrl->cand_count = 0u;  // them again before the cluster barrier of the first histogram pass
       ctrl->over_flag = 0u;
       ctrl->max_key = 0u;
     }
