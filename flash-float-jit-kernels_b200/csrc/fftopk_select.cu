@@ -206,6 +206,7 @@ __device__ __forceinline__ uint32_t filter_shard(const Shard& sh, float edge, ui
   // dense conversion of the thread's own entries
   kmax = 0u;
   const uint32_t own = min(cnt, lp);
+#pragma unroll 4
   for (uint32_t j = 0; j < own; ++j) mine[j] = raw_to_composite(mine[j], kmax);
   return cnt;
 }
@@ -953,6 +954,7 @@ __global__ void __launch_bounds__(NT, (NT == 512 ? FFTOPK_CTAS_512 : 1024 / NT))
       const uint32_t mycnt = min(cnt_all, lp);
       if (C == 1) {
         // single CTA: the finish reads the list where it lies; unused slots become "empty" (0)
+#pragma unroll 4
         for (uint32_t j = mycnt; j < lp; ++j) mine_l[j] = 0ull;
       }
       // hand the candidates to rank 0: one remote atomic per CTA allocates the range
