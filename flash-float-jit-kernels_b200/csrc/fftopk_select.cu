@@ -279,6 +279,15 @@ __device__ __forceinline__ void compute_sup(const uint32_t* hist, uint32_t* sup,
   }
 }
 
+// Cluster barrier; for a cluster of one CTA a block barrier does the same job for less.
+__device__ __forceinline__ void cluster_sync(cg::cluster_group& cluster, int C) {
+  if (C == 1) {
+    __syncthreads();
+  } else {
+    cluster.sync();
+  }
+}
+
 // What warp 0 knows after a cluster-wide threshold search.
 struct Picked {
   bool ok;            // false: the histogram holds fewer than `need` elements
@@ -315,7 +324,7 @@ __device__ __forceinline__ void cluster_pick(cg::cluster_group& cluster, int C, 
   // the cluster barrier instead - remote reductions behind a split arrive / wait barrier - was
   // measured and was not faster: the release of the extra arrive costs what the remote loads cost.)
   for (int i = tid; i < C * kSup; i += NT) {
-    const uint32_t* rs = cluster.map_shared_rank(s, i / kSup);
+    const uint32_t* rs = C == 1 ? s : cluster.map_shared_rank(s, i / kSup);
     red_shared_add(&tot[i % kSup], rs[i % kSup]);
   }
   __syncthreads();
@@ -347,7 +356,7 @@ __device__ __forceinline__ void cluster_pick(cg::cluster_group& cluster, int C, 
       const int q = i / kSup, f = i % kSup;
       uint32_t v = 0;
       if (f < fine) {
-        const uint32_t* rh = cluster.map_shared_rank(h, q);
+        const uint32_t* rh = C == 1 ? h : cluster.map_shared_rank(h, q);
         v = rh[ssel * fine + f];
         red_shared_add(&tot2[f], v);
       }
@@ -487,7 +496,7 @@ __device__ __forceinline__ int refine_from_data(RowCtx<NT>& cx, uint32_t& need, 
   uint32_t* xch = cx.xch;
 
   // peers may still be reading this CTA's histograms from the attempt that fell back
-  cluster.sync();
+  cluster_sync(cluster, C);
   {
     uint4* h4 = reinterpret_cast<uint4*>(cx.hist(0));
     for (int i = tid; i < kMaxBins / 4; i += NT) h4[i] = make_uint4(0u, 0u, 0u, 0u);
@@ -521,7 +530,7 @@ __device__ __forceinline__ int refine_from_data(RowCtx<NT>& cx, uint32_t& need, 
     uint32_t* h = cx.hist(r & 1);
     uint32_t* s = cx.sup(r & 1);
     compute_sup<NT>(h, s, nb);
-    cluster.sync();  // every CTA's histogram and super-bin sums of this round are complete
+    cluster_sync(cluster, C);  // every CTA's histogram and super-bin sums of this round are complete
     const uint32_t need_now = need;
     cluster_pick<NT>(
         cluster, C, h, s, xch, ctrl, pick_no, nb, [&](uint32_t) { return need_now; },
@@ -709,8 +718,8 @@ __global__ void __launch_bounds__(NT, (NT == 512 ? FFTOPK_CTAS_512 : 1024 / NT))
   cx.list = reinterpret_cast<uint64_t*>(reinterpret_cast<unsigned char*>(ctrl) + ((sizeof(Ctrl) + 127) & ~127u));
   // a cluster of one CTA has nobody to gather from: its candidate buffer IS the list
   cx.cand = C == 1 ? cx.list : cx.list + p.list_cap;
-  cx.ctrl0 = cluster.map_shared_rank(ctrl, 0);
-  cx.cand0 = cluster.map_shared_rank(cx.cand, 0);
+  cx.ctrl0 = C == 1 ? ctrl : cluster.map_shared_rank(ctrl, 0);
+  cx.cand0 = C == 1 ? cx.cand : cluster.map_shared_rank(cx.cand, 0);
   uint64_t* list = cx.list;
 
   // ---- shard geometry --------------------------------------------------------------------
@@ -822,7 +831,7 @@ __global__ void __launch_bounds__(NT, (NT == 512 ? FFTOPK_CTAS_512 : 1024 / NT))
   __syncthreads();
   compute_sup<NT>(cx.hist(0), cx.sup(0), kMaxBins);
   FFTOPK_MARK(2);
-  cluster.sync();  // #1: sample histograms complete
+  cluster_sync(cluster, C);  // #1: sample histograms complete
   FFTOPK_MARK(3);
 
   uint32_t need = kK;
@@ -918,7 +927,7 @@ __global__ void __launch_bounds__(NT, (NT == 512 ? FFTOPK_CTAS_512 : 1024 / NT))
       }
       __syncthreads();
       compute_sup<NT>(cx.hist(1), cx.sup(1), kMaxBins);
-      cluster.sync();  // #1b
+      cluster_sync(cluster, C);  // #1b
       uint32_t g2 = 0;
       cluster_pick<NT>(
           cluster, C, cx.hist(1), cx.sup(1), cx.xch, ctrl, pick_no, kMaxBins, [&](uint32_t) { return rem; },
@@ -1009,7 +1018,7 @@ __global__ void __launch_bounds__(NT, (NT == 512 ? FFTOPK_CTAS_512 : 1024 / NT))
         }
       }
       FFTOPK_MARK(46);
-      cluster.sync();  // #2: every candidate has landed in rank 0
+      cluster_sync(cluster, C);  // #2: every candidate has landed in rank 0
       FFTOPK_MARK(9);
       {
         // every thread reads rank 0's totals itself (no broadcast barrier; for rank 0, whose finish
@@ -1047,7 +1056,7 @@ __global__ void __launch_bounds__(NT, (NT == 512 ? FFTOPK_CTAS_512 : 1024 / NT))
   // path pushes right up to here, so the barrier comes first.
   const bool finish_first = (r < 0);  // uniform over the cluster
   FFTOPK_MARK(5);
-  if (!finish_first) cluster.sync();
+  if (!finish_first) cluster_sync(cluster, C);
   FFTOPK_MARK(6);
   if (mode == kModeGather && rank == 0) {
     // sampled path of a lone CTA: the whole list region, empty slots included
@@ -1060,7 +1069,7 @@ __global__ void __launch_bounds__(NT, (NT == 512 ? FFTOPK_CTAS_512 : 1024 / NT))
     cta_finish<NT>(cx.cand, n, need, hi, pfx, idx_bits, cx.hist(0), ctrl, out_idx, out_key,
                    (uint32_t)kK - need, cx.idx_offset, p.status, cx.page);
   }
-  if (finish_first) cluster.sync();
+  if (finish_first) cluster_sync(cluster, C);
   FFTOPK_MARK(7);
   if (tid == 0 && p.status && mode == kModeAbort) atomicOr(p.status, (uint32_t)FFTOPK_ST_INTERNAL);
 }
