@@ -459,6 +459,36 @@ def ours_arm(args, rank: int, local_rank: int, world: int) -> None:
         dist.destroy_process_group()
 
 
+def profile_case(name: str) -> None:
+    """Small fixed cases for profiler captures (`--case`): a few launches, one JSON line.
+    b1: B=1, L=1M decode call, eight rotated 4 MiB inputs. merge: the 8-shard candidate merge of a
+    B=4 batch (shards selected one after the other on this device)."""
+    from jit_kernel.distributed import _cuda_select, local_lengths, merge_candidates
+    from jit_kernel.topk_indexer import fast_topk
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    if name == "b1":
+        score, lengths = workloads.c2(L=1 << 20)
+        bufs = [torch.roll(score, i, 1).contiguous().to(dev) for i in range(40)]  # 160 MiB > L2
+        ld = lengths.to(dev)
+        out = torch.empty(1, K, dtype=torch.int32, device=dev)
+        for i in range(43):
+            fast_topk(bufs[i % 40], out, ld)
+        torch.cuda.synchronize()
+        print(json.dumps({"case": "b1", "launches": 43, "plan": __import__("jit_kernel._native", fromlist=["x"]).plan(1, 1 << 20)}))
+    else:
+        score, lengths = workloads.c5()
+        G, Ls = 8, score.size(1) // 8
+        parts = [_cuda_select(score[:, g * Ls:(g + 1) * Ls].contiguous().to(dev), local_lengths(lengths, Ls, g).to(dev), g * Ls)
+                 for g in range(G)]
+        cand = torch.stack(parts).contiguous()
+        for _ in range(6):
+            merge_candidates(cand)
+        torch.cuda.synchronize()
+        print(json.dumps({"case": "merge", "launches": 6}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -466,7 +496,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=50)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip the latency sweep and the CPU baseline")
+    ap.add_argument("--case", default=None, choices=["b1", "merge"], help="run one small fixed case (for profilers)")
     args = ap.parse_args()
+    if args.case:
+        profile_case(args.case)
+        return
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
