@@ -132,6 +132,9 @@ struct Ctrl {
   // by search number (each search clears the buffers of the next one)
   uint32_t tot[2][kSup];
   uint32_t tot2[2][kSup];
+  uint32_t totb[kSup];  // first sample round: super-bin totals of the second (finer) histogram
+  uint32_t dual_b;      // ... whether the finer histogram was usable, and for which top nibble
+  uint32_t dual_g;
   uint32_t wtot[32];
   uint32_t wmax[32];
   uint64_t small[kSmall];

@@ -405,13 +405,115 @@ __device__ __forceinline__ void cluster_pick(cg::cluster_group& cluster, int C, 
   FFTOPK_MARK(43);
 }
 
+// First search of the sampled path, over TWO sample histograms built in the same pass:
+//   A: key bits [31:20]   (4096 bins, valid for any data, 8 bins per octave of magnitude)
+//   B: key bits [27:16]   (4096 bins, 128 per octave) - meaningful only among keys that share the
+//      top four bits (sign and the three high exponent bits)
+// If every sampled key shares those four bits - one super-bin group of A holds the whole sample,
+// which is the normal case for indexer logits (one sign, magnitudes within a factor of 2^32) - the
+// pick is made on B and yields a 16-bit key prefix, fine enough that no second sample round is
+// needed; otherwise on A (12 bits). Same two barriers and two rounds of remote reads as one search.
+struct DualPick {
+  bool ok;
+  uint32_t prefix;  // the guessed key prefix ...
+  int pbits;        // ... and its length in bits (12 or 16)
+  uint32_t need2;   // sample rank still to go inside the guessed bin
+  uint32_t cnt;     // sample elements in the guessed bin
+  uint32_t total;   // sample size (cluster-wide)
+};
+
+template <int NT, class NeedFn>
+__device__ __forceinline__ DualPick cluster_pick_dual(cg::cluster_group& cluster, int C, const uint32_t* ha,
+                                                      const uint32_t* sa, const uint32_t* hb, const uint32_t* sb,
+                                                      Ctrl* ctrl, int& pick_no, NeedFn&& need_of) {
+  const int tid = threadIdx.x;
+  const int lane = tid & 31, warp = tid >> 5;
+  constexpr int fine = kMaxBins / kSup;
+  uint32_t* tot = ctrl->tot[pick_no & 1];
+  uint32_t* tot2 = ctrl->tot2[pick_no & 1];
+  for (int i = tid; i < C * kSup; i += NT) {
+    const int q = i / kSup, b = i % kSup;
+    const uint32_t* ra = C == 1 ? sa : cluster.map_shared_rank(sa, q);
+    const uint32_t* rb = C == 1 ? sb : cluster.map_shared_rank(sb, q);
+    red_shared_add(&tot[b], ra[b]);
+    red_shared_add(&ctrl->totb[b], rb[b]);
+  }
+  __syncthreads();
+  FFTOPK_MARK(40);
+  if (warp == 0) {
+    const uint32_t lo = tot[2 * lane], hi = tot[2 * lane + 1];
+    const uint32_t total = warp_sum(lo + hi);
+    const uint32_t need = need_of(total);
+    // four super-bins = 256 bins of A = one value of the top four key bits
+    const uint32_t pair = lo + hi;
+    const uint32_t grp = pair + __shfl_xor_sync(kFull, pair, 1);
+    const unsigned one = __ballot_sync(kFull, total > 0u && grp == total);
+    const bool use_b = one != 0u;
+    const uint32_t lob = ctrl->totb[2 * lane], hib = ctrl->totb[2 * lane + 1];
+    uint32_t above = 0, cnt = 0;
+    int ts = -1;
+    const bool ok = need > 0 && (use_b ? warp_pick64(lob, hib, need, ts, above, cnt) : warp_pick64(lo, hi, need, ts, above, cnt));
+    if (lane == 0) {
+      ctrl->sup_sel = ok ? ts : -1;
+      ctrl->sup_above = above;
+      ctrl->need = need;
+      ctrl->run_total = total;
+      ctrl->dual_b = use_b ? 1u : 0u;
+      ctrl->dual_g = use_b ? (uint32_t)((__ffs(one) - 1) >> 1) : 0u;
+    }
+  }
+  __syncthreads();
+  FFTOPK_MARK(41);
+  const int ssel = ctrl->sup_sel;
+  const bool use_b = ctrl->dual_b != 0u;
+  if (ssel >= 0) {
+    const uint32_t* h = use_b ? hb : ha;
+    for (int i = tid; i < C * kSup; i += NT) {
+      const int q = i / kSup, f = i % kSup;
+      const uint32_t* rh = C == 1 ? h : cluster.map_shared_rank(h, q);
+      red_shared_add(&tot2[f], rh[ssel * fine + f]);
+    }
+  }
+  __syncthreads();
+  FFTOPK_MARK(42);
+  if (tid < kSup) {
+    ctrl->tot[(pick_no + 1) & 1][tid] = 0u;
+    ctrl->tot2[(pick_no + 1) & 1][tid] = 0u;
+  }
+  ++pick_no;
+  if (warp == 0) {
+    int tf = -1;
+    uint32_t above_f = 0, cnt_t = 0;
+    bool ok = false;
+    if (ssel >= 0) {
+      const uint32_t lo = tot2[2 * lane], hi = tot2[2 * lane + 1];
+      ok = warp_pick64(lo, hi, ctrl->need - ctrl->sup_above, tf, above_f, cnt_t);
+    }
+    if (lane == 0) {
+      ctrl->t = ok ? ssel * fine + tf : -1;
+      ctrl->above = ok ? ctrl->need - ctrl->sup_above - above_f : 0u;
+      ctrl->cnt = cnt_t;
+    }
+  }
+  __syncthreads();
+  FFTOPK_MARK(43);
+  DualPick d;
+  d.ok = ctrl->t >= 0;
+  d.pbits = use_b ? 16 : 12;
+  d.prefix = use_b ? ((ctrl->dual_g << 12) | (uint32_t)ctrl->t) : (uint32_t)ctrl->t;
+  d.need2 = ctrl->above;
+  d.cnt = ctrl->cnt;
+  d.total = ctrl->run_total;
+  return d;
+}
+
 // Everything one CTA needs to know about its row and its shared memory.
 template <int NT>
 struct RowCtx {
   int C, rank;
   Shard sh;
   uint32_t* hist0;  // two histograms of kMaxBins words, back to back
-  uint32_t* sup0;   // two super-bin arrays of kSup words, back to back
+  uint32_t* sup0;   // three super-bin arrays of kSup words, back to back
   // (computed addresses instead of pointer arrays: indexing an array member with the round number
   // would force the whole struct into local memory)
   __device__ __forceinline__ uint32_t* hist(int i) const { return hist0 + i * kMaxBins; }
@@ -713,7 +815,7 @@ __global__ void __launch_bounds__(NT, (NT == 512 ? FFTOPK_CTAS_512 : 1024 / NT))
   extern __shared__ __align__(128) unsigned char smem_raw[];
   cx.hist0 = reinterpret_cast<uint32_t*>(smem_raw);
   cx.sup0 = cx.hist0 + 2 * kMaxBins;
-  cx.xch = cx.sup0 + 2 * kSup;                                             // kMaxCluster * 64 words
+  cx.xch = cx.sup0 + 3 * kSup;                                             // kMaxCluster * 64 words
   Ctrl* ctrl = cx.ctrl = reinterpret_cast<Ctrl*>(cx.xch + kMaxCluster * kSup);  // 8-byte aligned
   cx.list = reinterpret_cast<uint64_t*>(reinterpret_cast<unsigned char*>(ctrl) + ((sizeof(Ctrl) + 127) & ~127u));
   // a cluster of one CTA has nobody to gather from: its candidate buffer IS the list
@@ -746,6 +848,7 @@ __global__ void __launch_bounds__(NT, (NT == 512 ? FFTOPK_CTAS_512 : 1024 / NT))
   if (tid < kSup) {
     ctrl->tot[0][tid] = 0u;  // (the buffers with index 1 are cleared by the first search)
     ctrl->tot2[0][tid] = 0u;
+    ctrl->totb[tid] = 0u;
   }
   {
     uint4* h4 = reinterpret_cast<uint4*>(cx.hist(0));
@@ -820,8 +923,10 @@ __global__ void __launch_bounds__(NT, (NT == 512 ? FFTOPK_CTAS_512 : 1024 / NT))
         const float xv[4] = {xr[j].x, xr[j].y, xr[j].z, xr[j].w};
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          hist_add(h0, fftopk_key_from_bits(__float_as_uint(xv[e])) >> 20,
-                   in && (unsigned)(i0 + e) < (unsigned)len);
+          const uint32_t key = fftopk_key_from_bits(__float_as_uint(xv[e]));
+          const bool ok = in && (unsigned)(i0 + e) < (unsigned)len;
+          hist_add(h0, key >> 20, ok);
+          if (!exact) hist_add(h0 + kMaxBins, (key >> 16) & 0xfffu, ok);  // histogram B (see cluster_pick_dual)
         }
       }
     }
@@ -830,6 +935,7 @@ __global__ void __launch_bounds__(NT, (NT == 512 ? FFTOPK_CTAS_512 : 1024 / NT))
   // cluster-wide search, was measured: issuing the requests cost about as much as it saved.)
   __syncthreads();
   compute_sup<NT>(cx.hist(0), cx.sup(0), kMaxBins);
+  if (!exact) compute_sup<NT>(cx.hist(1), cx.sup(1), kMaxBins);
   FFTOPK_MARK(2);
   cluster_sync(cluster, C);  // #1: sample histograms complete
   FFTOPK_MARK(3);
@@ -884,53 +990,48 @@ __global__ void __launch_bounds__(NT, (NT == 512 ? FFTOPK_CTAS_512 : 1024 / NT))
     // need_of: sample rank whose true rank is >= k with overwhelming probability
     // (m expected sample elements among the true top k, plus five standard deviations).
     const float flen = (float)len;
-    int smode = kModeFallback;
-    uint32_t g1 = 0, rem = 0;
-    cluster_pick<NT>(
-        cluster, C, cx.hist(0), cx.sup(0), cx.xch, ctrl, pick_no, kMaxBins,
-        [&](uint32_t n_s) {
-          const float m = (float)kK * (float)n_s / flen;
-          const uint32_t rk = (uint32_t)(m + 5.0f * sqrtf(m) + 14.0f);
-          return rk < n_s ? rk : n_s;
-        },
-        [&](Picked& pk) {
-          // A 12-bit bin is coarse where values crowd into few exponents (8 bins per octave): if
-          // the sample says the guessed bin holds more than ~k row elements, a second sample round
-          // on the next 12 key bits sharpens the guess.
-          const float in_bin = (float)pk.cnt * flen / (float)(pk.total ? pk.total : 1u);
-          if (lane == 0) {
-            ctrl->mode = !pk.ok ? kModeFallback : (in_bin > (float)kK ? kModeNext : kModeGather);
-            ctrl->t = pk.t;
-            ctrl->above = pk.need2;
-          }
-        });
-    smode = ctrl->mode;
-    g1 = (uint32_t)ctrl->t;
-    rem = ctrl->above;
+    const DualPick dp = cluster_pick_dual<NT>(cluster, C, cx.hist(0), cx.sup(0), cx.hist(1), cx.sup(1), ctrl, pick_no,
+                                              [&](uint32_t n_s) {
+                                                const float m = (float)kK * (float)n_s / flen;
+                                                const uint32_t rk = (uint32_t)(m + 5.0f * sqrtf(m) + 14.0f);
+                                                return rk < n_s ? rk : n_s;
+                                              });
     FFTOPK_MARK(4);
-    uint32_t gkey = g1 << 20;
+    // If the sample says the guessed bin alone holds more than ~k row elements (values crowded
+    // into a sliver of the key space), a second sample round on the next 12 key bits sharpens it.
+    const float in_bin = (float)dp.cnt * flen / (float)(dp.total ? dp.total : 1u);
+    int smode = !dp.ok ? kModeFallback : (in_bin > (float)kK ? kModeNext : kModeGather);
+    uint32_t gkey = dp.prefix << (32 - dp.pbits);
     if (smode == kModeNext) {
+      const int sb = 32 - dp.pbits - 12;  // position of the next 12 bits
+      const uint32_t rem = dp.need2;
+      // Peers may still be reading, from this CTA, the histogram the guess was made on and both
+      // super-bin arrays; the other histogram buffer and the third super-bin array are free.
+      uint32_t* h1 = cx.hist(dp.pbits == 16 ? 0 : 1);
+      uint32_t* s1 = cx.sup(2);
       {
-        uint32_t* h1 = cx.hist(1);
+        uint4* h4 = reinterpret_cast<uint4*>(h1);
+        for (int i = tid; i < kMaxBins / 4; i += NT) h4[i] = make_uint4(0u, 0u, 0u, 0u);
+      }
+      __syncthreads();
 #pragma unroll
-        for (int j = 0; j < kRegSlabs; ++j) {
-          if (j < ns && gr[j] < sh.g1) {
-            const int e0 = 4 * gr[j] - sh.a;
-            const float xv[4] = {xr[j].x, xr[j].y, xr[j].z, xr[j].w};
+      for (int j = 0; j < kRegSlabs; ++j) {
+        if (j < ns && gr[j] < sh.g1) {
+          const int e0 = 4 * gr[j] - sh.a;
+          const float xv[4] = {xr[j].x, xr[j].y, xr[j].z, xr[j].w};
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const uint32_t key = fftopk_key_from_bits(__float_as_uint(xv[e]));
-              hist_add(h1, (key >> 8) & 0xfffu, (unsigned)(e0 + e) < (unsigned)len && (key >> 20) == g1);
-            }
+          for (int e = 0; e < 4; ++e) {
+            const uint32_t key = fftopk_key_from_bits(__float_as_uint(xv[e]));
+            hist_add(h1, (key >> sb) & 0xfffu,
+                     (unsigned)(e0 + e) < (unsigned)len && (key >> (32 - dp.pbits)) == dp.prefix);
           }
         }
       }
       __syncthreads();
-      compute_sup<NT>(cx.hist(1), cx.sup(1), kMaxBins);
+      compute_sup<NT>(h1, s1, kMaxBins);
       cluster_sync(cluster, C);  // #1b
-      uint32_t g2 = 0;
       cluster_pick<NT>(
-          cluster, C, cx.hist(1), cx.sup(1), cx.xch, ctrl, pick_no, kMaxBins, [&](uint32_t) { return rem; },
+          cluster, C, h1, s1, cx.xch, ctrl, pick_no, kMaxBins, [&](uint32_t) { return rem; },
           [&](Picked& pk) {
             if (lane == 0) {
               ctrl->mode = pk.ok ? kModeGather : kModeFallback;
@@ -938,8 +1039,7 @@ __global__ void __launch_bounds__(NT, (NT == 512 ? FFTOPK_CTAS_512 : 1024 / NT))
             }
           });
       smode = ctrl->mode;
-      g2 = (uint32_t)ctrl->t;
-      gkey |= g2 << 8;
+      gkey |= (uint32_t)ctrl->t << sb;
       FFTOPK_MARK(11);
     }
     if (smode == kModeGather) {
@@ -1099,7 +1199,7 @@ struct DeviceInfo {
 DeviceInfo g_dev[64];
 
 constexpr size_t fixed_smem_bytes() {
-  return (size_t)(2 * kMaxBins + 2 * kSup + kMaxCluster * kSup) * 4 + ((sizeof(Ctrl) + 127) & ~(size_t)127);
+  return (size_t)(2 * kMaxBins + 3 * kSup + kMaxCluster * kSup) * 4 + ((sizeof(Ctrl) + 127) & ~(size_t)127);
 }
 
 constexpr int kLatencyListCap = 6144, kLatencyCandCap = 16384;  // one CTA per SM: use the shared memory
