@@ -2,6 +2,7 @@
 // threshold bin, the histogram update, and the single-CTA "finish" that resolves a small
 // candidate list held in shared memory.
 #pragma once
+#include <type_traits>
 #include <cooperative_groups.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -140,36 +141,93 @@ struct Ctrl {
   uint64_t small[kSmall];
 };
 
-// Visit cand[tid], cand[tid + NT], ... with four independent shared-memory loads in flight per
-// thread (a plain loop waits out the full load latency once per element: measured 190 cycles
-// per element with 16 warps on the SM).
-template <int NT, class F>
-__device__ __forceinline__ void for_each_cand(const uint64_t* cand, int n, F&& f) {
-  int i = threadIdx.x;
-  for (; i + 3 * NT < n; i += 4 * NT) {
-    const uint64_t c0 = cand[i], c1 = cand[i + NT], c2 = cand[i + 2 * NT], c3 = cand[i + 3 * NT];
-    f(c0);
-    f(c1);
-    f(c2);
-    f(c3);
-  }
-  for (; i < n; i += NT) f(cand[i]);
-}
+// ---------------------------------------------------------------------------------------------
+// Candidate sources of the finish. A source tells a thread which candidates are its share:
+//   for_each_key(f)     f(key) for every slot of the share (any order, any trip count)
+//   for_each_uniform(f) f(composite) with the same trip count in all lanes of a warp (f may vote);
+//                       lanes without a candidate get 0, which is also what an empty slot holds
+// Loads are issued four at a time (a plain loop waits out the full shared-memory latency once per
+// element: measured 190 cycles per element with 16 warps on the SM).
+// ---------------------------------------------------------------------------------------------
 
-// The same over the high words (the keys) of the composites only.
-template <int NT, class F>
-__device__ __forceinline__ void for_each_key(const uint64_t* cand, int n, F&& f) {
-  const uint32_t* hi32 = reinterpret_cast<const uint32_t*>(cand) + 1;  // little endian: word 1 = key
-  int i = threadIdx.x;
-  for (; i + 3 * NT < n; i += 4 * NT) {
-    const uint32_t k0 = hi32[2 * i], k1 = hi32[2 * (i + NT)], k2 = hi32[2 * (i + 2 * NT)], k3 = hi32[2 * (i + 3 * NT)];
-    f(k0);
-    f(k1);
-    f(k2);
-    f(k3);
+// One dense array cand[0..n); slots equal to 0 are empty.
+template <int NT>
+struct DenseCands {
+  static constexpr bool kEmpties = true;
+  const uint64_t* cand;
+  int n;
+  template <class F>
+  __device__ __forceinline__ void for_each_key(F&& f) const {
+    const uint32_t* hi32 = reinterpret_cast<const uint32_t*>(cand) + 1;  // little endian: word 1 = key
+    int i = threadIdx.x;
+    for (; i + 3 * NT < n; i += 4 * NT) {
+      const uint32_t k0 = hi32[2 * i], k1 = hi32[2 * (i + NT)], k2 = hi32[2 * (i + 2 * NT)], k3 = hi32[2 * (i + 3 * NT)];
+      f(k0);
+      f(k1);
+      f(k2);
+      f(k3);
+    }
+    for (; i < n; i += NT) f(hi32[2 * i]);
   }
-  for (; i < n; i += NT) f(hi32[2 * i]);
-}
+  template <class F>
+  __device__ __forceinline__ void for_each_uniform(F&& f) const {
+    const int tid = threadIdx.x;
+    int i0 = 0;
+    for (; i0 + 3 * NT < n; i0 += 4 * NT) {
+      const int i = i0 + tid;
+      const uint64_t c0 = cand[i], c1 = cand[i + NT], c2 = cand[i + 2 * NT];
+      const uint64_t c3 = (i + 3 * NT < n) ? cand[i + 3 * NT] : 0ull;
+      f(c0);
+      f(c1);
+      f(c2);
+      f(c3);
+    }
+    for (; i0 < n; i0 += NT) f(i0 + tid < n ? cand[i0 + tid] : 0ull);
+  }
+};
+
+// What the filter of a lone CTA leaves behind: one dense segment per warp (each warp walks its own;
+// `wn`, its length, is the same in all lanes) plus the shared spill area of `sn` entries. No slot
+// is empty.
+template <int NT>
+struct WarpSegCands {
+  static constexpr bool kEmpties = false;
+  const uint64_t* seg;
+  int wn;
+  const uint64_t* spill;
+  int sn;
+  template <class F>
+  __device__ __forceinline__ void for_each_key(F&& f) const {
+    const uint32_t* hi32 = reinterpret_cast<const uint32_t*>(seg) + 1;
+    int i = lane_id();
+    for (; i + 96 < wn; i += 128) {
+      const uint32_t k0 = hi32[2 * i], k1 = hi32[2 * (i + 32)], k2 = hi32[2 * (i + 64)], k3 = hi32[2 * (i + 96)];
+      f(k0);
+      f(k1);
+      f(k2);
+      f(k3);
+    }
+    for (; i < wn; i += 32) f(hi32[2 * i]);
+    const uint32_t* sp32 = reinterpret_cast<const uint32_t*>(spill) + 1;
+    for (int j = threadIdx.x; j < sn; j += NT) f(sp32[2 * j]);
+  }
+  template <class F>
+  __device__ __forceinline__ void for_each_uniform(F&& f) const {
+    const int lane = lane_id();
+    int i0 = 0;
+    for (; i0 + 96 < wn; i0 += 128) {
+      const int i = i0 + lane;
+      const uint64_t c0 = seg[i], c1 = seg[i + 32], c2 = seg[i + 64];
+      const uint64_t c3 = (i + 96 < wn) ? seg[i + 96] : 0ull;
+      f(c0);
+      f(c1);
+      f(c2);
+      f(c3);
+    }
+    for (; i0 < wn; i0 += 32) f(i0 + lane < wn ? seg[i0 + lane] : 0ull);
+    for (int j0 = 0; j0 < sn; j0 += NT) f(j0 + (int)threadIdx.x < sn ? spill[j0 + threadIdx.x] : 0ull);
+  }
+};
 
 // Block-wide threshold pick over kFinishBins counts (descending bin order); result in ctrl->t
 // (-1 if the counts sum to less than need), ctrl->above, ctrl->cnt. Ends with a barrier.
@@ -225,8 +283,8 @@ __device__ __forceinline__ void block_pick(const uint32_t* hist, uint32_t need, 
 // `page`: optional per-row table; the value written is then page[idx] instead of idx + idx_offset
 // (the fused page-table transform of the reference's topk_transform_* kernels, :871-958).
 // ---------------------------------------------------------------------------------------------
-template <int NT>
-__device__ void cta_finish(const uint64_t* cand, int n, uint32_t need, int hi, uint64_t pfx, int idx_bits,
+template <int NT, class Src>
+__device__ void cta_finish(const Src& src, uint32_t need, int hi, uint64_t pfx, int idx_bits,
                            uint32_t* hist /* >= kFinishBins words */, Ctrl* ctrl, int32_t* out_idx, uint32_t* out_key,
                            uint32_t out_base, int32_t idx_offset, uint32_t* status,
                            const int32_t* page = nullptr /* when set: out = page[idx] */) {
@@ -240,7 +298,7 @@ __device__ void cta_finish(const uint64_t* cand, int n, uint32_t need, int hi, u
     // No prefix known: find the bits all candidates agree on (OR and AND over the list), so that
     // the first digit is spent where the candidates actually differ.
     uint32_t o_hi = 0u, o_lo = 0u, a_hi = ~0u, a_lo = ~0u;
-    for_each_cand<NT>(cand, n, [&](uint64_t c) {
+    src.for_each_uniform([&](uint64_t c) {
       if (c != 0ull) {
         o_hi |= (uint32_t)(c >> 32);
         o_lo |= (uint32_t)c;
@@ -272,13 +330,13 @@ __device__ void cta_finish(const uint64_t* cand, int n, uint32_t need, int hi, u
     FFTOPK_MARK(31);
   }
   // ---- radix rounds: only the threshold is determined here; nothing is written yet -----------
-  // Outcome: the winners are the candidates with (c >> fs) > fthr (strict) or >= fthr, plus, when
-  // the last <= 32 undecided candidates were ranked, the best `need2` of those (written there).
+  // Outcome: the threshold bin [t_lo, t_hi] of composites. Everything above t_hi wins; of the
+  // bin itself either everything wins (all_bin) or, when it holds <= 32 candidates, the best
+  // `need2` of them, found by ranking.
   const uint32_t need_total = need;
-  int fs = 0;
-  uint64_t fthr = ~0ull;
-  bool strict = false, found = false, counted = false;
-  uint32_t mine = 0;  // this thread's winners under the final predicate (valid when `counted`)
+  uint64_t t_lo = 0ull, t_hi = 0ull;
+  uint32_t need2 = 0, cnt = 0;
+  bool all_bin = false, found = false;
   for (int round = 0; round < 16 && hi > 0; ++round) {
     if (hi <= 32 && hi > idx_bits) {
       // constant run of ones in the inverted index: extend the prefix without a pass
@@ -296,11 +354,11 @@ __device__ void cta_finish(const uint64_t* cand, int n, uint32_t need, int hi, u
       // which no value maps to)
       const int hk = hi - 32, sk = sh - 32;
       const uint32_t pk = (uint32_t)pfx;
-      for_each_key<NT>(cand, n, [&](uint32_t k) {
-        if (k != 0u && (hk >= 32 || (k >> hk) == pk)) red_shared_add(&hist[(k >> sk) & dmask], 1u);
+      src.for_each_key([&](uint32_t k) {
+        if ((!Src::kEmpties || k != 0u) && (hk >= 32 || (k >> hk) == pk)) red_shared_add(&hist[(k >> sk) & dmask], 1u);
       });
     } else {
-      for_each_cand<NT>(cand, n, [&](uint64_t c) {
+      src.for_each_uniform([&](uint64_t c) {
         const bool act = (c != 0ull) && (hi >= 64 || (c >> hi) == pfx);
         if (act) red_shared_add(&hist[(uint32_t)(c >> sh) & dmask], 1u);
       });
@@ -314,54 +372,13 @@ __device__ void cta_finish(const uint64_t* cand, int n, uint32_t need, int hi, u
       if (tid == 0 && status) atomicOr(status, 2u);
       return;
     }
-    const uint32_t cnt = ctrl->cnt;
-    const uint32_t need2 = need - ctrl->above;
+    cnt = ctrl->cnt;
+    need2 = need - ctrl->above;
     const uint64_t pfx2 = (hi >= 64) ? (uint64_t)t : ((pfx << w) | (uint64_t)t);
-    if (cnt == need2) {  // the whole threshold bin wins
-      fs = sh;
-      fthr = pfx2;
-      found = true;
-      break;
-    }
-    if (cnt <= (uint32_t)kSmall) {
-      // The last <= 32 undecided candidates. One pass collects them and counts, per thread, the
-      // candidates that are above the threshold bin (the certain winners).
-      for_each_cand<NT>(cand, n, [&](uint64_t c) {
-        if (c != 0ull) {
-          const uint64_t top = c >> sh;
-          if (top > pfx2) {
-            ++mine;
-          } else if (top == pfx2) {
-            const uint32_t s = warp_alloc(&ctrl->small_n);
-            if (s < (uint32_t)kSmall) ctrl->small[s] = c;
-          }
-        }
-      });
-      __syncthreads();
-      {
-        // Rank by vote: warp i takes candidate i, every lane j compares it with candidate j; the
-        // number of larger ones is candidate i's rank, and the best need2 go straight to the
-        // output, behind the certain winners. (A 15-stage bitonic compare-exchange network over
-        // the same 32 values is a chain of 60 dependent shuffles; this is one ballot each.)
-        const uint64_t other = (lane < (int)cnt) ? ctrl->small[lane] : 0ull;
-        const uint32_t certain = need_total - need2;
-        for (int i = warp; i < (int)cnt; i += NT / 32) {
-          const uint64_t me = ctrl->small[i];
-          const uint32_t rank = (uint32_t)__popc(__ballot_sync(kFull, other > me));
-          if (lane == 0 && rank < need2) {
-            const uint32_t pos = out_base + certain + rank;
-            if (pos < (uint32_t)kK) {
-              const int32_t idx = (int32_t)(~(uint32_t)me);
-              out_idx[pos] = page ? __ldg(page + idx) : idx + idx_offset;
-              if (out_key) out_key[pos] = (uint32_t)(me >> 32);
-            }
-          }
-        }
-      }
-      fs = sh;
-      fthr = pfx2;
-      strict = true;
-      counted = true;
+    if (cnt == need2 || cnt <= (uint32_t)kSmall) {
+      t_lo = pfx2 << sh;
+      t_hi = t_lo + ((1ull << sh) - 1ull);
+      all_bin = (cnt == need2);
       found = true;
       break;
     }
@@ -375,34 +392,62 @@ __device__ void cta_finish(const uint64_t* cand, int n, uint32_t need, int hi, u
     if (tid == 0 && status) atomicOr(status, 2u);
     return;
   }
-  // ---- output: count per thread (unless the last pass did), one slot-allocating atomic per
-  // warp, then write ---------------------------------------------------------------------------
+  // ---- one pass writes the certain winners (a ballot and one slot-allocating atomic per warp
+  // and trip; the order of the output is unspecified) and sets the undecided candidates aside ----
   FFTOPK_MARK(32);
-  auto wins = [&](uint64_t c) {
-    const uint64_t top = c >> fs;
-    return c != 0ull && (strict ? top > fthr : top >= fthr);
-  };
-  if (!counted) for_each_cand<NT>(cand, n, [&](uint64_t c) { mine += wins(c) ? 1u : 0u; });
-  uint32_t incl = mine;
-#pragma unroll
-  for (int off = 1; off < 32; off <<= 1) {
-    const uint32_t v = __shfl_up_sync(kFull, incl, off);
-    if (lane >= off) incl += v;
-  }
-  uint32_t base = 0;
-  if (lane == 31) base = atom_shared_add(&ctrl->fslot, incl);
-  base = __shfl_sync(kFull, base, 31);
-  uint32_t pos = out_base + base + incl - mine;
-  for_each_cand<NT>(cand, n, [&](uint64_t c) {
-    if (wins(c)) {
-      if (pos < (uint32_t)kK) {
-        const int32_t idx = (int32_t)(~(uint32_t)c);
-        out_idx[pos] = page ? __ldg(page + idx) : idx + idx_offset;
-        if (out_key) out_key[pos] = (uint32_t)(c >> 32);
+  const uint64_t wthr = all_bin ? (t_lo ? t_lo - 1ull : 0ull) : t_hi;  // winners: c > wthr
+  const unsigned lt = (1u << lane) - 1u;
+  auto pass = [&](auto paged) {
+    src.for_each_uniform([&](uint64_t c) {
+      const bool win = c > wthr;
+      const unsigned b = __ballot_sync(kFull, win);
+      if (b) {
+        uint32_t base = 0;
+        if (lane == 0) base = atom_shared_add(&ctrl->fslot, (uint32_t)__popc(b));
+        base = __shfl_sync(kFull, base, 0);
+        const uint32_t pos = out_base + base + (uint32_t)__popc(b & lt);
+        if (win && pos < (uint32_t)kK) {
+          const int32_t idx = (int32_t)(~(uint32_t)c);
+          if constexpr (decltype(paged)::value) {
+            out_idx[pos] = __ldg(page + idx);
+          } else {
+            out_idx[pos] = idx + idx_offset;
+          }
+          if (out_key) out_key[pos] = (uint32_t)(c >> 32);
+        }
       }
-      ++pos;
+      if (!all_bin && !win && c >= t_lo && c != 0ull) {
+        const uint32_t s = warp_alloc(&ctrl->small_n);
+        if (s < (uint32_t)kSmall) ctrl->small[s] = c;
+      }
+    });
+  };
+  if (page) {
+    pass(std::true_type{});
+  } else {
+    pass(std::false_type{});
+  }
+  if (!all_bin) {
+    __syncthreads();
+    // Rank by vote: warp i takes candidate i, every lane j compares it with candidate j; the
+    // number of larger ones is candidate i's rank, and the best need2 go behind the certain
+    // winners. (A 15-stage bitonic compare-exchange network over the same 32 values is a chain
+    // of 60 dependent shuffles; this is one ballot each.)
+    const uint64_t other = (lane < (int)cnt) ? ctrl->small[lane] : 0ull;
+    const uint32_t certain = need_total - need2;
+    for (int i = warp; i < (int)cnt; i += NT / 32) {
+      const uint64_t me = ctrl->small[i];
+      const uint32_t rank = (uint32_t)__popc(__ballot_sync(kFull, other > me));
+      if (lane == 0 && rank < need2) {
+        const uint32_t pos = out_base + certain + rank;
+        if (pos < (uint32_t)kK) {
+          const int32_t idx = (int32_t)(~(uint32_t)me);
+          out_idx[pos] = page ? __ldg(page + idx) : idx + idx_offset;
+          if (out_key) out_key[pos] = (uint32_t)(me >> 32);
+        }
+      }
     }
-  });
+  }
 }
 
 }  // namespace fftopk

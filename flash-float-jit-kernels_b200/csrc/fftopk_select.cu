@@ -133,82 +133,95 @@ __device__ __noinline__ void spill_push(Ctrl* ctrl, uint64_t* spill, uint32_t sp
 
 // The one full read of the shard: every element x with !(x < edge) is kept as a
 // (key << 32 | ~idx) composite. Per loop trip a thread has U 128-bit loads in flight and spends
-// ONE compare per element, OR-ed per granule; only a granule with a hit enters the append code.
-// Every THREAD owns `lp` private slots of the shared-memory list and counts in a register, so
-// appending needs no atomic, no vote and no scan (allocating slots from one shared counter
-// serialised at ~20 cycles per candidate and dominated the pass; a per-warp shuffle scan per trip
-// still cost more than the compares). A thread with more than `lp` candidates spills the excess.
-// Returns the thread's candidate count (entries beyond lp went to the spill area); kmax is the
-// largest key among the thread's own entries.
+// one compare and one predicated OR per element on a pass mask. Candidates go to a segment of the
+// shared-memory list that belongs to the WARP and is filled densely: the warp walks its lanes'
+// hits together, one hit per lane and loop trip, and a ballot gives each its slot - no atomic, and
+// the segment's length lives in a register that is the same in all lanes. (Allocating from one
+// shared counter serialised at ~20 cycles per candidate; slots private to a thread left more than
+// half of the list empty, and every later pass paid for the empty slots.) The value of a hit is
+// fetched again (an L1/L2 hit) instead of being selected out of 4*U registers by a computed
+// index, and stored raw; a dense pass converts the segment afterwards. Candidates beyond the
+// segment's capacity go to the shared spill area.
+// Returns the number of candidates the warp found (those beyond seg_cap went to the spill area);
+// kmax is the largest key among the entries this lane converted.
 template <int NT, int U>
-__device__ __forceinline__ uint32_t filter_shard(const Shard& sh, float edge, uint64_t* mine, uint32_t lp, Ctrl* ctrl,
+__device__ __forceinline__ uint32_t filter_shard(const Shard& sh, float edge, uint64_t* seg, uint32_t seg_cap, Ctrl* ctrl,
                                                  uint64_t* spill, uint32_t spill_cap, uint32_t& kmax) {
   const int tid = threadIdx.x;
+  const int lane = tid & 31;
+  const unsigned lt = (1u << lane) - 1u;
   const float ninf = __uint_as_float(0xff800000u);
   const float4* base4 = reinterpret_cast<const float4*>(sh.gbase);
   const int fa = sh.a, fi1 = sh.i1, len = sh.len;
-  uint32_t cnt = 0;
-  auto keep = [&](uint32_t bits, int idx) {
-    const uint64_t raw = ((uint64_t)bits << 32) | (uint64_t)(uint32_t)idx;
-    if (cnt < lp) {
-      mine[cnt] = raw;
-    } else {
-      spill_push(ctrl, spill, spill_cap, raw);
+  uint32_t wcnt = 0;  // candidates of this warp so far (warp-uniform)
+  auto keep = [&](bool has, uint32_t bits, int idx) {  // called by the whole warp
+    const unsigned b = __ballot_sync(kFull, has);
+    if (has) {
+      const uint32_t pos = wcnt + (uint32_t)__popc(b & lt);
+      const uint64_t raw = ((uint64_t)bits << 32) | (uint64_t)(uint32_t)idx;
+      if (pos < seg_cap) {
+        seg[pos] = raw;
+      } else {
+        spill_push(ctrl, spill, spill_cap, raw);
+      }
     }
-    ++cnt;
+    wcnt += (uint32_t)__popc(b);
   };
   const uint32_t* base1 = reinterpret_cast<const uint32_t*>(sh.gbase);
   for (int gb = sh.i0; gb < fi1; gb += NT * U) {
     float4 x[U];
+    uint32_t vmask = 0;
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int g = gb + u * NT + tid;
-      x[u] = make_float4(ninf, ninf, ninf, ninf);  // padding: passes only an edge of -inf
-      if (g < fi1) x[u] = __ldg(base4 + g);
+      x[u] = make_float4(ninf, ninf, ninf, ninf);
+      if (g < fi1) {  // interior granules only: all four elements valid
+        x[u] = __ldg(base4 + g);
+        vmask |= 0xfu << (4 * u);
+      }
     }
-    // pass mask of this thread's 4*U elements: bit 4u+e. Granules without a hit (almost all of
-    // them) cost one OR-ed compare per element and nothing else.
+    // pass mask of this thread's 4*U elements: bit 4u+e
     uint32_t mask = 0;
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      if (!(x[u].x < edge) | !(x[u].y < edge) | !(x[u].z < edge) | !(x[u].w < edge)) {
-        uint32_t m = !(x[u].x < edge) ? 1u : 0u;
-        m |= !(x[u].y < edge) ? 2u : 0u;
-        m |= !(x[u].z < edge) ? 4u : 0u;
-        m |= !(x[u].w < edge) ? 8u : 0u;
-        if (gb + u * NT + tid < fi1) mask |= m << (4 * u);  // interior granules only: all four valid
-      }
+      if (!(x[u].x < edge)) mask |= 1u << (4 * u);
+      if (!(x[u].y < edge)) mask |= 2u << (4 * u);
+      if (!(x[u].z < edge)) mask |= 4u << (4 * u);
+      if (!(x[u].w < edge)) mask |= 8u << (4 * u);
     }
-    // One loop for all hits of the trip: the lanes of a warp work on their own hits side by side
-    // (a separate branch per element position would serialise them). The value is fetched again
-    // (an L1 hit) instead of being selected out of the registers by a computed index.
-    while (mask) {
+    mask &= vmask;  // (padding passes when the edge is -inf)
+    const int el0 = 4 * (gb + tid);
+    while (__any_sync(kFull, mask != 0u)) {
+      const bool has = mask != 0u;
       const int bit = __ffs(mask) - 1;
       mask &= mask - 1u;
-      const int el = 4 * (gb + (bit >> 2) * NT + tid) + (bit & 3);
-      keep(__ldg(base1 + el), el - fa);
+      const int el = el0 + (bit >> 2) * (4 * NT) + (bit & 3);
+      uint32_t bits = 0u;
+      if (has) bits = __ldg(base1 + el);
+      keep(has, bits, el - fa);
     }
   }
-  // edge granules [g0, i0) and [i1, g1): at most one each, visited by threads 0 and 32
-  {
+  // edge granules [g0, i0) and [i1, g1): at most one each, visited by lane 0 of warps 0 and 1
+  if (tid < 64) {  // (whole warps: keep() votes)
     const int ge = (tid == 0) ? sh.g0 : ((tid == 32) ? sh.i1 : -1);
     const int ge_end = (tid == 0) ? sh.i0 : sh.g1;
-    if (ge >= 0 && ge < ge_end) {
-      const float4 x = load_granule_partial(sh.gbase, sh.a, len, ge, ninf);
+    const bool mine = ge >= 0 && ge < ge_end;
+    if (__any_sync(kFull, mine)) {
+      float4 x = make_float4(ninf, ninf, ninf, ninf);
+      if (mine) x = load_granule_partial(sh.gbase, sh.a, len, ge, ninf);
       const int e0 = 4 * ge - fa;
       const float xv[4] = {x.x, x.y, x.z, x.w};
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        if ((unsigned)(e0 + e) < (unsigned)len && !(xv[e] < edge)) keep(__float_as_uint(xv[e]), e0 + e);
-      }
+      for (int e = 0; e < 4; ++e)
+        keep(mine && (unsigned)(e0 + e) < (unsigned)len && !(xv[e] < edge), __float_as_uint(xv[e]), e0 + e);
     }
   }
-  // dense conversion of the thread's own entries
+  // dense conversion of the warp's segment
   kmax = 0u;
-  const uint32_t own = min(cnt, lp);
-#pragma unroll 4
-  for (uint32_t j = 0; j < own; ++j) mine[j] = raw_to_composite(mine[j], kmax);
-  return cnt;
+  const uint32_t own = min(wcnt, seg_cap);
+  __syncwarp();
+  for (uint32_t j = lane; j < own; j += 32) seg[j] = raw_to_composite(seg[j], kmax);
+  return wcnt;
 }
 
 // Visit every valid element of the shard: op(key, idx). Interior granules are read with
@@ -947,6 +960,7 @@ __global__ void __launch_bounds__(NT, (NT == 512 ? FFTOPK_CTAS_512 : 1024 / NT))
   int pick_no = 0;        // number of cluster-wide searches so far (selects their total buffers)
   int fin_hi = 64;        // where the finish starts when the sampled path gathered (r < 0)
   uint64_t fin_pfx = 0ull;
+  int fin_wn = 0, fin_sn = 0;  // ... and, for a lone CTA, this warp's segment length and the spill count
 
   if (p.force_slow) {
     mode = kModeFallback;
@@ -1051,39 +1065,24 @@ __global__ void __launch_bounds__(NT, (NT == 512 ? FFTOPK_CTAS_512 : 1024 / NT))
 #ifdef FFTOPK_EXPERIMENT_NOPASS
       edge = __uint_as_float(0x7f800000u);  // experiment: nothing but +inf/NaN passes
 #endif
-      // list layout: NT * lp thread-private slots, then the spill area (an eighth of the list)
+      // list layout: one segment per warp, then the spill area (an eighth of the list)
       const uint32_t spill_cap = (uint32_t)p.list_cap / 8u;
-      const uint32_t lp = ((uint32_t)p.list_cap - spill_cap) / NT;
-      uint64_t* mine_l = list + (size_t)tid * lp;
-      uint64_t* spill = list + (size_t)NT * lp;
+      const uint32_t seg_cap = ((uint32_t)p.list_cap - spill_cap) / NW;
+      uint64_t* seg = list + (size_t)warp * seg_cap;
+      uint64_t* spill = list + (size_t)NW * seg_cap;
       uint32_t kmax = 0u;
-      const uint32_t cnt_all =
-          filter_shard<NT, (NT >= 1024 ? 4 : 8)>(sh, edge, mine_l, lp, ctrl, spill, spill_cap, kmax);
+      const uint32_t wcnt = filter_shard<NT, (NT >= 1024 ? 4 : 8)>(sh, edge, seg, seg_cap, ctrl, spill, spill_cap, kmax);
       FFTOPK_MARK(8);
-      const uint32_t mycnt = min(cnt_all, lp);
-      if (C == 1) {
-        // single CTA: the finish reads the list where it lies; unused slots become "empty" (0)
-#pragma unroll 4
-        for (uint32_t j = mycnt; j < lp; ++j) mine_l[j] = 0ull;
-      }
-      // hand the candidates to rank 0: one remote atomic per CTA allocates the range
-      uint32_t lincl = mycnt;
-#pragma unroll
-      for (int off = 1; off < 32; off <<= 1) {
-        const uint32_t v = __shfl_up_sync(kFull, lincl, off);
-        if (lane >= off) lincl += v;
-      }
+      const uint32_t wown = min(wcnt, seg_cap);
+      fin_wn = (int)wown;
       kmax = __reduce_max_sync(kFull, kmax);
-      if (lane == 31) {
-        ctrl->wtot[warp] = lincl;
+      if (lane == 0) {
+        ctrl->wtot[warp] = wown;
         ctrl->wmax[warp] = kmax;
       }
       __syncthreads();
-      if (C == 1) {  // (the spill count is final only now)
-        const uint32_t spill_n1 = min(ctrl->lcount, spill_cap);
-        for (uint32_t j = spill_n1 + tid; j < spill_cap; j += NT) spill[j] = 0ull;
-      }
       FFTOPK_MARK(44);
+      // hand the candidates to rank 0: one remote atomic per CTA allocates the range
       if (warp == 0) {
         const uint32_t wmine = lane < NW ? ctrl->wtot[lane] : 0u;
         uint32_t incl = wmine;
@@ -1106,14 +1105,14 @@ __global__ void __launch_bounds__(NT, (NT == 512 ? FFTOPK_CTAS_512 : 1024 / NT))
       }
       __syncthreads();
       FFTOPK_MARK(45);
+      fin_sn = (int)min(ctrl->lcount, spill_cap);
       if (C > 1) {
-        const uint32_t dst = ctrl->wtot[warp] + lincl - mycnt;
-        for (uint32_t j = 0; j < mycnt; ++j) {
-          if (dst + j < (uint32_t)p.cand_cap) cx.cand0[dst + j] = mine_l[j];
+        const uint32_t dst = ctrl->wtot[warp];
+        for (uint32_t j = lane; j < wown; j += 32) {
+          if (dst + j < (uint32_t)p.cand_cap) cx.cand0[dst + j] = seg[j];
         }
-        const uint32_t spill_n = min(ctrl->lcount, spill_cap);
         const uint32_t sbase = ctrl->base_c;
-        for (uint32_t j = tid; j < spill_n; j += NT) {
+        for (uint32_t j = tid; j < (uint32_t)fin_sn; j += NT) {
           if (sbase + j < (uint32_t)p.cand_cap) cx.cand0[sbase + j] = spill[j];
         }
       }
@@ -1159,15 +1158,21 @@ __global__ void __launch_bounds__(NT, (NT == 512 ? FFTOPK_CTAS_512 : 1024 / NT))
   if (!finish_first) cluster_sync(cluster, C);
   FFTOPK_MARK(6);
   if (mode == kModeGather && rank == 0) {
-    // sampled path of a lone CTA: the whole list region, empty slots included
-    const int spill_cap1 = p.list_cap / 8;
-    const int n = (r < 0 && C == 1) ? NT * ((p.list_cap - spill_cap1) / NT) + spill_cap1
-                                    : (int)min(ctrl->cand_count, (uint32_t)p.cand_cap);
     const int hi = r < 0 ? fin_hi : 32 + round_shift(r);
     const uint64_t pfx = r < 0 ? fin_pfx : (uint64_t)P;
-    int idx_bits = 32 - __clz(len - 1);
-    cta_finish<NT>(cx.cand, n, need, hi, pfx, idx_bits, cx.hist(0), ctrl, out_idx, out_key,
-                   (uint32_t)kK - need, cx.idx_offset, p.status, cx.page);
+    const int idx_bits = 32 - __clz(len - 1);
+    if (r < 0 && C == 1) {
+      // sampled path of a lone CTA: the warps' segments where the filter left them
+      const uint32_t spill_cap1 = (uint32_t)p.list_cap / 8u;
+      const uint32_t seg_cap1 = ((uint32_t)p.list_cap - spill_cap1) / NW;
+      const WarpSegCands<NT> src{list + (size_t)warp * seg_cap1, fin_wn, list + (size_t)NW * seg_cap1, fin_sn};
+      cta_finish<NT>(src, need, hi, pfx, idx_bits, cx.hist(0), ctrl, out_idx, out_key, (uint32_t)kK - need,
+                     cx.idx_offset, p.status, cx.page);
+    } else {
+      const DenseCands<NT> src{cx.cand, (int)min(ctrl->cand_count, (uint32_t)p.cand_cap)};
+      cta_finish<NT>(src, need, hi, pfx, idx_bits, cx.hist(0), ctrl, out_idx, out_key, (uint32_t)kK - need,
+                     cx.idx_offset, p.status, cx.page);
+    }
   }
   if (finish_first) cluster_sync(cluster, C);
   FFTOPK_MARK(7);

@@ -21,6 +21,10 @@ __device__ __forceinline__ void trace_mark(int id, bool who) {
   }
 }
 #define FFTOPK_MARK(id) trace_mark((id), blockIdx.x == 0 && threadIdx.x == 0)
+#elif defined(FFTOPK_STOP_AFTER)
+// Instruction-count experiments: the kernel body returns at mark FFTOPK_STOP_AFTER (only marks
+// placed directly in a kernel of one-CTA clusters make sense here; results are then garbage).
+#define FFTOPK_MARK(id) do { if ((id) == FFTOPK_STOP_AFTER) return; } while (0)
 #else
 #define FFTOPK_MARK(id) ((void)0)
 #endif
