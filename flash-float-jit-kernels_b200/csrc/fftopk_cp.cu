@@ -147,7 +147,7 @@ __global__ void __launch_bounds__(NT, 1) merge2048_kernel(const MergeSrc src, in
     return;
   }
   const DenseCands<NT> all{cand, n};
-  cta_finish<NT>(all, (uint32_t)kK, 64, 0ull, 31, hist, ctrl, out_idx, out_key, 0u, 0, status);
+  cta_finish<NT>(all, (uint32_t)kK, 1ull, 0ull, 0ull, false, 31, hist, ctrl, out_idx, out_key, 0u, 0, status);  // range unknown
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -136,6 +136,10 @@ struct Ctrl {
   uint32_t totb[kSup];  // first sample round: super-bin totals of the second (finer) histogram
   uint32_t dual_b;      // ... whether the finer histogram was usable, and for which top nibble
   uint32_t dual_g;
+  uint32_t need_hi;       // first sample round of a lone CTA: sample rank that bounds the threshold from
+  int32_t sup_sel_hi;     // above, the super-bin it falls in, the sample elements above that super-bin,
+  uint32_t sup_above_hi;  // and the bin found for it (-1: none)
+  int32_t focus_bin;
   uint32_t wtot[32];
   uint32_t wmax[32];
   uint64_t small[kSmall];
@@ -146,6 +150,7 @@ struct Ctrl {
 //   for_each_key(f)     f(key) for every slot of the share (any order, any trip count)
 //   for_each_uniform(f) f(composite) with the same trip count in all lanes of a warp (f may vote);
 //                       lanes without a candidate get 0, which is also what an empty slot holds
+//   for_each_uniform4(f4)  the same, four composites per call
 // Loads are issued four at a time (a plain loop waits out the full shared-memory latency once per
 // element: measured 190 cycles per element with 16 warps on the SM).
 // ---------------------------------------------------------------------------------------------
@@ -169,20 +174,26 @@ struct DenseCands {
     }
     for (; i < n; i += NT) f(hi32[2 * i]);
   }
+  template <class F4>
+  __device__ __forceinline__ void for_each_uniform4(F4&& f4) const {
+    const int tid = threadIdx.x;
+    for (int i0 = 0; i0 < n; i0 += 4 * NT) {
+      const int i = i0 + tid;
+      const uint64_t c0 = (i < n) ? cand[i] : 0ull;
+      const uint64_t c1 = (i + NT < n) ? cand[i + NT] : 0ull;
+      const uint64_t c2 = (i + 2 * NT < n) ? cand[i + 2 * NT] : 0ull;
+      const uint64_t c3 = (i + 3 * NT < n) ? cand[i + 3 * NT] : 0ull;
+      f4(c0, c1, c2, c3);
+    }
+  }
   template <class F>
   __device__ __forceinline__ void for_each_uniform(F&& f) const {
-    const int tid = threadIdx.x;
-    int i0 = 0;
-    for (; i0 + 3 * NT < n; i0 += 4 * NT) {
-      const int i = i0 + tid;
-      const uint64_t c0 = cand[i], c1 = cand[i + NT], c2 = cand[i + 2 * NT];
-      const uint64_t c3 = (i + 3 * NT < n) ? cand[i + 3 * NT] : 0ull;
+    for_each_uniform4([&](uint64_t c0, uint64_t c1, uint64_t c2, uint64_t c3) {
       f(c0);
       f(c1);
       f(c2);
       f(c3);
-    }
-    for (; i0 < n; i0 += NT) f(i0 + tid < n ? cand[i0 + tid] : 0ull);
+    });
   }
 };
 
@@ -211,21 +222,35 @@ struct WarpSegCands {
     const uint32_t* sp32 = reinterpret_cast<const uint32_t*>(spill) + 1;
     for (int j = threadIdx.x; j < sn; j += NT) f(sp32[2 * j]);
   }
+  template <class F4>
+  __device__ __forceinline__ void for_each_uniform4(F4&& f4) const {
+    const int lane = lane_id();
+    for (int i0 = 0; i0 < wn; i0 += 128) {
+      const int i = i0 + lane;
+      const uint64_t c0 = (i < wn) ? seg[i] : 0ull;
+      const uint64_t c1 = (i + 32 < wn) ? seg[i + 32] : 0ull;
+      const uint64_t c2 = (i + 64 < wn) ? seg[i + 64] : 0ull;
+      const uint64_t c3 = (i + 96 < wn) ? seg[i + 96] : 0ull;
+      f4(c0, c1, c2, c3);
+    }
+    const int tid = threadIdx.x;
+    for (int j0 = 0; j0 < sn; j0 += 4 * NT) {
+      const int j = j0 + tid;
+      const uint64_t c0 = (j < sn) ? spill[j] : 0ull;
+      const uint64_t c1 = (j + NT < sn) ? spill[j + NT] : 0ull;
+      const uint64_t c2 = (j + 2 * NT < sn) ? spill[j + 2 * NT] : 0ull;
+      const uint64_t c3 = (j + 3 * NT < sn) ? spill[j + 3 * NT] : 0ull;
+      f4(c0, c1, c2, c3);
+    }
+  }
   template <class F>
   __device__ __forceinline__ void for_each_uniform(F&& f) const {
-    const int lane = lane_id();
-    int i0 = 0;
-    for (; i0 + 96 < wn; i0 += 128) {
-      const int i = i0 + lane;
-      const uint64_t c0 = seg[i], c1 = seg[i + 32], c2 = seg[i + 64];
-      const uint64_t c3 = (i + 96 < wn) ? seg[i + 96] : 0ull;
+    for_each_uniform4([&](uint64_t c0, uint64_t c1, uint64_t c2, uint64_t c3) {
       f(c0);
       f(c1);
       f(c2);
       f(c3);
-    }
-    for (; i0 < wn; i0 += 32) f(i0 + lane < wn ? seg[i0 + lane] : 0ull);
-    for (int j0 = 0; j0 < sn; j0 += NT) f(j0 + (int)threadIdx.x < sn ? spill[j0 + threadIdx.x] : 0ull);
+    });
   }
 };
 
@@ -270,23 +295,55 @@ __device__ __forceinline__ void block_pick(const uint32_t* hist, uint32_t need, 
 }
 
 // ---------------------------------------------------------------------------------------------
-// Single-CTA finish. `cand` holds n composites c = (key << 32) | ~idx in shared memory; entries
-// equal to 0 are empty. All non-empty composites agree on the bits at and above `hi`
-// (their value there is `pfx`; hi == 64 means no common prefix). Writes the `need` largest
-// composites' indices (and keys) to out_idx[out_base ...], in unspecified order.
+// Digit rule of a finish round over the composite range [lo, cap]: digit(c) = min((c - lo) >>
+// shift, kFinishBins - 1). The shift is chosen so that [lo, focus] spreads over the bins below the
+// last one; everything above `focus` (cap >= focus >= lo) lands in the last bin. With focus == cap
+// this is a plain radix digit of the range; a caller that knows where in the range the threshold
+// will fall passes a tighter focus and gets finer bins there.
+// ---------------------------------------------------------------------------------------------
+struct FinishDigit {
+  uint64_t lo;
+  int shift;
+  __device__ __forceinline__ uint32_t of(uint64_t c) const {
+    const uint64_t d = (c - lo) >> shift;
+    return d < (uint64_t)(kFinishBins - 1) ? (uint32_t)d : (uint32_t)(kFinishBins - 1);
+  }
+  // the same for a digit that depends on the key alone (shift >= 32 and the low word of lo is 0)
+  __device__ __forceinline__ uint32_t of_key(uint32_t k) const {
+    const uint32_t d = (k - (uint32_t)(lo >> 32)) >> (shift - 32);
+    return d < (uint32_t)(kFinishBins - 1) ? d : (uint32_t)(kFinishBins - 1);
+  }
+  __device__ __forceinline__ bool key_only() const { return shift >= 32 && (uint32_t)lo == 0u; }
+};
+
+__device__ __forceinline__ FinishDigit make_finish_digit(uint64_t lo, uint64_t focus) {
+  const uint64_t width = focus - lo;
+  const int bits = width ? 64 - __clzll((long long)width) : 0;
+  int shift = bits > kFinishBits ? bits - kFinishBits : 0;
+  if ((width >> shift) >= (uint64_t)(kFinishBins - 1)) ++shift;  // keep the last bin for what lies above
+  return FinishDigit{lo, shift};
+}
+
+// ---------------------------------------------------------------------------------------------
+// Single-CTA finish. The source holds composites c = (key << 32) | ~idx in shared memory (0 =
+// empty slot), all of them inside [lo, cap]; lo > cap means "range unknown" and costs a pass
+// that finds it. Writes the `need` largest composites' indices (and keys) to
+// out_idx[out_base ...], in unspecified order.
 //
 // Replaces the reference's refinement rounds on shared-memory survivors and its CAS insertion
 // tail (topk_indexer_radix.cu:686-781, 109-141, 788-850). Because the index is part of the
-// composite, equal values are resolved towards the lower index by the same radix passes, and
-// the last <= 32 undecided candidates go through a warp compare-exchange network.
+// composite, equal values are resolved towards the lower index by the same rounds, and the last
+// <= 32 undecided candidates are ranked by one vote each.
+// `focus`: see FinishDigit. `have_hist`: the caller has already built round 0's histogram in
+// `hist`, with make_finish_digit(lo, focus).
 // `idx_bits`: all indices are < 2^idx_bits, so the inverted-index bits above that are all ones.
 // `page`: optional per-row table; the value written is then page[idx] instead of idx + idx_offset
 // (the fused page-table transform of the reference's topk_transform_* kernels, :871-958).
 // ---------------------------------------------------------------------------------------------
 template <int NT, class Src>
-__device__ void cta_finish(const Src& src, uint32_t need, int hi, uint64_t pfx, int idx_bits,
-                           uint32_t* hist /* >= kFinishBins words */, Ctrl* ctrl, int32_t* out_idx, uint32_t* out_key,
-                           uint32_t out_base, int32_t idx_offset, uint32_t* status,
+__device__ void cta_finish(const Src& src, uint32_t need, uint64_t lo, uint64_t cap, uint64_t focus, bool have_hist,
+                           int idx_bits, uint32_t* hist /* >= kFinishBins words */, Ctrl* ctrl, int32_t* out_idx,
+                           uint32_t* out_key, uint32_t out_base, int32_t idx_offset, uint32_t* status,
                            const int32_t* page = nullptr /* when set: out = page[idx] */) {
   const int tid = threadIdx.x;
   const int lane = tid & 31, warp = tid >> 5;
@@ -294,42 +351,37 @@ __device__ void cta_finish(const Src& src, uint32_t need, int hi, uint64_t pfx, 
     ctrl->fslot = 0u;  // (every path below has a block barrier before these are used)
     ctrl->small_n = 0u;
   }
-  if (hi >= 64) {
-    // No prefix known: find the bits all candidates agree on (OR and AND over the list), so that
-    // the first digit is spent where the candidates actually differ.
-    uint32_t o_hi = 0u, o_lo = 0u, a_hi = ~0u, a_lo = ~0u;
-    src.for_each_uniform([&](uint64_t c) {
-      if (c != 0ull) {
-        o_hi |= (uint32_t)(c >> 32);
-        o_lo |= (uint32_t)c;
-        a_hi &= (uint32_t)(c >> 32);
-        a_lo &= (uint32_t)c;
+  if (lo > cap) {
+    // Range unknown: the smallest and the largest key present bound it.
+    uint32_t kmin = ~0u, kmax = 0u;
+    src.for_each_key([&](uint32_t k) {
+      if (k != 0u) {
+        kmin = min(kmin, k);
+        kmax = max(kmax, k);
       }
     });
-    o_hi = __reduce_or_sync(kFull, o_hi);
-    o_lo = __reduce_or_sync(kFull, o_lo);
-    a_hi = __reduce_and_sync(kFull, a_hi);
-    a_lo = __reduce_and_sync(kFull, a_lo);
+    kmin = __reduce_min_sync(kFull, kmin);
+    kmax = __reduce_max_sync(kFull, kmax);
     if (lane == 0) {
-      hist[4 * warp + 0] = o_hi;
-      hist[4 * warp + 1] = o_lo;
-      hist[4 * warp + 2] = a_hi;
-      hist[4 * warp + 3] = a_lo;
+      hist[2 * warp + 0] = kmin;
+      hist[2 * warp + 1] = kmax;
     }
     __syncthreads();
     const bool in = lane < NT / 32;
-    o_hi = __reduce_or_sync(kFull, in ? hist[4 * lane + 0] : 0u);
-    o_lo = __reduce_or_sync(kFull, in ? hist[4 * lane + 1] : 0u);
-    a_hi = __reduce_and_sync(kFull, in ? hist[4 * lane + 2] : ~0u);
-    a_lo = __reduce_and_sync(kFull, in ? hist[4 * lane + 3] : ~0u);
-    const uint64_t o = ((uint64_t)o_hi << 32) | o_lo;
-    const uint64_t diff = o ^ (((uint64_t)a_hi << 32) | a_lo);
-    hi = diff ? 64 - __clzll((long long)diff) : 1;
-    if (hi < 64) pfx = o >> hi;
+    kmin = __reduce_min_sync(kFull, in ? hist[2 * lane + 0] : ~0u);
+    kmax = __reduce_max_sync(kFull, in ? hist[2 * lane + 1] : 0u);
+    lo = (uint64_t)kmin << 32;
+    cap = ((uint64_t)kmax << 32) | 0xffffffffull;
+    if (lo > cap) {  // no candidate at all
+      if (tid == 0 && status) atomicOr(status, 2u);
+      return;
+    }
+    focus = cap;
+    have_hist = false;
     __syncthreads();  // the scratch words are about to be cleared as the histogram
     FFTOPK_MARK(31);
   }
-  // ---- radix rounds: only the threshold is determined here; nothing is written yet -----------
+  // ---- rounds: only the threshold is determined here; nothing is written yet ---------------------
   // Outcome: the threshold bin [t_lo, t_hi] of composites. Everything above t_hi wins; of the
   // bin itself either everything wins (all_bin) or, when it holds <= 32 candidates, the best
   // `need2` of them, found by ranking.
@@ -337,33 +389,35 @@ __device__ void cta_finish(const Src& src, uint32_t need, int hi, uint64_t pfx, 
   uint64_t t_lo = 0ull, t_hi = 0ull;
   uint32_t need2 = 0, cnt = 0;
   bool all_bin = false, found = false;
-  for (int round = 0; round < 16 && hi > 0; ++round) {
-    if (hi <= 32 && hi > idx_bits) {
-      // constant run of ones in the inverted index: extend the prefix without a pass
-      const int skip = hi - idx_bits;
-      pfx = (pfx << skip) | ((1ull << skip) - 1ull);
-      hi = idx_bits;
+  for (int round = 0; round < 24; ++round) {
+    if ((uint32_t)(lo >> 32) == (uint32_t)(cap >> 32)) {
+      // one key left: the inverted indices all start with the same run of ones
+      const uint64_t floor_lo = (lo & 0xffffffff00000000ull) | (uint64_t)(~((idx_bits >= 32 ? 0u : (1u << idx_bits)) - 1u));
+      if (lo < floor_lo && floor_lo <= cap) {
+        if (focus < floor_lo) focus = cap;
+        lo = floor_lo;
+        have_hist = false;
+      }
     }
-    const int w = hi < kFinishBits ? hi : kFinishBits;
-    const int sh = hi - w;
-    const uint32_t dmask = (1u << w) - 1u;
-    for (int b = tid; b < kFinishBins; b += NT) hist[b] = 0u;
-    __syncthreads();
-    if (sh >= 32 && hi < 64) {
-      // the digit lies inside the key: work on the high words only (an empty slot has key 0,
-      // which no value maps to)
-      const int hk = hi - 32, sk = sh - 32;
-      const uint32_t pk = (uint32_t)pfx;
-      src.for_each_key([&](uint32_t k) {
-        if ((!Src::kEmpties || k != 0u) && (hk >= 32 || (k >> hk) == pk)) red_shared_add(&hist[(k >> sk) & dmask], 1u);
-      });
-    } else {
-      src.for_each_uniform([&](uint64_t c) {
-        const bool act = (c != 0ull) && (hi >= 64 || (c >> hi) == pfx);
-        if (act) red_shared_add(&hist[(uint32_t)(c >> sh) & dmask], 1u);
-      });
+    if (focus < lo || focus > cap) focus = cap;
+    const FinishDigit dg = make_finish_digit(lo, focus);
+    if (!(round == 0 && have_hist)) {
+      for (int b = tid; b < kFinishBins; b += NT) hist[b] = 0u;
+      __syncthreads();
+      const uint64_t span = cap - lo;
+      if (dg.key_only()) {
+        // the digit depends on the key alone: work on the high words only (an empty slot has key 0)
+        const uint32_t klo = (uint32_t)(lo >> 32), kspan = (uint32_t)(span >> 32);
+        src.for_each_key([&](uint32_t k) {
+          if ((!Src::kEmpties || k != 0u) && (k - klo) <= kspan) red_shared_add(&hist[dg.of_key(k)], 1u);
+        });
+      } else {
+        src.for_each_uniform([&](uint64_t c) {
+          if (c != 0ull && (c - lo) <= span) red_shared_add(&hist[dg.of(c)], 1u);
+        });
+      }
+      __syncthreads();
     }
-    __syncthreads();
     FFTOPK_MARK(16);
     block_pick<NT>(hist, need, ctrl);
     FFTOPK_MARK(17);
@@ -374,16 +428,16 @@ __device__ void cta_finish(const Src& src, uint32_t need, int hi, uint64_t pfx, 
     }
     cnt = ctrl->cnt;
     need2 = need - ctrl->above;
-    const uint64_t pfx2 = (hi >= 64) ? (uint64_t)t : ((pfx << w) | (uint64_t)t);
+    t_lo = lo + ((uint64_t)t << dg.shift);
+    t_hi = (t == kFinishBins - 1) ? cap : t_lo + ((1ull << dg.shift) - 1ull);
+    if (t_hi > cap || t_hi < t_lo) t_hi = cap;
     if (cnt == need2 || cnt <= (uint32_t)kSmall) {
-      t_lo = pfx2 << sh;
-      t_hi = t_lo + ((1ull << sh) - 1ull);
       all_bin = (cnt == need2);
       found = true;
       break;
     }
-    pfx = pfx2;
-    hi = sh;
+    lo = t_lo;
+    cap = focus = t_hi;
     need = need2;
     __syncthreads();  // every thread has read ctrl->t/cnt/above before the next round rewrites them
   }
@@ -397,28 +451,45 @@ __device__ void cta_finish(const Src& src, uint32_t need, int hi, uint64_t pfx, 
   FFTOPK_MARK(32);
   const uint64_t wthr = all_bin ? (t_lo ? t_lo - 1ull : 0ull) : t_hi;  // winners: c > wthr
   const unsigned lt = (1u << lane) - 1u;
+  // Slots come from one shared counter; the warps' atomics on it serialise (~30 cycles each), so
+  // a warp allocates for four candidates per lane with one of them.
   auto pass = [&](auto paged) {
-    src.for_each_uniform([&](uint64_t c) {
-      const bool win = c > wthr;
-      const unsigned b = __ballot_sync(kFull, win);
-      if (b) {
+    src.for_each_uniform4([&](uint64_t c0, uint64_t c1, uint64_t c2, uint64_t c3) {
+      const uint64_t c[4] = {c0, c1, c2, c3};
+      unsigned b[4];
+      uint32_t nwin = 0;
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        b[u] = __ballot_sync(kFull, c[u] > wthr);
+        nwin += (uint32_t)__popc(b[u]);
+      }
+      if (nwin) {
         uint32_t base = 0;
-        if (lane == 0) base = atom_shared_add(&ctrl->fslot, (uint32_t)__popc(b));
-        base = __shfl_sync(kFull, base, 0);
-        const uint32_t pos = out_base + base + (uint32_t)__popc(b & lt);
-        if (win && pos < (uint32_t)kK) {
-          const int32_t idx = (int32_t)(~(uint32_t)c);
-          if constexpr (decltype(paged)::value) {
-            out_idx[pos] = __ldg(page + idx);
-          } else {
-            out_idx[pos] = idx + idx_offset;
+        if (lane == 0) base = atom_shared_add(&ctrl->fslot, nwin);
+        base = out_base + __shfl_sync(kFull, base, 0);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const uint32_t pos = base + (uint32_t)__popc(b[u] & lt);
+          if (c[u] > wthr && pos < (uint32_t)kK) {
+            const int32_t idx = (int32_t)(~(uint32_t)c[u]);
+            if constexpr (decltype(paged)::value) {
+              out_idx[pos] = __ldg(page + idx);
+            } else {
+              out_idx[pos] = idx + idx_offset;
+            }
+            if (out_key) out_key[pos] = (uint32_t)(c[u] >> 32);
           }
-          if (out_key) out_key[pos] = (uint32_t)(c >> 32);
+          base += (uint32_t)__popc(b[u]);
         }
       }
-      if (!all_bin && !win && c >= t_lo && c != 0ull) {
-        const uint32_t s = warp_alloc(&ctrl->small_n);
-        if (s < (uint32_t)kSmall) ctrl->small[s] = c;
+      if (!all_bin) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          if (c[u] <= wthr && c[u] >= t_lo && c[u] != 0ull) {
+            const uint32_t s = warp_alloc(&ctrl->small_n);
+            if (s < (uint32_t)kSmall) ctrl->small[s] = c[u];
+          }
+        }
       }
     });
   };
@@ -427,6 +498,7 @@ __device__ void cta_finish(const Src& src, uint32_t need, int hi, uint64_t pfx, 
   } else {
     pass(std::false_type{});
   }
+  FFTOPK_MARK(33);
   if (!all_bin) {
     __syncthreads();
     // Rank by vote: warp i takes candidate i, every lane j compares it with candidate j; the

@@ -143,10 +143,10 @@ __device__ __noinline__ void spill_push(Ctrl* ctrl, uint64_t* spill, uint32_t sp
 // index, and stored raw; a dense pass converts the segment afterwards. Candidates beyond the
 // segment's capacity go to the shared spill area.
 // Returns the number of candidates the warp found (those beyond seg_cap went to the spill area);
-// kmax is the largest key among the entries this lane converted.
-template <int NT, int U>
+// kmax is the largest key among the entries this lane converted; post(key) is called for each of them.
+template <int NT, int U, class Post>
 __device__ __forceinline__ uint32_t filter_shard(const Shard& sh, float edge, uint64_t* seg, uint32_t seg_cap, Ctrl* ctrl,
-                                                 uint64_t* spill, uint32_t spill_cap, uint32_t& kmax) {
+                                                 uint64_t* spill, uint32_t spill_cap, uint32_t& kmax, Post&& post) {
   const int tid = threadIdx.x;
   const int lane = tid & 31;
   const unsigned lt = (1u << lane) - 1u;
@@ -168,16 +168,22 @@ __device__ __forceinline__ uint32_t filter_shard(const Shard& sh, float edge, ui
     wcnt += (uint32_t)__popc(b);
   };
   const uint32_t* base1 = reinterpret_cast<const uint32_t*>(sh.gbase);
-  for (int gb = sh.i0; gb < fi1; gb += NT * U) {
+  // one trip over granules gb + u*NT + tid, u < U; a `full` trip lies inside the shard entirely
+  auto trip = [&](int gb, auto full) {
     float4 x[U];
-    uint32_t vmask = 0;
+    uint32_t vmask = ~0u;
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int g = gb + u * NT + tid;
-      x[u] = make_float4(ninf, ninf, ninf, ninf);
-      if (g < fi1) {  // interior granules only: all four elements valid
+      if constexpr (decltype(full)::value) {
         x[u] = __ldg(base4 + g);
-        vmask |= 0xfu << (4 * u);
+      } else {
+        x[u] = make_float4(ninf, ninf, ninf, ninf);
+        if (g < fi1) {
+          x[u] = __ldg(base4 + g);
+        } else {
+          vmask &= ~(0xfu << (4 * u));  // (padding would pass an edge of -inf)
+        }
       }
     }
     // pass mask of this thread's 4*U elements: bit 4u+e
@@ -189,7 +195,7 @@ __device__ __forceinline__ uint32_t filter_shard(const Shard& sh, float edge, ui
       if (!(x[u].z < edge)) mask |= 4u << (4 * u);
       if (!(x[u].w < edge)) mask |= 8u << (4 * u);
     }
-    mask &= vmask;  // (padding passes when the edge is -inf)
+    if constexpr (!decltype(full)::value) mask &= vmask;
     const int el0 = 4 * (gb + tid);
     while (__any_sync(kFull, mask != 0u)) {
       const bool has = mask != 0u;
@@ -200,7 +206,10 @@ __device__ __forceinline__ uint32_t filter_shard(const Shard& sh, float edge, ui
       if (has) bits = __ldg(base1 + el);
       keep(has, bits, el - fa);
     }
-  }
+  };
+  int gb = sh.i0;
+  for (; gb + NT * U <= fi1; gb += NT * U) trip(gb, std::true_type{});
+  if (gb < fi1) trip(gb, std::false_type{});
   // edge granules [g0, i0) and [i1, g1): at most one each, visited by lane 0 of warps 0 and 1
   if (tid < 64) {  // (whole warps: keep() votes)
     const int ge = (tid == 0) ? sh.g0 : ((tid == 32) ? sh.i1 : -1);
@@ -220,7 +229,11 @@ __device__ __forceinline__ uint32_t filter_shard(const Shard& sh, float edge, ui
   kmax = 0u;
   const uint32_t own = min(wcnt, seg_cap);
   __syncwarp();
-  for (uint32_t j = lane; j < own; j += 32) seg[j] = raw_to_composite(seg[j], kmax);
+  for (uint32_t j = lane; j < own; j += 32) {
+    const uint64_t c = raw_to_composite(seg[j], kmax);
+    seg[j] = c;
+    post((uint32_t)(c >> 32));
+  }
   return wcnt;
 }
 
@@ -433,12 +446,14 @@ struct DualPick {
   uint32_t need2;   // sample rank still to go inside the guessed bin
   uint32_t cnt;     // sample elements in the guessed bin
   uint32_t total;   // sample size (cluster-wide)
+  int focus_bin;    // lone CTA only: bin (same width as the guess) the threshold will not lie above; -1: unknown
 };
 
-template <int NT, class NeedFn>
+template <int NT, class NeedFn, class NeedHiFn>
 __device__ __forceinline__ DualPick cluster_pick_dual(cg::cluster_group& cluster, int C, const uint32_t* ha,
                                                       const uint32_t* sa, const uint32_t* hb, const uint32_t* sb,
-                                                      Ctrl* ctrl, int& pick_no, NeedFn&& need_of) {
+                                                      bool dual, Ctrl* ctrl, int& pick_no, NeedFn&& need_of,
+                                                      NeedHiFn&& need_hi_of) {
   const int tid = threadIdx.x;
   const int lane = tid & 31, warp = tid >> 5;
   constexpr int fine = kMaxBins / kSup;
@@ -447,9 +462,11 @@ __device__ __forceinline__ DualPick cluster_pick_dual(cg::cluster_group& cluster
   for (int i = tid; i < C * kSup; i += NT) {
     const int q = i / kSup, b = i % kSup;
     const uint32_t* ra = C == 1 ? sa : cluster.map_shared_rank(sa, q);
-    const uint32_t* rb = C == 1 ? sb : cluster.map_shared_rank(sb, q);
     red_shared_add(&tot[b], ra[b]);
-    red_shared_add(&ctrl->totb[b], rb[b]);
+    if (dual) {
+      const uint32_t* rb = C == 1 ? sb : cluster.map_shared_rank(sb, q);
+      red_shared_add(&ctrl->totb[b], rb[b]);
+    }
   }
   __syncthreads();
   FFTOPK_MARK(40);
@@ -460,13 +477,24 @@ __device__ __forceinline__ DualPick cluster_pick_dual(cg::cluster_group& cluster
     // four super-bins = 256 bins of A = one value of the top four key bits
     const uint32_t pair = lo + hi;
     const uint32_t grp = pair + __shfl_xor_sync(kFull, pair, 1);
-    const unsigned one = __ballot_sync(kFull, total > 0u && grp == total);
+    const unsigned one = __ballot_sync(kFull, dual && total > 0u && grp == total);
     const bool use_b = one != 0u;
     const uint32_t lob = ctrl->totb[2 * lane], hib = ctrl->totb[2 * lane + 1];
     uint32_t above = 0, cnt = 0;
     int ts = -1;
-    const bool ok = need > 0 && (use_b ? warp_pick64(lob, hib, need, ts, above, cnt) : warp_pick64(lo, hi, need, ts, above, cnt));
+    const uint32_t plo = use_b ? lob : lo, phi = use_b ? hib : hi;
+    const bool ok = need > 0 && warp_pick64(plo, phi, need, ts, above, cnt);
+    // A lone CTA (the throughput plan) also brackets the threshold from above: the bin of a sample
+    // rank the true threshold lies below with the same confidence. The finish then spends its
+    // first digit between the two bins instead of on the whole range up to the row's maximum.
+    uint32_t need_hi = C == 1 ? need_hi_of(total) : 0u;
+    int ts_hi = -1;
+    uint32_t above_hi = 0, cnt_hi = 0;
+    if (need_hi > 0 && !warp_pick64(plo, phi, need_hi, ts_hi, above_hi, cnt_hi)) ts_hi = -1;
     if (lane == 0) {
+      ctrl->need_hi = need_hi;
+      ctrl->sup_sel_hi = ts_hi;
+      ctrl->sup_above_hi = above_hi;
       ctrl->sup_sel = ok ? ts : -1;
       ctrl->sup_above = above;
       ctrl->need = need;
@@ -502,15 +530,27 @@ __device__ __forceinline__ DualPick cluster_pick_dual(cg::cluster_group& cluster
       const uint32_t lo = tot2[2 * lane], hi = tot2[2 * lane + 1];
       ok = warp_pick64(lo, hi, ctrl->need - ctrl->sup_above, tf, above_f, cnt_t);
     }
+    int focus_bin = -1;
+    const int ssel_hi = ctrl->sup_sel_hi;
+    if (ok && ssel_hi == ssel) {
+      const uint32_t lo = tot2[2 * lane], hi = tot2[2 * lane + 1];
+      int tf_hi = -1;
+      uint32_t a2 = 0, c2 = 0;
+      if (warp_pick64(lo, hi, ctrl->need_hi - ctrl->sup_above_hi, tf_hi, a2, c2)) focus_bin = ssel * fine + tf_hi;
+    } else if (ok && ssel_hi > ssel) {
+      focus_bin = ssel_hi * fine + (fine - 1);
+    }
     if (lane == 0) {
       ctrl->t = ok ? ssel * fine + tf : -1;
       ctrl->above = ok ? ctrl->need - ctrl->sup_above - above_f : 0u;
       ctrl->cnt = cnt_t;
+      ctrl->focus_bin = focus_bin;
     }
   }
   __syncthreads();
   FFTOPK_MARK(43);
   DualPick d;
+  d.focus_bin = ctrl->focus_bin;
   d.ok = ctrl->t >= 0;
   d.pbits = use_b ? 16 : 12;
   d.prefix = use_b ? ((ctrl->dual_g << 12) | (uint32_t)ctrl->t) : (uint32_t)ctrl->t;
@@ -851,6 +891,10 @@ __global__ void __launch_bounds__(NT, (NT == 512 ? FFTOPK_CTAS_512 : 1024 / NT))
   const int n_g = sh.g1 - sh.g0;
   // Whole shard in registers (same answer in every CTA of the cluster: `per` is rank-independent).
   const bool exact = per <= NT * kRegSlabs;
+  // A second, finer sample histogram (see cluster_pick_dual) saves a cluster-wide sample round on
+  // crowded data. A lone CTA does that round without any cluster traffic, and only when it is
+  // needed, which costs it less than building the second histogram for every row.
+  const bool dual = !exact && C > 1;
   // sampled mode: slabs read per warp
   #ifndef FFTOPK_SAMPLE_GRANULES
 #define FFTOPK_SAMPLE_GRANULES 2048
@@ -939,7 +983,7 @@ __global__ void __launch_bounds__(NT, (NT == 512 ? FFTOPK_CTAS_512 : 1024 / NT))
           const uint32_t key = fftopk_key_from_bits(__float_as_uint(xv[e]));
           const bool ok = in && (unsigned)(i0 + e) < (unsigned)len;
           hist_add(h0, key >> 20, ok);
-          if (!exact) hist_add(h0 + kMaxBins, (key >> 16) & 0xfffu, ok);  // histogram B (see cluster_pick_dual)
+          if (dual) hist_add(h0 + kMaxBins, (key >> 16) & 0xfffu, ok);  // histogram B (see cluster_pick_dual)
         }
       }
     }
@@ -948,7 +992,7 @@ __global__ void __launch_bounds__(NT, (NT == 512 ? FFTOPK_CTAS_512 : 1024 / NT))
   // cluster-wide search, was measured: issuing the requests cost about as much as it saved.)
   __syncthreads();
   compute_sup<NT>(cx.hist(0), cx.sup(0), kMaxBins);
-  if (!exact) compute_sup<NT>(cx.hist(1), cx.sup(1), kMaxBins);
+  if (dual) compute_sup<NT>(cx.hist(1), cx.sup(1), kMaxBins);
   FFTOPK_MARK(2);
   cluster_sync(cluster, C);  // #1: sample histograms complete
   FFTOPK_MARK(3);
@@ -958,8 +1002,13 @@ __global__ void __launch_bounds__(NT, (NT == 512 ? FFTOPK_CTAS_512 : 1024 / NT))
   int r = 0;
   int mode = kModeAbort;
   int pick_no = 0;        // number of cluster-wide searches so far (selects their total buffers)
-  int fin_hi = 64;        // where the finish starts when the sampled path gathered (r < 0)
-  uint64_t fin_pfx = 0ull;
+  // what the finish starts from when the sampled path gathered (r < 0): the candidates' range,
+  // the bound the first digit is focused below, and whether that digit's histogram is built
+  // (as keys: the composites' bounds are (lo << 32) and (cap << 32) | 0xffffffff)
+  uint32_t fin_lo = 0u, fin_cap = 0u, fin_focus = 0u;
+  bool fin_hist = false;
+  auto low_end = [](uint32_t key) { return (uint64_t)key << 32; };
+  auto high_end = [](uint32_t key) { return ((uint64_t)key << 32) | 0xffffffffull; };
   int fin_wn = 0, fin_sn = 0;  // ... and, for a lone CTA, this warp's segment length and the spill count
 
   if (p.force_slow) {
@@ -1004,11 +1053,16 @@ __global__ void __launch_bounds__(NT, (NT == 512 ? FFTOPK_CTAS_512 : 1024 / NT))
     // need_of: sample rank whose true rank is >= k with overwhelming probability
     // (m expected sample elements among the true top k, plus five standard deviations).
     const float flen = (float)len;
-    const DualPick dp = cluster_pick_dual<NT>(cluster, C, cx.hist(0), cx.sup(0), cx.hist(1), cx.sup(1), ctrl, pick_no,
+    const DualPick dp = cluster_pick_dual<NT>(cluster, C, cx.hist(0), cx.sup(0), cx.hist(1), cx.sup(1), dual, ctrl, pick_no,
                                               [&](uint32_t n_s) {
                                                 const float m = (float)kK * (float)n_s / flen;
                                                 const uint32_t rk = (uint32_t)(m + 5.0f * sqrtf(m) + 14.0f);
                                                 return rk < n_s ? rk : n_s;
+                                              },
+                                              [&](uint32_t n_s) {  // the mirror image; 0: no such rank
+                                                const float m = (float)kK * (float)n_s / flen;
+                                                const float rk = m - 5.0f * sqrtf(m) - 14.0f;
+                                                return rk >= 1.0f ? (uint32_t)rk : 0u;
                                               });
     FFTOPK_MARK(4);
     // If the sample says the guessed bin alone holds more than ~k row elements (values crowded
@@ -1071,7 +1125,25 @@ __global__ void __launch_bounds__(NT, (NT == 512 ? FFTOPK_CTAS_512 : 1024 / NT))
       uint64_t* seg = list + (size_t)warp * seg_cap;
       uint64_t* spill = list + (size_t)NW * seg_cap;
       uint32_t kmax = 0u;
-      const uint32_t wcnt = filter_shard<NT, (NT >= 1024 ? 4 : 8)>(sh, edge, seg, seg_cap, ctrl, spill, spill_cap, kmax);
+      // A lone CTA that knows a bin the threshold will not lie above builds the histogram of the
+      // finish's first round while it converts its candidates (they pass through registers there
+      // anyway): the digit rule needs only the guess and that bound.
+      const uint32_t lowkey = (gkey > 0x007fffffu && gkey <= 0xff800000u) ? gkey : 0u;
+      fin_lo = lowkey;
+      if (C == 1 && dp.focus_bin >= 0) {
+        fin_focus = (((uint32_t)dp.focus_bin + 1u) << (32 - dp.pbits)) - 1u;
+        fin_hist = fin_focus >= lowkey && make_finish_digit(low_end(lowkey), high_end(fin_focus)).key_only();
+      }
+      if (fin_hist) {  // (uniform over the CTA)
+        uint32_t* fh = cx.hist(0);
+        for (int b = tid; b < kFinishBins; b += NT) fh[b] = 0u;
+        __syncthreads();
+      }
+      uint32_t* fh = cx.hist(0);
+      const uint32_t wcnt = filter_shard<NT, (NT >= 1024 ? 4 : 8)>(
+          sh, edge, seg, seg_cap, ctrl, spill, spill_cap, kmax, [&](uint32_t key) {
+            if (fin_hist) red_shared_add(&fh[make_finish_digit(low_end(fin_lo), high_end(fin_focus)).of_key(key)], 1u);
+          });
       FFTOPK_MARK(8);
       const uint32_t wown = min(wcnt, seg_cap);
       fin_wn = (int)wown;
@@ -1106,6 +1178,11 @@ __global__ void __launch_bounds__(NT, (NT == 512 ? FFTOPK_CTAS_512 : 1024 / NT))
       __syncthreads();
       FFTOPK_MARK(45);
       fin_sn = (int)min(ctrl->lcount, spill_cap);
+      if (fin_hist) {  // the entries that went to the spill area
+        const uint32_t* sp32 = reinterpret_cast<const uint32_t*>(spill) + 1;
+        const FinishDigit dg = make_finish_digit(low_end(fin_lo), high_end(fin_focus));
+        for (int j = tid; j < fin_sn; j += NT) red_shared_add(&fh[dg.of_key(sp32[2 * j])], 1u);
+      }
       if (C > 1) {
         const uint32_t dst = ctrl->wtot[warp];
         for (uint32_t j = lane; j < wown; j += 32) {
@@ -1130,13 +1207,13 @@ __global__ void __launch_bounds__(NT, (NT == 512 ? FFTOPK_CTAS_512 : 1024 / NT))
         // can hold: start over with full histograms
         const uint32_t room = C == 1 ? 0xffffffffu : (uint32_t)p.cand_cap;  // (a lone CTA keeps them in the list)
         mode = (over == 0u && total >= (uint32_t)kK && total <= room) ? kModeGather : kModeFallback;
-        // every candidate's key lies in [lowkey, maxkey]: the bits those two share are a prefix of
-        // all of them, so the finish starts at the first bit where they differ
-        const uint32_t lowkey = (gkey > 0x007fffffu && gkey <= 0xff800000u) ? gkey : 0u;
-        const uint32_t diff = lowkey ^ maxkey;
-        const int kb = diff ? 32 - __clz((int)diff) : 0;
-        fin_hi = 32 + kb;
-        fin_pfx = kb >= 32 ? 0ull : (uint64_t)(maxkey >> kb);
+        // every candidate's key lies in [lowkey, maxkey]
+        fin_cap = maxkey;
+        if (fin_hist) {
+          if (fin_cap < fin_focus) fin_cap = fin_focus;  // (a looser bound keeps the digit rule of the histogram)
+        } else {
+          fin_focus = fin_cap;
+        }
       }
       need = kK;
       P = 0;
@@ -1147,6 +1224,9 @@ __global__ void __launch_bounds__(NT, (NT == 512 ? FFTOPK_CTAS_512 : 1024 / NT))
     }
   }
 
+#ifdef FFTOPK_DEBUG_FALLBACK
+  if (mode == kModeFallback && tid == 0 && p.status) atomicOr(p.status, 8u);
+#endif
   if (mode == kModeFallback) mode = refine_from_data<NT>(cx, need, P, r, pick_no);
 
   // Candidates that peers pushed into rank 0 are complete after a cluster barrier. The sampled
@@ -1158,22 +1238,26 @@ __global__ void __launch_bounds__(NT, (NT == 512 ? FFTOPK_CTAS_512 : 1024 / NT))
   if (!finish_first) cluster_sync(cluster, C);
   FFTOPK_MARK(6);
   if (mode == kModeGather && rank == 0) {
-    const int hi = r < 0 ? fin_hi : 32 + round_shift(r);
-    const uint64_t pfx = r < 0 ? fin_pfx : (uint64_t)P;
     const int idx_bits = 32 - __clz(len - 1);
     if (r < 0 && C == 1) {
       // sampled path of a lone CTA: the warps' segments where the filter left them
       const uint32_t spill_cap1 = (uint32_t)p.list_cap / 8u;
       const uint32_t seg_cap1 = ((uint32_t)p.list_cap - spill_cap1) / NW;
       const WarpSegCands<NT> src{list + (size_t)warp * seg_cap1, fin_wn, list + (size_t)NW * seg_cap1, fin_sn};
-      cta_finish<NT>(src, need, hi, pfx, idx_bits, cx.hist(0), ctrl, out_idx, out_key, (uint32_t)kK - need,
-                     cx.idx_offset, p.status, cx.page);
+      cta_finish<NT>(src, need, low_end(fin_lo), high_end(fin_cap), high_end(fin_focus), fin_hist, idx_bits, cx.hist(0),
+                     ctrl, out_idx, out_key,
+                     (uint32_t)kK - need, cx.idx_offset, p.status, cx.page);
     } else {
+      // every candidate shares the key prefix P above bit `sh` of the key (sampled path: range known)
+      const int sh = r < 0 ? 0 : round_shift(r);
+      const uint64_t lo = r < 0 ? low_end(fin_lo) : ((uint64_t)P << (32 + sh));
+      const uint64_t cap = r < 0 ? high_end(fin_cap) : (lo | ((1ull << (32 + sh)) - 1ull));
       const DenseCands<NT> src{cx.cand, (int)min(ctrl->cand_count, (uint32_t)p.cand_cap)};
-      cta_finish<NT>(src, need, hi, pfx, idx_bits, cx.hist(0), ctrl, out_idx, out_key, (uint32_t)kK - need,
+      cta_finish<NT>(src, need, lo, cap, cap, false, idx_bits, cx.hist(0), ctrl, out_idx, out_key, (uint32_t)kK - need,
                      cx.idx_offset, p.status, cx.page);
     }
   }
+  FFTOPK_MARK(34);
   if (finish_first) cluster_sync(cluster, C);
   FFTOPK_MARK(7);
   if (tid == 0 && p.status && mode == kModeAbort) atomicOr(p.status, (uint32_t)FFTOPK_ST_INTERNAL);
