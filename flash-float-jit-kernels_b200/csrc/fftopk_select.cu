@@ -138,13 +138,16 @@ __device__ __noinline__ void spill_push(Ctrl* ctrl, uint64_t* spill, uint32_t sp
 // hits together, one hit per lane and loop trip, and a ballot gives each its slot - no atomic, and
 // the segment's length lives in a register that is the same in all lanes. (Allocating from one
 // shared counter serialised at ~20 cycles per candidate; slots private to a thread left more than
-// half of the list empty, and every later pass paid for the empty slots.) The value of a hit is
-// fetched again (an L1/L2 hit) instead of being selected out of 4*U registers by a computed
-// index, and stored raw; a dense pass converts the segment afterwards. Candidates beyond the
-// segment's capacity go to the shared spill area.
+// half of the list empty, and every later pass paid for the empty slots.) A hit's value cannot be
+// selected out of 4*U registers by a computed index, so it is fetched again. kStage = false does
+// that inside the hit loop (the loads of the warps of a CTA overlap; best when hits are few and
+// the latency of one call counts); kStage = true stores only the row index there and fetches all
+// values in the dense pass that builds the composites afterwards, several loads in flight per
+// lane (best when most trips have hits: a dependent load per trip of the hit loop would stall
+// the warp each time). Candidates beyond the segment's capacity go to the shared spill area.
 // Returns the number of candidates the warp found (those beyond seg_cap went to the spill area);
 // kmax is the largest key among the entries this lane converted; post(key) is called for each of them.
-template <int NT, int U, class Post>
+template <int NT, int U, bool kStage, class Post>
 __device__ __forceinline__ uint32_t filter_shard(const Shard& sh, float edge, uint64_t* seg, uint32_t seg_cap, Ctrl* ctrl,
                                                  uint64_t* spill, uint32_t spill_cap, uint32_t& kmax, Post&& post) {
   const int tid = threadIdx.x;
@@ -154,20 +157,25 @@ __device__ __forceinline__ uint32_t filter_shard(const Shard& sh, float edge, ui
   const float4* base4 = reinterpret_cast<const float4*>(sh.gbase);
   const int fa = sh.a, fi1 = sh.i1, len = sh.len;
   uint32_t wcnt = 0;  // candidates of this warp so far (warp-uniform)
-  auto keep = [&](bool has, uint32_t bits, int idx) {  // called by the whole warp
+  const uint32_t* base1 = reinterpret_cast<const uint32_t*>(sh.gbase);
+  uint32_t* seg32 = reinterpret_cast<uint32_t*>(seg);  // staging: candidate j's row index in word j
+  auto keep = [&](bool has, int idx) {  // called by the whole warp
     const unsigned b = __ballot_sync(kFull, has);
     if (has) {
       const uint32_t pos = wcnt + (uint32_t)__popc(b & lt);
-      const uint64_t raw = ((uint64_t)bits << 32) | (uint64_t)(uint32_t)idx;
-      if (pos < seg_cap) {
-        seg[pos] = raw;
+      if (kStage && pos < seg_cap) {
+        seg32[pos] = (uint32_t)idx;
       } else {
-        spill_push(ctrl, spill, spill_cap, raw);
+        const uint64_t raw = ((uint64_t)__ldg(base1 + idx + fa) << 32) | (uint64_t)(uint32_t)idx;
+        if (pos < seg_cap) {
+          seg[pos] = raw;
+        } else {
+          spill_push(ctrl, spill, spill_cap, raw);
+        }
       }
     }
     wcnt += (uint32_t)__popc(b);
   };
-  const uint32_t* base1 = reinterpret_cast<const uint32_t*>(sh.gbase);
   // one trip over granules gb + u*NT + tid, u < U; a `full` trip lies inside the shard entirely
   auto trip = [&](int gb, auto full) {
     float4 x[U];
@@ -201,10 +209,7 @@ __device__ __forceinline__ uint32_t filter_shard(const Shard& sh, float edge, ui
       const bool has = mask != 0u;
       const int bit = __ffs(mask) - 1;
       mask &= mask - 1u;
-      const int el = el0 + (bit >> 2) * (4 * NT) + (bit & 3);
-      uint32_t bits = 0u;
-      if (has) bits = __ldg(base1 + el);
-      keep(has, bits, el - fa);
+      keep(has, el0 + (bit >> 2) * (4 * NT) + (bit & 3) - fa);
     }
   };
   int gb = sh.i0;
@@ -222,17 +227,44 @@ __device__ __forceinline__ uint32_t filter_shard(const Shard& sh, float edge, ui
       const float xv[4] = {x.x, x.y, x.z, x.w};
 #pragma unroll
       for (int e = 0; e < 4; ++e)
-        keep(mine && (unsigned)(e0 + e) < (unsigned)len && !(xv[e] < edge), __float_as_uint(xv[e]), e0 + e);
+        keep(mine && (unsigned)(e0 + e) < (unsigned)len && !(xv[e] < edge), e0 + e);
     }
   }
-  // dense conversion of the warp's segment
+  // Dense conversion of the warp's segment.
   kmax = 0u;
   const uint32_t own = min(wcnt, seg_cap);
   __syncwarp();
-  for (uint32_t j = lane; j < own; j += 32) {
-    const uint64_t c = raw_to_composite(seg[j], kmax);
-    seg[j] = c;
-    post((uint32_t)(c >> 32));
+  if constexpr (kStage) {
+    // Fetch the values again (L1/L2 hits, four loads in flight per lane) and expand the staged
+    // indices into composites in place, from the top down: the composites of entries
+    // [j0, j0 + 128) cover words [2*j0, 2*j0 + 256), which holds no index not yet read.
+    for (int j0 = (int)((own + 127u) & ~127u) - 128; j0 >= 0; j0 -= 128) {
+      uint32_t idx[4], bits[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const uint32_t j = (uint32_t)j0 + 32u * u + lane;
+        idx[u] = j < own ? seg32[j] : 0u;
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) bits[u] = __ldg(base1 + idx[u] + fa);  // (index 0 is always readable)
+      __syncwarp();
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const uint32_t j = (uint32_t)j0 + 32u * u + lane;
+        if (j < own) {
+          const uint64_t c = raw_to_composite(((uint64_t)bits[u] << 32) | idx[u], kmax);
+          seg[j] = c;
+          post((uint32_t)(c >> 32));
+        }
+      }
+      __syncwarp();
+    }
+  } else {
+    for (uint32_t j = lane; j < own; j += 32) {
+      const uint64_t c = raw_to_composite(seg[j], kmax);
+      seg[j] = c;
+      post((uint32_t)(c >> 32));
+    }
   }
   return wcnt;
 }
@@ -1140,10 +1172,14 @@ __global__ void __launch_bounds__(NT, (NT == 512 ? FFTOPK_CTAS_512 : 1024 / NT))
         __syncthreads();
       }
       uint32_t* fh = cx.hist(0);
-      const uint32_t wcnt = filter_shard<NT, (NT >= 1024 ? 4 : 8)>(
-          sh, edge, seg, seg_cap, ctrl, spill, spill_cap, kmax, [&](uint32_t key) {
-            if (fin_hist) red_shared_add(&fh[make_finish_digit(low_end(fin_lo), high_end(fin_focus)).of_key(key)], 1u);
-          });
+      auto round0 = [&](uint32_t key) {
+        if (fin_hist) red_shared_add(&fh[make_finish_digit(low_end(fin_lo), high_end(fin_focus)).of_key(key)], 1u);
+      };
+      constexpr int U = NT >= 1024 ? 4 : 8;
+      // about 1.5 k candidates per row: up to ~192K elements most trips of the hit loop have work
+      const bool stage = len <= 196608;
+      const uint32_t wcnt = stage ? filter_shard<NT, U, true>(sh, edge, seg, seg_cap, ctrl, spill, spill_cap, kmax, round0)
+                                  : filter_shard<NT, U, false>(sh, edge, seg, seg_cap, ctrl, spill, spill_cap, kmax, round0);
       FFTOPK_MARK(8);
       const uint32_t wown = min(wcnt, seg_cap);
       fin_wn = (int)wown;
@@ -1293,7 +1329,12 @@ constexpr size_t fixed_smem_bytes() {
 
 constexpr int kLatencyListCap = 6144, kLatencyCandCap = 16384;  // one CTA per SM: use the shared memory
 constexpr int kBatchListCap = 4096, kBatchCandCap = 4096;       // several CTAs per SM
-constexpr int kOverlapListCap1 = 9216;                          // one CTA per row: list = candidates
+// One CTA per row (list = candidates), two CTAs per SM. Rows of up to ~192K elements leave about
+// 3600 candidates; with the small list two CTAs take 2 x 90 KB of the SM's 256 KB and the rest
+// stays L1, which the value re-reads of the filter hit (measured on B=64 ragged rows <= 128K:
+// 5.3 us per call with lists of 4608..7168 entries, 6.2 us with 8192 or more).
+constexpr int kOverlapListCap1 = 6144, kOverlapListCap1Long = 9216;
+constexpr int64_t kOverlapShortRow = 196608;
 constexpr int kOverlapListCap = 3072, kOverlapCandCap = 6144;   // two CTAs per SM
 
 
@@ -1385,7 +1426,7 @@ Plan make_plan(const DeviceInfo& d, int B, int64_t L) {
     if (ct < pl.cluster) pl.cluster = ct;
     pl.threads = 512;
     if (pl.cluster == 1) {
-      pl.list_cap = kOverlapListCap1;
+      pl.list_cap = L <= kOverlapShortRow ? kOverlapListCap1 : kOverlapListCap1Long;
     } else {
       pl.list_cap = kOverlapListCap;
       pl.cand_cap = kOverlapCandCap;
