@@ -136,10 +136,7 @@ struct Ctrl {
   uint32_t totb[kSup];  // first sample round: super-bin totals of the second (finer) histogram
   uint32_t dual_b;      // ... whether the finer histogram was usable, and for which top nibble
   uint32_t dual_g;
-  uint32_t need_hi;       // first sample round of a lone CTA: sample rank that bounds the threshold from
-  int32_t sup_sel_hi;     // above, the super-bin it falls in, the sample elements above that super-bin,
-  uint32_t sup_above_hi;  // and the bin found for it (-1: none)
-  int32_t focus_bin;
+  int32_t focus_bin;    // first sample round of a lone CTA: bin the threshold will not lie above (-1: none)
   uint32_t wtot[32];
   uint32_t wmax[32];
   uint64_t small[kSmall];

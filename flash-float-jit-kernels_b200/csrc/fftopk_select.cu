@@ -179,7 +179,8 @@ __device__ __forceinline__ uint32_t filter_shard(const Shard& sh, float edge, ui
   // one trip over granules gb + u*NT + tid, u < U; a `full` trip lies inside the shard entirely
   auto trip = [&](int gb, auto full) {
     float4 x[U];
-    uint32_t vmask = ~0u;
+    using Mask = std::conditional_t<(U > 8), uint64_t, uint32_t>;
+    Mask vmask = ~(Mask)0;
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int g = gb + u * NT + tid;
@@ -190,25 +191,25 @@ __device__ __forceinline__ uint32_t filter_shard(const Shard& sh, float edge, ui
         if (g < fi1) {
           x[u] = __ldg(base4 + g);
         } else {
-          vmask &= ~(0xfu << (4 * u));  // (padding would pass an edge of -inf)
+          vmask &= ~((Mask)0xfu << (4 * u));  // (padding would pass an edge of -inf)
         }
       }
     }
     // pass mask of this thread's 4*U elements: bit 4u+e
-    uint32_t mask = 0;
+    Mask mask = 0;
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      if (!(x[u].x < edge)) mask |= 1u << (4 * u);
-      if (!(x[u].y < edge)) mask |= 2u << (4 * u);
-      if (!(x[u].z < edge)) mask |= 4u << (4 * u);
-      if (!(x[u].w < edge)) mask |= 8u << (4 * u);
+      if (!(x[u].x < edge)) mask |= (Mask)1u << (4 * u);
+      if (!(x[u].y < edge)) mask |= (Mask)2u << (4 * u);
+      if (!(x[u].z < edge)) mask |= (Mask)4u << (4 * u);
+      if (!(x[u].w < edge)) mask |= (Mask)8u << (4 * u);
     }
     if constexpr (!decltype(full)::value) mask &= vmask;
     const int el0 = 4 * (gb + tid);
-    while (__any_sync(kFull, mask != 0u)) {
-      const bool has = mask != 0u;
-      const int bit = __ffs(mask) - 1;
-      mask &= mask - 1u;
+    while (__any_sync(kFull, mask != 0)) {
+      const bool has = mask != 0;
+      const int bit = (sizeof(Mask) == 8 ? __ffsll((long long)mask) : __ffs((int)mask)) - 1;
+      mask &= mask - 1;
       keep(has, el0 + (bit >> 2) * (4 * NT) + (bit & 3) - fa);
     }
   };
@@ -489,6 +490,51 @@ __device__ __forceinline__ DualPick cluster_pick_dual(cg::cluster_group& cluster
   const int tid = threadIdx.x;
   const int lane = tid & 31, warp = tid >> 5;
   constexpr int fine = kMaxBins / kSup;
+  if (C == 1) {
+    // A lone CTA has nothing to exchange: one warp reads the super-bin sums, picks, reads the fine
+    // bins of the super-bins it needs and picks again; one block barrier publishes the result.
+    // (The totals buffers stay untouched, so the search counter does not advance.)
+    // It also brackets the threshold from above: the bin of the mirror-image sample rank, which
+    // the true threshold lies below with the same confidence. The finish then spends its first
+    // digit between the two bins instead of on the whole range up to the row's maximum.
+    if (warp == 0) {
+      const uint32_t lo = sa[2 * lane], hi = sa[2 * lane + 1];
+      const uint32_t total = warp_sum(lo + hi);
+      const uint32_t need = need_of(total);
+      const uint32_t need_hi = need_hi_of(total);
+      int ts = -1, ts_hi = -1, tf = -1, focus_bin = -1;
+      uint32_t above = 0, cnt = 0, above_hi = 0, cnt_hi = 0, above_f = 0, cnt_t = 0;
+      bool ok = need > 0 && warp_pick64(lo, hi, need, ts, above, cnt);
+      if (ok) {
+        const uint32_t flo = ha[ts * fine + 2 * lane], fhi = ha[ts * fine + 2 * lane + 1];
+        ok = warp_pick64(flo, fhi, need - above, tf, above_f, cnt_t);
+        if (ok && need_hi > 0 && warp_pick64(lo, hi, need_hi, ts_hi, above_hi, cnt_hi)) {
+          int tf_hi = -1;
+          uint32_t a2 = 0, c2 = 0;
+          const uint32_t glo = ha[ts_hi * fine + 2 * lane], ghi = ha[ts_hi * fine + 2 * lane + 1];
+          if (warp_pick64(glo, ghi, need_hi - above_hi, tf_hi, a2, c2)) focus_bin = ts_hi * fine + tf_hi;
+        }
+      }
+      if (lane == 0) {
+        ctrl->t = ok ? ts * fine + tf : -1;
+        ctrl->above = ok ? need - above - above_f : 0u;
+        ctrl->cnt = cnt_t;
+        ctrl->run_total = total;
+        ctrl->focus_bin = focus_bin;
+      }
+    }
+    __syncthreads();
+    FFTOPK_MARK(43);
+    DualPick d;
+    d.focus_bin = ctrl->focus_bin;
+    d.ok = ctrl->t >= 0;
+    d.pbits = 12;
+    d.prefix = (uint32_t)ctrl->t;
+    d.need2 = ctrl->above;
+    d.cnt = ctrl->cnt;
+    d.total = ctrl->run_total;
+    return d;
+  }
   uint32_t* tot = ctrl->tot[pick_no & 1];
   uint32_t* tot2 = ctrl->tot2[pick_no & 1];
   for (int i = tid; i < C * kSup; i += NT) {
@@ -516,17 +562,7 @@ __device__ __forceinline__ DualPick cluster_pick_dual(cg::cluster_group& cluster
     int ts = -1;
     const uint32_t plo = use_b ? lob : lo, phi = use_b ? hib : hi;
     const bool ok = need > 0 && warp_pick64(plo, phi, need, ts, above, cnt);
-    // A lone CTA (the throughput plan) also brackets the threshold from above: the bin of a sample
-    // rank the true threshold lies below with the same confidence. The finish then spends its
-    // first digit between the two bins instead of on the whole range up to the row's maximum.
-    uint32_t need_hi = C == 1 ? need_hi_of(total) : 0u;
-    int ts_hi = -1;
-    uint32_t above_hi = 0, cnt_hi = 0;
-    if (need_hi > 0 && !warp_pick64(plo, phi, need_hi, ts_hi, above_hi, cnt_hi)) ts_hi = -1;
     if (lane == 0) {
-      ctrl->need_hi = need_hi;
-      ctrl->sup_sel_hi = ts_hi;
-      ctrl->sup_above_hi = above_hi;
       ctrl->sup_sel = ok ? ts : -1;
       ctrl->sup_above = above;
       ctrl->need = need;
@@ -562,27 +598,16 @@ __device__ __forceinline__ DualPick cluster_pick_dual(cg::cluster_group& cluster
       const uint32_t lo = tot2[2 * lane], hi = tot2[2 * lane + 1];
       ok = warp_pick64(lo, hi, ctrl->need - ctrl->sup_above, tf, above_f, cnt_t);
     }
-    int focus_bin = -1;
-    const int ssel_hi = ctrl->sup_sel_hi;
-    if (ok && ssel_hi == ssel) {
-      const uint32_t lo = tot2[2 * lane], hi = tot2[2 * lane + 1];
-      int tf_hi = -1;
-      uint32_t a2 = 0, c2 = 0;
-      if (warp_pick64(lo, hi, ctrl->need_hi - ctrl->sup_above_hi, tf_hi, a2, c2)) focus_bin = ssel * fine + tf_hi;
-    } else if (ok && ssel_hi > ssel) {
-      focus_bin = ssel_hi * fine + (fine - 1);
-    }
     if (lane == 0) {
       ctrl->t = ok ? ssel * fine + tf : -1;
       ctrl->above = ok ? ctrl->need - ctrl->sup_above - above_f : 0u;
       ctrl->cnt = cnt_t;
-      ctrl->focus_bin = focus_bin;
     }
   }
   __syncthreads();
   FFTOPK_MARK(43);
   DualPick d;
-  d.focus_bin = ctrl->focus_bin;
+  d.focus_bin = -1;
   d.ok = ctrl->t >= 0;
   d.pbits = use_b ? 16 : 12;
   d.prefix = use_b ? ((ctrl->dual_g << 12) | (uint32_t)ctrl->t) : (uint32_t)ctrl->t;
@@ -922,7 +947,10 @@ __global__ void __launch_bounds__(NT, (NT == 512 ? FFTOPK_CTAS_512 : 1024 / NT))
   sh.i1 = max(sh.i0, min(sh.g1, ((sh.a + len) & 3) ? gn - 1 : gn));
   const int n_g = sh.g1 - sh.g0;
   // Whole shard in registers (same answer in every CTA of the cluster: `per` is rank-independent).
-  const bool exact = per <= NT * kRegSlabs;
+#ifndef FFTOPK_EXACT_SLABS
+#define FFTOPK_EXACT_SLABS kRegSlabs
+#endif
+  const bool exact = per <= NT * FFTOPK_EXACT_SLABS;
   // A second, finer sample histogram (see cluster_pick_dual) saves a cluster-wide sample round on
   // crowded data. A lone CTA does that round without any cluster traffic, and only when it is
   // needed, which costs it less than building the second histogram for every row.
@@ -1175,7 +1203,10 @@ __global__ void __launch_bounds__(NT, (NT == 512 ? FFTOPK_CTAS_512 : 1024 / NT))
       auto round0 = [&](uint32_t key) {
         if (fin_hist) red_shared_add(&fh[make_finish_digit(low_end(fin_lo), high_end(fin_focus)).of_key(key)], 1u);
       };
-      constexpr int U = NT >= 1024 ? 4 : 8;
+#ifndef FFTOPK_U512
+#define FFTOPK_U512 8
+#endif
+      constexpr int U = NT >= 1024 ? 4 : FFTOPK_U512;
       // about 1.5 k candidates per row: up to ~192K elements most trips of the hit loop have work
       const bool stage = len <= 196608;
       const uint32_t wcnt = stage ? filter_shard<NT, U, true>(sh, edge, seg, seg_cap, ctrl, spill, spill_cap, kmax, round0)
