@@ -52,7 +52,7 @@ N_ROTATE = 8
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one select2048 launch on this workload, from the
 # ncu capture summarised in profiles/ (None until a capture exists)
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 16754688  # profiles/select2048_ragged_b64.md (throughput plan)
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 16774315  # profiles/select2048_ragged_b64.md (throughput plan, mean of 3 launches)
 
 
 def measured_peak_gbs():
@@ -462,7 +462,8 @@ def ours_arm(args, rank: int, local_rank: int, world: int) -> None:
 def profile_case(name: str) -> None:
     """Small fixed cases for profiler captures (`--case`): a few launches, one JSON line.
     b1: B=1, L=1M decode call, eight rotated 4 MiB inputs. merge: the 8-shard candidate merge of a
-    B=4 batch (shards selected one after the other on this device)."""
+    B=4 batch (shards selected one after the other on this device). tp / serial: the bench's ragged
+    B=64 batch in the throughput plan / the default plan, 12 launches over 8 rotated inputs."""
     from jit_kernel.distributed import _cuda_select, local_lengths, merge_candidates
     from jit_kernel.topk_indexer import fast_topk
 
@@ -477,6 +478,18 @@ def profile_case(name: str) -> None:
             fast_topk(bufs[i % 40], out, ld)
         torch.cuda.synchronize()
         print(json.dumps({"case": "b1", "launches": 43, "plan": __import__("jit_kernel._native", fromlist=["x"]).plan(1, 1 << 20)}))
+    elif name in ("tp", "serial"):
+        from jit_kernel import _native
+        _native.set_overlap(name == "tp")
+        score, lengths = workloads.c3()
+        bufs = [torch.roll(score, i, 0).contiguous().to(dev) for i in range(8)]  # 256 MiB > L2
+        lens = [torch.roll(lengths, i, 0).contiguous().to(dev) for i in range(8)]
+        out = torch.empty(score.size(0), K, dtype=torch.int32, device=dev)
+        for i in range(12):
+            fast_topk(bufs[i % 8], out, lens[i % 8])
+        torch.cuda.synchronize()
+        print(json.dumps({"case": name, "launches": 12, "plan": _native.plan(score.size(0), score.size(1))}))
+        _native.set_overlap(False)
     else:
         score, lengths = workloads.c5()
         G, Ls = 8, score.size(1) // 8
@@ -496,7 +509,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=50)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip the latency sweep and the CPU baseline")
-    ap.add_argument("--case", default=None, choices=["b1", "merge"], help="run one small fixed case (for profilers)")
+    ap.add_argument("--case", default=None, choices=["b1", "merge", "tp", "serial"], help="run one small fixed case (for profilers)")
     args = ap.parse_args()
     if args.case:
         profile_case(args.case)
