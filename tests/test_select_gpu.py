@@ -313,3 +313,67 @@ def test_cuda_graph_capture_and_replay():
     graph.replay()
     torch.cuda.synchronize()
     orc.check_result(s.numpy(), ln.numpy(), out.cpu().numpy(), what="graph replay")
+
+
+def _awkward_rows(L, seed):
+    """Rows that stress the sampled path of a lone CTA: what the sample sees is not what decides."""
+    g = torch.Generator().manual_seed(seed)
+    rows = []
+    base = torch.randn(L, generator=g)
+    # windows of ~1900 winners at several offsets: some fall between the sampled slabs, so the
+    # threshold lies above anything the sample suggested (the last bin of the finish's first digit)
+    for off in (130, 777, 1500, 2300, 5000, 40001):
+        off = min(off, L - 1900)
+        r = base.clone()
+        r[off:off + 1900] = 100.0 + torch.rand(1900, generator=g)
+        rows.append(r)
+    # the same with exact duplicates inside the window (ties decided by index)
+    r = base.clone()
+    r[3000:4900] = 50.0
+    rows.append(r)
+    # sum of weighted relu heads (one sign), bf16-rounded values (many ties), two values only
+    heads = torch.relu(torch.randn(16, L, generator=g)) * torch.rand(16, 1, generator=g)
+    rows.append(heads.sum(0))
+    rows.append(base.to(torch.bfloat16).to(torch.float32))
+    rows.append((torch.rand(L, generator=g) < 0.01).to(torch.float32))
+    rows.append(torch.full((L,), 3.0))
+    # sorted rows: every winner at one end
+    rows.append(torch.arange(L, dtype=torch.float32) * 1e-3)
+    rows.append(torch.arange(L, dtype=torch.float32).flip(0) * 1e-3)
+    # negative values only, and a row whose winners straddle zero
+    rows.append(-torch.rand(L, generator=g) - 1.0)
+    r = -torch.rand(L, generator=g)
+    r[::97] = torch.rand(r[::97].numel(), generator=g)
+    rows.append(r)
+    return torch.stack(rows).contiguous()
+
+
+@pytest.mark.parametrize("L", [9000, 40000, 131072, 250000])
+@pytest.mark.parametrize("overlap", [True, False])
+def test_awkward_rows_in_both_launch_plans(L, overlap):
+    """Throughput plan (one 512-thread CTA per row, finish over the warps' segments with a focused
+    first digit) and default plan on rows whose sample is misleading."""
+    s = _awkward_rows(L, seed=L)
+    ln = torch.full((s.size(0),), L, dtype=torch.int32)
+    ln[1] = L - 3
+    ln[2] = L // 2 + 1
+    pad = 64 - s.size(0) if overlap else 0  # the throughput plan uses one CTA per row from 38 rows on
+    if pad:
+        s = torch.cat([s, torch.randn(pad, L, generator=torch.Generator().manual_seed(L + 1))])
+        ln = torch.cat([ln, torch.randint(2049, L + 1, (pad,), generator=torch.Generator().manual_seed(L + 2), dtype=torch.int32)])
+    _native.set_overlap(overlap)
+    try:
+        if overlap:
+            assert _native.plan(s.size(0), L)["cluster_ctas"] == 1
+        check(s, ln, what=f"awkward rows L={L} overlap={overlap}")
+    finally:
+        _native.set_overlap(False)
+
+
+@pytest.mark.parametrize("list_cap", [2304, 3072])
+def test_lone_cta_segment_overflow(list_cap):
+    """Warp segments too small for the candidates: the spill area, then the full-histogram path."""
+    _native.set_tuning(cluster_ctas=1, threads=512, list_cap=list_cap)
+    s, ln = workloads.c3(B=8, L=131072)
+    check(s, ln, what=f"lone CTA list_cap={list_cap}")
+    check(_awkward_rows(60000, 5), torch.full((15,), 60000, dtype=torch.int32), what=f"lone CTA awkward list_cap={list_cap}")
