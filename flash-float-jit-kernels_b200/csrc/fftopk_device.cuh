@@ -19,7 +19,10 @@ constexpr int kSup = 64;               // super-bins per histogram (each sums kM
 constexpr int kMaxCluster = 16;        // CTAs per row (non-portable cluster size on B200)
 constexpr int kFinishBits = 11;        // digit width of the single-CTA finish
 constexpr int kFinishBins = 1 << kFinishBits;
-constexpr int kSmall = 32;             // candidates resolved by one warp's compare-exchange network
+#ifndef FFTOPK_KSMALL
+#define FFTOPK_KSMALL 256
+#endif
+constexpr int kSmall = FFTOPK_KSMALL;            // undecided candidates that are ranked directly instead of another radix round
 constexpr unsigned kFull = 0xffffffffu;
 
 __device__ __forceinline__ int lane_id() { return threadIdx.x & 31; }
@@ -330,7 +333,7 @@ __device__ __forceinline__ FinishDigit make_finish_digit(uint64_t lo, uint64_t f
 // Replaces the reference's refinement rounds on shared-memory survivors and its CAS insertion
 // tail (topk_indexer_radix.cu:686-781, 109-141, 788-850). Because the index is part of the
 // composite, equal values are resolved towards the lower index by the same rounds, and the last
-// <= 32 undecided candidates are ranked by one vote each.
+// <= 256 undecided candidates are ranked by votes.
 // `focus`: see FinishDigit. `have_hist`: the caller has already built round 0's histogram in
 // `hist`, with make_finish_digit(lo, focus).
 // `idx_bits`: all indices are < 2^idx_bits, so the inverted-index bits above that are all ones.
@@ -380,7 +383,7 @@ __device__ void cta_finish(const Src& src, uint32_t need, uint64_t lo, uint64_t 
   }
   // ---- rounds: only the threshold is determined here; nothing is written yet ---------------------
   // Outcome: the threshold bin [t_lo, t_hi] of composites. Everything above t_hi wins; of the
-  // bin itself either everything wins (all_bin) or, when it holds <= 32 candidates, the best
+  // bin itself either everything wins (all_bin) or, when it holds <= kSmall candidates, the best
   // `need2` of them, found by ranking.
   const uint32_t need_total = need;
   uint64_t t_lo = 0ull, t_hi = 0ull;
@@ -498,15 +501,22 @@ __device__ void cta_finish(const Src& src, uint32_t need, uint64_t lo, uint64_t 
   FFTOPK_MARK(33);
   if (!all_bin) {
     __syncthreads();
-    // Rank by vote: warp i takes candidate i, every lane j compares it with candidate j; the
-    // number of larger ones is candidate i's rank, and the best need2 go behind the certain
-    // winners. (A 15-stage bitonic compare-exchange network over the same 32 values is a chain
-    // of 60 dependent shuffles; this is one ballot each.)
-    const uint64_t other = (lane < (int)cnt) ? ctrl->small[lane] : 0ull;
+    // Rank by vote: warp i takes candidate i, the lanes compare it with the candidates j (32 per
+    // step); the number of larger ones is candidate i's rank, and the best need2 go behind the
+    // certain winners. Up to 256 undecided candidates are cheaper to rank like this (at most 64
+    // votes per warp) than to split by another round - rows of low-precision logits have
+    // hundreds of exact duplicates at the threshold. (A bitonic compare-exchange network over 32
+    // values is a chain of 60 dependent shuffles; this is one ballot per 32 comparisons.)
     const uint32_t certain = need_total - need2;
+    const int nchunk = ((int)cnt + 31) >> 5;
     for (int i = warp; i < (int)cnt; i += NT / 32) {
       const uint64_t me = ctrl->small[i];
-      const uint32_t rank = (uint32_t)__popc(__ballot_sync(kFull, other > me));
+      uint32_t rank = 0;
+      for (int ch = 0; ch < nchunk; ++ch) {
+        const int j = ch * 32 + lane;
+        const uint64_t other = (j < (int)cnt) ? ctrl->small[j] : 0ull;
+        rank += (uint32_t)__popc(__ballot_sync(kFull, other > me));
+      }
       if (lane == 0 && rank < need2) {
         const uint32_t pos = out_base + certain + rank;
         if (pos < (uint32_t)kK) {

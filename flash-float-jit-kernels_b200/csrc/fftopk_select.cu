@@ -6,24 +6,27 @@
 //
 // Shape of the computation for one row of `len` > 2048 valid fp32 logits, C CTAs in the cluster,
 // each owning a contiguous shard of the row:
-//   1. SAMPLE. Every warp reads one 512-byte slab; the slabs are spread evenly over the shards,
-//      so the cluster samples the row uniformly in position. The top 12 bits of the
-//      order-preserving key are histogrammed per CTA (4096 bins). When the whole shard fits in
-//      registers (<= 4 granules per thread) the "sample" is the shard and step 2 is exact.
+//   1. SAMPLE. Every warp reads one to four 512-byte slabs; the slabs are spread evenly over the
+//      shards, so the cluster samples the row uniformly in position. The top 12 bits of the
+//      order-preserving key are histogrammed per CTA (4096 bins); a cluster also histograms key
+//      bits [27:16], which give a 16-bit guess when the whole sample shares its top four key bits.
+//      When the whole shard fits in registers (<= 4 granules per thread) the "sample" is the
+//      shard and step 2 is exact.
 //   2. PICK. After ONE cluster barrier every CTA reads its peers' 64 super-bin sums, then the 64
 //      fine bins of the threshold super-bin, over distributed shared memory, and finds the bin
 //      with a warp-shuffle suffix scan (no L2 atomics, no reduce-then-broadcast). From a sample it
 //      takes the bin whose sample rank is the expected rank of the k-th element plus five standard
-//      deviations: a lower bound of the true threshold with overwhelming probability.
-//   3. FILTER. One streaming pass over the shard (128-bit loads, eight in flight per thread) with
-//      ONE float compare per element against the bin's lower edge; the few thousand elements that
-//      pass go to a per-CTA list in shared memory as (key << 32 | ~index) composites. This is the
-//      only full read of the row.
-//   4. RESOLVE. The lists are histogrammed, a second cluster pick gives the exact threshold bin,
-//      elements above it are written straight to the output, the threshold bin's elements are
-//      pushed into rank 0's shared memory, and after the last cluster barrier rank 0 finishes with
-//      radix passes over the composites and a warp compare-exchange network for the last <= 32.
-//      The inverted index in the composite makes equal values resolve to the lower index.
+//      deviations: a lower bound of the true threshold with overwhelming probability. A lone CTA
+//      does all of this in one warp and also finds the mirror-image upper bound.
+//   3. FILTER. One streaming pass over the shard (128-bit loads, four or eight in flight per
+//      thread) with ONE float compare per element against the bin's lower edge; the few thousand
+//      elements that pass are appended, by ballot, to dense per-warp segments of a list in shared
+//      memory and become (key << 32 | ~index) composites. This is the only full read of the row.
+//   4. GATHER + FINISH. The segments are copied into rank 0's shared memory (one remote atomic per
+//      CTA reserves the range), and after the second cluster barrier rank 0 finishes: radix rounds
+//      over the composites' range, one fused output pass, and the last <= 256 undecided
+//      candidates ranked by votes. A lone CTA finishes over its segments where they lie. The
+//      inverted index in the composite makes equal values resolve to the lower index.
 //   5. If the guess admitted fewer than k elements, a list overflowed or the threshold bin is
 //      larger than rank 0's buffer (heavy ties, rows of equal values), the cluster falls back to
 //      full histograms over the data: 12 + 12 + 8 key bits, re-reading the shard from L2 each
@@ -1514,8 +1517,8 @@ int fftopk_set_tuning(int32_t cluster_ctas, int32_t threads, int32_t list_cap, i
                       int32_t force_full_histogram) {
   if (cluster_ctas > 0 && (cluster_ctas > kMaxCluster || (cluster_ctas & (cluster_ctas - 1)))) return FFTOPK_EINVAL;
   if (threads > 0 && threads != 256 && threads != 512 && threads != 1024) return FFTOPK_EINVAL;
-  if (cand_cap > 0 && (cand_cap < kSmall || cand_cap > 16384)) return FFTOPK_EINVAL;
-  if (list_cap > 0 && (list_cap < kSmall || list_cap > 16384)) return FFTOPK_EINVAL;
+  if (cand_cap > 0 && (cand_cap < 32 || cand_cap > 16384)) return FFTOPK_EINVAL;
+  if (list_cap > 0 && (list_cap < 32 || list_cap > 16384)) return FFTOPK_EINVAL;
   g_tuning.cluster = cluster_ctas;
   g_tuning.threads = threads;
   g_tuning.list_cap = list_cap;
