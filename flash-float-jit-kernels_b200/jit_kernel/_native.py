@@ -38,6 +38,8 @@ EXPORTS = (
     "fftopk_select2048_cp",
     "fftopk_merge2048_cp",
     "fftopk_topk2048_sliced_noalloc",
+    "fftopk_host_workspace_bytes",
+    "fftopk_select2048_host",
     "fftopk_key_of",
     "fftopk_plan",
     "fftopk_set_tuning",
@@ -113,6 +115,11 @@ def lib() -> ctypes.CDLL:
     L.fftopk_topk2048_sliced_noalloc.restype = c.c_int
     L.fftopk_topk2048_sliced_noalloc.argtypes = [c.c_void_p, c.c_int64, c.c_int32, c.c_int64, c.c_void_p, c.c_int32,
                                                  c.c_void_p, c.c_void_p, c.c_void_p]
+    L.fftopk_host_workspace_bytes.restype = c.c_size_t
+    L.fftopk_host_workspace_bytes.argtypes = [c.c_int32, c.c_int64]
+    L.fftopk_select2048_host.restype = c.c_int
+    L.fftopk_select2048_host.argtypes = [c.c_void_p, c.c_int64, c.c_int32, c.c_int64, c.c_void_p, c.c_void_p,
+                                         c.c_void_p, c.c_size_t, c.c_void_p, c.c_void_p]
     L.fftopk_key_of.restype = c.c_uint32
     L.fftopk_key_of.argtypes = [c.c_float]
     L.fftopk_plan.restype = c.c_int

@@ -118,6 +118,60 @@ def fast_topk_v3(
     return topk_indices
 
 
+_host_workspaces = {}
+
+
+def fast_topk_v3_host(
+    score: torch.Tensor,
+    lengths: torch.Tensor,
+    topk: int,
+    out: Optional[torch.Tensor] = None,
+    device=None,
+) -> torch.Tensor:
+    """fast_topk_v3 for a caller whose tensors are in HOST memory (no counterpart in the reference,
+    whose driver does score.cuda() / fast_topk_v3 / .cpu() itself, benchmark/bench_topk.py:90-146).
+
+    score (B, L) float32 and lengths (B) int32 are CPU tensors (pinned memory makes the copies
+    asynchronous); the result is an int32 CPU tensor (B, topk) - `out` if given. Only the valid
+    prefix of every row is copied to the device, so a ragged batch moves about half the bytes of
+    its padded matrix. Everything is enqueued on the current stream of `device`; the call returns
+    without synchronising: synchronise that stream before reading the result.
+    The device staging area is cached per (device, B, L).
+    """
+    assert topk == 2048, "fast_topk_v3_host only supports topk=2048"
+    if score.is_cuda or lengths.is_cuda:
+        raise RuntimeError("score and lengths must be CPU tensors")
+    if score.dtype != torch.float32 or lengths.dtype != torch.int32:
+        raise RuntimeError("score must be float32 and lengths int32")
+    if score.dim() != 2 or lengths.dim() != 1 or lengths.numel() != score.size(0):
+        raise RuntimeError("score must be (B, L) and lengths (B)")
+    if score.size(0) and score.size(1) and score.stride(1) != 1:
+        raise RuntimeError("score must have unit inner stride")
+    lengths = lengths.contiguous()
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    B, L = score.size(0), score.size(1)
+    if out is None:
+        out = torch.empty((B, topk), dtype=torch.int32, pin_memory=True)
+    elif out.is_cuda or out.dtype != torch.int32 or tuple(out.shape) != (B, topk) or not out.is_contiguous():
+        raise RuntimeError("out must be a contiguous int32 CPU tensor of shape (B, topk)")
+    if B == 0:
+        return out
+    lib = _native.lib()
+    nbytes = int(lib.fftopk_host_workspace_bytes(B, L))
+    ws = _host_workspaces.get((dev, B, L))
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(nbytes + 256, dtype=torch.uint8, device=dev)
+        _host_workspaces[(dev, B, L)] = ws
+    base = (ws.data_ptr() + 255) & ~255
+    with torch.cuda.device(dev):
+        stream = torch.cuda.current_stream(dev)
+        _native.check(
+            lib.fftopk_select2048_host(score.data_ptr(), score.stride(0) if B > 1 else L, B, L, lengths.data_ptr(),
+                                       out.data_ptr(), base, nbytes, _status_word(dev).data_ptr(), stream.cuda_stream),
+            "fftopk_select2048_host")
+    return out
+
+
 def fast_topk_transform_fused(
     score: torch.Tensor,
     lengths: torch.Tensor,

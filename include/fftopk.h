@@ -197,6 +197,26 @@ int fftopk_topk2048_sliced_noalloc(const float* score, int64_t row_stride, int32
                                    uint32_t* status, void* cuda_stream);
 
 /*
+ * The selector for a caller whose buffers are in HOST memory: score, lengths and the result.
+ * Replaces, for such a caller, the tensor.cuda() / fast_topk_v3 / .cpu() sequence of the
+ * reference's benchmark driver (benchmark/bench_topk.py:90-146) with one call that enqueues, on
+ * `cuda_stream`: host->device copies of the valid prefix of each row ONLY (lengths are read on the
+ * host; the padding of a ragged batch never crosses PCIe), fftopk_select2048, and the
+ * device->host copy of the indices. Returns once everything is enqueued; synchronise the stream
+ * before reading h_out_idx. Use pinned host memory for asynchronous copies.
+ *
+ *   h_score, h_row_stride, B, L, h_lengths   as for fftopk_select2048, but host pointers
+ *   h_out_idx      [B, 2048] int32, host
+ *   d_workspace    device staging area of at least fftopk_host_workspace_bytes(B, L) bytes,
+ *                  256-byte aligned; owned by the caller (nothing is allocated here)
+ *   d_status       optional device status word, as for fftopk_select2048
+ */
+size_t fftopk_host_workspace_bytes(int32_t B, int64_t L);
+int fftopk_select2048_host(const float* h_score, int64_t h_row_stride, int32_t B, int64_t L,
+                           const int32_t* h_lengths, int32_t* h_out_idx, void* d_workspace,
+                           size_t workspace_bytes, uint32_t* d_status, void* cuda_stream);
+
+/*
  * Radix key of one fp32 value, computed on the host with the same function the kernels use
  * (the order-preserving map the reference defines as convert_to_uint32,
  * topk_indexer_radix.cu:206-209, plus -0.0 / NaN canonicalisation). For tests and bindings.
