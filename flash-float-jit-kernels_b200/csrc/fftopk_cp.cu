@@ -147,7 +147,7 @@ __global__ void __launch_bounds__(NT, 1) merge2048_kernel(const MergeSrc src, in
     return;
   }
   const DenseCands<NT> all{cand, n};
-  cta_finish<NT>(all, (uint32_t)kK, 1ull, 0ull, 0ull, false, 31, hist, ctrl, out_idx, out_key, 0u, 0, status);  // range unknown
+  cta_finish<NT>(all, (uint32_t)kK, 1ull, 0ull, 0ull, false, 31, hist, ctrl, out_idx, out_key, 0u, (uint32_t)kK, 0, status);  // range unknown
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -14,6 +14,7 @@ namespace fftopk {
 namespace cg = cooperative_groups;
 
 constexpr int kK = 2048;               // reference: TopK (topk_indexer_radix.cu:69)
+constexpr int kMaxK = 4096;            // largest k of the general entry point (fftopk_select_topk)
 constexpr int kMaxBins = 4096;         // widest digit of the distributed rounds: 12 bits
 constexpr int kSup = 64;               // super-bins per histogram (each sums kMaxBins/64 bins)
 constexpr int kMaxCluster = 16;        // CTAs per row (non-portable cluster size on B200)
@@ -343,7 +344,8 @@ __device__ __forceinline__ FinishDigit make_finish_digit(uint64_t lo, uint64_t f
 template <int NT, class Src>
 __device__ void cta_finish(const Src& src, uint32_t need, uint64_t lo, uint64_t cap, uint64_t focus, bool have_hist,
                            int idx_bits, uint32_t* hist /* >= kFinishBins words */, Ctrl* ctrl, int32_t* out_idx,
-                           uint32_t* out_key, uint32_t out_base, int32_t idx_offset, uint32_t* status,
+                           uint32_t* out_key, uint32_t out_base, uint32_t out_slots /* k of the row */,
+                           int32_t idx_offset, uint32_t* status,
                            const int32_t* page = nullptr /* when set: out = page[idx] */) {
   const int tid = threadIdx.x;
   const int lane = tid & 31, warp = tid >> 5;
@@ -470,7 +472,7 @@ __device__ void cta_finish(const Src& src, uint32_t need, uint64_t lo, uint64_t 
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
           const uint32_t pos = base + (uint32_t)__popc(b[u] & lt);
-          if (c[u] > wthr && pos < (uint32_t)kK) {
+          if (c[u] > wthr && pos < out_slots) {
             const int32_t idx = (int32_t)(~(uint32_t)c[u]);
             if constexpr (decltype(paged)::value) {
               out_idx[pos] = __ldg(page + idx);
@@ -519,7 +521,7 @@ __device__ void cta_finish(const Src& src, uint32_t need, uint64_t lo, uint64_t 
       }
       if (lane == 0 && rank < need2) {
         const uint32_t pos = out_base + certain + rank;
-        if (pos < (uint32_t)kK) {
+        if (pos < out_slots) {
           const int32_t idx = (int32_t)(~(uint32_t)me);
           out_idx[pos] = page ? __ldg(page + idx) : idx + idx_offset;
           if (out_key) out_key[pos] = (uint32_t)(me >> 32);

@@ -54,6 +54,7 @@ struct SelectParams {
   uint32_t* out_key;
   uint32_t* status;
   int32_t B;
+  int32_t k;  // elements selected per row (the reference's op: 2048); output rows have k slots
   int32_t idx_offset;
   int32_t list_cap;  // per-CTA candidate list capacity (entries), multiple of 16
   int32_t cand_cap;  // rank 0's gathered-candidate capacity (entries), multiple of 16
@@ -644,12 +645,13 @@ struct RowCtx {
   int32_t cand_cap;
   int32_t list_cap;
   uint32_t* status;
+  uint32_t k;  // elements to select per row (2048 for the reference's op)
 };
 
 template <int NT>
 __device__ __forceinline__ void emit_winner(const RowCtx<NT>& cx, uint32_t base_w, uint32_t key, int idx) {
   const uint32_t pos = base_w + warp_alloc(&cx.ctrl->wslot);
-  if (pos < (uint32_t)kK) {
+  if (pos < cx.k) {
     cx.out_idx[pos] = cx.page ? __ldg(cx.page + idx) : idx + cx.idx_offset;
     if (cx.out_key) cx.out_key[pos] = key;
   }
@@ -735,7 +737,7 @@ __device__ __forceinline__ int refine_from_data(RowCtx<NT>& cx, uint32_t& need, 
   }
   __syncthreads();
 
-  need = kK;
+  need = cx.k;
   P = 0;
   int mode = kModeAbort;
   for (r = 0;; ++r) {
@@ -815,7 +817,7 @@ __device__ __forceinline__ int refine_from_data(RowCtx<NT>& cx, uint32_t& need, 
       const uint32_t tie_prefix = ctrl->tie_prefix;
       const uint32_t local_c = ctrl->local_c;
       const uint32_t quota = need > tie_prefix ? min(need - tie_prefix, local_c) : 0u;
-      const uint32_t obase = (uint32_t)kK - need + tie_prefix;
+      const uint32_t obase = cx.k - need + tie_prefix;
       uint32_t run = 0;  // ties seen so far in this shard (uniform over the CTA)
       for (int gb = sh.g0; gb < sh.g1 && run < quota; gb += NT) {
         const int g = gb + tid;
@@ -846,7 +848,7 @@ __device__ __forceinline__ int refine_from_data(RowCtx<NT>& cx, uint32_t& need, 
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           if (m[j]) {
-            if (rnk < quota && obase + rnk < (uint32_t)kK) {
+            if (rnk < quota && obase + rnk < cx.k) {
               cx.out_idx[obase + rnk] = cx.page ? __ldg(cx.page + i0 + j) : i0 + j + cx.idx_offset;
               if (cx.out_key) cx.out_key[obase + rnk] = Pn;
             }
@@ -865,7 +867,9 @@ __device__ __forceinline__ int refine_from_data(RowCtx<NT>& cx, uint32_t& need, 
 #ifndef FFTOPK_CTAS_512
 #define FFTOPK_CTAS_512 2
 #endif
-template <int NT>
+// kAnyK = false: k is the constant 2048 of the reference's op (the compiler folds it: one register
+// less in a kernel that sits at its register limit); true: k comes from the parameters.
+template <int NT, bool kAnyK = false>
 __global__ void __launch_bounds__(NT, (NT == 512 ? FFTOPK_CTAS_512 : 1024 / NT)) select2048_kernel(const SelectParams p) {
   RowCtx<NT> cx;
   cg::cluster_group cluster = cg::this_cluster();
@@ -890,8 +894,9 @@ __global__ void __launch_bounds__(NT, (NT == 512 ? FFTOPK_CTAS_512 : 1024 / NT))
   const int len = (int)len64;
   const float* rowp = p.score + (int64_t)row * p.row_stride + row_start;
   const int64_t cp_shift = p.cp_flag ? (int64_t)((__ldcg(p.cp_flag) + 1u) & 1u) * p.cp_half_words : 0;
-  int32_t* out_idx = cx.out_idx = p.out_idx + cp_shift + (int64_t)row * kK;
-  uint32_t* out_key = cx.out_key = p.out_key ? p.out_key + cp_shift + (int64_t)row * kK : nullptr;
+  const uint32_t K = cx.k = kAnyK ? (uint32_t)p.k : (uint32_t)kK;
+  int32_t* out_idx = cx.out_idx = p.out_idx + cp_shift + (int64_t)row * K;
+  uint32_t* out_key = cx.out_key = p.out_key ? p.out_key + cp_shift + (int64_t)row * K : nullptr;
   cx.idx_offset = p.idx_offset + (p.row_offsets ? __ldg(p.row_offsets + row) : 0);
   cx.page = nullptr;
   if (p.src_page_table) {
@@ -913,9 +918,9 @@ __global__ void __launch_bounds__(NT, (NT == 512 ? FFTOPK_CTAS_512 : 1024 / NT))
   cx.status = p.status;
 
   // Short rows: 0..len-1 then -1 (reference: naive_topk_cuda, topk_indexer_radix.cu:152-163).
-  if (len <= kK) {
+  if (len <= (int)K) {
     if (rank == 0) {
-      for (int i = tid; i < kK; i += NT) {
+      for (int i = tid; i < (int)K; i += NT) {
         out_idx[i] = i < len ? (cx.page ? __ldg(cx.page + i) : i + cx.idx_offset) : -1;
         if (out_key) out_key[i] = i < len ? fftopk_key_from_bits(__float_as_uint(__ldg(rowp + i))) : 0u;
       }
@@ -1060,7 +1065,7 @@ __global__ void __launch_bounds__(NT, (NT == 512 ? FFTOPK_CTAS_512 : 1024 / NT))
   cluster_sync(cluster, C);  // #1: sample histograms complete
   FFTOPK_MARK(3);
 
-  uint32_t need = kK;
+  uint32_t need = K;
   uint32_t P = 0;
   int r = 0;
   int mode = kModeAbort;
@@ -1079,7 +1084,7 @@ __global__ void __launch_bounds__(NT, (NT == 512 ? FFTOPK_CTAS_512 : 1024 / NT))
   } else if (exact) {
     // ---- the sample is the row: its histogram gives the threshold bin directly -----------------
     cluster_pick<NT>(
-        cluster, C, cx.hist(0), cx.sup(0), cx.xch, ctrl, pick_no, kMaxBins, [&](uint32_t) { return (uint32_t)kK; },
+        cluster, C, cx.hist(0), cx.sup(0), cx.xch, ctrl, pick_no, kMaxBins, [&](uint32_t) { return K; },
         [&](Picked& pk) { decide_and_allocate<NT>(cx, pk, kModeFallback, false); });
     mode = ctrl->mode;
     FFTOPK_MARK(4);
@@ -1118,12 +1123,12 @@ __global__ void __launch_bounds__(NT, (NT == 512 ? FFTOPK_CTAS_512 : 1024 / NT))
     const float flen = (float)len;
     const DualPick dp = cluster_pick_dual<NT>(cluster, C, cx.hist(0), cx.sup(0), cx.hist(1), cx.sup(1), dual, ctrl, pick_no,
                                               [&](uint32_t n_s) {
-                                                const float m = (float)kK * (float)n_s / flen;
+                                                const float m = (float)K * (float)n_s / flen;
                                                 const uint32_t rk = (uint32_t)(m + 5.0f * sqrtf(m) + 14.0f);
                                                 return rk < n_s ? rk : n_s;
                                               },
                                               [&](uint32_t n_s) {  // the mirror image; 0: no such rank
-                                                const float m = (float)kK * (float)n_s / flen;
+                                                const float m = (float)K * (float)n_s / flen;
                                                 const float rk = m - 5.0f * sqrtf(m) - 14.0f;
                                                 return rk >= 1.0f ? (uint32_t)rk : 0u;
                                               });
@@ -1136,7 +1141,7 @@ __global__ void __launch_bounds__(NT, (NT == 512 ? FFTOPK_CTAS_512 : 1024 / NT))
 #ifndef FFTOPK_1B_FACTOR
 #define FFTOPK_1B_FACTOR 2.0f
 #endif
-    int smode = !dp.ok ? kModeFallback : (in_bin > FFTOPK_1B_FACTOR * (float)kK ? kModeNext : kModeGather);
+    int smode = !dp.ok ? kModeFallback : (in_bin > FFTOPK_1B_FACTOR * (float)K ? kModeNext : kModeGather);
     uint32_t gkey = dp.prefix << (32 - dp.pbits);
     if (smode == kModeNext) {
       const int sb = 32 - dp.pbits - 12;  // position of the next 12 bits
@@ -1281,7 +1286,7 @@ __global__ void __launch_bounds__(NT, (NT == 512 ? FFTOPK_CTAS_512 : 1024 / NT))
         // fewer than k admitted (the guess was too high), a list overflowed, or more than rank 0
         // can hold: start over with full histograms
         const uint32_t room = C == 1 ? 0xffffffffu : (uint32_t)p.cand_cap;  // (a lone CTA keeps them in the list)
-        mode = (over == 0u && total >= (uint32_t)kK && total <= room) ? kModeGather : kModeFallback;
+        mode = (over == 0u && total >= K && total <= room) ? kModeGather : kModeFallback;
         // every candidate's key lies in [lowkey, maxkey]
         fin_cap = maxkey;
         if (fin_hist) {
@@ -1290,7 +1295,7 @@ __global__ void __launch_bounds__(NT, (NT == 512 ? FFTOPK_CTAS_512 : 1024 / NT))
           fin_focus = fin_cap;
         }
       }
-      need = kK;
+      need = K;
       P = 0;
       r = -1;  // finish first, final barrier afterwards
       FFTOPK_MARK(10);
@@ -1321,14 +1326,14 @@ __global__ void __launch_bounds__(NT, (NT == 512 ? FFTOPK_CTAS_512 : 1024 / NT))
       const WarpSegCands<NT> src{list + (size_t)warp * seg_cap1, fin_wn, list + (size_t)NW * seg_cap1, fin_sn};
       cta_finish<NT>(src, need, low_end(fin_lo), high_end(fin_cap), high_end(fin_focus), fin_hist, idx_bits, cx.hist(0),
                      ctrl, out_idx, out_key,
-                     (uint32_t)kK - need, cx.idx_offset, p.status, cx.page);
+                     K - need, K, cx.idx_offset, p.status, cx.page);
     } else {
       // every candidate shares the key prefix P above bit `sh` of the key (sampled path: range known)
       const int sh = r < 0 ? 0 : round_shift(r);
       const uint64_t lo = r < 0 ? low_end(fin_lo) : ((uint64_t)P << (32 + sh));
       const uint64_t cap = r < 0 ? high_end(fin_cap) : (lo | ((1ull << (32 + sh)) - 1ull));
       const DenseCands<NT> src{cx.cand, (int)min(ctrl->cand_count, (uint32_t)p.cand_cap)};
-      cta_finish<NT>(src, need, lo, cap, cap, false, idx_bits, cx.hist(0), ctrl, out_idx, out_key, (uint32_t)kK - need,
+      cta_finish<NT>(src, need, lo, cap, cap, false, idx_bits, cx.hist(0), ctrl, out_idx, out_key, K - need, K,
                      cx.idx_offset, p.status, cx.page);
     }
   }
@@ -1382,6 +1387,10 @@ int setup_kernel(int smem_optin) {
   cudaError_t e = cudaFuncSetAttribute(select2048_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_optin);
   if (e != cudaSuccess) return cuda_fail(e);
   e = cudaFuncSetAttribute(select2048_kernel<NT>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+  if (e != cudaSuccess) return cuda_fail(e);
+  e = cudaFuncSetAttribute(select2048_kernel<NT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_optin);
+  if (e != cudaSuccess) return cuda_fail(e);
+  e = cudaFuncSetAttribute(select2048_kernel<NT, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
   if (e != cudaSuccess) return cuda_fail(e);
   return 0;
 }
@@ -1556,8 +1565,8 @@ static int launch_select(const float* score, int64_t row_stride, int32_t B, int6
                          const int32_t* row_starts, int32_t* out_idx, uint32_t* out_key, int32_t idx_offset,
                          uint32_t* status, void* cuda_stream, const int32_t* src_page_table, int64_t src_stride,
                          const int32_t* cu_seqlens_q, int32_t prefill_bs, const int32_t* row_offsets,
-                         const uint32_t* cp_flag = nullptr, int64_t cp_half_words = 0) {
-  if (B < 0 || L < 0 || row_stride < 0) return FFTOPK_EINVAL;
+                         const uint32_t* cp_flag = nullptr, int64_t cp_half_words = 0, int32_t k = kK) {
+  if (B < 0 || L < 0 || row_stride < 0 || k < 1 || k > kMaxK) return FFTOPK_EINVAL;
   if (B == 0) return FFTOPK_OK;
   if (!score || !lengths || !out_idx) return FFTOPK_EINVAL;
   if ((reinterpret_cast<uintptr_t>(score) & 3u) != 0) return FFTOPK_EINVAL;
@@ -1565,7 +1574,12 @@ static int launch_select(const float* score, int64_t row_stride, int32_t B, int6
   DeviceInfo* d = nullptr;
   int rc = device_info(&d);
   if (rc) return rc;
-  const Plan pl = make_plan(*d, B, L);
+  Plan pl = make_plan(*d, B, L);
+  if (k > kK && pl.cluster == 1 && g_tuning.list_cap <= 0) {
+    // more winners than the lone-CTA list was sized for: the long-row list
+    pl.list_cap = pl.cand_cap = kOverlapListCap1Long;
+    pl.smem_bytes = (int)(fixed_smem_bytes() + (size_t)pl.list_cap * 8);
+  }
 
   SelectParams p;
   p.score = score;
@@ -1577,6 +1591,7 @@ static int launch_select(const float* score, int64_t row_stride, int32_t B, int6
   p.out_key = out_key;
   p.status = status;
   p.B = B;
+  p.k = k;
   p.idx_offset = idx_offset;
   p.list_cap = pl.list_cap;
   p.cand_cap = pl.cand_cap;
@@ -1609,12 +1624,13 @@ static int launch_select(const float* score, int64_t row_stride, int32_t B, int6
     cfg.numAttrs = 2;
   }
   cudaError_t e;
+  const bool any_k = k != kK;
   if (pl.threads == 1024) {
-    e = cudaLaunchKernelEx(&cfg, select2048_kernel<1024>, p);
+    e = any_k ? cudaLaunchKernelEx(&cfg, select2048_kernel<1024, true>, p) : cudaLaunchKernelEx(&cfg, select2048_kernel<1024>, p);
   } else if (pl.threads == 512) {
-    e = cudaLaunchKernelEx(&cfg, select2048_kernel<512>, p);
+    e = any_k ? cudaLaunchKernelEx(&cfg, select2048_kernel<512, true>, p) : cudaLaunchKernelEx(&cfg, select2048_kernel<512>, p);
   } else {
-    e = cudaLaunchKernelEx(&cfg, select2048_kernel<256>, p);
+    e = any_k ? cudaLaunchKernelEx(&cfg, select2048_kernel<256, true>, p) : cudaLaunchKernelEx(&cfg, select2048_kernel<256>, p);
   }
   if (e != cudaSuccess) return cuda_fail(e);
   return FFTOPK_OK;
@@ -1625,6 +1641,13 @@ int fftopk_select2048(const float* score, int64_t row_stride, int32_t B, int64_t
                       uint32_t* status, void* cuda_stream) {
   return launch_select(score, row_stride, B, L, lengths, row_starts, out_idx, out_key, idx_offset, status, cuda_stream,
                        nullptr, 0, nullptr, 0, nullptr);
+}
+
+int fftopk_select_topk(const float* score, int64_t row_stride, int32_t B, int64_t L, const int32_t* lengths,
+                       const int32_t* row_starts, int32_t k, int32_t* out_idx, uint32_t* out_key, int32_t idx_offset,
+                       uint32_t* status, void* cuda_stream) {
+  return launch_select(score, row_stride, B, L, lengths, row_starts, out_idx, out_key, idx_offset, status, cuda_stream,
+                       nullptr, 0, nullptr, 0, nullptr, nullptr, 0, k);
 }
 
 int fftopk_select2048_page_table(const float* score, int64_t row_stride, int32_t B, int64_t L,

@@ -27,6 +27,7 @@ EXPORTS = (
     "fftopk_strerror",
     "fftopk_last_cuda_error",
     "fftopk_select2048",
+    "fftopk_select_topk",
     "fftopk_select2048_page_table",
     "fftopk_select2048_ragged",
     "fftopk_merge2048",
@@ -115,6 +116,9 @@ def lib() -> ctypes.CDLL:
     L.fftopk_topk2048_sliced_noalloc.restype = c.c_int
     L.fftopk_topk2048_sliced_noalloc.argtypes = [c.c_void_p, c.c_int64, c.c_int32, c.c_int64, c.c_void_p, c.c_int32,
                                                  c.c_void_p, c.c_void_p, c.c_void_p]
+    L.fftopk_select_topk.restype = c.c_int
+    L.fftopk_select_topk.argtypes = [c.c_void_p, c.c_int64, c.c_int32, c.c_int64, c.c_void_p, c.c_void_p, c.c_int32,
+                                     c.c_void_p, c.c_void_p, c.c_int32, c.c_void_p, c.c_void_p]
     L.fftopk_host_workspace_bytes.restype = c.c_size_t
     L.fftopk_host_workspace_bytes.argtypes = [c.c_int32, c.c_int64]
     L.fftopk_select2048_host.restype = c.c_int

@@ -118,6 +118,32 @@ def fast_topk_v3(
     return topk_indices
 
 
+def fast_topk_general(
+    score: torch.Tensor,
+    lengths: torch.Tensor,
+    topk: int,
+    row_starts: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """fast_topk_v3 for any 1 <= topk <= 4096 (the reference's op asserts topk == 2048,
+    topk_indexer.py:62-64). Same arguments, same result layout with `topk` columns."""
+    if not (1 <= int(topk) <= 4096):
+        raise ValueError("topk must be in [1, 4096]")
+    assert score.dim() == 2
+    _check_inputs(score, lengths, row_starts)
+    out = torch.empty((score.size(0), int(topk)), dtype=torch.int32, device=score.device)
+    if score.size(0) == 0:
+        return out
+    lib = _native.lib()
+    with torch.cuda.device(score.device):
+        stream = torch.cuda.current_stream(score.device)
+        rc = lib.fftopk_select_topk(score.data_ptr(), score.stride(0) if score.size(0) > 1 else max(score.stride(0), 0),
+                                    score.size(0), score.size(1), lengths.data_ptr(),
+                                    None if row_starts is None else row_starts.data_ptr(), int(topk), out.data_ptr(),
+                                    None, 0, _status_word(score.device).data_ptr(), stream.cuda_stream)
+    _native.check(rc, "fftopk_select_topk")
+    return out
+
+
 _host_workspaces = {}
 
 

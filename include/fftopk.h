@@ -84,6 +84,17 @@ int fftopk_select2048(const float* score, int64_t row_stride, int32_t B, int64_t
                       uint32_t* status, void* cuda_stream);
 
 /*
+ * The same selection for another k: the `k` largest valid entries of every row, 1 <= k <= 4096
+ * (FFTOPK_EINVAL otherwise). The reference's op is fixed at 2048 (topk_indexer.py:62-64 asserts it;
+ * TopK is a compile-time constant, topk_indexer_radix.cu:69); indexer configurations with 512, 1024
+ * or 4096 selected tokens need this. out_idx (and out_key) are [B, k]; rows with lengths[b] <= k
+ * hold 0..len-1 followed by -1. Everything else as for fftopk_select2048.
+ */
+int fftopk_select_topk(const float* score, int64_t row_stride, int32_t B, int64_t L,
+                       const int32_t* lengths, const int32_t* row_starts, int32_t k, int32_t* out_idx,
+                       uint32_t* out_key, int32_t idx_offset, uint32_t* status, void* cuda_stream);
+
+/*
  * Selection fused with the step that follows it in a sparse-attention decode / prefill layer.
  * Replace fast_topk_transform_interface and fast_topk_transform_ragged_interface
  * (topk_indexer_radix.cu:1160-1250) with their three kernels (:871-995), which the reference

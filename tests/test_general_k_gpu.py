@@ -1,0 +1,80 @@
+"""GPU parity tests of the general-k entry point (fftopk_select_topk through fast_topk_general):
+k = 512, 1024, 4096 and odd values against the oracle, bit-exact, in both launch plans."""
+import pytest
+import torch
+
+import workloads
+from jit_kernel import _native
+from jit_kernel.topk_indexer import fast_topk_general, fast_topk_v3, kernel_status
+from oracle import topk_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+
+def _check(score, lengths, k, row_starts=None, what=""):
+    dev = torch.device("cuda", 0)
+    rs = None if row_starts is None else row_starts.to(dev)
+    got = fast_topk_general(score.to(dev), lengths.to(dev), k, row_starts=rs)
+    torch.cuda.synchronize()
+    assert tuple(got.shape) == (score.size(0), k)
+    orc.check_result(score.numpy(), lengths.numpy(), got.cpu().numpy(),
+                     None if row_starts is None else row_starts.numpy(), k, None, what)
+    assert kernel_status() == 0
+
+
+@pytest.fixture(autouse=True)
+def _reset():
+    _native.set_tuning()
+    _native.set_overlap(False)
+    yield
+    _native.set_tuning()
+    _native.set_overlap(False)
+
+
+@pytest.mark.parametrize("k", [1, 31, 512, 1024, 2048, 3000, 4096])
+def test_decode_rows(k):
+    for L in (20000, 300000):
+        s, ln = workloads.c2(L=L)
+        _check(s, ln, k, what=f"k={k} L={L}")
+
+
+@pytest.mark.parametrize("k", [512, 1024, 4096])
+@pytest.mark.parametrize("overlap", [False, True])
+def test_ragged_batch(k, overlap):
+    s, ln = workloads.c3(B=48, L=70000, min_len=100)
+    _native.set_overlap(overlap)
+    _check(s, ln, k, what=f"ragged k={k} overlap={overlap}")
+
+
+@pytest.mark.parametrize("k", [512, 4096])
+def test_ties_short_rows_and_row_starts(k):
+    s, ln = workloads.c4(B=4, L=100000)
+    _check(s, ln, k, what=f"ties k={k}")
+    g = torch.Generator().manual_seed(k)
+    s = torch.randn(5, 9000, generator=g)
+    ln = torch.tensor([k, k - 1, k + 1, 0, 5000], dtype=torch.int32)
+    rs = torch.tensor([0, 7, 100, 0, 4000], dtype=torch.int32)
+    _check(s, ln, k, rs, what=f"short rows k={k}")
+    eq = torch.full((2, 50000), 1.5)
+    _check(eq, torch.tensor([50000, 4097], dtype=torch.int32), k, what=f"all equal k={k}")
+
+
+@pytest.mark.parametrize("cluster", [1, 4, 16])
+def test_every_path_with_k_4096(cluster):
+    _native.set_tuning(cluster_ctas=cluster)
+    s, ln = workloads.c5(B=2, L=200000)
+    _check(s, ln, 4096, what=f"k=4096 C={cluster}")
+    _native.set_tuning(cluster_ctas=cluster, force_full_histogram=True)
+    _check(s, ln, 1024, what=f"k=1024 full-hist C={cluster}")
+
+
+def test_same_as_the_fixed_entry_point_and_argument_errors():
+    dev = torch.device("cuda", 0)
+    s, ln = workloads.c3(B=8, L=30000)
+    a = fast_topk_general(s.to(dev), ln.to(dev), 2048).cpu()
+    b = fast_topk_v3(s.to(dev), ln.to(dev), 2048).cpu()
+    assert torch.equal(a.sort(dim=1).values, b.sort(dim=1).values)
+    with pytest.raises(ValueError):
+        fast_topk_general(s.to(dev), ln.to(dev), 0)
+    with pytest.raises(ValueError):
+        fast_topk_general(s.to(dev), ln.to(dev), 4097)
