@@ -28,6 +28,8 @@ EXPORTS = (
     "fftopk_last_cuda_error",
     "fftopk_select2048",
     "fftopk_select_topk",
+    "fftopk_widen_workspace_bytes",
+    "fftopk_select_topk_16bit",
     "fftopk_select2048_page_table",
     "fftopk_select2048_ragged",
     "fftopk_merge2048",
@@ -119,6 +121,11 @@ def lib() -> ctypes.CDLL:
     L.fftopk_select_topk.restype = c.c_int
     L.fftopk_select_topk.argtypes = [c.c_void_p, c.c_int64, c.c_int32, c.c_int64, c.c_void_p, c.c_void_p, c.c_int32,
                                      c.c_void_p, c.c_void_p, c.c_int32, c.c_void_p, c.c_void_p]
+    L.fftopk_widen_workspace_bytes.restype = c.c_size_t
+    L.fftopk_widen_workspace_bytes.argtypes = [c.c_int32, c.c_int64]
+    L.fftopk_select_topk_16bit.restype = c.c_int
+    L.fftopk_select_topk_16bit.argtypes = [c.c_void_p, c.c_int32, c.c_int64, c.c_int32, c.c_int64, c.c_void_p, c.c_void_p,
+                                           c.c_int32, c.c_void_p, c.c_void_p, c.c_size_t, c.c_void_p, c.c_void_p]
     L.fftopk_host_workspace_bytes.restype = c.c_size_t
     L.fftopk_host_workspace_bytes.argtypes = [c.c_int32, c.c_int64]
     L.fftopk_select2048_host.restype = c.c_int

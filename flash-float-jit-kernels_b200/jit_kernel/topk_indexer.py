@@ -129,6 +129,8 @@ def fast_topk_general(
     if not (1 <= int(topk) <= 4096):
         raise ValueError("topk must be in [1, 4096]")
     assert score.dim() == 2
+    if score.is_cuda and score.dtype in (torch.float16, torch.bfloat16):
+        return _fast_topk_16bit(score, lengths, int(topk), row_starts)
     _check_inputs(score, lengths, row_starts)
     out = torch.empty((score.size(0), int(topk)), dtype=torch.int32, device=score.device)
     if score.size(0) == 0:
@@ -141,6 +143,41 @@ def fast_topk_general(
                                     None if row_starts is None else row_starts.data_ptr(), int(topk), out.data_ptr(),
                                     None, 0, _status_word(score.device).data_ptr(), stream.cuda_stream)
     _native.check(rc, "fftopk_select_topk")
+    return out
+
+
+_widen_workspaces = {}
+
+
+def _fast_topk_16bit(score, lengths, topk, row_starts):
+    """fp16 / bf16 scores (fftopk_select_topk_16bit): widened to fp32 in a cached workspace, then
+    the fp32 selector. Functional, not tuned."""
+    if score.stride(1) != 1 and score.size(0) and score.size(1):
+        raise RuntimeError("score must have unit inner stride")
+    if lengths.dtype != torch.int32 or not lengths.is_cuda or lengths.numel() != score.size(0) or not lengths.is_contiguous():
+        raise RuntimeError("lengths must be a contiguous CUDA int32 tensor of shape [B]")
+    if row_starts is not None and (row_starts.dtype != torch.int32 or not row_starts.is_cuda
+                                   or row_starts.numel() != score.size(0) or not row_starts.is_contiguous()):
+        raise RuntimeError("row_starts must be a contiguous CUDA int32 tensor of shape [B]")
+    B, L = score.size(0), score.size(1)
+    out = torch.empty((B, topk), dtype=torch.int32, device=score.device)
+    if B == 0:
+        return out
+    lib = _native.lib()
+    nbytes = int(lib.fftopk_widen_workspace_bytes(B, L))
+    key = (score.device, B, L)
+    ws = _widen_workspaces.get(key)
+    if ws is None or ws.numel() < nbytes + 256:
+        ws = torch.empty(nbytes + 256, dtype=torch.uint8, device=score.device)
+        _widen_workspaces[key] = ws
+    base = (ws.data_ptr() + 255) & ~255
+    with torch.cuda.device(score.device):
+        stream = torch.cuda.current_stream(score.device)
+        rc = lib.fftopk_select_topk_16bit(score.data_ptr(), 0 if score.dtype == torch.float16 else 1,
+                                          score.stride(0) if B > 1 else max(score.stride(0), 0), B, L, lengths.data_ptr(),
+                                          None if row_starts is None else row_starts.data_ptr(), topk, out.data_ptr(),
+                                          base, nbytes, _status_word(score.device).data_ptr(), stream.cuda_stream)
+    _native.check(rc, "fftopk_select_topk_16bit")
     return out
 
 

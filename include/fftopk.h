@@ -208,6 +208,22 @@ int fftopk_topk2048_sliced_noalloc(const float* score, int64_t row_stride, int32
                                    uint32_t* status, void* cuda_stream);
 
 /*
+ * fftopk_select_topk for fp16 or bf16 scores (the reference's op takes fp32 only: CHECK of the
+ * dtype, topk_indexer_radix.cu:1003-1016). Functional, not tuned: the rows' valid ranges are
+ * widened to fp32 - exact and order-preserving - into the caller's workspace
+ * (fftopk_widen_workspace_bytes(B, L) bytes of device memory, 256-byte aligned), then the fp32
+ * selector runs on it, so a 16-bit row costs about as much HBM traffic as five reads of it.
+ * row_stride is in elements. B <= 65535.
+ */
+#define FFTOPK_DTYPE_FP16 0
+#define FFTOPK_DTYPE_BF16 1
+size_t fftopk_widen_workspace_bytes(int32_t B, int64_t L);
+int fftopk_select_topk_16bit(const void* score16, int32_t dtype, int64_t row_stride, int32_t B, int64_t L,
+                             const int32_t* lengths, const int32_t* row_starts, int32_t k,
+                             int32_t* out_idx, void* d_workspace, size_t workspace_bytes,
+                             uint32_t* status, void* cuda_stream);
+
+/*
  * The selector for a caller whose buffers are in HOST memory: score, lengths and the result.
  * Replaces, for such a caller, the tensor.cuda() / fast_topk_v3 / .cpu() sequence of the
  * reference's benchmark driver (benchmark/bench_topk.py:90-146) with one call that enqueues, on

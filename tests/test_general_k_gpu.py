@@ -78,3 +78,29 @@ def test_same_as_the_fixed_entry_point_and_argument_errors():
         fast_topk_general(s.to(dev), ln.to(dev), 0)
     with pytest.raises(ValueError):
         fast_topk_general(s.to(dev), ln.to(dev), 4097)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("k", [512, 2048])
+def test_16bit_scores(dtype, k):
+    """fp16 / bf16 scores: same index set as the oracle on the widened values (many exact ties)."""
+    dev = torch.device("cuda", 0)
+    s, ln = workloads.c3(B=12, L=60000, min_len=100)
+    s16 = s.to(dtype)
+    got = fast_topk_general(s16.to(dev), ln.to(dev), k)
+    torch.cuda.synchronize()
+    orc.check_result(s16.to(torch.float32).numpy(), ln.numpy(), got.cpu().numpy(), None, k, None, f"{dtype} k={k}")
+    # unaligned views, row_starts, a decode row
+    wide = torch.randn(3, 50011, generator=torch.Generator().manual_seed(9)).to(dtype)
+    view = wide[:, 3:50003]
+    ln2 = torch.tensor([40000, 2049, 49990], dtype=torch.int32)
+    rs = torch.tensor([5, 0, 9], dtype=torch.int32)
+    got = fast_topk_general(wide.to(dev)[:, 3:50003], ln2.to(dev), k, row_starts=rs.to(dev))
+    torch.cuda.synchronize()
+    orc.check_result(view.to(torch.float32).contiguous().numpy(), ln2.numpy(), got.cpu().numpy(), rs.numpy(), k, None,
+                     f"{dtype} k={k} row_starts")
+    s1, l1 = workloads.c2(L=300000)
+    got = fast_topk_general(s1.to(dtype).to(dev), l1.to(dev), k)
+    torch.cuda.synchronize()
+    orc.check_result(s1.to(dtype).to(torch.float32).numpy(), l1.numpy(), got.cpu().numpy(), None, k, None, f"{dtype} decode")
+    assert kernel_status() == 0
