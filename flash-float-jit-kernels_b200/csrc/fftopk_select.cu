@@ -31,6 +31,17 @@
 //      larger than rank 0's buffer (heavy ties, rows of equal values), the cluster falls back to
 //      full histograms over the data: 12 + 12 + 8 key bits, re-reading the shard from L2 each
 //      round, and exact ties left after 32 bits are taken in index order, shard by shard.
+//
+// Build-time knobs (all optional, for experiments; the defaults are what was measured best):
+//   FFTOPK_SAMPLE_GRANULES  granules the cluster samples per row and thread column (2048)
+//   FFTOPK_EXACT_SLABS      granules per thread up to which the shard stays in registers (4)
+//   FFTOPK_1B_FACTOR        second sample round when the guessed bin holds more than factor*k (2)
+//   FFTOPK_U512             128-bit loads in flight per thread of the 512-thread filter (8; 16 allowed)
+//   FFTOPK_CTAS_512         512-thread CTAs per SM the register budget allows (2)
+//   FFTOPK_KSMALL           undecided candidates ranked by votes (256)
+//   FFTOPK_TRACE / FFTOPK_STOP_AFTER=<mark> / FFTOPK_EXPERIMENT_NOPASS / FFTOPK_DEBUG_FALLBACK
+//                           phase timestamps, early return at a phase mark, a filter nothing
+//                           passes, a status bit when the full-histogram path is taken
 #include <cooperative_groups.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -1462,7 +1473,10 @@ Plan make_plan(const DeviceInfo& d, int B, int64_t L) {
   const int by_len = floor_pow2(L / 2048 > 0 ? L / 2048 : 1);
   if (c > by_len) c = by_len;
   pl.cluster = c < 1 ? 1 : c;
-  pl.threads = 1024;
+  // Short rows spread over many CTAs leave a thread one or two granules: 512 threads do the same
+  // with cheaper block barriers (measured at B=1 and B=4: 10.2-11.0 us against 11.4-12.3 us for
+  // L = 16K and 32K; from 64K on 1024 threads win).
+  pl.threads = (L <= 32768 && pl.cluster >= 8) ? 512 : 1024;
   const bool one_per_sm = (int64_t)rows * pl.cluster <= d.sm_count;
   pl.list_cap = one_per_sm ? kLatencyListCap : kBatchListCap;
   pl.cand_cap = one_per_sm ? kLatencyCandCap : kBatchCandCap;
