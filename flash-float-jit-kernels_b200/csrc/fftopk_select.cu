@@ -1375,6 +1375,7 @@ struct DeviceInfo {
   int smem_optin = 0;
   int cc_major = 0;
   int max_cluster = 0;  // largest cluster size that can be scheduled with the latency-mode footprint
+  int active16 = 0, active8 = 0;  // clusters of that size the device holds at once (same footprint)
 };
 DeviceInfo g_dev[64];
 
@@ -1426,23 +1427,35 @@ int device_info(DeviceInfo** out) {
     if (rc) return rc;
     rc = setup_kernel<256>(d.smem_optin);
     if (rc) return rc;
-    // can a 16-CTA cluster with the latency-mode shared-memory footprint be co-scheduled?
+    // can a 16-CTA cluster with the latency-mode shared-memory footprint be co-scheduled, and how
+    // many clusters of 16 / of 8 CTAs does the device hold at once? (A cluster lives inside one
+    // GPC, so fewer 16-CTA clusters fit than SM count / 16: a batch with more rows than that would
+    // run in two waves.)
     d.max_cluster = 8;
-    {
+    d.active16 = 0;
+    d.active8 = d.sm_count / 8;
+    for (int cs = 16; cs >= 8; cs /= 2) {
       cudaLaunchConfig_t cfg = {};
-      cfg.gridDim = dim3(16, 1, 1);
+      cfg.gridDim = dim3(cs * 32, 1, 1);
       cfg.blockDim = dim3(1024, 1, 1);
       cfg.dynamicSmemBytes = fixed_smem_bytes() + (size_t)(kLatencyListCap + kLatencyCandCap) * 8;
       cudaLaunchAttribute at[1];
       at[0].id = cudaLaunchAttributeClusterDimension;
-      at[0].val.clusterDim.x = 16;
+      at[0].val.clusterDim.x = cs;
       at[0].val.clusterDim.y = 1;
       at[0].val.clusterDim.z = 1;
       cfg.attrs = at;
       cfg.numAttrs = 1;
       int nclusters = 0;
       e = cudaOccupancyMaxActiveClusters(&nclusters, select2048_kernel<1024>, &cfg);
-      if (e == cudaSuccess && nclusters >= 1) d.max_cluster = 16;
+      if (e == cudaSuccess && nclusters >= 1) {
+        if (cs == 16) {
+          d.max_cluster = 16;
+          d.active16 = nclusters;
+        } else {
+          d.active8 = nclusters;
+        }
+      }
       (void)cudaGetLastError();
     }
     d.ready = true;
@@ -1470,6 +1483,8 @@ Plan make_plan(const DeviceInfo& d, int B, int64_t L) {
   // so many that a shard drops below ~2K elements.
   int c = floor_pow2(d.sm_count / rows > 0 ? d.sm_count / rows : 1);
   if (c > d.max_cluster) c = d.max_cluster;
+  if (c == 16 && rows > d.active16) c = 8;  // all rows in one wave
+  if (c == 8 && rows > d.active8) c = 4;
   const int by_len = floor_pow2(L / 2048 > 0 ? L / 2048 : 1);
   if (c > by_len) c = by_len;
   pl.cluster = c < 1 ? 1 : c;
