@@ -52,8 +52,8 @@ WORKLOAD = "ragged batched decode: B=64, padded L=131072, lengths U[1024,131072]
 N_ROTATE = 8
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one select2048 launch on this workload, from the
-# ncu capture summarised in profiles/ (None until a capture exists)
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 16774315  # profiles/select2048_ragged_b64.md (throughput plan, mean of 3 launches)
+# ncu capture of the throughput plan (None until a capture exists)
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 16774315  # throughput plan, mean of 3 captured launches
 
 
 def measured_peak_gbs():
