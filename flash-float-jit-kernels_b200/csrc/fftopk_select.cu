@@ -10,7 +10,7 @@
 //      shards, so the cluster samples the row uniformly in position. The top 12 bits of the
 //      order-preserving key are histogrammed per CTA (4096 bins); a cluster also histograms key
 //      bits [27:16], which give a 16-bit guess when the whole sample shares its top four key bits.
-//      When the whole shard fits in registers (<= 4 granules per thread) the "sample" is the
+//      When the whole shard fits in registers (<= 3 granules per thread) the "sample" is the
 //      shard and step 2 is exact.
 //   2. PICK. After ONE cluster barrier every CTA reads its peers' 64 super-bin sums, then the 64
 //      fine bins of the threshold super-bin, over distributed shared memory, and finds the bin
@@ -34,7 +34,7 @@
 //
 // Build-time knobs (all optional, for experiments; the defaults are what was measured best):
 //   FFTOPK_SAMPLE_GRANULES  granules the cluster samples per row and thread column (2048)
-//   FFTOPK_EXACT_SLABS      granules per thread up to which the shard stays in registers (4)
+//   FFTOPK_EXACT_SLABS      granules per thread up to which the shard stays in registers (3)
 //   FFTOPK_1B_FACTOR        second sample round when the guessed bin holds more than factor*k (2)
 //   FFTOPK_U512             128-bit loads in flight per thread of the 512-thread filter (8; 16 allowed)
 //   FFTOPK_CTAS_512         512-thread CTAs per SM the register budget allows (2)
@@ -967,7 +967,7 @@ __global__ void __launch_bounds__(NT, (NT == 512 ? FFTOPK_CTAS_512 : 1024 / NT))
   const int n_g = sh.g1 - sh.g0;
   // Whole shard in registers (same answer in every CTA of the cluster: `per` is rank-independent).
 #ifndef FFTOPK_EXACT_SLABS
-#define FFTOPK_EXACT_SLABS kRegSlabs
+#define FFTOPK_EXACT_SLABS 3  // (with 4 the 256K row of the decode sweep took 16.4 us instead of 13.9 us)
 #endif
   const bool exact = per <= NT * FFTOPK_EXACT_SLABS;
   // A second, finer sample histogram (see cluster_pick_dual) saves a cluster-wide sample round on
