@@ -8,7 +8,15 @@
 Prints ONE JSON line (rank 0). A step is one call of the op on one batch of the ragged batched
 decode workload (B=64 rows, padded L=131072, valid lengths uniform in [1024, 131072], fp32
 N(0,1) logits, -inf padding, k=2048). With N GPUs every rank processes its own 64-row batch
-(rows are independent: no collective on the data path), so `value` = 64*N*K rows / time.
+(rows are independent: no collective on the data path), so `value` = 64*N rows per step / time
+per step.
+
+Timed region: the K-step sequence is captured in a CUDA graph (several repetitions of it per
+graph when K is small, so that a graph holds >= 200 calls) and the graph is replayed until the
+region lasts >= 50 ms; `ms_per_step` = region / calls in it, `replays` = how often the K-step
+sequence ran, `gpu_launches` = calls in the region. A step is ~5 us, so K steps alone (0.1 ms at
+K = 20) would measure the fill and drain of the launch pipeline, not the kernel; that figure is
+kept as `cold_start_ms_per_step`.
 
   value      rows/s with the inputs resident in HBM, eight 32 MiB input buffers rotated so that no
              step finds its input in L2 (256 MiB > 126 MB L2). The steps are independent batches
@@ -21,7 +29,13 @@ N(0,1) logits, -inf padding, k=2048). With N GPUs every rank processes its own 6
              kernel, D2H copy of the indices, all inside the timed region
   roofline   algorithmic bytes per launch / measured launch time, against the measured HBM peak
   latency    p50 microseconds per call at B=1 for the decode sweep L = 64K .. 1M (the other half of
-             the headline metric), L2-warm (the reference's own method) and with rotated buffers
+             the headline metric), L2-warm (the reference's own method; also as a fraction of the
+             L2 read bandwidth measured with the library's probe) and with rotated buffers
+  large_batch  one serialised call at B=256 and B=512 of the same ragged distribution: the rate a
+             single call reaches when the batch alone fills the device
+  context_parallel  (N > 1) config 5 through the three context-parallel variants: first checked
+             bit-exact against single-device torch (every rank, also on the tie-stress config),
+             then timed; timings are null when the check fails
   cpu_baseline  torch.topk on the host cores on the same batch (what the reference's benchmark
              uses as ground truth, benchmark/bench_topk.py:25-42)
 
@@ -51,9 +65,16 @@ METRIC = "rows/s at B=64 (top-2048 per row, ragged batched decode)"
 WORKLOAD = "ragged batched decode: B=64, padded L=131072, lengths U[1024,131072], fp32 N(0,1), k=2048"
 N_ROTATE = 8
 FALLBACK_HBM_GBS = 6650.0
+MIN_REGION_S = 0.05      # a timed region lasts at least this long
+MIN_GRAPH_CALLS = 200    # a captured graph holds at least this many calls
 # dram__bytes_read.sum + dram__bytes_write.sum of one select2048 launch on this workload, from the
-# ncu capture of the throughput plan (None until a capture exists)
+# ncu capture of the throughput plan (profiles/select2048_ragged_b64.md)
 NCU_TRAFFIC_BYTES_PER_LAUNCH = 16774315  # throughput plan, mean of 3 captured launches
+
+
+def bench_config():
+    """The `config` object of the JSON line: the workload only, identical in both arms."""
+    return {"workload": WORKLOAD, "rows_per_gpu": 64, "padded_L": 131072, "k": K}
 
 
 def measured_peak_gbs():
@@ -175,7 +196,7 @@ def reference_arm(args, rank: int) -> None:
         "impl": "reference", "metric": METRIC, "value": value, "unit": "rows/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3 * rows / rows_per_step,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-        "data": "synthetic", "config": {"workload": WORKLOAD, "where": "host cores, torch.topk"},
+        "data": "synthetic", "config": bench_config(), "run": {"where": "host cores, torch.topk"},
         "cpu_baseline": {"value": value, "unit": "rows/s", "cores": cores, "kind": "port", "sample": sample,
                          "what": "torch.topk(score[b,:len], 2048, sorted=False) per row, the reference "
                                  "benchmark's ground truth"},
@@ -212,7 +233,65 @@ def time_graph(graph, stream, replays: int = 1):
     return e0.elapsed_time(e1) * 1e-3  # seconds
 
 
-def latency_sweep(dev, stream, fast_topk):
+def timed_region(step, steps: int, stream, min_s: float = MIN_REGION_S):
+    """Captures the `steps`-step sequence - repeated so that the graph holds >= MIN_GRAPH_CALLS calls
+    - and returns (graph, calls per graph, replays needed for a region of >= min_s seconds)."""
+    reps_in_graph = max(1, -(-MIN_GRAPH_CALLS // steps))
+    calls = reps_in_graph * steps
+    graph = capture_steps(step, calls, stream)
+    time_graph(graph, stream)  # upload + warm-up
+    t1 = min(time_graph(graph, stream) for _ in range(2))
+    replays = max(1, int(np.ceil(min_s / max(t1, 1e-7))))
+    return graph, calls, reps_in_graph, replays
+
+
+def measure_l2_read_gbs(dev, stream):
+    """Read bandwidth of L2-resident data, all SMs reading (the library's probe): GB/s for a 4 MiB
+    and a 32 MiB buffer; the HBM figure from a 1 GiB buffer alongside."""
+    import ctypes
+
+    from jit_kernel import _native
+    lib = _native.lib()
+    sink = torch.zeros(1, dtype=torch.int32, device=dev)
+    out = {}
+    for name, nbytes, to_read in (("l2_4MiB", 4 << 20, 40 << 30), ("l2_32MiB", 32 << 20, 40 << 30),
+                                  ("hbm_1GiB", 1 << 30, 16 << 30)):
+        buf = torch.empty(nbytes // 4, dtype=torch.float32, device=dev).normal_()
+        got = ctypes.c_size_t()
+        best = 0.0
+        with torch.cuda.stream(stream):
+            for rep in range(4):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(stream)
+                _native.check(lib.fftopk_probe_read_bandwidth(buf.data_ptr(), nbytes, to_read, sink.data_ptr(),
+                                                              ctypes.byref(got), stream.cuda_stream), "probe")
+                e1.record(stream)
+                e1.synchronize()
+                if rep:
+                    best = max(best, got.value / (e0.elapsed_time(e1) * 1e-3) / 1e9)
+        out[name] = best
+        del buf
+    return out
+
+
+def measure_h2d_gbs(dev, stream, nbytes: int = 64 << 20):
+    """Pinned host -> device copy bandwidth of this box (one cudaMemcpyAsync of 64 MiB, best of 5)."""
+    h = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
+    d = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    best = 0.0
+    with torch.cuda.stream(stream):
+        for rep in range(6):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            d.copy_(h, non_blocking=True)
+            e1.record(stream)
+            e1.synchronize()
+            if rep:
+                best = max(best, nbytes / (e0.elapsed_time(e1) * 1e-3) / 1e9)
+    return best
+
+
+def latency_sweep(dev, stream, fast_topk, l2_gbs=None):
     """p50 us per call at B=1 over the decode sweep; warm = same buffer every call (L2-resident,
     the reference's method), cold = buffers rotated over > L2 bytes."""
     out = {}
@@ -235,31 +314,114 @@ def latency_sweep(dev, stream, fast_topk):
         nbytes = workloads.algorithmic_bytes(lengths, L)
         res["bytes"] = nbytes
         res["cold_gbs"] = nbytes / res["cold"]["p50_us"] / 1e3
+        res["warm_gbs"] = nbytes / res["warm"]["p50_us"] / 1e3
+        if l2_gbs:
+            res["warm_frac_l2"] = res["warm_gbs"] / l2_gbs
         out[str(L)] = res
         del bufs
     return out
 
 
+def large_batch_leg(dev, stream, fast_topk, peak_gbs):
+    """One serialised call (default launch mode, no overlap between calls) on a batch large enough
+    to fill the device by itself: B=256 and B=512 rows of the bench's ragged distribution, inputs
+    larger than L2 (two rotated buffers)."""
+    L = 131072
+    out = []
+    for B in (256, 512):
+        g = torch.Generator().manual_seed(workloads.SEED + B)
+        lengths = torch.randint(1024, L + 1, (B,), generator=g, dtype=torch.int32)
+        ld = lengths.to(dev)
+        bufs = []
+        for i in range(2):
+            torch.manual_seed(1234 + i)
+            bufs.append(torch.randn(B, L, dtype=torch.float32, device=dev))
+        res = torch.empty(B, K, dtype=torch.int32, device=dev)
+        with torch.cuda.stream(stream):
+            for i in range(3):
+                fast_topk(bufs[i % 2], res, ld)
+        stream.synchronize()
+        n = 20
+        gr = capture_steps(lambda i: fast_topk(bufs[i % 2], res, ld), n, stream)
+        time_graph(gr, stream)
+        sec = min(time_graph(gr, stream) for _ in range(5)) / n
+        nbytes = workloads.algorithmic_bytes(lengths, L)
+        out.append({"B": B, "us_per_call": sec * 1e6, "rows_per_s": B / sec, "gbs": nbytes / sec / 1e9,
+                    "frac": nbytes / sec / 1e9 / peak_gbs, "bytes": nbytes})
+        del bufs, gr
+    return out
+
+
+class TorchGroundTruth:
+    """Single-device ground truth of a batch, computed here with torch alone: the k largest of every
+    full row, equal values resolved to the lower index (stable descending sort), and as a second
+    statement the value multiset of torch.topk (north_star: 'bit-exact against single-device
+    torch.topk'; the check style of benchmark/bench_topk.py:55-87)."""
+
+    def __init__(self, score: torch.Tensor, lengths: torch.Tensor):
+        self.score = score
+        self.rows = []
+        for b in range(score.size(0)):
+            n = int(lengths[b])
+            row = score[b, :n]
+            want = torch.sort(torch.sort(row, descending=True, stable=True).indices[:K]).values
+            vals = torch.sort(torch.topk(row, min(n, K)).values).values
+            assert torch.equal(torch.sort(row[want]).values, vals)  # the two statements agree
+            self.rows.append((want, vals))
+
+    def matches(self, got: torch.Tensor) -> bool:
+        got = got.cpu()
+        for b, (want, vals) in enumerate(self.rows):
+            have = torch.sort(got[b][got[b] >= 0].to(torch.int64)).values
+            if have.numel() != want.numel() or not torch.equal(have, want):
+                return False
+            if not torch.equal(torch.sort(self.score[b][have]).values, vals):
+                return False
+        return True
+
+
 def context_parallel_leg(dev, rank: int, world: int):
-    """Config 5: B=4, L=1M split evenly over the ranks; local select, exchange, merge. Two variants:
-    NCCL all-gather + merge kernel, and the fused gather-and-merge over IPC-mapped peer buffers.
-    Eager calls, CUDA events, max over ranks."""
+    """Config 5: B=4, L=1M split evenly over the ranks; local select, exchange, merge. Three
+    variants: NCCL all-gather + merge kernel, the fused gather-and-merge over IPC-mapped peer
+    buffers called eagerly, and the same as a replayed CUDA graph. Each variant is first checked on
+    every rank against the single-device result (config 5 and the tie-stress config 4 at B=2,
+    L=131072), outside every timed region; then timed with CUDA events, max over ranks."""
     import torch.distributed as dist
 
-    from jit_kernel.distributed import FusedContextParallelTopk, fast_topk_v3_context_parallel
+    from jit_kernel.distributed import FusedContextParallelTopk, fast_topk_v3_context_parallel, local_lengths
+    from jit_kernel.topk_indexer import kernel_status
+
+    def all_ok(flag: bool) -> bool:
+        t = torch.tensor([1 if flag else 0], dtype=torch.int32, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        return bool(t.item())
 
     score, lengths = workloads.c5()
+    B = score.size(0)
     Ls = score.size(1) // world
     shard = score[:, rank * Ls:(rank + 1) * Ls].contiguous().to(dev)
-    fused = FusedContextParallelTopk(max_rows=score.size(0))
-    out = {"workload": f"B=4, L=1048576 over {world} GPUs, k=2048"}
-    reps = 50
-    # the fused path again as a replayed CUDA graph (its epochs live on the device): no Python
-    # between the kernels
-    from jit_kernel.distributed import local_lengths
     lens_dev = local_lengths(lengths, Ls, rank).to(dev)
-    res = torch.empty(score.size(0), K, dtype=torch.int32, device=dev)
-    fused.run_into(shard, lens_dev, res)
+    t_score, t_len = workloads.c4(B=2, L=131072)
+    t_Ls = t_score.size(1) // world
+    t_shard = t_score[:, rank * t_Ls:(rank + 1) * t_Ls].contiguous().to(dev)
+    fused = FusedContextParallelTopk(max_rows=B)
+    out = {"workload": f"B=4, L=1048576 over {world} GPUs, k=2048", "parity": {}}
+    truth, t_truth = TorchGroundTruth(score, lengths), TorchGroundTruth(t_score, t_len)
+
+    # ---- parity first, outside every timed region ------------------------------------------------
+    par = out["parity"]
+    got = fast_topk_v3_context_parallel(shard, lengths, K)
+    par["nccl"] = "bit-exact" if all_ok(truth.matches(got)) else "MISMATCH"
+    ok = True
+    for _ in range(3):
+        ok = truth.matches(fused(shard, lengths)) and ok
+    par["fused"] = "bit-exact" if all_ok(ok) else "MISMATCH"
+    ok = t_truth.matches(fast_topk_v3_context_parallel(t_shard, t_len, K))
+    ok = t_truth.matches(fused(t_shard, t_len)) and ok
+    par["ties"] = "bit-exact" if all_ok(ok) else "MISMATCH"
+    # the fused path as a replayed CUDA graph (its epochs live on the device): no Python between the
+    # kernels; replayed several times so that both halves of the comm buffer are used
+    res = torch.empty(B, K, dtype=torch.int32, device=dev)
     torch.cuda.synchronize()
     dist.barrier()
     side = torch.cuda.Stream(device=dev)
@@ -268,6 +430,18 @@ def context_parallel_leg(dev, rank: int, world: int):
         with torch.cuda.graph(graph, stream=side):
             fused.run_into(shard, lens_dev, res)
     dist.barrier()
+    ok = True
+    for _ in range(4):
+        res.fill_(-5)
+        graph.replay()
+        torch.cuda.synchronize()
+        ok = truth.matches(res) and ok
+        dist.barrier()
+    par["fused_graph"] = "bit-exact" if all_ok(ok) else "MISMATCH"
+    all_exact = all(v == "bit-exact" for v in par.values())
+
+    # ---- timing ----------------------------------------------------------------------------------
+    reps = 50
     for name, fn in (("nccl_allgather_merge", lambda: fast_topk_v3_context_parallel(shard, lengths, K)),
                      ("fused_peer_merge", lambda: fused(shard, lengths)),
                      ("fused_peer_merge_graph", graph.replay)):
@@ -283,7 +457,14 @@ def context_parallel_leg(dev, rank: int, world: int):
         e1.synchronize()
         t = torch.tensor([e0.elapsed_time(e1) / reps * 1e3], dtype=torch.float64, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        out[name + "_us_per_call"] = float(t.item())
+        out[name + "_us_per_call"] = float(t.item()) if all_exact else None
+    torch.cuda.synchronize()
+    st = torch.tensor([kernel_status(dev)], dtype=torch.int32, device=dev)
+    dist.all_reduce(st, op=dist.ReduceOp.MAX)
+    out["kernel_status"] = int(st.item())  # 0: no bounded wait on a peer ran out, no internal error
+    if out["kernel_status"] != 0:
+        for name in ("nccl_allgather_merge", "fused_peer_merge", "fused_peer_merge_graph"):
+            out[name + "_us_per_call"] = None
     fused.close()
     return out
 
@@ -301,7 +482,7 @@ def ours_arm(args, rank: int, local_rank: int, world: int) -> None:
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     stream = torch.cuda.Stream(device=dev)
-    steps, warmup = args.steps, max(args.warmup, 3)
+    steps, warmup = max(1, args.steps), max(args.warmup, 3)
 
     # ---- workload: every rank its own 64-row batch, N_ROTATE device copies with different data --
     score, lengths = workloads.c3(seed=workloads.SEED + rank)
@@ -312,7 +493,12 @@ def ours_arm(args, rank: int, local_rank: int, world: int) -> None:
         bufs.append(torch.roll(bufs[0], shifts=i, dims=0).contiguous())
     lens_rot = [torch.roll(ld, shifts=i, dims=0).contiguous() for i in range(N_ROTATE)]
     outs = [torch.empty(B, K, dtype=torch.int32, device=dev) for _ in range(N_ROTATE)]
-    nbytes = workloads.algorithmic_bytes(lengths, L)
+    nbytes_rank = workloads.algorithmic_bytes(lengths, L)
+    nbytes_total = nbytes_rank
+    if world > 1:  # every rank drew its own lengths: the job's bytes are the sum over the ranks
+        t = torch.tensor([nbytes_rank], dtype=torch.int64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        nbytes_total = int(t.item())
 
     def step(i):
         fast_topk(bufs[i % N_ROTATE], outs[i % N_ROTATE], lens_rot[i % N_ROTATE])
@@ -324,53 +510,42 @@ def ours_arm(args, rank: int, local_rank: int, world: int) -> None:
         for i in range(warmup):
             step(i)
     stream.synchronize()
-    n_serial = min(steps, 200)
-    g_serial = capture_steps(step, n_serial, stream)
-    time_graph(g_serial, stream)
-    serial_sec = min(time_graph(g_serial, stream) for _ in range(3)) / n_serial
+    g_serial, calls_s, _, replays_s = timed_region(step, steps, stream, min_s=0.02)
+    serial_sec = time_graph(g_serial, stream, replays_s) / (replays_s * calls_s)
     del g_serial
 
     # ---- throughput mode for the headline -------------------------------------------------------
     _native.set_overlap(True)
     plan = _native.plan(B, L)
-
-    # ---- warm-up (also the first call, which sets kernel attributes, outside any capture) -------
+    # warm-up (also the first call, which sets kernel attributes, outside any capture)
     with torch.cuda.stream(stream):
         for i in range(warmup):
             step(i)
     stream.synchronize()
-    chunk = min(steps, 500)
-    n_chunks, rest = divmod(steps, chunk)
-    g_chunk = capture_steps(step, chunk, stream)
-    g_rest = capture_steps(step, rest, stream) if rest else None
-    time_graph(g_chunk, stream)  # graph warm-up (upload)
-    if g_rest is not None:
-        time_graph(g_rest, stream)
+    # the K steps alone, once: what a cold start of the launch pipeline costs
+    g_cold = capture_steps(step, steps, stream)
+    time_graph(g_cold, stream)
+    cold_sec_per_step = min(time_graph(g_cold, stream) for _ in range(3)) / steps
+    del g_cold
+    graph, calls, reps_in_graph, replays = timed_region(step, steps, stream)
 
-    # ---- timed region: exactly `steps` calls, barrier + synchronize on both sides ---------------
+    # ---- timed region: barrier + synchronize on both sides, clocks sampled inside ---------------
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
         torch.cuda.synchronize()
     with ClockSampler(physical_gpu_index(local_rank)) as clk:
-        sec = time_graph(g_chunk, stream, n_chunks)
-        if g_rest is not None:
-            sec += time_graph(g_rest, stream)
+        sec = time_graph(graph, stream, replays)
         torch.cuda.synchronize()
-        note = "sampled during the timed region"
-        if len(clk.samples) < 5:
-            # the timed region was shorter than a few NVML polls: keep the same load running
-            t_end = time.perf_counter() + 0.06
-            while time.perf_counter() < t_end:
-                time_graph(g_chunk, stream)
-            note = "timed region too short for NVML polling; sampled under the same load right after it"
     if world > 1:
         dist.barrier()
         t = torch.tensor([sec], dtype=torch.float64, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         sec = float(t.item())
-    sec_per_step = sec / steps
-    value = B * world * steps / sec
+    launches = replays * calls
+    sec_per_step = sec / launches
+    value = B * world / sec_per_step
+    del graph
 
     _native.set_overlap(False)
     # ---- end to end through the public op with host buffers ------------------------------------
@@ -409,7 +584,7 @@ def ours_arm(args, rank: int, local_rank: int, world: int) -> None:
         try:
             cp = context_parallel_leg(dev, rank, world)
         except Exception as e:  # an extra: never lose the headline over it
-            cp = {"error": repr(e)[:200]}
+            cp = {"error": repr(e)[:300]}
 
     status = kernel_status(dev)
     if rank != 0:
@@ -418,34 +593,49 @@ def ours_arm(args, rank: int, local_rank: int, world: int) -> None:
         return
 
     peak, peak_src = measured_peak_gbs()
-    achieved = nbytes / sec_per_step / 1e9
+    achieved = nbytes_total / world / sec_per_step / 1e9  # per GPU: the job's bytes / N / slowest rank's time
     line = {
         "metric": METRIC, "value": value, "unit": "rows/s", "n_gpus": world, "steps": steps, "warmup": warmup,
         "ms_per_step": sec_per_step * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "rows_per_gpu": B, "l2": f"{N_ROTATE} input buffers of {4 * B * L >> 20} MiB "
-                   "rotated (> 126 MB L2)", "timing": "CUDA graph of the steps, CUDA events on its stream",
-                   "mode": "throughput: fftopk_set_overlap(1), consecutive calls are programmatic dependent "
-                           "launches and may overlap; one output buffer per rotated input",
-                   "plan": plan},
+        "dtype": "f32", "data": "synthetic", "config": bench_config(),
+        "replays": replays * reps_in_graph, "timed_region_ms": sec * 1e3,
+        "cold_start_ms_per_step": cold_sec_per_step * 1e3,
+        "run": {"l2": f"{N_ROTATE} input buffers of {4 * B * L >> 20} MiB rotated (> 126 MB L2)",
+                "timing": f"CUDA graph of {calls} calls ({reps_in_graph} x the {steps}-step sequence) replayed "
+                          f"{replays} times, CUDA events on its stream; cold_start_ms_per_step = the {steps} steps "
+                          "alone, one replay",
+                "mode": "throughput: fftopk_set_overlap(1), consecutive calls are programmatic dependent "
+                        "launches and may overlap; one output buffer per rotated input",
+                "plan": plan},
         "serial": {"us_per_call": serial_sec * 1e6, "rows_per_s": B * world / serial_sec,
-                   "gbs": nbytes / serial_sec / 1e9, "plan": plan_serial,
+                   "gbs": nbytes_rank / serial_sec / 1e9, "frac": nbytes_rank / serial_sec / 1e9 / peak, "plan": plan_serial,
                    "note": "same steps, default serialised launches (fftopk_set_overlap(0)), this rank"},
-        "clocks": clk.summary(note),
+        "clocks": clk.summary("sampled during the timed region"),
         "e2e": {"value": e2e_value, "unit": "rows/s", "h2d_bytes_per_step": h2d_bytes,
-                "d2h_bytes_per_step": 4 * B * K, "steps": e2e_steps},
-        "gpu_launches": steps,
+                "d2h_bytes_per_step": 4 * B * K, "steps": e2e_steps, "ms_per_step": e2e_sec / e2e_steps * 1e3},
+        "gpu_launches": launches,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "peak_source": peak_src,
-                     "algorithmic_bytes_per_launch": nbytes, "us_per_launch": sec_per_step * 1e6,
+                     "algorithmic_bytes_per_launch": nbytes_total / world, "us_per_launch": sec_per_step * 1e6,
+                     "cold_start_frac": nbytes_total / world / cold_sec_per_step / 1e9 / peak,
                      "frac_of_nominal_8TBs": achieved / 8000.0},
         "kernel_status": status,
     }
     if cp is not None:
         line["context_parallel"] = cp
     if not args.no_extras:
-        line["latency"] = latency_sweep(dev, stream, fast_topk)
+        probes = measure_l2_read_gbs(dev, stream)
+        h2d_peak = measure_h2d_gbs(dev, stream)
+        line["probes"] = {"read_gbs": probes, "pinned_h2d_gbs": h2d_peak,
+                          "how": "fftopk_probe_read_bandwidth (128-bit ld.global.cg, all SMs) / one 64 MiB pinned copy"}
+        e2e_gbs = (h2d_bytes + 4 * B * K) / (e2e_sec / e2e_steps) / 1e9
+        line["e2e"]["roofline"] = {"bound": "pcie", "achieved": e2e_gbs, "peak": h2d_peak, "unit": "GB/s",
+                                   "frac": e2e_gbs / h2d_peak if h2d_peak else None,
+                                   "note": "bytes copied per step (valid prefixes in, indices out) / step time, per GPU, "
+                                           "against this box's measured pinned host-to-device copy rate"}
+        line["latency"] = latency_sweep(dev, stream, fast_topk, probes.get("l2_4MiB"))
         line["p50_us_B1_L1M"] = line["latency"]["1048576"]["warm"]["p50_us"]
+        line["large_batch"] = large_batch_leg(dev, stream, fast_topk, peak)
         # CPU baseline on this box's host cores, bounded: the 64-row batch a few times (~20 ms each)
         cpu_reps = 10
         cpu_sec = time_cpu(score, lengths, cpu_reps, 2)

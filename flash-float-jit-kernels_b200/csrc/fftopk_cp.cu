@@ -21,13 +21,8 @@
 #include "fftopk_trace.cuh"
 #include "fftopk_device.cuh"
 #include "fftopk_host.h"
+#include "fftopk_internal.h"
 #include "fftopk_key.h"
-
-// defined in fftopk_select.cu (internal, not part of the public header)
-extern "C" int fftopk_select2048_into_comm(const float* score, int64_t row_stride, int32_t B, int64_t L,
-                                           const int32_t* lengths, int32_t* idx_plane0, uint32_t* key_plane0,
-                                           int32_t idx_offset, const uint32_t* flag, int64_t half_words,
-                                           uint32_t* status, void* cuda_stream);
 
 namespace fftopk {
 
@@ -136,8 +131,10 @@ __global__ void __launch_bounds__(NT, 1) merge2048_kernel(const MergeSrc src, in
       const uint64_t c = cand[i];
       if (c != 0ull) {
         const uint32_t pos = warp_alloc(&ctrl->fslot);
-        out_idx[pos] = (int32_t)(~(uint32_t)c);
-        if (out_key) out_key[pos] = (uint32_t)(c >> 32);
+        if (FFTOPK_CHECK(9, pos, kK, status)) {
+          out_idx[pos] = (int32_t)(~(uint32_t)c);
+          if (out_key) out_key[pos] = (uint32_t)(c >> 32);
+        }
       }
     }
     for (int i = (int)total + tid; i < kK; i += NT) {
@@ -172,7 +169,8 @@ __global__ void slice_lengths_kernel(const int32_t* __restrict__ lengths, int B,
     const int g = i / kStaticMaxRows, b = i % kStaticMaxRows;
     int64_t v = 0;
     if (b < B) {
-      const int64_t lg = L - g * ls < ls ? L - g * ls : ls;
+      int64_t lg = L - g * ls < ls ? L - g * ls : ls;  // columns of slice g (0 when the slice starts beyond L)
+      lg = lg < 0 ? 0 : lg;
       int64_t len = lengths[b];
       len = len < 0 ? 0 : (len > L ? L : len);
       v = len - g * ls;
@@ -184,25 +182,36 @@ __global__ void slice_lengths_kernel(const int32_t* __restrict__ lengths, int B,
 
 }  // namespace fftopk
 
+#ifdef FFTOPK_CHECKED
+namespace fftopk {
+int checked_read_merge(uint32_t rec[4]) {
+  const uint32_t zero[4] = {0u, 0u, 0u, 0u};
+  cudaError_t e = cudaMemcpyFromSymbol(rec, g_check_rec, sizeof(zero));
+  if (e == cudaSuccess) e = cudaMemcpyToSymbol(g_check_rec, zero, sizeof(zero));
+  return e == cudaSuccess ? 0 : cuda_fail(e);
+}
+}  // namespace fftopk
+#endif
+
 namespace {
 using namespace fftopk;
 
-bool g_merge_ready[64];
+DeviceOnce g_merge_once[kMaxDevices];
 
+// First call on a device (any thread): the merge kernel's shared-memory attribute.
 int merge_setup() {
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return cuda_fail(e);
-  if (dev < 0 || dev >= 64) return FFTOPK_EDEVICE;
-  if (!g_merge_ready[dev]) {
+  if (dev < 0 || dev >= kMaxDevices) return FFTOPK_EDEVICE;
+  return g_merge_once[dev].run([&] {
     int optin = 0;
-    e = cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
-    if (e != cudaSuccess) return cuda_fail(e);
-    e = cudaFuncSetAttribute(merge2048_kernel<1024>, cudaFuncAttributeMaxDynamicSharedMemorySize, optin);
-    if (e != cudaSuccess) return cuda_fail(e);
-    g_merge_ready[dev] = true;
-  }
-  return 0;
+    cudaError_t e2 = cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+    if (e2 != cudaSuccess) return cuda_fail(e2);
+    e2 = cudaFuncSetAttribute(merge2048_kernel<1024>, cudaFuncAttributeMaxDynamicSharedMemorySize, optin);
+    if (e2 != cudaSuccess) return cuda_fail(e2);
+    return 0;
+  });
 }
 
 size_t merge_smem(int G) {
@@ -214,20 +223,23 @@ size_t merge_smem(int G) {
 size_t comm_words(int32_t b_cap) { return (size_t)4 * b_cap * kK + kCommFlagWords; }
 
 // Device address of g_static_scratch on the current device, looked up once per device.
-void* g_static_ptr[64];
+void* g_static_ptr[kMaxDevices];
+DeviceOnce g_static_once[kMaxDevices];
 
 int static_scratch_ptr(void** out) {
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return cuda_fail(e);
-  if (dev < 0 || dev >= 64) return FFTOPK_EDEVICE;
-  if (g_static_ptr[dev] == nullptr) {
+  if (dev < 0 || dev >= kMaxDevices) return FFTOPK_EDEVICE;
+  const int rc = g_static_once[dev].run([&] {
     void* p = nullptr;
-    e = cudaGetSymbolAddress(&p, g_static_scratch);  // with device `dev` current
-    if (e != cudaSuccess) return cuda_fail(e);
-    if (p == nullptr) return FFTOPK_EDEVICE;
+    cudaError_t e2 = cudaGetSymbolAddress(&p, g_static_scratch);  // with device `dev` current
+    if (e2 != cudaSuccess) return cuda_fail(e2);
+    if (p == nullptr) return (int)FFTOPK_EDEVICE;
     g_static_ptr[dev] = p;
-  }
+    return 0;
+  });
+  if (rc) return rc;
   *out = g_static_ptr[dev];
   return 0;
 }
@@ -313,17 +325,26 @@ int fftopk_select2048_cp(const float* score, int64_t row_stride, int32_t B, int6
   uint32_t* flag = reinterpret_cast<uint32_t*>(static_cast<int32_t*>(comm) + (size_t)4 * b_cap * kK);
   const int64_t half = (int64_t)2 * b_cap * kK;
   if (B > 0) {
-    int rc;
-    if (epoch != 0u) {
-      int32_t* base = static_cast<int32_t*>(comm) + (size_t)(epoch & 1u) * half;
-      rc = fftopk_select2048(score, row_stride, B, L, lengths, nullptr, base,
-                             reinterpret_cast<uint32_t*>(base + (size_t)b_cap * kK), idx_offset, status, cuda_stream);
-    } else {  // device-side epoch: the kernel picks the half from the flag it finds
-      int32_t* base = static_cast<int32_t*>(comm);
-      rc = fftopk_select2048_into_comm(score, row_stride, B, L, lengths, base,
-                                       reinterpret_cast<uint32_t*>(base + (size_t)b_cap * kK), idx_offset, flag, half,
-                                       status, cuda_stream);
+    SelectCall c;
+    c.score = score;
+    c.row_stride = row_stride;
+    c.B = B;
+    c.L = L;
+    c.lengths = lengths;
+    c.idx_offset = idx_offset;
+    c.status = status;
+    c.cuda_stream = cuda_stream;
+    c.may_overlap = false;  // the publish kernel and the peers' merges consume this launch's output
+    // host-side epoch: the half is known here; device-side epoch (0): the kernel picks the half
+    // from the flag it finds
+    int32_t* base = static_cast<int32_t*>(comm) + (epoch != 0u ? (size_t)(epoch & 1u) * half : 0);
+    c.out_idx = base;
+    c.out_key = reinterpret_cast<uint32_t*>(base + (size_t)b_cap * kK);
+    if (epoch == 0u) {
+      c.cp_flag = flag;
+      c.cp_half_words = half;
     }
+    const int rc = launch_select(c);
     if (rc) return rc;
   }
   publish_kernel<<<1, 1, 0, static_cast<cudaStream_t>(cuda_stream)>>>(flag, epoch);
@@ -389,8 +410,19 @@ int fftopk_topk2048_sliced_noalloc(const float* score, int64_t row_stride, int32
     const int64_t first = (int64_t)g * ls;
     const int64_t lg = L - first < ls ? (L - first > 0 ? L - first : 0) : ls;
     // every slot of the slice's planes is rewritten by this call: nothing has to start at zero
-    rc = fftopk_select2048(score + first, row_stride, B, lg, slice_len + (size_t)g * kStaticMaxRows, nullptr, idx_plane,
-                           key_plane, (int32_t)first, status, cuda_stream);
+    SelectCall c;
+    c.score = score + (lg > 0 ? first : 0);
+    c.row_stride = row_stride;
+    c.B = B;
+    c.L = lg;
+    c.lengths = slice_len + (size_t)g * kStaticMaxRows;
+    c.out_idx = idx_plane;
+    c.out_key = key_plane;
+    c.idx_offset = (int32_t)first;
+    c.status = status;
+    c.cuda_stream = cuda_stream;
+    c.may_overlap = false;  // reads the slice lengths written by the kernel enqueued just above
+    rc = launch_select(c);
     if (rc) return rc;
     src.idx[g] = idx_plane;
     src.key[g] = key_plane;

@@ -7,6 +7,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "../../include/fftopk.h"
+#include "fftopk_decide.h"
 #include "fftopk_key.h"
 
 namespace fftopk {
@@ -18,8 +20,6 @@ constexpr int kMaxK = 4096;            // largest k of the general entry point (
 constexpr int kMaxBins = 4096;         // widest digit of the distributed rounds: 12 bits
 constexpr int kSup = 64;               // super-bins per histogram (each sums kMaxBins/64 bins)
 constexpr int kMaxCluster = 16;        // CTAs per row (non-portable cluster size on B200)
-constexpr int kFinishBits = 11;        // digit width of the single-CTA finish
-constexpr int kFinishBins = 1 << kFinishBits;
 #ifndef FFTOPK_KSMALL
 #define FFTOPK_KSMALL 256
 #endif
@@ -27,6 +27,29 @@ constexpr int kSmall = FFTOPK_KSMALL;            // undecided candidates that ar
 constexpr unsigned kFull = 0xffffffffu;
 
 __device__ __forceinline__ int lane_id() { return threadIdx.x & 31; }
+
+// Checked build (-DFFTOPK_CHECKED): every index that the selection logic guarantees to be in
+// range - an output slot below k, a candidate slot the decision step has made room for, a staged
+// row index below the row length, the winner count of a finish - is tested before use. A failing
+// test skips the access, raises FFTOPK_ST_CHECK in the status word and, if it is the first one,
+// leaves (site, index, limit, block) in a device-side record that fftopk_checked_read() returns.
+// Capacity limits that the algorithm handles by design (a full candidate list makes the row fall
+// back to full histograms) are not violations. The production build compiles the tests away.
+#ifdef FFTOPK_CHECKED
+static __device__ unsigned int g_check_rec[4];
+static __device__ __noinline__ void check_fail(int site, uint32_t idx, uint32_t limit, uint32_t* status) {
+  if (atomicCAS(&g_check_rec[0], 0u, (unsigned)site) == 0u) {
+    g_check_rec[1] = idx;
+    g_check_rec[2] = limit;
+    g_check_rec[3] = blockIdx.x;
+  }
+  if (status) atomicOr(status, (uint32_t)FFTOPK_ST_CHECK);
+}
+#define FFTOPK_CHECK(site, idx, limit, status) \
+  (((uint32_t)(idx) < (uint32_t)(limit)) ? true : (::fftopk::check_fail((site), (uint32_t)(idx), (uint32_t)(limit), (status)), false))
+#else
+#define FFTOPK_CHECK(site, idx, limit, status) true
+#endif
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -144,7 +167,13 @@ struct Ctrl {
   uint32_t wtot[32];
   uint32_t wmax[32];
   uint64_t small[kSmall];
+#ifdef FFTOPK_CHECKED
+  uint32_t* status_ptr;  // the call's status word, for checks in code that has no other way to it
+#endif
 };
+#ifdef FFTOPK_CHECKED
+#define ctrl_status(c) ((c)->status_ptr)
+#endif
 
 // ---------------------------------------------------------------------------------------------
 // Candidate sources of the finish. A source tells a thread which candidates are its share:
@@ -296,36 +325,6 @@ __device__ __forceinline__ void block_pick(const uint32_t* hist, uint32_t need, 
 }
 
 // ---------------------------------------------------------------------------------------------
-// Digit rule of a finish round over the composite range [lo, cap]: digit(c) = min((c - lo) >>
-// shift, kFinishBins - 1). The shift is chosen so that [lo, focus] spreads over the bins below the
-// last one; everything above `focus` (cap >= focus >= lo) lands in the last bin. With focus == cap
-// this is a plain radix digit of the range; a caller that knows where in the range the threshold
-// will fall passes a tighter focus and gets finer bins there.
-// ---------------------------------------------------------------------------------------------
-struct FinishDigit {
-  uint64_t lo;
-  int shift;
-  __device__ __forceinline__ uint32_t of(uint64_t c) const {
-    const uint64_t d = (c - lo) >> shift;
-    return d < (uint64_t)(kFinishBins - 1) ? (uint32_t)d : (uint32_t)(kFinishBins - 1);
-  }
-  // the same for a digit that depends on the key alone (shift >= 32 and the low word of lo is 0)
-  __device__ __forceinline__ uint32_t of_key(uint32_t k) const {
-    const uint32_t d = (k - (uint32_t)(lo >> 32)) >> (shift - 32);
-    return d < (uint32_t)(kFinishBins - 1) ? d : (uint32_t)(kFinishBins - 1);
-  }
-  __device__ __forceinline__ bool key_only() const { return shift >= 32 && (uint32_t)lo == 0u; }
-};
-
-__device__ __forceinline__ FinishDigit make_finish_digit(uint64_t lo, uint64_t focus) {
-  const uint64_t width = focus - lo;
-  const int bits = width ? 64 - __clzll((long long)width) : 0;
-  int shift = bits > kFinishBits ? bits - kFinishBits : 0;
-  if ((width >> shift) >= (uint64_t)(kFinishBins - 1)) ++shift;  // keep the last bin for what lies above
-  return FinishDigit{lo, shift};
-}
-
-// ---------------------------------------------------------------------------------------------
 // Single-CTA finish. The source holds composites c = (key << 32) | ~idx in shared memory (0 =
 // empty slot), all of them inside [lo, cap]; lo > cap means "range unknown" and costs a pass
 // that finds it. Writes the `need` largest composites' indices (and keys) to
@@ -335,7 +334,7 @@ __device__ __forceinline__ FinishDigit make_finish_digit(uint64_t lo, uint64_t f
 // tail (topk_indexer_radix.cu:686-781, 109-141, 788-850). Because the index is part of the
 // composite, equal values are resolved towards the lower index by the same rounds, and the last
 // <= 256 undecided candidates are ranked by votes.
-// `focus`: see FinishDigit. `have_hist`: the caller has already built round 0's histogram in
+// `focus`: see FinishDigit (fftopk_decide.h). `have_hist`: the caller has already built round 0's histogram in
 // `hist`, with make_finish_digit(lo, focus).
 // `idx_bits`: all indices are < 2^idx_bits, so the inverted-index bits above that are all ones.
 // `page`: optional per-row table; the value written is then page[idx] instead of idx + idx_offset
@@ -394,7 +393,7 @@ __device__ void cta_finish(const Src& src, uint32_t need, uint64_t lo, uint64_t 
   for (int round = 0; round < 24; ++round) {
     if ((uint32_t)(lo >> 32) == (uint32_t)(cap >> 32)) {
       // one key left: the inverted indices all start with the same run of ones
-      const uint64_t floor_lo = (lo & 0xffffffff00000000ull) | (uint64_t)(~((idx_bits >= 32 ? 0u : (1u << idx_bits)) - 1u));
+      const uint64_t floor_lo = single_key_floor(lo, idx_bits);
       if (lo < floor_lo && floor_lo <= cap) {
         if (focus < floor_lo) focus = cap;
         lo = floor_lo;
@@ -430,9 +429,7 @@ __device__ void cta_finish(const Src& src, uint32_t need, uint64_t lo, uint64_t 
     }
     cnt = ctrl->cnt;
     need2 = need - ctrl->above;
-    t_lo = lo + ((uint64_t)t << dg.shift);
-    t_hi = (t == kFinishBins - 1) ? cap : t_lo + ((1ull << dg.shift) - 1ull);
-    if (t_hi > cap || t_hi < t_lo) t_hi = cap;
+    finish_bin_range(dg, lo, cap, t, t_lo, t_hi);
     if (cnt == need2 || cnt <= (uint32_t)kSmall) {
       all_bin = (cnt == need2);
       found = true;
@@ -472,7 +469,7 @@ __device__ void cta_finish(const Src& src, uint32_t need, uint64_t lo, uint64_t 
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
           const uint32_t pos = base + (uint32_t)__popc(b[u] & lt);
-          if (c[u] > wthr && pos < out_slots) {
+          if (c[u] > wthr && FFTOPK_CHECK(3, pos, out_slots, status) && pos < out_slots) {
             const int32_t idx = (int32_t)(~(uint32_t)c[u]);
             if constexpr (decltype(paged)::value) {
               out_idx[pos] = __ldg(page + idx);
@@ -489,7 +486,7 @@ __device__ void cta_finish(const Src& src, uint32_t need, uint64_t lo, uint64_t 
         for (int u = 0; u < 4; ++u) {
           if (c[u] <= wthr && c[u] >= t_lo && c[u] != 0ull) {
             const uint32_t s = warp_alloc(&ctrl->small_n);
-            if (s < (uint32_t)kSmall) ctrl->small[s] = c[u];
+            if (FFTOPK_CHECK(4, s, kSmall, status) && s < (uint32_t)kSmall) ctrl->small[s] = c[u];
           }
         }
       }
@@ -501,6 +498,17 @@ __device__ void cta_finish(const Src& src, uint32_t need, uint64_t lo, uint64_t 
     pass(std::false_type{});
   }
   FFTOPK_MARK(33);
+#ifdef FFTOPK_CHECKED
+  {
+    // every certain winner took exactly one slot, every undecided candidate was set aside
+    __syncthreads();
+    const uint32_t want_w = all_bin ? need_total : need_total - need2;
+    if (tid == 0) {
+      if (ctrl->fslot != want_w) check_fail(10, ctrl->fslot, want_w, status);
+      if (!all_bin && ctrl->small_n != cnt) check_fail(11, ctrl->small_n, cnt, status);
+    }
+  }
+#endif
   if (!all_bin) {
     __syncthreads();
     // Rank by vote: warp i takes candidate i, the lanes compare it with the candidates j (32 per
@@ -521,7 +529,7 @@ __device__ void cta_finish(const Src& src, uint32_t need, uint64_t lo, uint64_t 
       }
       if (lane == 0 && rank < need2) {
         const uint32_t pos = out_base + certain + rank;
-        if (pos < out_slots) {
+        if (FFTOPK_CHECK(5, pos, out_slots, status) && pos < out_slots) {
           const int32_t idx = (int32_t)(~(uint32_t)me);
           out_idx[pos] = page ? __ldg(page + idx) : idx + idx_offset;
           if (out_key) out_key[pos] = (uint32_t)(me >> 32);

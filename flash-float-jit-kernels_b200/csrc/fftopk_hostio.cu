@@ -18,6 +18,7 @@
 
 #include "../../include/fftopk.h"
 #include "fftopk_host.h"
+#include "fftopk_internal.h"
 
 namespace {
 
@@ -105,6 +106,34 @@ __global__ void __launch_bounds__(256) widen_rows_kernel(const T16* __restrict__
   }
 }
 
+// Read-only bandwidth probe: all threads of the grid walk the buffer together, 128 bits per load,
+// eight independent loads in flight per thread, wrapping around until `rounds` rounds are done.
+// Loads bypass L1 (ld.global.cg), so a buffer that fits in L2 measures L2 read bandwidth and a
+// buffer much larger than L2 measures HBM read bandwidth. The XOR of everything read goes to
+// `sink` so that no load can be dropped.
+__global__ void __launch_bounds__(1024) read_probe_kernel(const uint4* __restrict__ buf, uint32_t n16, uint32_t rounds,
+                                                         uint32_t* __restrict__ sink) {
+  constexpr int U = 8;
+  const uint32_t nthreads = gridDim.x * blockDim.x;
+  uint32_t idx = (blockIdx.x * blockDim.x + threadIdx.x) % n16;
+  const uint32_t step = nthreads % n16;
+  uint32_t acc = 0u;
+  for (uint32_t r = 0; r < rounds; ++r) {
+    uint4 v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      asm volatile("ld.global.cg.v4.u32 {%0, %1, %2, %3}, [%4];"
+                   : "=r"(v[u].x), "=r"(v[u].y), "=r"(v[u].z), "=r"(v[u].w)
+                   : "l"(buf + idx));
+      idx += step;
+      if (idx >= n16) idx -= n16;
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) acc ^= v[u].x ^ v[u].y ^ v[u].z ^ v[u].w;
+  }
+  if (acc == 0x9e3779b9u) *sink = acc;  // (practically never true; keeps the loads alive)
+}
+
 // The address under which the device sees a host buffer, or nullptr if it cannot (pageable memory).
 const float* device_view_of_host(const float* h) {
   cudaPointerAttributes attr;
@@ -170,10 +199,40 @@ int fftopk_select2048_host(const float* h_score, int64_t h_row_stride, int32_t B
       b = e;
     }
   }
-  const int rc = fftopk_select2048(d_score, h.row_stride, B, L, d_len, nullptr, d_out, nullptr, 0, d_status, cuda_stream);
+  fftopk::SelectCall c;
+  c.score = d_score;
+  c.row_stride = h.row_stride;
+  c.B = B;
+  c.L = L;
+  c.lengths = d_len;
+  c.out_idx = d_out;
+  c.status = d_status;
+  c.cuda_stream = cuda_stream;
+  c.may_overlap = false;  // reads what the gather kernel / the copies enqueued above have staged
+  const int rc = fftopk::launch_select(c);
   if (rc) return rc;
   err = cudaMemcpyAsync(h_out_idx, d_out, (size_t)B * 2048 * 4, cudaMemcpyDeviceToHost, stream);
   if (err != cudaSuccess) return fftopk::cuda_fail(err);
+  return FFTOPK_OK;
+}
+
+int fftopk_probe_read_bandwidth(const void* d_buf, size_t bytes, size_t bytes_to_read, uint32_t* d_sink,
+                                size_t* bytes_read, void* cuda_stream) {
+  if (!d_buf || !d_sink || !bytes_read || bytes < 16 || (reinterpret_cast<uintptr_t>(d_buf) & 15u) != 0) return FFTOPK_EINVAL;
+  if (bytes / 16 > 0x7fffffffull) return FFTOPK_ERANGE;
+  int dev = 0, sms = 0;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err == cudaSuccess) err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (err != cudaSuccess) return fftopk::cuda_fail(err);
+  const uint32_t n16 = (uint32_t)(bytes / 16);
+  const size_t per_round = (size_t)sms * 2 * 1024 * 8 * 16;  // two CTAs of 1024 threads per SM
+  size_t rounds = (bytes_to_read + per_round - 1) / per_round;
+  rounds = rounds < 1 ? 1 : (rounds > 0x7fffffffull ? 0x7fffffffull : rounds);
+  read_probe_kernel<<<dim3((unsigned)sms * 2), 1024, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
+      static_cast<const uint4*>(d_buf), n16, (uint32_t)rounds, d_sink);
+  err = cudaGetLastError();
+  if (err != cudaSuccess) return fftopk::cuda_fail(err);
+  *bytes_read = rounds * per_round;
   return FFTOPK_OK;
 }
 
@@ -206,7 +265,19 @@ int fftopk_select_topk_16bit(const void* score16, int32_t dtype, int64_t row_str
   }
   cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) return fftopk::cuda_fail(err);
-  return fftopk_select_topk(d_score, d_stride, B, L, lengths, row_starts, k, out_idx, nullptr, 0, status, cuda_stream);
+  fftopk::SelectCall call;
+  call.score = d_score;
+  call.row_stride = d_stride;
+  call.B = B;
+  call.L = L;
+  call.lengths = lengths;
+  call.row_starts = row_starts;
+  call.k = k;
+  call.out_idx = out_idx;
+  call.status = status;
+  call.cuda_stream = cuda_stream;
+  call.may_overlap = false;  // reads the workspace the widening kernel enqueued above has written
+  return fftopk::launch_select(call);
 }
 
 }  // extern "C"

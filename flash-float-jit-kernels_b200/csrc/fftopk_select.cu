@@ -39,9 +39,7 @@
 //   FFTOPK_U512             128-bit loads in flight per thread of the 512-thread filter (8; 16 allowed)
 //   FFTOPK_CTAS_512         512-thread CTAs per SM the register budget allows (2)
 //   FFTOPK_KSMALL           undecided candidates ranked by votes (256)
-//   FFTOPK_TRACE / FFTOPK_STOP_AFTER=<mark> / FFTOPK_EXPERIMENT_NOPASS / FFTOPK_DEBUG_FALLBACK
-//                           phase timestamps, early return at a phase mark, a filter nothing
-//                           passes, a status bit when the full-histogram path is taken
+//   FFTOPK_TRACE            phase timestamps of block 0 (changes no result)
 #include <cooperative_groups.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -50,6 +48,7 @@
 #include "fftopk_trace.cuh"
 #include "fftopk_device.cuh"
 #include "fftopk_host.h"
+#include "fftopk_internal.h"
 #include "fftopk_key.h"
 
 namespace fftopk {
@@ -262,7 +261,10 @@ __device__ __forceinline__ uint32_t filter_shard(const Shard& sh, float edge, ui
         idx[u] = j < own ? seg32[j] : 0u;
       }
 #pragma unroll
-      for (int u = 0; u < 4; ++u) bits[u] = __ldg(base1 + idx[u] + fa);  // (index 0 is always readable)
+      for (int u = 0; u < 4; ++u) {
+        if (!FFTOPK_CHECK(7, idx[u], len, ctrl_status(ctrl))) idx[u] = 0u;
+        bits[u] = __ldg(base1 + idx[u] + fa);  // (index 0 is always readable)
+      }
       __syncwarp();
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
@@ -570,7 +572,7 @@ __device__ __forceinline__ DualPick cluster_pick_dual(cg::cluster_group& cluster
     // four super-bins = 256 bins of A = one value of the top four key bits
     const uint32_t pair = lo + hi;
     const uint32_t grp = pair + __shfl_xor_sync(kFull, pair, 1);
-    const unsigned one = __ballot_sync(kFull, dual && total > 0u && grp == total);
+    const unsigned one = __ballot_sync(kFull, fine_histogram_usable(dual, total, grp));
     const bool use_b = one != 0u;
     const uint32_t lob = ctrl->totb[2 * lane], hib = ctrl->totb[2 * lane + 1];
     uint32_t above = 0, cnt = 0;
@@ -625,7 +627,7 @@ __device__ __forceinline__ DualPick cluster_pick_dual(cg::cluster_group& cluster
   d.focus_bin = -1;
   d.ok = ctrl->t >= 0;
   d.pbits = use_b ? 16 : 12;
-  d.prefix = use_b ? ((ctrl->dual_g << 12) | (uint32_t)ctrl->t) : (uint32_t)ctrl->t;
+  d.prefix = guess_prefix(use_b, ctrl->dual_g, (uint32_t)ctrl->t);
   d.need2 = ctrl->above;
   d.cnt = ctrl->cnt;
   d.total = ctrl->run_total;
@@ -662,7 +664,7 @@ struct RowCtx {
 template <int NT>
 __device__ __forceinline__ void emit_winner(const RowCtx<NT>& cx, uint32_t base_w, uint32_t key, int idx) {
   const uint32_t pos = base_w + warp_alloc(&cx.ctrl->wslot);
-  if (pos < cx.k) {
+  if (FFTOPK_CHECK(1, pos, cx.k, cx.status) && pos < cx.k) {
     cx.out_idx[pos] = cx.page ? __ldg(cx.page + idx) : idx + cx.idx_offset;
     if (cx.out_key) cx.out_key[pos] = key;
   }
@@ -810,7 +812,8 @@ __device__ __forceinline__ int refine_from_data(RowCtx<NT>& cx, uint32_t& need, 
             emit_winner<NT>(cx, base_w, key, idx);
           } else if (hh == Pn) {
             const uint32_t slot = base_c + warp_alloc(&ctrl->cslot);
-            if (slot < (uint32_t)cx.cand_cap) cx.cand0[slot] = ((uint64_t)key << 32) | (uint64_t)(~(uint32_t)idx);
+            if (FFTOPK_CHECK(2, slot, cx.cand_cap, cx.status) && slot < (uint32_t)cx.cand_cap)
+              cx.cand0[slot] = ((uint64_t)key << 32) | (uint64_t)(~(uint32_t)idx);
           }
         }
       });
@@ -820,8 +823,10 @@ __device__ __forceinline__ int refine_from_data(RowCtx<NT>& cx, uint32_t& need, 
         if (((hh >> w) == Pold) && hh >= Pn) emit_winner<NT>(cx, base_w, key, idx);
       });
     } else {  // kModeTies: all 32 key bits are fixed; Pn is the threshold key itself
+      // (only keys under this round's prefix: larger prefixes were written by the earlier rounds,
+      // and the slots reserved here are for this round's winners alone)
       scan_shard<NT>(sh, [&](uint32_t key, int idx) {
-        if (key > Pn) emit_winner<NT>(cx, base_w, key, idx);
+        if ((key >> w) == Pold && key > Pn) emit_winner<NT>(cx, base_w, key, idx);
       });
       // Exact duplicates of the threshold key: the first `need` of them in index order win.
       // Shards are contiguous and ordered by rank, so this CTA takes its first `quota`.
@@ -859,7 +864,7 @@ __device__ __forceinline__ int refine_from_data(RowCtx<NT>& cx, uint32_t& need, 
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           if (m[j]) {
-            if (rnk < quota && obase + rnk < cx.k) {
+            if (rnk < quota && FFTOPK_CHECK(6, obase + rnk, cx.k, cx.status) && obase + rnk < cx.k) {
               cx.out_idx[obase + rnk] = cx.page ? __ldg(cx.page + i0 + j) : i0 + j + cx.idx_offset;
               if (cx.out_key) cx.out_key[obase + rnk] = Pn;
             }
@@ -999,6 +1004,9 @@ __global__ void __launch_bounds__(NT, (NT == 512 ? FFTOPK_CTAS_512 : 1024 / NT))
       ctrl->cslot = 0u;
       ctrl->lcount = 0u;
       ctrl->spill_kmax = 0u;
+#ifdef FFTOPK_CHECKED
+      ctrl->status_ptr = p.status;
+#endif
     }
   }
   // ---- sample (or, for a shard that fits in registers, the whole shard) ------------------------
@@ -1119,7 +1127,7 @@ __global__ void __launch_bounds__(NT, (NT == 512 ? FFTOPK_CTAS_512 : 1024 / NT))
                 emit_winner<NT>(cx, base_w, key, i0 + e);
               } else if (bin == t) {
                 const uint32_t slot = base_c + warp_alloc(&ctrl->cslot);
-                if (slot < (uint32_t)p.cand_cap)
+                if (FFTOPK_CHECK(2, slot, p.cand_cap, p.status) && slot < (uint32_t)p.cand_cap)
                   cx.cand0[slot] = ((uint64_t)key << 32) | (uint64_t)(~(uint32_t)(i0 + e));
               }
             }
@@ -1133,27 +1141,19 @@ __global__ void __launch_bounds__(NT, (NT == 512 ? FFTOPK_CTAS_512 : 1024 / NT))
     // (m expected sample elements among the true top k, plus five standard deviations).
     const float flen = (float)len;
     const DualPick dp = cluster_pick_dual<NT>(cluster, C, cx.hist(0), cx.sup(0), cx.hist(1), cx.sup(1), dual, ctrl, pick_no,
-                                              [&](uint32_t n_s) {
-                                                const float m = (float)K * (float)n_s / flen;
-                                                const uint32_t rk = (uint32_t)(m + 5.0f * sqrtf(m) + 14.0f);
-                                                return rk < n_s ? rk : n_s;
-                                              },
-                                              [&](uint32_t n_s) {  // the mirror image; 0: no such rank
-                                                const float m = (float)K * (float)n_s / flen;
-                                                const float rk = m - 5.0f * sqrtf(m) - 14.0f;
-                                                return rk >= 1.0f ? (uint32_t)rk : 0u;
-                                              });
+                                              [&](uint32_t n_s) { return sample_lower_rank(K, n_s, flen); },
+                                              [&](uint32_t n_s) { return sample_upper_rank(K, n_s, flen); });
     FFTOPK_MARK(4);
     // If the sample says the guessed bin alone holds more than ~2k row elements (values crowded
     // into a sliver of the key space), a second sample round on the next 12 key bits sharpens it.
     // (Below that, carrying the extra candidates is cheaper than the round: measured 1.0-1.5 us
     // per call on N(0,1) rows of 384K..2M elements.)
-    const float in_bin = (float)dp.cnt * flen / (float)(dp.total ? dp.total : 1u);
 #ifndef FFTOPK_1B_FACTOR
 #define FFTOPK_1B_FACTOR 2.0f
 #endif
-    int smode = !dp.ok ? kModeFallback : (in_bin > FFTOPK_1B_FACTOR * (float)K ? kModeNext : kModeGather);
-    uint32_t gkey = dp.prefix << (32 - dp.pbits);
+    int smode = !dp.ok ? kModeFallback
+                       : (sample_bin_too_coarse(dp.cnt, dp.total, flen, K, FFTOPK_1B_FACTOR) ? kModeNext : kModeGather);
+    uint32_t gkey = guess_key(dp.prefix, dp.pbits);
     if (smode == kModeNext) {
       const int sb = 32 - dp.pbits - 12;  // position of the next 12 bits
       const uint32_t rem = dp.need2;
@@ -1198,11 +1198,7 @@ __global__ void __launch_bounds__(NT, (NT == 512 ? FFTOPK_CTAS_512 : 1024 / NT))
       // Lower edge of the guess as a float: key(x) >= gkey  <=>  !(x < edge), NaN included.
       // Keys outside the range real values map to (below -inf's key / above +inf's) admit
       // everything instead; that only lengthens the lists.
-      float edge = __uint_as_float(0xff800000u);  // -inf
-      if (gkey > 0x007fffffu && gkey <= 0xff800000u) edge = __uint_as_float(fftopk_bits_from_key(gkey));
-#ifdef FFTOPK_EXPERIMENT_NOPASS
-      edge = __uint_as_float(0x7f800000u);  // experiment: nothing but +inf/NaN passes
-#endif
+      const float edge = __uint_as_float(guess_edge_bits(gkey));
       // list layout: one segment per warp, then the spill area (an eighth of the list)
       const uint32_t spill_cap = (uint32_t)p.list_cap / 8u;
       const uint32_t seg_cap = ((uint32_t)p.list_cap - spill_cap) / NW;
@@ -1212,7 +1208,7 @@ __global__ void __launch_bounds__(NT, (NT == 512 ? FFTOPK_CTAS_512 : 1024 / NT))
       // A lone CTA that knows a bin the threshold will not lie above builds the histogram of the
       // finish's first round while it converts its candidates (they pass through registers there
       // anyway): the digit rule needs only the guess and that bound.
-      const uint32_t lowkey = (gkey > 0x007fffffu && gkey <= 0xff800000u) ? gkey : 0u;
+      const uint32_t lowkey = guess_low_key(gkey);
       fin_lo = lowkey;
       if (C == 1 && dp.focus_bin >= 0) {
         fin_focus = (((uint32_t)dp.focus_bin + 1u) << (32 - dp.pbits)) - 1u;
@@ -1297,7 +1293,7 @@ __global__ void __launch_bounds__(NT, (NT == 512 ? FFTOPK_CTAS_512 : 1024 / NT))
         // fewer than k admitted (the guess was too high), a list overflowed, or more than rank 0
         // can hold: start over with full histograms
         const uint32_t room = C == 1 ? 0xffffffffu : (uint32_t)p.cand_cap;  // (a lone CTA keeps them in the list)
-        mode = (over == 0u && total >= K && total <= room) ? kModeGather : kModeFallback;
+        mode = sampled_attempt_ok(over, total, K, room) ? kModeGather : kModeFallback;
         // every candidate's key lies in [lowkey, maxkey]
         fin_cap = maxkey;
         if (fin_hist) {
@@ -1315,9 +1311,6 @@ __global__ void __launch_bounds__(NT, (NT == 512 ? FFTOPK_CTAS_512 : 1024 / NT))
     }
   }
 
-#ifdef FFTOPK_DEBUG_FALLBACK
-  if (mode == kModeFallback && tid == 0 && p.status) atomicOr(p.status, 8u);
-#endif
   if (mode == kModeFallback) mode = refine_from_data<NT>(cx, need, P, r, pick_no);
 
   // Candidates that peers pushed into rank 0 are complete after a cluster barrier. The sampled
@@ -1363,21 +1356,28 @@ namespace {
 
 using namespace fftopk;
 
-
+// Process-wide overrides (fftopk_set_tuning, fftopk_set_overlap). Writers and readers go through
+// the mutex; every launch works on its own snapshot.
 struct Tuning {
   int cluster = -1, threads = -1, list_cap = -1, cand_cap = -1, force_slow = 0, overlap = 0;
 };
+std::mutex g_tuning_mu;
 Tuning g_tuning;
 
+Tuning tuning_snapshot() {
+  std::lock_guard<std::mutex> lock(g_tuning_mu);
+  return g_tuning;
+}
+
 struct DeviceInfo {
-  bool ready = false;
+  DeviceOnce once;
   int sm_count = 0;
   int smem_optin = 0;
   int cc_major = 0;
   int max_cluster = 0;  // largest cluster size that can be scheduled with the latency-mode footprint
   int active16 = 0, active8 = 0;  // clusters of that size the device holds at once (same footprint)
 };
-DeviceInfo g_dev[64];
+DeviceInfo g_dev[kMaxDevices];
 
 constexpr size_t fixed_smem_bytes() {
   return (size_t)(2 * kMaxBins + 3 * kSup + kMaxCluster * kSup) * 4 + ((sizeof(Ctrl) + 127) & ~(size_t)127);
@@ -1407,59 +1407,64 @@ int setup_kernel(int smem_optin) {
   return 0;
 }
 
+int init_device(DeviceInfo& d, int dev) {
+  cudaDeviceProp prop;
+  cudaError_t e = cudaGetDeviceProperties(&prop, dev);
+  if (e != cudaSuccess) return cuda_fail(e);
+  d.sm_count = prop.multiProcessorCount;
+  d.smem_optin = (int)prop.sharedMemPerBlockOptin;
+  d.cc_major = prop.major;
+  if (prop.major < 10) return FFTOPK_EDEVICE;
+  int rc = setup_kernel<1024>(d.smem_optin);
+  if (rc) return rc;
+  rc = setup_kernel<512>(d.smem_optin);
+  if (rc) return rc;
+  rc = setup_kernel<256>(d.smem_optin);
+  if (rc) return rc;
+  // can a 16-CTA cluster with the latency-mode shared-memory footprint be co-scheduled, and how
+  // many clusters of 16 / of 8 CTAs does the device hold at once? (A cluster lives inside one
+  // GPC, so fewer 16-CTA clusters fit than SM count / 16: a batch with more rows than that would
+  // run in two waves.)
+  d.max_cluster = 8;
+  d.active16 = 0;
+  d.active8 = d.sm_count / 8;
+  for (int cs = 16; cs >= 8; cs /= 2) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(cs * 32, 1, 1);
+    cfg.blockDim = dim3(1024, 1, 1);
+    cfg.dynamicSmemBytes = fixed_smem_bytes() + (size_t)(kLatencyListCap + kLatencyCandCap) * 8;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = cs;
+    at[0].val.clusterDim.y = 1;
+    at[0].val.clusterDim.z = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    int nclusters = 0;
+    e = cudaOccupancyMaxActiveClusters(&nclusters, select2048_kernel<1024>, &cfg);
+    if (e == cudaSuccess && nclusters >= 1) {
+      if (cs == 16) {
+        d.max_cluster = 16;
+        d.active16 = nclusters;
+      } else {
+        d.active8 = nclusters;
+      }
+    }
+    (void)cudaGetLastError();
+  }
+  return 0;
+}
+
+// Properties of the current device; the first call on a device (any thread) sets the kernels'
+// function attributes.
 int device_info(DeviceInfo** out) {
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return cuda_fail(e);
-  if (dev < 0 || dev >= 64) return FFTOPK_EDEVICE;
+  if (dev < 0 || dev >= kMaxDevices) return FFTOPK_EDEVICE;
   DeviceInfo& d = g_dev[dev];
-  if (!d.ready) {
-    cudaDeviceProp prop;
-    e = cudaGetDeviceProperties(&prop, dev);
-    if (e != cudaSuccess) return cuda_fail(e);
-    d.sm_count = prop.multiProcessorCount;
-    d.smem_optin = (int)prop.sharedMemPerBlockOptin;
-    d.cc_major = prop.major;
-    if (prop.major < 10) return FFTOPK_EDEVICE;
-    int rc = setup_kernel<1024>(d.smem_optin);
-    if (rc) return rc;
-    rc = setup_kernel<512>(d.smem_optin);
-    if (rc) return rc;
-    rc = setup_kernel<256>(d.smem_optin);
-    if (rc) return rc;
-    // can a 16-CTA cluster with the latency-mode shared-memory footprint be co-scheduled, and how
-    // many clusters of 16 / of 8 CTAs does the device hold at once? (A cluster lives inside one
-    // GPC, so fewer 16-CTA clusters fit than SM count / 16: a batch with more rows than that would
-    // run in two waves.)
-    d.max_cluster = 8;
-    d.active16 = 0;
-    d.active8 = d.sm_count / 8;
-    for (int cs = 16; cs >= 8; cs /= 2) {
-      cudaLaunchConfig_t cfg = {};
-      cfg.gridDim = dim3(cs * 32, 1, 1);
-      cfg.blockDim = dim3(1024, 1, 1);
-      cfg.dynamicSmemBytes = fixed_smem_bytes() + (size_t)(kLatencyListCap + kLatencyCandCap) * 8;
-      cudaLaunchAttribute at[1];
-      at[0].id = cudaLaunchAttributeClusterDimension;
-      at[0].val.clusterDim.x = cs;
-      at[0].val.clusterDim.y = 1;
-      at[0].val.clusterDim.z = 1;
-      cfg.attrs = at;
-      cfg.numAttrs = 1;
-      int nclusters = 0;
-      e = cudaOccupancyMaxActiveClusters(&nclusters, select2048_kernel<1024>, &cfg);
-      if (e == cudaSuccess && nclusters >= 1) {
-        if (cs == 16) {
-          d.max_cluster = 16;
-          d.active16 = nclusters;
-        } else {
-          d.active8 = nclusters;
-        }
-      }
-      (void)cudaGetLastError();
-    }
-    d.ready = true;
-  }
+  const int rc = d.once.run([&] { return init_device(d, dev); });
+  if (rc) return rc;
   *out = &d;
   return 0;
 }
@@ -1475,8 +1480,9 @@ int floor_pow2(int64_t v) {
 }
 
 // Replaces the reference's split heuristic (topk_indexer_radix.cu:1081-1111: at most 8 CTAs per
-// row, a hard-coded SM count of 132).
-Plan make_plan(const DeviceInfo& d, int B, int64_t L) {
+// row, a hard-coded SM count of 132). `overlap`: the launch may overlap its neighbours on the
+// stream (throughput plan).
+Plan make_plan(const DeviceInfo& d, const Tuning& tn, bool overlap, int B, int64_t L) {
   Plan pl;
   const int rows = B > 0 ? B : 1;
   // CTAs per row: as many as keep the whole grid resident at once with one CTA per SM, but never
@@ -1495,7 +1501,17 @@ Plan make_plan(const DeviceInfo& d, int B, int64_t L) {
   const bool one_per_sm = (int64_t)rows * pl.cluster <= d.sm_count;
   pl.list_cap = one_per_sm ? kLatencyListCap : kBatchListCap;
   pl.cand_cap = one_per_sm ? kLatencyCandCap : kBatchCandCap;
-  if (g_tuning.overlap) {
+  if (rows > d.sm_count) {
+    // More rows than SMs: the batch fills the device by itself. One 512-thread CTA per row with
+    // the list of the throughput plan, two CTAs per SM (measured on ragged rows of up to 128K
+    // elements: 29.7 us per call at B=256 and 52.6 us at B=512, against 38.5 / 68.1 us with 1024
+    // threads; a list of 4096 entries split over 32 warps overflowed its segments and sent rows
+    // to the full-histogram path: 78 / 113 us).
+    pl.cluster = 1;
+    pl.threads = 512;
+    pl.list_cap = L <= kOverlapShortRow ? kOverlapListCap1 : kOverlapListCap1Long;
+  }
+  if (overlap) {
     // Back-to-back calls may overlap: what counts is work per row, not the latency of one call.
     // Few CTAs per row (less cluster traffic per row), 512 threads and about 110 KB of shared
     // memory so that two CTAs - of different calls - share an SM, and about four calls in flight.
@@ -1509,20 +1525,115 @@ Plan make_plan(const DeviceInfo& d, int B, int64_t L) {
       pl.cand_cap = kOverlapCandCap;
     }
   }
-  if (g_tuning.cluster > 0) pl.cluster = g_tuning.cluster;
-  if (g_tuning.threads > 0) pl.threads = g_tuning.threads;
-  if (g_tuning.list_cap > 0) pl.list_cap = (g_tuning.list_cap + 15) & ~15;
-  if (g_tuning.cand_cap > 0) pl.cand_cap = (g_tuning.cand_cap + 15) & ~15;
+  if (tn.cluster > 0) pl.cluster = tn.cluster;
+  if (tn.threads > 0) pl.threads = tn.threads;
+  if (tn.list_cap > 0) pl.list_cap = (tn.list_cap + 15) & ~15;
+  if (tn.cand_cap > 0) pl.cand_cap = (tn.cand_cap + 15) & ~15;
   if (pl.cluster == 1) pl.cand_cap = pl.list_cap;  // one CTA per row: the two buffers are the same memory
   pl.smem_bytes = (int)(fixed_smem_bytes() + (size_t)(pl.cluster == 1 ? pl.list_cap : pl.list_cap + pl.cand_cap) * 8);
   return pl;
 }
 
+SelectCall basic_call(const float* score, int64_t row_stride, int32_t B, int64_t L, const int32_t* lengths,
+                      const int32_t* row_starts, int32_t* out_idx, uint32_t* out_key, int32_t idx_offset,
+                      uint32_t* status, void* cuda_stream) {
+  SelectCall c;
+  c.score = score;
+  c.row_stride = row_stride;
+  c.B = B;
+  c.L = L;
+  c.lengths = lengths;
+  c.row_starts = row_starts;
+  c.out_idx = out_idx;
+  c.out_key = out_key;
+  c.idx_offset = idx_offset;
+  c.status = status;
+  c.cuda_stream = cuda_stream;
+  return c;
+}
+
 }  // namespace
+
+namespace fftopk {
+
+int launch_select(const SelectCall& c) {
+  if (c.B < 0 || c.L < 0 || c.row_stride < 0 || c.k < 1 || c.k > kMaxK) return FFTOPK_EINVAL;
+  if (c.B == 0) return FFTOPK_OK;
+  if (!c.score || !c.lengths || !c.out_idx) return FFTOPK_EINVAL;
+  if ((reinterpret_cast<uintptr_t>(c.score) & 3u) != 0) return FFTOPK_EINVAL;
+  if (c.L > (int64_t)0x7fffffff - 8 || (int64_t)c.B * kMaxCluster > (int64_t)0x7fffffff) return FFTOPK_ERANGE;
+  DeviceInfo* d = nullptr;
+  int rc = device_info(&d);
+  if (rc) return rc;
+  const Tuning tn = tuning_snapshot();
+  const bool overlap = tn.overlap != 0 && c.may_overlap;
+  Plan pl = make_plan(*d, tn, overlap, c.B, c.L);
+  if (c.k > kK && pl.cluster == 1 && tn.list_cap <= 0) {
+    // more winners than the lone-CTA list was sized for: the long-row list
+    pl.list_cap = pl.cand_cap = kOverlapListCap1Long;
+    pl.smem_bytes = (int)(fixed_smem_bytes() + (size_t)pl.list_cap * 8);
+  }
+
+  SelectParams p;
+  p.score = c.score;
+  p.row_stride = c.row_stride;
+  p.L = c.L;
+  p.lengths = c.lengths;
+  p.row_starts = c.row_starts;
+  p.out_idx = c.out_idx;
+  p.out_key = c.out_key;
+  p.status = c.status;
+  p.B = c.B;
+  p.k = c.k;
+  p.idx_offset = c.idx_offset;
+  p.list_cap = pl.list_cap;
+  p.cand_cap = pl.cand_cap;
+  p.force_slow = tn.force_slow;
+  p.overlap = overlap ? 1 : 0;
+  p.src_page_table = c.src_page_table;
+  p.src_stride = c.src_stride;
+  p.cu_seqlens_q = c.cu_seqlens_q;
+  p.prefill_bs = c.prefill_bs;
+  p.row_offsets = c.row_offsets;
+  p.cp_flag = c.cp_flag;
+  p.cp_half_words = c.cp_half_words;
+  if ((size_t)pl.smem_bytes > (size_t)d->smem_optin) return FFTOPK_ERANGE;
+
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)c.B * (unsigned)pl.cluster, 1, 1);
+  cfg.blockDim = dim3((unsigned)pl.threads, 1, 1);
+  cfg.dynamicSmemBytes = (size_t)pl.smem_bytes;
+  cfg.stream = static_cast<cudaStream_t>(c.cuda_stream);
+  cudaLaunchAttribute at[2];
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = (unsigned)pl.cluster;
+  at[0].val.clusterDim.y = 1;
+  at[0].val.clusterDim.z = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = 1;
+  if (overlap) {
+    at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.numAttrs = 2;
+  }
+  cudaError_t e;
+  const bool any_k = c.k != kK;
+  if (pl.threads == 1024) {
+    e = any_k ? cudaLaunchKernelEx(&cfg, select2048_kernel<1024, true>, p) : cudaLaunchKernelEx(&cfg, select2048_kernel<1024>, p);
+  } else if (pl.threads == 512) {
+    e = any_k ? cudaLaunchKernelEx(&cfg, select2048_kernel<512, true>, p) : cudaLaunchKernelEx(&cfg, select2048_kernel<512>, p);
+  } else {
+    e = any_k ? cudaLaunchKernelEx(&cfg, select2048_kernel<256, true>, p) : cudaLaunchKernelEx(&cfg, select2048_kernel<256>, p);
+  }
+  if (e != cudaSuccess) return cuda_fail(e);
+  return FFTOPK_OK;
+}
+
+}  // namespace fftopk
 
 extern "C" {
 
-int fftopk_version(void) { return 100; }
+int fftopk_version(void) { return 200; }
 
 const char* fftopk_strerror(int code) {
   switch (code) {
@@ -1537,14 +1648,26 @@ const char* fftopk_strerror(int code) {
 
 int fftopk_last_cuda_error(void) { return fftopk::g_last_cuda_error; }
 
+#ifdef FFTOPK_CHECKED
+// Checked builds only: the first violation recorded by the selection kernels (rec[0..3]) and by the
+// merge kernel (rec[4..7]) as (site, index, limit, block); site 0 = none. Clears both records.
+int fftopk_checked_read(uint32_t rec[8]) {
+  const uint32_t zero[4] = {0u, 0u, 0u, 0u};
+  cudaError_t e = cudaMemcpyFromSymbol(rec, fftopk::g_check_rec, sizeof(zero));
+  if (e == cudaSuccess) e = cudaMemcpyToSymbol(fftopk::g_check_rec, zero, sizeof(zero));
+  if (e != cudaSuccess) return fftopk::cuda_fail(e);
+  return fftopk::checked_read_merge(rec + 4);
+}
+#endif
+
 #ifdef FFTOPK_TRACE
-int fftopk_debug_read_trace(unsigned long long* times, int* ids, int* n) {
+int fftopk_trace_read(unsigned long long* times, int* ids, int* n) {
   cudaError_t e = cudaMemcpyFromSymbol(n, fftopk::g_trace_n, sizeof(int));
   if (e == cudaSuccess) e = cudaMemcpyFromSymbol(times, fftopk::g_trace_t, sizeof(unsigned long long) * fftopk::kTraceCap);
   if (e == cudaSuccess) e = cudaMemcpyFromSymbol(ids, fftopk::g_trace_id, sizeof(int) * fftopk::kTraceCap);
   return (int)e;
 }
-int fftopk_debug_clear_trace(void) {
+int fftopk_trace_clear(void) {
   const int z = 0;
   return (int)cudaMemcpyToSymbol(fftopk::g_trace_n, &z, sizeof(int));
 }
@@ -1562,6 +1685,7 @@ int fftopk_set_tuning(int32_t cluster_ctas, int32_t threads, int32_t list_cap, i
   if (threads > 0 && threads != 256 && threads != 512 && threads != 1024) return FFTOPK_EINVAL;
   if (cand_cap > 0 && (cand_cap < 32 || cand_cap > 16384)) return FFTOPK_EINVAL;
   if (list_cap > 0 && (list_cap < 32 || list_cap > 16384)) return FFTOPK_EINVAL;
+  std::lock_guard<std::mutex> lock(g_tuning_mu);
   g_tuning.cluster = cluster_ctas;
   g_tuning.threads = threads;
   g_tuning.list_cap = list_cap;
@@ -1571,6 +1695,7 @@ int fftopk_set_tuning(int32_t cluster_ctas, int32_t threads, int32_t list_cap, i
 }
 
 int fftopk_set_overlap(int32_t enable) {
+  std::lock_guard<std::mutex> lock(g_tuning_mu);
   g_tuning.overlap = enable ? 1 : 0;
   return FFTOPK_OK;
 }
@@ -1580,7 +1705,8 @@ int fftopk_plan(int32_t B, int64_t L, int32_t plan[6]) {
   DeviceInfo* d = nullptr;
   int rc = device_info(&d);
   if (rc) return rc;
-  const Plan pl = make_plan(*d, B, L);
+  const Tuning tn = tuning_snapshot();
+  const Plan pl = make_plan(*d, tn, tn.overlap != 0, B, L);
   plan[0] = pl.cluster;
   plan[1] = pl.threads;
   plan[2] = pl.smem_bytes;
@@ -1590,93 +1716,19 @@ int fftopk_plan(int32_t B, int64_t L, int32_t plan[6]) {
   return FFTOPK_OK;
 }
 
-static int launch_select(const float* score, int64_t row_stride, int32_t B, int64_t L, const int32_t* lengths,
-                         const int32_t* row_starts, int32_t* out_idx, uint32_t* out_key, int32_t idx_offset,
-                         uint32_t* status, void* cuda_stream, const int32_t* src_page_table, int64_t src_stride,
-                         const int32_t* cu_seqlens_q, int32_t prefill_bs, const int32_t* row_offsets,
-                         const uint32_t* cp_flag = nullptr, int64_t cp_half_words = 0, int32_t k = kK) {
-  if (B < 0 || L < 0 || row_stride < 0 || k < 1 || k > kMaxK) return FFTOPK_EINVAL;
-  if (B == 0) return FFTOPK_OK;
-  if (!score || !lengths || !out_idx) return FFTOPK_EINVAL;
-  if ((reinterpret_cast<uintptr_t>(score) & 3u) != 0) return FFTOPK_EINVAL;
-  if (L > (int64_t)0x7fffffff - 8 || (int64_t)B * kMaxCluster > (int64_t)0x7fffffff) return FFTOPK_ERANGE;
-  DeviceInfo* d = nullptr;
-  int rc = device_info(&d);
-  if (rc) return rc;
-  Plan pl = make_plan(*d, B, L);
-  if (k > kK && pl.cluster == 1 && g_tuning.list_cap <= 0) {
-    // more winners than the lone-CTA list was sized for: the long-row list
-    pl.list_cap = pl.cand_cap = kOverlapListCap1Long;
-    pl.smem_bytes = (int)(fixed_smem_bytes() + (size_t)pl.list_cap * 8);
-  }
-
-  SelectParams p;
-  p.score = score;
-  p.row_stride = row_stride;
-  p.L = L;
-  p.lengths = lengths;
-  p.row_starts = row_starts;
-  p.out_idx = out_idx;
-  p.out_key = out_key;
-  p.status = status;
-  p.B = B;
-  p.k = k;
-  p.idx_offset = idx_offset;
-  p.list_cap = pl.list_cap;
-  p.cand_cap = pl.cand_cap;
-  p.force_slow = g_tuning.force_slow;
-  p.overlap = g_tuning.overlap;
-  p.src_page_table = src_page_table;
-  p.src_stride = src_stride;
-  p.cu_seqlens_q = cu_seqlens_q;
-  p.prefill_bs = prefill_bs;
-  p.row_offsets = row_offsets;
-  p.cp_flag = cp_flag;
-  p.cp_half_words = cp_half_words;
-  if ((size_t)pl.smem_bytes > (size_t)d->smem_optin) return FFTOPK_ERANGE;
-
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)B * (unsigned)pl.cluster, 1, 1);
-  cfg.blockDim = dim3((unsigned)pl.threads, 1, 1);
-  cfg.dynamicSmemBytes = (size_t)pl.smem_bytes;
-  cfg.stream = static_cast<cudaStream_t>(cuda_stream);
-  cudaLaunchAttribute at[2];
-  at[0].id = cudaLaunchAttributeClusterDimension;
-  at[0].val.clusterDim.x = (unsigned)pl.cluster;
-  at[0].val.clusterDim.y = 1;
-  at[0].val.clusterDim.z = 1;
-  cfg.attrs = at;
-  cfg.numAttrs = 1;
-  if (g_tuning.overlap) {
-    at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    at[1].val.programmaticStreamSerializationAllowed = 1;
-    cfg.numAttrs = 2;
-  }
-  cudaError_t e;
-  const bool any_k = k != kK;
-  if (pl.threads == 1024) {
-    e = any_k ? cudaLaunchKernelEx(&cfg, select2048_kernel<1024, true>, p) : cudaLaunchKernelEx(&cfg, select2048_kernel<1024>, p);
-  } else if (pl.threads == 512) {
-    e = any_k ? cudaLaunchKernelEx(&cfg, select2048_kernel<512, true>, p) : cudaLaunchKernelEx(&cfg, select2048_kernel<512>, p);
-  } else {
-    e = any_k ? cudaLaunchKernelEx(&cfg, select2048_kernel<256, true>, p) : cudaLaunchKernelEx(&cfg, select2048_kernel<256>, p);
-  }
-  if (e != cudaSuccess) return cuda_fail(e);
-  return FFTOPK_OK;
-}
-
 int fftopk_select2048(const float* score, int64_t row_stride, int32_t B, int64_t L, const int32_t* lengths,
                       const int32_t* row_starts, int32_t* out_idx, uint32_t* out_key, int32_t idx_offset,
                       uint32_t* status, void* cuda_stream) {
-  return launch_select(score, row_stride, B, L, lengths, row_starts, out_idx, out_key, idx_offset, status, cuda_stream,
-                       nullptr, 0, nullptr, 0, nullptr);
+  return launch_select(basic_call(score, row_stride, B, L, lengths, row_starts, out_idx, out_key, idx_offset, status,
+                                  cuda_stream));
 }
 
 int fftopk_select_topk(const float* score, int64_t row_stride, int32_t B, int64_t L, const int32_t* lengths,
                        const int32_t* row_starts, int32_t k, int32_t* out_idx, uint32_t* out_key, int32_t idx_offset,
                        uint32_t* status, void* cuda_stream) {
-  return launch_select(score, row_stride, B, L, lengths, row_starts, out_idx, out_key, idx_offset, status, cuda_stream,
-                       nullptr, 0, nullptr, 0, nullptr, nullptr, 0, k);
+  SelectCall c = basic_call(score, row_stride, B, L, lengths, row_starts, out_idx, out_key, idx_offset, status, cuda_stream);
+  c.k = k;
+  return launch_select(c);
 }
 
 int fftopk_select2048_page_table(const float* score, int64_t row_stride, int32_t B, int64_t L,
@@ -1684,24 +1736,21 @@ int fftopk_select2048_page_table(const float* score, int64_t row_stride, int32_t
                                  const int32_t* src_page_table, int64_t src_stride, const int32_t* cu_seqlens_q,
                                  int32_t prefill_bs, uint32_t* status, void* cuda_stream) {
   if (B > 0 && (!src_page_table || src_stride < 0 || prefill_bs < 1 || prefill_bs > B)) return FFTOPK_EINVAL;
-  return launch_select(score, row_stride, B, L, lengths, row_starts, dst_page_table, nullptr, 0, status, cuda_stream,
-                       src_page_table, src_stride, cu_seqlens_q, prefill_bs, nullptr);
-}
-
-// internal: selection into the half of a comm buffer that the next device-side epoch owns
-int fftopk_select2048_into_comm(const float* score, int64_t row_stride, int32_t B, int64_t L, const int32_t* lengths,
-                                int32_t* idx_plane0, uint32_t* key_plane0, int32_t idx_offset, const uint32_t* flag,
-                                int64_t half_words, uint32_t* status, void* cuda_stream) {
-  return launch_select(score, row_stride, B, L, lengths, nullptr, idx_plane0, key_plane0, idx_offset, status,
-                       cuda_stream, nullptr, 0, nullptr, 0, nullptr, flag, half_words);
+  SelectCall c = basic_call(score, row_stride, B, L, lengths, row_starts, dst_page_table, nullptr, 0, status, cuda_stream);
+  c.src_page_table = src_page_table;
+  c.src_stride = src_stride;
+  c.cu_seqlens_q = cu_seqlens_q;
+  c.prefill_bs = prefill_bs;
+  return launch_select(c);
 }
 
 int fftopk_select2048_ragged(const float* score, int64_t row_stride, int32_t B, int64_t L, const int32_t* lengths,
                              const int32_t* row_starts, int32_t* topk_indices_ragged,
                              const int32_t* topk_indices_offset, uint32_t* status, void* cuda_stream) {
   if (B > 0 && !topk_indices_offset) return FFTOPK_EINVAL;
-  return launch_select(score, row_stride, B, L, lengths, row_starts, topk_indices_ragged, nullptr, 0, status,
-                       cuda_stream, nullptr, 0, nullptr, 0, topk_indices_offset);
+  SelectCall c = basic_call(score, row_stride, B, L, lengths, row_starts, topk_indices_ragged, nullptr, 0, status, cuda_stream);
+  c.row_offsets = topk_indices_offset;
+  return launch_select(c);
 }
 
 }  // extern "C"

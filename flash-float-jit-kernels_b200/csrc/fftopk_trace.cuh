@@ -1,5 +1,9 @@
 // Phase timestamps for debugging (compiled in only with -DFFTOPK_TRACE; the production build
-// turns every mark into nothing). Thread 0 of block 0 appends (id, %globaltimer) pairs to a log.
+// turns every mark into nothing and exports neither function below). Thread 0 of block 0 appends
+// (id, %globaltimer) pairs to a log, which a -DFFTOPK_TRACE build of the library hands out through
+//   int fftopk_trace_read(unsigned long long times[128], int ids[128], int* n);
+//   int fftopk_trace_clear(void);
+// (both return a cudaError_t). A trace build changes no result.
 #pragma once
 #include <stdint.h>
 namespace fftopk {
@@ -21,10 +25,6 @@ __device__ __forceinline__ void trace_mark(int id, bool who) {
   }
 }
 #define FFTOPK_MARK(id) trace_mark((id), blockIdx.x == 0 && threadIdx.x == 0)
-#elif defined(FFTOPK_STOP_AFTER)
-// Instruction-count experiments: the kernel body returns at mark FFTOPK_STOP_AFTER (only marks
-// placed directly in a kernel of one-CTA clusters make sense here; results are then garbage).
-#define FFTOPK_MARK(id) do { if ((id) == FFTOPK_STOP_AFTER) return; } while (0)
 #else
 #define FFTOPK_MARK(id) ((void)0)
 #endif

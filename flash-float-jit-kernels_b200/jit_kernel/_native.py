@@ -43,6 +43,7 @@ EXPORTS = (
     "fftopk_topk2048_sliced_noalloc",
     "fftopk_host_workspace_bytes",
     "fftopk_select2048_host",
+    "fftopk_probe_read_bandwidth",
     "fftopk_key_of",
     "fftopk_plan",
     "fftopk_set_tuning",
@@ -131,6 +132,9 @@ def lib() -> ctypes.CDLL:
     L.fftopk_select2048_host.restype = c.c_int
     L.fftopk_select2048_host.argtypes = [c.c_void_p, c.c_int64, c.c_int32, c.c_int64, c.c_void_p, c.c_void_p,
                                          c.c_void_p, c.c_size_t, c.c_void_p, c.c_void_p]
+    L.fftopk_probe_read_bandwidth.restype = c.c_int
+    L.fftopk_probe_read_bandwidth.argtypes = [c.c_void_p, c.c_size_t, c.c_size_t, c.c_void_p, c.POINTER(c.c_size_t),
+                                              c.c_void_p]
     L.fftopk_key_of.restype = c.c_uint32
     L.fftopk_key_of.argtypes = [c.c_float]
     L.fftopk_plan.restype = c.c_int

@@ -7,6 +7,7 @@ one thread-block cluster per row. There is no Triton, no backend dispatch and no
 """
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
@@ -14,6 +15,12 @@ import torch
 from . import _native
 
 TOPK = _native.K
+
+#: debugging aid: with FFTOPK_CHECK_STATUS=1 in the environment every op synchronises its stream
+#: after the launch and raises if a kernel has reported anything in the device status word (an
+#: internal inconsistency, a bounded wait on a peer that ran out). Off by default: the ops are
+#: enqueue-only and never synchronise.
+CHECK_STATUS = os.environ.get("FFTOPK_CHECK_STATUS", "0") not in ("", "0")
 
 _status_words: dict[int, torch.Tensor] = {}
 
@@ -31,6 +38,14 @@ def kernel_status(device=None) -> int:
     """FFTOPK_ST_* bits the kernels have raised on `device` since the process started."""
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
     return int(_status_word(dev).item()) & 0xFFFFFFFF
+
+
+def _after_launch(device: torch.device, what: str) -> None:
+    if CHECK_STATUS:
+        torch.cuda.current_stream(device).synchronize()
+        st = kernel_status(device)
+        if st:
+            raise _native.FFTopkError(f"{what}: the kernels reported status {st:#x} (FFTOPK_ST_* bits, include/fftopk.h)")
 
 
 def _check_inputs(score, lengths, row_starts, out=None):
@@ -86,6 +101,7 @@ def fast_topk(score: torch.Tensor, indices: torch.Tensor, lengths: torch.Tensor,
             indices.data_ptr(), keys.data_ptr() if keys is not None else None, int(idx_offset),
             _status_word(score.device).data_ptr(), stream)
     _native.check(rc, "fftopk_select2048")
+    _after_launch(score.device, "fftopk_select2048")
 
 
 def fast_topk_v3(
@@ -143,6 +159,7 @@ def fast_topk_general(
                                     None if row_starts is None else row_starts.data_ptr(), int(topk), out.data_ptr(),
                                     None, 0, _status_word(score.device).data_ptr(), stream.cuda_stream)
     _native.check(rc, "fftopk_select_topk")
+    _after_launch(score.device, "fftopk_select_topk")
     return out
 
 
@@ -178,6 +195,7 @@ def _fast_topk_16bit(score, lengths, topk, row_starts):
                                           None if row_starts is None else row_starts.data_ptr(), topk, out.data_ptr(),
                                           base, nbytes, _status_word(score.device).data_ptr(), stream.cuda_stream)
     _native.check(rc, "fftopk_select_topk_16bit")
+    _after_launch(score.device, "fftopk_select_topk_16bit")
     return out
 
 
@@ -232,6 +250,7 @@ def fast_topk_v3_host(
             lib.fftopk_select2048_host(score.data_ptr(), score.stride(0) if B > 1 else L, B, L, lengths.data_ptr(),
                                        out.data_ptr(), base, nbytes, _status_word(dev).data_ptr(), stream.cuda_stream),
             "fftopk_select2048_host")
+    _after_launch(dev, "fftopk_select2048_host")
     return out
 
 
@@ -278,6 +297,7 @@ def fast_topk_transform_fused(
             None if is_decode else cu_seqlens_q.data_ptr(), prefill_bs,
             _status_word(score.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
     _native.check(rc, "fftopk_select2048_page_table")
+    _after_launch(score.device, "fftopk_select2048_page_table")
     return dst
 
 
@@ -312,4 +332,5 @@ def fast_topk_transform_ragged_fused(
             topk_indices_offset.data_ptr(), _status_word(score.device).data_ptr(),
             torch.cuda.current_stream().cuda_stream)
     _native.check(rc, "fftopk_select2048_ragged")
+    _after_launch(score.device, "fftopk_select2048_ragged")
     return out

@@ -42,6 +42,10 @@ enum {
   FFTOPK_ST_STAGE_TIMEOUT = 1, /* reserved                                                  */
   FFTOPK_ST_INTERNAL = 2,      /* an internal count did not add up (should never be seen)  */
   FFTOPK_ST_PEER_TIMEOUT = 4,  /* merge: a bounded wait on a peer's ready flag ran out      */
+  FFTOPK_ST_GUESS_MISSED = 8,  /* warm start: a row's previous threshold was unusable; the row  */
+                               /* was selected from scratch (informational, result is exact)   */
+  FFTOPK_ST_CHECK = 16,        /* checked build (-DFFTOPK_CHECKED) only: an index the logic     */
+                               /* guarantees to be in range was not; the access was skipped    */
 };
 
 /* Library version: major*10000 + minor*100 + patch. */
@@ -242,6 +246,20 @@ size_t fftopk_host_workspace_bytes(int32_t B, int64_t L);
 int fftopk_select2048_host(const float* h_score, int64_t h_row_stride, int32_t B, int64_t L,
                            const int32_t* h_lengths, int32_t* h_out_idx, void* d_workspace,
                            size_t workspace_bytes, uint32_t* d_status, void* cuda_stream);
+
+/*
+ * Measurement aid, not part of the selection path (no reference counterpart): a read-only bandwidth
+ * probe. One kernel in which every SM reads the buffer with 128-bit loads that bypass L1, wrapping
+ * around until about `bytes_to_read` bytes have been read in total; *bytes_read receives the exact
+ * count. Timed by the caller (CUDA events around the call). A buffer that fits in L2 (a few MiB)
+ * gives the L2 read bandwidth of the device - the roof of a selection whose row is L2-resident,
+ * the regime a CUDA-graph replay over one buffer measures - and a buffer several times the L2
+ * size gives the HBM read bandwidth.
+ *   d_buf   device, 16-byte aligned, `bytes` bytes (>= 16), any contents
+ *   d_sink  device, uint32 [1], scratch the kernel may write
+ */
+int fftopk_probe_read_bandwidth(const void* d_buf, size_t bytes, size_t bytes_to_read, uint32_t* d_sink,
+                                size_t* bytes_read, void* cuda_stream);
 
 /*
  * Radix key of one fp32 value, computed on the host with the same function the kernels use

@@ -85,6 +85,30 @@ def test_no_alloc_entry_point_matches_allocating_path_twice_in_a_row():
             assert int((got[b] >= 0).sum()) == n
 
 
+@pytest.mark.parametrize("L,G,lens", [
+    (100003, 7, [100003, 50001, 14287, 14286, 3000]),  # L not a multiple of the slice count; lengths at slice edges
+    (10001, 8, [10001, 9000, 2049, 2048, 100]),        # slices of 1251 columns: every slice is shorter than k
+    (5, 8, [5, 3, 0]),                                 # fewer columns than slices: slices of length 0
+    (4100, 3, [4100, 4099, 1367, 1366]),               # a row that ends exactly where a slice does
+])
+def test_no_alloc_entry_point_odd_slicings(L, G, lens):
+    """Slices that do not divide the row, slices of 2048 or fewer columns and empty slices, compared
+    with the plain entry point (fftopk_select2048) and the oracle."""
+    lib = _native.lib()
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(L + G)
+    score = torch.randn(len(lens), L, generator=g)
+    score[:, ::7] = 0.5  # exact ties across slice borders
+    lengths = torch.tensor(lens, dtype=torch.int32)
+    got = _no_alloc(lib, dev, score, lengths, G)
+    from jit_kernel.topk_indexer import fast_topk_v3
+    plain = fast_topk_v3(score.to(dev), lengths.to(dev), K).cpu().numpy()
+    exp = orc.numpy_oracle(score.numpy(), lengths.numpy(), K)
+    for b in range(len(lens)):
+        assert np.array_equal(np.sort(got[b]), np.sort(plain[b])), f"row {b}: differs from fftopk_select2048"
+        assert np.array_equal(np.sort(got[b]), np.sort(exp[b])), f"row {b}: differs from the oracle"
+
+
 def test_no_alloc_entry_point_refuses_sizes_beyond_its_scratch():
     lib = _native.lib()
     dev = torch.device("cuda", 0)
