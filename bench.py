@@ -381,9 +381,11 @@ class TorchGroundTruth:
 
 
 def context_parallel_leg(dev, rank: int, world: int):
-    """Config 5: B=4, L=1M split evenly over the ranks; local select, exchange, merge. Three
-    variants: NCCL all-gather + merge kernel, the fused gather-and-merge over IPC-mapped peer
-    buffers called eagerly, and the same as a replayed CUDA graph. Each variant is first checked on
+    """Config 5: B=4, L=1M split evenly over the ranks; local select, exchange, merge. Variants:
+    NCCL all-gather + merge kernel; the fused path over IPC-mapped peer buffers - ONE kernel per
+    rank that selects, publishes, pulls the peers' candidates and merges - called eagerly and as a
+    replayed CUDA graph; and the two-kernel form of the fused path (selection with publication,
+    then a merge kernel that waits and pulls) as a replayed graph. Each variant is first checked on
     every rank against the single-device result (config 5 and the tie-stress config 4 at B=2,
     L=131072), outside every timed region; then timed with CUDA events, max over ranks."""
     import torch.distributed as dist
@@ -405,6 +407,7 @@ def context_parallel_leg(dev, rank: int, world: int):
     t_Ls = t_score.size(1) // world
     t_shard = t_score[:, rank * t_Ls:(rank + 1) * t_Ls].contiguous().to(dev)
     fused = FusedContextParallelTopk(max_rows=B)
+    fused2 = FusedContextParallelTopk(max_rows=B, single_launch=False)
     out = {"workload": f"B=4, L=1048576 over {world} GPUs, k=2048", "parity": {}}
     truth, t_truth = TorchGroundTruth(score, lengths), TorchGroundTruth(t_score, t_len)
 
@@ -418,33 +421,39 @@ def context_parallel_leg(dev, rank: int, world: int):
     par["fused"] = "bit-exact" if all_ok(ok) else "MISMATCH"
     ok = t_truth.matches(fast_topk_v3_context_parallel(t_shard, t_len, K))
     ok = t_truth.matches(fused(t_shard, t_len)) and ok
+    ok = t_truth.matches(fused2(t_shard, t_len)) and ok
     par["ties"] = "bit-exact" if all_ok(ok) else "MISMATCH"
     # the fused path as a replayed CUDA graph (its epochs live on the device): no Python between the
     # kernels; replayed several times so that both halves of the comm buffer are used
     res = torch.empty(B, K, dtype=torch.int32, device=dev)
-    torch.cuda.synchronize()
-    dist.barrier()
     side = torch.cuda.Stream(device=dev)
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.stream(side):
-        with torch.cuda.graph(graph, stream=side):
-            fused.run_into(shard, lens_dev, res)
-    dist.barrier()
-    ok = True
-    for _ in range(4):
-        res.fill_(-5)
-        graph.replay()
+    graphs = {}
+    for name, obj in (("fused_graph", fused), ("two_launch_graph", fused2)):
+        obj.run_into(shard, lens_dev, res)  # (first use of this path outside the capture)
         torch.cuda.synchronize()
-        ok = truth.matches(res) and ok
         dist.barrier()
-    par["fused_graph"] = "bit-exact" if all_ok(ok) else "MISMATCH"
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side):
+                obj.run_into(shard, lens_dev, res)
+        dist.barrier()
+        ok = True
+        for _ in range(4):
+            res.fill_(-5)
+            graph.replay()
+            torch.cuda.synchronize()
+            ok = truth.matches(res) and ok
+            dist.barrier()
+        par[name] = "bit-exact" if all_ok(ok) else "MISMATCH"
+        graphs[name] = graph
     all_exact = all(v == "bit-exact" for v in par.values())
 
     # ---- timing ----------------------------------------------------------------------------------
     reps = 50
     for name, fn in (("nccl_allgather_merge", lambda: fast_topk_v3_context_parallel(shard, lengths, K)),
                      ("fused_peer_merge", lambda: fused(shard, lengths)),
-                     ("fused_peer_merge_graph", graph.replay)):
+                     ("fused_peer_merge_graph", graphs["fused_graph"].replay),
+                     ("fused_two_launch_graph", graphs["two_launch_graph"].replay)):
         for _ in range(5):
             fn()
         torch.cuda.synchronize()
@@ -463,9 +472,11 @@ def context_parallel_leg(dev, rank: int, world: int):
     dist.all_reduce(st, op=dist.ReduceOp.MAX)
     out["kernel_status"] = int(st.item())  # 0: no bounded wait on a peer ran out, no internal error
     if out["kernel_status"] != 0:
-        for name in ("nccl_allgather_merge", "fused_peer_merge", "fused_peer_merge_graph"):
+        for name in ("nccl_allgather_merge", "fused_peer_merge", "fused_peer_merge_graph", "fused_two_launch_graph"):
             out[name + "_us_per_call"] = None
+    out["single_launch"] = bool(fused.single_launch)
     fused.close()
+    fused2.close()
     return out
 
 

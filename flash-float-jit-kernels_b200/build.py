@@ -22,7 +22,7 @@ LIB_DIR = ROOT / "lib"
 LIB_PATH = LIB_DIR / "libfftopk.so"
 SOURCES = [CSRC / "fftopk_select.cu", CSRC / "fftopk_cp.cu", CSRC / "fftopk_hostio.cu"]
 HEADERS = [CSRC / "fftopk_device.cuh", CSRC / "fftopk_key.h", CSRC / "fftopk_host.h", CSRC / "fftopk_trace.cuh",
-           CSRC / "fftopk_internal.h", CSRC / "fftopk_decide.h", ROOT.parent / "include" / "fftopk.h"]
+           CSRC / "fftopk_internal.h", CSRC / "fftopk_decide.h", CSRC / "fftopk_merge.cuh", ROOT.parent / "include" / "fftopk.h"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -3,16 +3,19 @@
 //
 // Every GPU selects a local top-2048 over its slice of the sequence (fftopk_select2048 with keys
 // and a global index offset). The global top-2048 is contained in the union of the local ones, so
-// one CTA per row loads the G*2048 (key, global index) candidates into shared memory and runs the
-// same single-CTA finish the selector uses.
+// one cluster per row - one CTA per shard - pulls the G*2048 (key, global index) candidates,
+// drops those below the largest of the shards' own 2048-th keys, and its first CTA runs the same
+// single-CTA finish the selector uses on what is left.
 //
 //  * fftopk_merge2048: candidates already gathered into local memory (NCCL all-gather).
 //  * fftopk_merge2048_cp: every rank published its candidates in a buffer its peers have mapped
-//    (CUDA IPC over NVLink); the merge kernel itself waits - bounded - for each peer's epoch flag
-//    and pulls the peer's candidates with plain loads. Gather and merge are one kernel; there is no
-//    multicast load and no library kernel that touches peer memory.
+//    (CUDA IPC over NVLink) - the selection kernel's last CTA releases the buffer's epoch flag -
+//    and the merge kernel itself waits - bounded - for each shard's flag and pulls the shard's
+//    candidates with plain loads. Gather and merge are one kernel; there is no multicast load and
+//    no library kernel that touches peer memory.
 //
 // No reference counterpart: the reference has no multi-GPU path.
+#include <cooperative_groups.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <string.h>
@@ -23,128 +26,43 @@
 #include "fftopk_host.h"
 #include "fftopk_internal.h"
 #include "fftopk_key.h"
+#include "fftopk_merge.cuh"
 
 namespace fftopk {
 
-constexpr int kMaxShards = 8;
-constexpr int kCommFlagWords = 32;  // one 128-byte line for the epoch flag
+constexpr int kMergeThreads = 512;
 
-// Where the candidates of each shard live, and (fused mode) the flag that says they are there.
-struct MergeSrc {
-  const int32_t* idx[kMaxShards];
-  const uint32_t* key[kMaxShards];
-  const uint32_t* flag[kMaxShards];  // nullptr: no wait
-  uint32_t epoch;                    // epoch to wait for; 0 with own_flag set: read it from own_flag
-  const uint32_t* own_flag;          // this rank's published epoch (device-side epochs)
-  int64_t half_words;                // device-side epochs: idx/key point at half 0, add (e & 1) * half_words
-  unsigned long long wait_ns;
-};
-
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-
-__device__ __forceinline__ unsigned long long global_timer_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-
-// Publishes "my candidates of this epoch are written": runs after the select kernel in stream
-// order, fences its writes system-wide and releases the flag.
+// Publishes an epoch without a selection in front of it (a call with no rows): fences and
+// releases the flag. Selections publish by themselves (last CTA of select2048_kernel).
 __global__ void publish_kernel(uint32_t* flag, uint32_t epoch) {
   if (epoch == 0u) epoch = __ldcg(flag) + 1u;  // device-side epochs: the next one
   __threadfence_system();
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(epoch) : "memory");
+  st_release_sys(flag, epoch);
 }
 
+// One cluster per row, one CTA per shard (see merge_row).
 template <int NT>
 __global__ void __launch_bounds__(NT, 1) merge2048_kernel(const MergeSrc src, int G, int B,
                                                          int32_t* __restrict__ out_idx_all,
                                                          uint32_t* __restrict__ out_key_all, uint32_t* status) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
-  uint32_t* hist = reinterpret_cast<uint32_t*>(smem_raw);
-  Ctrl* ctrl = reinterpret_cast<Ctrl*>(hist + kFinishBins);
-  uint64_t* cand = reinterpret_cast<uint64_t*>(reinterpret_cast<unsigned char*>(ctrl) + ((sizeof(Ctrl) + 127) & ~127u));
-  const int row = blockIdx.x;
-  const int tid = threadIdx.x;
-  const int n = G * kK;
-  int32_t* out_idx = out_idx_all + (int64_t)row * kK;
-  uint32_t* out_key = out_key_all ? out_key_all + (int64_t)row * kK : nullptr;
-
-  if (tid == 0) {
-    ctrl->run_total = 0u;
-    ctrl->pub_flag = 0u;
-  }
-  // device-side epochs: this rank's own flag already holds the epoch of this call (its publish
-  // kernel ran earlier on the same stream)
+  MergeSmem sm;
+  sm.hist = reinterpret_cast<uint32_t*>(smem_raw);
+  sm.sup = sm.hist + kMaxBins;
+  sm.xch = sm.sup + kSup;
+  sm.ctrl = reinterpret_cast<Ctrl*>(sm.xch + kMaxCluster * kSup);
+  sm.cand = reinterpret_cast<uint64_t*>(reinterpret_cast<unsigned char*>(sm.ctrl) + ((sizeof(Ctrl) + 127) & ~127u));
+  sm.cand_cap = G * kK;
+  cg::cluster_group cluster = cg::this_cluster();
+  const int g = G == 1 ? 0 : (int)cluster.block_rank();
+  const int row = (int)(blockIdx.x / (unsigned)G);
+  // device-side epochs: this rank's own flag already holds the epoch of this call (its selection
+  // published earlier on the same stream)
   const uint32_t epoch = (src.epoch == 0u && src.own_flag != nullptr) ? __ldcg(src.own_flag) : src.epoch;
   const int64_t half_shift = src.own_flag != nullptr && src.epoch == 0u ? (int64_t)(epoch & 1u) * src.half_words : 0;
-  __syncthreads();
-  // Fused mode: thread g waits until shard g's owner has published this epoch. The wait is
-  // bounded: when it runs out the row is filled with -1, a status bit is raised and the kernel
-  // returns normally, so a peer that never arrives cannot hang this GPU.
-  if (tid < G && src.flag[tid] != nullptr) {
-    const unsigned long long t0 = global_timer_ns();
-    bool ok = false;
-    for (;;) {
-      if ((int32_t)(ld_acquire_sys(src.flag[tid]) - epoch) >= 0) {
-        ok = true;
-        break;
-      }
-      if (global_timer_ns() - t0 > src.wait_ns) break;
-      __nanosleep(200);
-    }
-    if (!ok) ctrl->pub_flag = 1u;
-  }
-  __syncthreads();
-  if (ctrl->pub_flag) {
-    for (int i = tid; i < kK; i += NT) {
-      out_idx[i] = -1;
-      if (out_key) out_key[i] = 0u;
-    }
-    if (tid == 0 && status) atomicOr(status, (uint32_t)FFTOPK_ST_PEER_TIMEOUT);
-    return;
-  }
-  uint32_t nvalid = 0;
-  for (int i = tid; i < n; i += NT) {
-    const int g = i / kK, j = i % kK;
-    const int64_t off = (int64_t)row * kK + j;
-    // L2-coherent loads: the data may have been written by another GPU a moment ago
-    const int32_t idx = __ldcg(src.idx[g] + half_shift + off);
-    const uint32_t key = __ldcg(src.key[g] + half_shift + off);
-    const bool v = idx >= 0;
-    cand[i] = v ? (((uint64_t)key << 32) | (uint64_t)(~(uint32_t)idx)) : 0ull;
-    nvalid += v ? 1u : 0u;
-  }
-  nvalid = warp_sum(nvalid);
-  if ((tid & 31) == 0 && nvalid) red_shared_add(&ctrl->run_total, nvalid);
-  __syncthreads();
-  const uint32_t total = ctrl->run_total;
-  if (total <= (uint32_t)kK) {
-    // fewer candidates than k: keep them all (gather order), pad with -1
-    if (tid == 0) ctrl->fslot = 0u;
-    __syncthreads();
-    for (int i = tid; i < n; i += NT) {
-      const uint64_t c = cand[i];
-      if (c != 0ull) {
-        const uint32_t pos = warp_alloc(&ctrl->fslot);
-        if (FFTOPK_CHECK(9, pos, kK, status)) {
-          out_idx[pos] = (int32_t)(~(uint32_t)c);
-          if (out_key) out_key[pos] = (uint32_t)(c >> 32);
-        }
-      }
-    }
-    for (int i = (int)total + tid; i < kK; i += NT) {
-      out_idx[i] = -1;
-      if (out_key) out_key[i] = 0u;
-    }
-    return;
-  }
-  const DenseCands<NT> all{cand, n};
-  cta_finish<NT>(all, (uint32_t)kK, 1ull, 0ull, 0ull, false, 31, hist, ctrl, out_idx, out_key, 0u, (uint32_t)kK, 0, status);  // range unknown
+  merge_row<NT>(cluster, G, G, g, sm, src.idx[g] + half_shift + (int64_t)row * kK, src.key[g] + half_shift + (int64_t)row * kK,
+                src.flag[g], nullptr, epoch, src.wait_ns, out_idx_all + (int64_t)row * kK,
+                out_key_all ? out_key_all + (int64_t)row * kK : nullptr, status);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -208,19 +126,39 @@ int merge_setup() {
     int optin = 0;
     cudaError_t e2 = cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
     if (e2 != cudaSuccess) return cuda_fail(e2);
-    e2 = cudaFuncSetAttribute(merge2048_kernel<1024>, cudaFuncAttributeMaxDynamicSharedMemorySize, optin);
+    e2 = cudaFuncSetAttribute(merge2048_kernel<kMergeThreads>, cudaFuncAttributeMaxDynamicSharedMemorySize, optin);
     if (e2 != cudaSuccess) return cuda_fail(e2);
     return 0;
   });
 }
 
 size_t merge_smem(int G) {
-  return (size_t)kFinishBins * 4 + ((sizeof(Ctrl) + 127) & ~(size_t)127) + (size_t)G * kK * 8;
+  return (size_t)(kMaxBins + kSup + kMaxCluster * kSup) * 4 + ((sizeof(Ctrl) + 127) & ~(size_t)127) + (size_t)G * kK * 8;
+}
+
+// One cluster of G CTAs per row.
+int launch_merge(const MergeSrc& src, int G, int B, int32_t* out_idx, uint32_t* out_key, uint32_t* status,
+                 cudaStream_t stream) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)B * (unsigned)G, 1, 1);
+  cfg.blockDim = dim3(kMergeThreads, 1, 1);
+  cfg.dynamicSmemBytes = merge_smem(G);
+  cfg.stream = stream;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = (unsigned)G;
+  at[0].val.clusterDim.y = 1;
+  at[0].val.clusterDim.z = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = 1;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, merge2048_kernel<kMergeThreads>, src, G, B, out_idx, out_key, status);
+  if (e != cudaSuccess) return cuda_fail(e);
+  return FFTOPK_OK;
 }
 
 // comm buffer layout, in 32-bit words, for a row capacity of b_cap:
-//   [parity 0: index plane b_cap*2048 | key plane b_cap*2048][parity 1: same][flag line: 32 words]
-size_t comm_words(int32_t b_cap) { return (size_t)4 * b_cap * kK + kCommFlagWords; }
+// see CommLayout (fftopk_internal.h)
+size_t comm_words(int32_t b_cap) { return comm_total_words(b_cap); }
 
 // Device address of g_static_scratch on the current device, looked up once per device.
 void* g_static_ptr[kMaxDevices];
@@ -263,11 +201,7 @@ int fftopk_merge2048(const uint32_t* cand_key, const int32_t* cand_idx, int64_t 
     src.idx[g] = cand_idx + (int64_t)g * shard_stride;
     src.key[g] = cand_key + (int64_t)g * shard_stride;
   }
-  merge2048_kernel<1024><<<dim3((unsigned)B), dim3(1024), merge_smem(G), static_cast<cudaStream_t>(cuda_stream)>>>(
-      src, G, B, out_idx, out_key, status);
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) return cuda_fail(e);
-  return FFTOPK_OK;
+  return launch_merge(src, G, B, out_idx, out_key, status, static_cast<cudaStream_t>(cuda_stream));
 }
 
 int fftopk_comm_bytes(int32_t b_cap, size_t* bytes) {
@@ -344,9 +278,11 @@ int fftopk_select2048_cp(const float* score, int64_t row_stride, int32_t B, int6
       c.cp_flag = flag;
       c.cp_half_words = half;
     }
-    const int rc = launch_select(c);
-    if (rc) return rc;
+    c.cp_publish = flag;  // the selection's last CTA fences and releases the epoch flag
+    c.cp_epoch = epoch;
+    return launch_select(c);
   }
+  // no rows: the epoch still has to advance
   publish_kernel<<<1, 1, 0, static_cast<cudaStream_t>(cuda_stream)>>>(flag, epoch);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e);
@@ -375,11 +311,22 @@ int fftopk_merge2048_cp(void* const* comms, int32_t G, int32_t own, int32_t B, i
   src.own_flag = src.flag[own];
   src.half_words = (int64_t)2 * b_cap * kK;
   src.wait_ns = (unsigned long long)wait_ms * 1000000ull;
-  merge2048_kernel<1024><<<dim3((unsigned)B), dim3(1024), merge_smem(G), static_cast<cudaStream_t>(cuda_stream)>>>(
-      src, G, B, out_idx, out_key, status);
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) return cuda_fail(e);
-  return FFTOPK_OK;
+  return launch_merge(src, G, B, out_idx, out_key, status, static_cast<cudaStream_t>(cuda_stream));
+}
+
+int fftopk_topk2048_cp(const float* score, int64_t row_stride, int32_t B, int64_t L, const int32_t* lengths,
+                       int32_t idx_offset, void* const* comms, int32_t G, int32_t own, int32_t b_cap, uint32_t epoch,
+                       int32_t wait_ms, int32_t* out_idx, uint32_t* status, void* cuda_stream) {
+  SelectCall c;
+  c.score = score;
+  c.row_stride = row_stride;
+  c.B = B;
+  c.L = L;
+  c.lengths = lengths;
+  c.idx_offset = idx_offset;
+  c.status = status;
+  c.cuda_stream = cuda_stream;
+  return launch_select_merge(c, comms, G, own, b_cap, epoch, wait_ms, out_idx);
 }
 
 int fftopk_topk2048_sliced_noalloc(const float* score, int64_t row_stride, int32_t B, int64_t L,
@@ -427,11 +374,7 @@ int fftopk_topk2048_sliced_noalloc(const float* score, int64_t row_stride, int32
     src.idx[g] = idx_plane;
     src.key[g] = key_plane;
   }
-  merge2048_kernel<1024><<<dim3((unsigned)B), dim3(1024), merge_smem(slices), stream>>>(src, slices, B, out_idx, nullptr,
-                                                                                      status);
-  e = cudaGetLastError();
-  if (e != cudaSuccess) return cuda_fail(e);
-  return FFTOPK_OK;
+  return launch_merge(src, slices, B, out_idx, nullptr, status, stream);
 }
 
 }  // extern "C"

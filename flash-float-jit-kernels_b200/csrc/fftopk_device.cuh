@@ -10,6 +10,7 @@
 #include "../../include/fftopk.h"
 #include "fftopk_decide.h"
 #include "fftopk_key.h"
+#include "fftopk_trace.cuh"
 
 namespace fftopk {
 
@@ -166,6 +167,9 @@ struct Ctrl {
   int32_t focus_bin;    // first sample round of a lone CTA: bin the threshold will not lie above (-1: none)
   uint32_t wtot[32];
   uint32_t wmax[32];
+  // merge of candidate lists: this CTA's record about its shard, read by the cluster's other CTAs
+  uint32_t merge_count;  // valid candidates
+  uint32_t merge_fail;   // the bounded wait for the shard's flag ran out
   uint64_t small[kSmall];
 #ifdef FFTOPK_CHECKED
   uint32_t* status_ptr;  // the call's status word, for checks in code that has no other way to it
@@ -174,6 +178,200 @@ struct Ctrl {
 #ifdef FFTOPK_CHECKED
 #define ctrl_status(c) ((c)->status_ptr)
 #endif
+
+// What a cluster does after a threshold search (see decide_and_allocate).
+enum Mode : int { kModeNext = 0, kModeGather = 1, kModeTakeAll = 2, kModeTies = 3, kModeAbort = 4, kModeFallback = 5 };
+
+// Sum each group of nb/64 consecutive bins into sup[0..63].
+template <int NT>
+__device__ __forceinline__ void compute_sup(const uint32_t* hist, uint32_t* sup, int nb) {
+  const int tid = threadIdx.x;
+  if (nb == kMaxBins) {
+    constexpr int PER = kMaxBins / NT;            // bins per thread: 4 (1024 thr), 8 (512)
+    constexpr int TPS = (kMaxBins / kSup) / PER;  // threads per super-bin: 16, 8
+    uint32_t s = 0;
+    const uint4* h4 = reinterpret_cast<const uint4*>(hist) + tid * (PER / 4);
+#pragma unroll
+    for (int j = 0; j < PER / 4; ++j) {
+      const uint4 v = h4[j];
+      s += v.x + v.y + v.z + v.w;
+    }
+#pragma unroll
+    for (int off = TPS / 2; off > 0; off >>= 1) s += __shfl_xor_sync(kFull, s, off);
+    if ((tid % TPS) == 0) sup[tid / TPS] = s;
+  } else {  // 256 bins
+    if (tid < kSup) {
+      const uint4 v = reinterpret_cast<const uint4*>(hist)[tid];
+      sup[tid] = v.x + v.y + v.z + v.w;
+    }
+  }
+}
+
+// Cluster barrier; for a cluster of one CTA a block barrier does the same job for less.
+__device__ __forceinline__ void cluster_sync(cg::cluster_group& cluster, int C) {
+  if (C == 1) {
+    __syncthreads();
+  } else {
+    cluster.sync();
+  }
+}
+
+// What warp 0 knows after a cluster-wide threshold search.
+struct Picked {
+  bool ok;            // false: the histogram holds fewer than `need` elements
+  int t;              // threshold bin
+  uint32_t need2;     // elements still to take from bin t
+  uint32_t cnt;       // cluster-wide population of bin t
+  uint32_t local_w;   // this CTA's elements in bins above t
+  uint32_t local_c;   // this CTA's elements in bin t
+  uint32_t total;     // cluster-wide number of histogrammed elements
+  uint32_t any_flag;  // OR of the peers' published flags
+  int tf;             // t's position inside its super-bin (index into xch rows)
+};
+
+// Cluster-wide threshold search on per-CTA histograms `h` (nb bins) with super-bin sums `s`,
+// both complete and published by a cluster barrier before the call. Every CTA reads its peers'
+// 64 super-bin sums, then the fine bins of the threshold super-bin, over distributed shared
+// memory; warp 0 picks with shuffle scans. need_of(total) maps the cluster-wide element count
+// to the rank searched for. `post(picked)` runs in warp 0 (all lanes) before the closing
+// barrier; the results it wants every thread to see go through `ctrl`.
+// Replaces parallel_reduce_histogram + radix_prefix_sum of the reference
+// (topk_indexer_radix.cu:80-107, 232-279), which reduce to rank 0 and broadcast back with three
+// cluster barriers and eight block barriers per round.
+template <int NT, class NeedFn, class Post>
+__device__ __forceinline__ void cluster_pick(cg::cluster_group& cluster, int C, const uint32_t* h, const uint32_t* s,
+                                             uint32_t* xch, Ctrl* ctrl, int& pick_no, int nb, NeedFn&& need_of,
+                                             Post&& post) {
+  const int tid = threadIdx.x;
+  const int lane = tid & 31, warp = tid >> 5;
+  const int fine = nb / kSup;
+  uint32_t* tot = ctrl->tot[pick_no & 1];
+  uint32_t* tot2 = ctrl->tot2[pick_no & 1];
+  // (A) cluster-wide super-bin totals: one remote word per thread, summed with shared-memory
+  // reductions instead of a serial loop over the ranks. (Pushing the sums into the peers before
+  // the cluster barrier instead - remote reductions behind a split arrive / wait barrier - was
+  // measured and was not faster: the release of the extra arrive costs what the remote loads cost.)
+  for (int i = tid; i < C * kSup; i += NT) {
+    const uint32_t* rs = C == 1 ? s : cluster.map_shared_rank(s, i / kSup);
+    red_shared_add(&tot[i % kSup], rs[i % kSup]);
+  }
+  __syncthreads();
+  FFTOPK_MARK(40);
+  // Warp 0 picks and publishes through the control block. (Letting every warp pick for itself
+  // saves the two broadcast barriers but was measured slower: 32 warps running the same shuffle
+  // scans get in each other's way.)
+  if (warp == 0) {
+    const uint32_t lo = tot[2 * lane], hi = tot[2 * lane + 1];
+    const uint32_t total = warp_sum(lo + hi);
+    const uint32_t need = need_of(total);
+    uint32_t above = 0, cnt = 0;
+    int ts = -1;
+    const bool ok = need > 0 && warp_pick64(lo, hi, need, ts, above, cnt);
+    if (lane == 0) {
+      ctrl->sup_sel = ok ? ts : -1;
+      ctrl->sup_above = above;
+      ctrl->need = need;
+      ctrl->run_total = total;
+    }
+  }
+  __syncthreads();
+  FFTOPK_MARK(41);
+  const int ssel = ctrl->sup_sel;
+  // (B) fine bins of the threshold super-bin: pulled from every peer, kept per rank in xch (the
+  // tie path wants them) and summed into tot2
+  if (ssel >= 0) {
+    for (int i = tid; i < C * kSup; i += NT) {
+      const int q = i / kSup, f = i % kSup;
+      uint32_t v = 0;
+      if (f < fine) {
+        const uint32_t* rh = C == 1 ? h : cluster.map_shared_rank(h, q);
+        v = rh[ssel * fine + f];
+        red_shared_add(&tot2[f], v);
+      }
+      xch[i] = v;
+    }
+  }
+  __syncthreads();
+  FFTOPK_MARK(42);
+  // the buffers of the next search: their last readers passed the barrier above long ago
+  if (tid < kSup) {
+    ctrl->tot[(pick_no + 1) & 1][tid] = 0u;
+    ctrl->tot2[(pick_no + 1) & 1][tid] = 0u;
+  }
+  ++pick_no;
+  if (warp == 0) {
+    Picked pk;
+    pk.ok = false;
+    pk.t = -1;
+    pk.need2 = pk.cnt = pk.local_w = pk.local_c = 0;
+    pk.total = ctrl->run_total;
+    pk.any_flag = 0u;
+    pk.tf = 0;
+    if (ssel >= 0) {
+      const uint32_t lo = tot2[2 * lane], hi = tot2[2 * lane + 1];
+      const uint32_t need = ctrl->need, sup_above = ctrl->sup_above;
+      int tf = -1;
+      uint32_t above_f = 0, cnt_t = 0;
+      if (warp_pick64(lo, hi, need - sup_above, tf, above_f, cnt_t)) {
+        pk.ok = true;
+        pk.tf = tf;
+        pk.t = ssel * fine + tf;
+        pk.need2 = need - sup_above - above_f;
+        pk.cnt = cnt_t;
+        uint32_t lw = 0;
+        lw += (2 * lane > ssel) ? s[2 * lane] : 0u;
+        lw += (2 * lane + 1 > ssel) ? s[2 * lane + 1] : 0u;
+        lw += (2 * lane < fine && 2 * lane > tf) ? h[ssel * fine + 2 * lane] : 0u;
+        lw += (2 * lane + 1 < fine && 2 * lane + 1 > tf) ? h[ssel * fine + 2 * lane + 1] : 0u;
+        pk.local_w = warp_sum(lw);
+        pk.local_c = h[pk.t];
+      }
+    }
+    post(pk);  // warp 0 only; what the other warps need goes through the control block
+  }
+  __syncthreads();
+  FFTOPK_MARK(43);
+}
+
+// Standard decision after a search with need = what is still missing of k: either the threshold
+// bin is taken whole, or its population fits rank 0's buffer and is gathered there, or
+// `otherwise` (a mode) applies. Output and candidate slots are allocated with one remote atomic
+// each on rank 0's counters.
+// `cx` is anything with the members ctrl, ctrl0 (rank 0's control block) and cand_cap.
+template <class Ctx>
+__device__ __forceinline__ void decide_and_allocate(const Ctx& cx, const Picked& pk, int otherwise,
+                                                    bool force_otherwise) {
+  int md = kModeAbort;
+  uint32_t base_w = 0, base_c = 0, lw = pk.local_w;
+  if (pk.ok) {
+    if (force_otherwise) {
+      md = otherwise;
+    } else if (pk.cnt == pk.need2) {
+      md = kModeTakeAll;
+      lw += pk.local_c;
+    } else if (pk.cnt <= (uint32_t)cx.cand_cap) {
+      md = kModeGather;
+    } else {
+      md = otherwise;
+    }
+    if (lane_id() == 0 && md != kModeFallback) {
+      base_w = atomicAdd(&cx.ctrl0->win_count, lw);
+      if (md == kModeGather) base_c = atomicAdd(&cx.ctrl0->cand_count, pk.local_c);
+    }
+  }
+  if (lane_id() == 0) {
+    Ctrl* ctrl = cx.ctrl;
+    ctrl->mode = md;
+    ctrl->t = pk.t;
+    ctrl->above = pk.need2;
+    ctrl->cnt = pk.cnt;
+    ctrl->base_w = base_w;
+    ctrl->base_c = base_c;
+    ctrl->local_c = pk.local_c;
+    ctrl->wslot = 0u;
+    ctrl->cslot = 0u;
+  }
+}
 
 // ---------------------------------------------------------------------------------------------
 // Candidate sources of the finish. A source tells a thread which candidates are its share:

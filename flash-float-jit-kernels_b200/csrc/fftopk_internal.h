@@ -1,5 +1,6 @@
 // Interfaces shared by the translation units of libfftopk.so that are not part of the C ABI.
 #pragma once
+#include <stddef.h>
 #include <stdint.h>
 
 #include <atomic>
@@ -32,6 +33,8 @@ struct SelectCall {
   // context-parallel publication (see SelectParams in fftopk_select.cu)
   const uint32_t* cp_flag = nullptr;
   int64_t cp_half_words = 0;
+  uint32_t* cp_publish = nullptr;  // flag line of the comm buffer: the launch's last CTA releases it
+  uint32_t cp_epoch = 0;
   // false: this launch consumes what a kernel enqueued just before it by the library itself has
   // produced (gathered rows, widened scores, slice lengths), or hands its output to a kernel the
   // library enqueues right after it. Such a launch keeps plain stream order whatever
@@ -41,6 +44,10 @@ struct SelectCall {
 };
 
 int launch_select(const SelectCall& c);
+// selection + exchange + merge in one launch (context-parallel mode); uses score, row_stride, B, L,
+// lengths, idx_offset, status and cuda_stream of `c`
+int launch_select_merge(const SelectCall& c, void* const* comms, int32_t G, int32_t own, int32_t b_cap, uint32_t epoch,
+                        int32_t wait_ms, int32_t* out_idx);
 
 // Once-per-device set-up slots (function attributes, symbol addresses): the first caller on a
 // device runs `init` under a lock, everybody else sees `ready` with acquire semantics.
@@ -59,6 +66,26 @@ struct DeviceOnce {
 };
 
 constexpr int kMaxDevices = 64;
+
+// Layout of a context-parallel comm buffer for up to b_cap rows, in 32-bit words (K = 2048):
+//   two-launch protocol (fftopk_select2048_cp / fftopk_merge2048_cp)
+//     [half 0: index plane b_cap*K | key plane b_cap*K][half 1: the same]
+//     [epoch flag peers poll: one 128-byte line][arrival counter of the publishing launch: one line]
+//   single-launch protocol (fftopk_topk2048_cp)
+//     [epoch counter of every row: one line each]
+//     [local selection output: index plane b_cap*K | key plane b_cap*K]
+//     [inbox: 2 halves x 8 source shards x b_cap rows x K packets of 4 words]
+// The two protocols use disjoint regions and separate epoch counts.
+constexpr int kCommFlagWords = 64;
+constexpr int kCommArriveWord = 32;
+constexpr int kCommRowFlagWords = 32;
+constexpr int kCommMaxShards = 8;
+constexpr int kCommK = 2048;
+inline size_t comm_rowflag_offset(int32_t b_cap) { return (size_t)4 * b_cap * kCommK + kCommFlagWords; }
+inline size_t comm_stage_offset(int32_t b_cap) { return comm_rowflag_offset(b_cap) + (size_t)b_cap * kCommRowFlagWords; }
+inline size_t comm_inbox_offset(int32_t b_cap) { return comm_stage_offset(b_cap) + (size_t)2 * b_cap * kCommK; }
+inline size_t comm_inbox_half_words(int32_t b_cap) { return (size_t)kCommMaxShards * b_cap * kCommK * 4; }
+inline size_t comm_total_words(int32_t b_cap) { return comm_inbox_offset(b_cap) + 2 * comm_inbox_half_words(b_cap); }
 
 #ifdef FFTOPK_CHECKED
 int checked_read_merge(uint32_t rec[4]);  // fftopk_cp.cu's copy of the violation record; clears it

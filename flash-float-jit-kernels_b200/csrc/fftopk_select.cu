@@ -43,6 +43,7 @@
 #include <cooperative_groups.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <string.h>
 
 #include "../../include/fftopk.h"
 #include "fftopk_trace.cuh"
@@ -50,6 +51,7 @@
 #include "fftopk_host.h"
 #include "fftopk_internal.h"
 #include "fftopk_key.h"
+#include "fftopk_merge.cuh"
 
 namespace fftopk {
 
@@ -82,9 +84,14 @@ struct SelectParams {
   // epoch writes), so that a captured CUDA graph can be replayed
   const uint32_t* cp_flag;
   int64_t cp_half_words;
+  // ... and its announcement: when cp_publish is set, the last CTA of the grid to finish (arrival
+  // counter at cp_publish[kCommArriveWord]) fences and releases the epoch flag cp_publish[0] at
+  // system scope, so that peers that acquire the flag see every output of this launch. cp_epoch is
+  // the value to store, or 0 for "the flag's current value plus one".
+  uint32_t* cp_publish;
+  uint32_t cp_epoch;
 };
 
-enum Mode : int { kModeNext = 0, kModeGather = 1, kModeTakeAll = 2, kModeTies = 3, kModeAbort = 4, kModeFallback = 5 };
 
 constexpr int kRegSlabs = 4;  // granules a thread keeps in registers when the whole shard fits
 
@@ -330,157 +337,6 @@ __device__ __forceinline__ void scan_shard(const Shard& sh, Op&& op) {
   }
 }
 
-// Sum each group of nb/64 consecutive bins into sup[0..63].
-template <int NT>
-__device__ __forceinline__ void compute_sup(const uint32_t* hist, uint32_t* sup, int nb) {
-  const int tid = threadIdx.x;
-  if (nb == kMaxBins) {
-    constexpr int PER = kMaxBins / NT;            // bins per thread: 4 (1024 thr), 8 (512)
-    constexpr int TPS = (kMaxBins / kSup) / PER;  // threads per super-bin: 16, 8
-    uint32_t s = 0;
-    const uint4* h4 = reinterpret_cast<const uint4*>(hist) + tid * (PER / 4);
-#pragma unroll
-    for (int j = 0; j < PER / 4; ++j) {
-      const uint4 v = h4[j];
-      s += v.x + v.y + v.z + v.w;
-    }
-#pragma unroll
-    for (int off = TPS / 2; off > 0; off >>= 1) s += __shfl_xor_sync(kFull, s, off);
-    if ((tid % TPS) == 0) sup[tid / TPS] = s;
-  } else {  // 256 bins
-    if (tid < kSup) {
-      const uint4 v = reinterpret_cast<const uint4*>(hist)[tid];
-      sup[tid] = v.x + v.y + v.z + v.w;
-    }
-  }
-}
-
-// Cluster barrier; for a cluster of one CTA a block barrier does the same job for less.
-__device__ __forceinline__ void cluster_sync(cg::cluster_group& cluster, int C) {
-  if (C == 1) {
-    __syncthreads();
-  } else {
-    cluster.sync();
-  }
-}
-
-// What warp 0 knows after a cluster-wide threshold search.
-struct Picked {
-  bool ok;            // false: the histogram holds fewer than `need` elements
-  int t;              // threshold bin
-  uint32_t need2;     // elements still to take from bin t
-  uint32_t cnt;       // cluster-wide population of bin t
-  uint32_t local_w;   // this CTA's elements in bins above t
-  uint32_t local_c;   // this CTA's elements in bin t
-  uint32_t total;     // cluster-wide number of histogrammed elements
-  uint32_t any_flag;  // OR of the peers' published flags
-  int tf;             // t's position inside its super-bin (index into xch rows)
-};
-
-// Cluster-wide threshold search on per-CTA histograms `h` (nb bins) with super-bin sums `s`,
-// both complete and published by a cluster barrier before the call. Every CTA reads its peers'
-// 64 super-bin sums, then the fine bins of the threshold super-bin, over distributed shared
-// memory; warp 0 picks with shuffle scans. need_of(total) maps the cluster-wide element count
-// to the rank searched for. `post(picked)` runs in warp 0 (all lanes) before the closing
-// barrier; the results it wants every thread to see go through `ctrl`.
-// Replaces parallel_reduce_histogram + radix_prefix_sum of the reference
-// (topk_indexer_radix.cu:80-107, 232-279), which reduce to rank 0 and broadcast back with three
-// cluster barriers and eight block barriers per round.
-template <int NT, class NeedFn, class Post>
-__device__ __forceinline__ void cluster_pick(cg::cluster_group& cluster, int C, const uint32_t* h, const uint32_t* s,
-                                             uint32_t* xch, Ctrl* ctrl, int& pick_no, int nb, NeedFn&& need_of,
-                                             Post&& post) {
-  const int tid = threadIdx.x;
-  const int lane = tid & 31, warp = tid >> 5;
-  const int fine = nb / kSup;
-  uint32_t* tot = ctrl->tot[pick_no & 1];
-  uint32_t* tot2 = ctrl->tot2[pick_no & 1];
-  // (A) cluster-wide super-bin totals: one remote word per thread, summed with shared-memory
-  // reductions instead of a serial loop over the ranks. (Pushing the sums into the peers before
-  // the cluster barrier instead - remote reductions behind a split arrive / wait barrier - was
-  // measured and was not faster: the release of the extra arrive costs what the remote loads cost.)
-  for (int i = tid; i < C * kSup; i += NT) {
-    const uint32_t* rs = C == 1 ? s : cluster.map_shared_rank(s, i / kSup);
-    red_shared_add(&tot[i % kSup], rs[i % kSup]);
-  }
-  __syncthreads();
-  FFTOPK_MARK(40);
-  // Warp 0 picks and publishes through the control block. (Letting every warp pick for itself
-  // saves the two broadcast barriers but was measured slower: 32 warps running the same shuffle
-  // scans get in each other's way.)
-  if (warp == 0) {
-    const uint32_t lo = tot[2 * lane], hi = tot[2 * lane + 1];
-    const uint32_t total = warp_sum(lo + hi);
-    const uint32_t need = need_of(total);
-    uint32_t above = 0, cnt = 0;
-    int ts = -1;
-    const bool ok = need > 0 && warp_pick64(lo, hi, need, ts, above, cnt);
-    if (lane == 0) {
-      ctrl->sup_sel = ok ? ts : -1;
-      ctrl->sup_above = above;
-      ctrl->need = need;
-      ctrl->run_total = total;
-    }
-  }
-  __syncthreads();
-  FFTOPK_MARK(41);
-  const int ssel = ctrl->sup_sel;
-  // (B) fine bins of the threshold super-bin: pulled from every peer, kept per rank in xch (the
-  // tie path wants them) and summed into tot2
-  if (ssel >= 0) {
-    for (int i = tid; i < C * kSup; i += NT) {
-      const int q = i / kSup, f = i % kSup;
-      uint32_t v = 0;
-      if (f < fine) {
-        const uint32_t* rh = C == 1 ? h : cluster.map_shared_rank(h, q);
-        v = rh[ssel * fine + f];
-        red_shared_add(&tot2[f], v);
-      }
-      xch[i] = v;
-    }
-  }
-  __syncthreads();
-  FFTOPK_MARK(42);
-  // the buffers of the next search: their last readers passed the barrier above long ago
-  if (tid < kSup) {
-    ctrl->tot[(pick_no + 1) & 1][tid] = 0u;
-    ctrl->tot2[(pick_no + 1) & 1][tid] = 0u;
-  }
-  ++pick_no;
-  if (warp == 0) {
-    Picked pk;
-    pk.ok = false;
-    pk.t = -1;
-    pk.need2 = pk.cnt = pk.local_w = pk.local_c = 0;
-    pk.total = ctrl->run_total;
-    pk.any_flag = 0u;
-    pk.tf = 0;
-    if (ssel >= 0) {
-      const uint32_t lo = tot2[2 * lane], hi = tot2[2 * lane + 1];
-      const uint32_t need = ctrl->need, sup_above = ctrl->sup_above;
-      int tf = -1;
-      uint32_t above_f = 0, cnt_t = 0;
-      if (warp_pick64(lo, hi, need - sup_above, tf, above_f, cnt_t)) {
-        pk.ok = true;
-        pk.tf = tf;
-        pk.t = ssel * fine + tf;
-        pk.need2 = need - sup_above - above_f;
-        pk.cnt = cnt_t;
-        uint32_t lw = 0;
-        lw += (2 * lane > ssel) ? s[2 * lane] : 0u;
-        lw += (2 * lane + 1 > ssel) ? s[2 * lane + 1] : 0u;
-        lw += (2 * lane < fine && 2 * lane > tf) ? h[ssel * fine + 2 * lane] : 0u;
-        lw += (2 * lane + 1 < fine && 2 * lane + 1 > tf) ? h[ssel * fine + 2 * lane + 1] : 0u;
-        pk.local_w = warp_sum(lw);
-        pk.local_c = h[pk.t];
-      }
-    }
-    post(pk);  // warp 0 only; what the other warps need goes through the control block
-  }
-  __syncthreads();
-  FFTOPK_MARK(43);
-}
-
 // First search of the sampled path, over TWO sample histograms built in the same pass:
 //   A: key bits [31:20]   (4096 bins, valid for any data, 8 bins per octave of magnitude)
 //   B: key bits [27:16]   (4096 bins, 128 per octave) - meaningful only among keys that share the
@@ -670,45 +526,6 @@ __device__ __forceinline__ void emit_winner(const RowCtx<NT>& cx, uint32_t base_
   }
 }
 
-// Standard decision after a search with need = what is still missing of k: either the threshold
-// bin is taken whole, or its population fits rank 0's buffer and is gathered there, or
-// `otherwise` (a mode) applies. Output and candidate slots are allocated with one remote atomic
-// each on rank 0's counters.
-template <int NT>
-__device__ __forceinline__ void decide_and_allocate(const RowCtx<NT>& cx, const Picked& pk, int otherwise,
-                                                    bool force_otherwise) {
-  int md = kModeAbort;
-  uint32_t base_w = 0, base_c = 0, lw = pk.local_w;
-  if (pk.ok) {
-    if (force_otherwise) {
-      md = otherwise;
-    } else if (pk.cnt == pk.need2) {
-      md = kModeTakeAll;
-      lw += pk.local_c;
-    } else if (pk.cnt <= (uint32_t)cx.cand_cap) {
-      md = kModeGather;
-    } else {
-      md = otherwise;
-    }
-    if (lane_id() == 0 && md != kModeFallback) {
-      base_w = atomicAdd(&cx.ctrl0->win_count, lw);
-      if (md == kModeGather) base_c = atomicAdd(&cx.ctrl0->cand_count, pk.local_c);
-    }
-  }
-  if (lane_id() == 0) {
-    Ctrl* ctrl = cx.ctrl;
-    ctrl->mode = md;
-    ctrl->t = pk.t;
-    ctrl->above = pk.need2;
-    ctrl->cnt = pk.cnt;
-    ctrl->base_w = base_w;
-    ctrl->base_c = base_c;
-    ctrl->local_c = pk.local_c;
-    ctrl->wslot = 0u;
-    ctrl->cslot = 0u;
-  }
-}
-
 // -----------------------------------------------------------------------------------------
 // Full-histogram path: every round re-reads the shard (from L2) and histograms the next key
 // digit of the elements that still match the threshold prefix. Handles anything: lists that
@@ -766,7 +583,7 @@ __device__ __forceinline__ int refine_from_data(RowCtx<NT>& cx, uint32_t& need, 
         cluster, C, h, s, xch, ctrl, pick_no, nb, [&](uint32_t) { return need_now; },
         [&](Picked& pk) {
           const bool last = (shift == 0);
-          decide_and_allocate<NT>(cx, pk, last ? kModeTies : kModeNext, false);
+          decide_and_allocate(cx, pk, last ? kModeTies : kModeNext, false);
           if (pk.ok && last && pk.cnt > (uint32_t)cx.cand_cap && pk.cnt != pk.need2) {
             // exact duplicates of the threshold key: ties before this shard, in rank order
             const uint32_t tp = (lane < rank) ? xch[lane * kSup + pk.tf] : 0u;
@@ -885,8 +702,8 @@ __device__ __forceinline__ int refine_from_data(RowCtx<NT>& cx, uint32_t& need, 
 #endif
 // kAnyK = false: k is the constant 2048 of the reference's op (the compiler folds it: one register
 // less in a kernel that sits at its register limit); true: k comes from the parameters.
-template <int NT, bool kAnyK = false>
-__global__ void __launch_bounds__(NT, (NT == 512 ? FFTOPK_CTAS_512 : 1024 / NT)) select2048_kernel(const SelectParams p) {
+template <int NT, bool kAnyK>
+__device__ __forceinline__ void select_row(const SelectParams& p) {
   RowCtx<NT> cx;
   cg::cluster_group cluster = cg::this_cluster();
   const int C = cx.C = (int)cluster.num_blocks();
@@ -1104,7 +921,7 @@ __global__ void __launch_bounds__(NT, (NT == 512 ? FFTOPK_CTAS_512 : 1024 / NT))
     // ---- the sample is the row: its histogram gives the threshold bin directly -----------------
     cluster_pick<NT>(
         cluster, C, cx.hist(0), cx.sup(0), cx.xch, ctrl, pick_no, kMaxBins, [&](uint32_t) { return K; },
-        [&](Picked& pk) { decide_and_allocate<NT>(cx, pk, kModeFallback, false); });
+        [&](Picked& pk) { decide_and_allocate(cx, pk, kModeFallback, false); });
     mode = ctrl->mode;
     FFTOPK_MARK(4);
     if (mode == kModeGather || mode == kModeTakeAll) {
@@ -1347,6 +1164,110 @@ __global__ void __launch_bounds__(NT, (NT == 512 ? FFTOPK_CTAS_512 : 1024 / NT))
   if (tid == 0 && p.status && mode == kModeAbort) atomicOr(p.status, (uint32_t)FFTOPK_ST_INTERNAL);
 }
 
+template <int NT, bool kAnyK = false>
+__global__ void __launch_bounds__(NT, (NT == 512 ? FFTOPK_CTAS_512 : 1024 / NT)) select2048_kernel(const SelectParams p) {
+  select_row<NT, kAnyK>(p);
+  if (p.cp_publish) {
+    // Context-parallel publication folded into the selection: every thread fences its output
+    // writes, the CTA arrives, and the last CTA of the grid releases the epoch flag system-wide
+    // (peers acquire it in their merge kernel). The counter goes back to zero for the next launch,
+    // which stream order keeps behind this one.
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      uint32_t* arrive = p.cp_publish + kCommArriveWord;
+      uint32_t old;
+      asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(old) : "l"(arrive) : "memory");
+      if (old == gridDim.x - 1u) {
+        *arrive = 0u;
+        const uint32_t epoch = p.cp_epoch ? p.cp_epoch : __ldcg(p.cp_publish) + 1u;
+        __threadfence_system();
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.cp_publish), "r"(epoch) : "memory");
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Context-parallel top-2048 in ONE launch per GPU: local selection, exchange and merge. Every GPU
+// holds a contiguous slice of each row. The row's cluster first selects the local top 2048 of its
+// slice (keys and global indices) exactly as select2048_kernel does; its first CTA then PUSHES the
+// 2048 candidates as self-validating packets {index, epoch, key, epoch} into the inbox of every
+// GPU, its own included, with plain 16-byte stores over NVLink - no flag, no fence (a system-scope
+// fence was measured at 4.5 us per publication), no round trip. After that CTA g of the cluster
+// (g < G) polls, in its own GPU's memory and with a time limit, the packets shard g sent for the
+// row, and the cluster merges the G lists (merge_row). No second launch, no collective call, no
+// launch-wide synchronisation: a row is merged as soon as its own G slices have been selected.
+// The inbox has two halves that alternate by epoch parity: a GPU can only start call e+2 after
+// its own call e+1 has seen every peer's packets of e+1, which the peer sent after it had finished
+// call e and with it every read of its inbox half e.
+// ---------------------------------------------------------------------------------------------
+struct CpFused {
+  uint4* inbox[kMaxShards];   // inbox (half 0, source shard 0, row 0) of every GPU, own included
+  uint32_t* row_epoch;        // this GPU's epoch counter of row 0; row r's is kCommRowFlagWords * r further
+  int64_t inbox_half_packets; // packets between the two halves of an inbox
+  unsigned long long wait_ns;
+  int32_t* out_idx;           // [B, 2048] merged result
+  uint32_t epoch;             // epoch of this call, or 0: each row counter's value plus one
+  int32_t G, own, b_cap;
+};
+
+template <int NT>
+__global__ void __launch_bounds__(NT, (NT == 512 ? FFTOPK_CTAS_512 : 1024 / NT)) select_merge2048_kernel(const SelectParams p,
+                                                                                                      const CpFused f) {
+  cg::cluster_group cluster = cg::this_cluster();
+  const int C = (int)cluster.num_blocks();
+  const int rank = (int)cluster.block_rank();
+  const int row = (int)(blockIdx.x / (unsigned)C);
+  const int tid = threadIdx.x;
+  uint32_t* my_epoch = f.row_epoch + (int64_t)row * kCommRowFlagWords;
+  // (the previous call's update of the counter is complete - stream order - and this call's comes
+  // at the very end: every CTA of the cluster reads the same value)
+  const uint32_t epoch = f.epoch ? f.epoch : __ldcg(my_epoch) + 1u;
+  select_row<NT, false>(p);
+  // Every output of the row is written: by this CTA, or by its peers before a cluster barrier
+  // this CTA has passed.
+  FFTOPK_MARK(60);
+  // packets of (half, source shard, row): ((half * 8 + shard) * b_cap + row) * 2048
+  const int64_t half_off = (int64_t)(epoch & 1u) * f.inbox_half_packets;
+  if (rank == 0) {
+    __syncthreads();
+    constexpr int PER = kK / NT;
+    const int32_t* lidx = p.out_idx + (int64_t)row * kK;
+    const uint32_t* lkey = p.out_key + (int64_t)row * kK;
+    const int64_t dst_off = half_off + ((int64_t)f.own * f.b_cap + row) * kK;
+    int32_t ci[PER];
+    uint32_t ck[PER];
+#pragma unroll
+    for (int u = 0; u < PER; ++u) {
+      ci[u] = __ldcg(lidx + u * NT + tid);
+      ck[u] = __ldcg(lkey + u * NT + tid);
+    }
+    for (int d = 0; d < f.G; ++d) {
+      uint4* dst = f.inbox[d] + dst_off;
+#pragma unroll
+      for (int u = 0; u < PER; ++u) st_packet(dst + u * NT + tid, ci[u], ck[u], epoch);
+    }
+  }
+  FFTOPK_MARK(61);
+  // ---- merge: same carve of the dynamic shared memory as the selection --------------------------
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  MergeSmem sm;
+  sm.hist = reinterpret_cast<uint32_t*>(smem_raw);
+  sm.sup = sm.hist + 2 * kMaxBins;
+  sm.xch = sm.sup + 3 * kSup;
+  sm.ctrl = reinterpret_cast<Ctrl*>(sm.xch + kMaxCluster * kSup);
+  sm.cand = reinterpret_cast<uint64_t*>(reinterpret_cast<unsigned char*>(sm.ctrl) + ((sizeof(Ctrl) + 127) & ~127u));
+  sm.cand_cap = C == 1 ? p.list_cap : p.list_cap + p.cand_cap;
+  const uint4* mine = rank < f.G ? f.inbox[f.own] + half_off + ((int64_t)rank * f.b_cap + row) * kK : nullptr;
+  merge_row<NT>(cluster, C, f.G, rank, sm, nullptr, nullptr, nullptr, mine, epoch, f.wait_ns,
+                f.out_idx + (int64_t)row * kK, nullptr, p.status);
+  // the row's epoch counter moves on only now: every CTA of the cluster read it before the first
+  // cluster barrier of the merge
+  if (rank == 0 && tid == 0 && f.epoch == 0u) *my_epoch = epoch;
+  FFTOPK_MARK(69);
+}
+
 }  // namespace fftopk
 
 // =============================================================================================
@@ -1404,6 +1325,12 @@ int setup_kernel(int smem_optin) {
   if (e != cudaSuccess) return cuda_fail(e);
   e = cudaFuncSetAttribute(select2048_kernel<NT, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
   if (e != cudaSuccess) return cuda_fail(e);
+  if constexpr (NT >= 512) {
+    e = cudaFuncSetAttribute(select_merge2048_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_optin);
+    if (e != cudaSuccess) return cuda_fail(e);
+    e = cudaFuncSetAttribute(select_merge2048_kernel<NT>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    if (e != cudaSuccess) return cuda_fail(e);
+  }
   return 0;
 }
 
@@ -1597,6 +1524,8 @@ int launch_select(const SelectCall& c) {
   p.row_offsets = c.row_offsets;
   p.cp_flag = c.cp_flag;
   p.cp_half_words = c.cp_half_words;
+  p.cp_publish = c.cp_publish;
+  p.cp_epoch = c.cp_epoch;
   if ((size_t)pl.smem_bytes > (size_t)d->smem_optin) return FFTOPK_ERANGE;
 
   cudaLaunchConfig_t cfg = {};
@@ -1625,6 +1554,75 @@ int launch_select(const SelectCall& c) {
   } else {
     e = any_k ? cudaLaunchKernelEx(&cfg, select2048_kernel<256, true>, p) : cudaLaunchKernelEx(&cfg, select2048_kernel<256>, p);
   }
+  if (e != cudaSuccess) return cuda_fail(e);
+  return FFTOPK_OK;
+}
+
+// Single-launch context-parallel call (see select_merge2048_kernel). FFTOPK_ERANGE when the
+// launch plan for (B, L) gives a row fewer CTAs than there are shards or too little shared memory
+// for the merge: the caller then uses the two-launch sequence.
+int launch_select_merge(const SelectCall& c, void* const* comms, int32_t G, int32_t own, int32_t b_cap, uint32_t epoch,
+                        int32_t wait_ms, int32_t* out_idx) {
+  if (c.B < 0 || c.L < 0 || c.row_stride < 0) return FFTOPK_EINVAL;
+  if (!comms || G < 1 || own < 0 || own >= G || b_cap < 1 || c.B > b_cap || wait_ms < 0) return FFTOPK_EINVAL;
+  if (G > kMaxShards) return FFTOPK_ERANGE;
+  if (c.B == 0) return FFTOPK_OK;
+  if (!c.score || !c.lengths || !out_idx) return FFTOPK_EINVAL;
+  if ((reinterpret_cast<uintptr_t>(c.score) & 3u) != 0) return FFTOPK_EINVAL;
+  if (c.L > (int64_t)0x7fffffff - 8) return FFTOPK_ERANGE;
+  DeviceInfo* d = nullptr;
+  int rc = device_info(&d);
+  if (rc) return rc;
+  const Tuning tn = tuning_snapshot();
+  const Plan pl = make_plan(*d, tn, false, c.B, c.L);
+  const int room = pl.cluster == 1 ? pl.list_cap : pl.list_cap + pl.cand_cap;
+  if (pl.cluster < G || room < G * kK || pl.threads < 512 || (size_t)pl.smem_bytes > (size_t)d->smem_optin) return FFTOPK_ERANGE;
+
+  SelectParams p;
+  memset(&p, 0, sizeof(p));
+  CpFused f;
+  memset(&f, 0, sizeof(f));
+  for (int g = 0; g < G; ++g) {
+    if (!comms[g]) return FFTOPK_EINVAL;
+    f.inbox[g] = reinterpret_cast<uint4*>(static_cast<int32_t*>(comms[g]) + comm_inbox_offset(b_cap));
+  }
+  int32_t* own_words = static_cast<int32_t*>(comms[own]);
+  f.row_epoch = reinterpret_cast<uint32_t*>(own_words + comm_rowflag_offset(b_cap));
+  f.inbox_half_packets = (int64_t)(comm_inbox_half_words(b_cap) / 4);
+  f.wait_ns = (unsigned long long)wait_ms * 1000000ull;
+  f.out_idx = out_idx;
+  f.epoch = epoch;
+  f.G = G;
+  f.own = own;
+  f.b_cap = b_cap;
+  p.score = c.score;
+  p.row_stride = c.row_stride;
+  p.L = c.L;
+  p.lengths = c.lengths;
+  p.out_idx = own_words + comm_stage_offset(b_cap);  // local selection output, pushed from there
+  p.out_key = reinterpret_cast<uint32_t*>(p.out_idx + (size_t)b_cap * kK);
+  p.status = c.status;
+  p.B = c.B;
+  p.k = kK;
+  p.idx_offset = c.idx_offset;
+  p.list_cap = pl.list_cap;
+  p.cand_cap = pl.cand_cap;
+  p.force_slow = tn.force_slow;
+
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)c.B * (unsigned)pl.cluster, 1, 1);
+  cfg.blockDim = dim3((unsigned)pl.threads, 1, 1);
+  cfg.dynamicSmemBytes = (size_t)pl.smem_bytes;
+  cfg.stream = static_cast<cudaStream_t>(c.cuda_stream);
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = (unsigned)pl.cluster;
+  at[0].val.clusterDim.y = 1;
+  at[0].val.clusterDim.z = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = 1;
+  const cudaError_t e = pl.threads == 1024 ? cudaLaunchKernelEx(&cfg, select_merge2048_kernel<1024>, p, f)
+                                           : cudaLaunchKernelEx(&cfg, select_merge2048_kernel<512>, p, f);
   if (e != cudaSuccess) return cuda_fail(e);
   return FFTOPK_OK;
 }

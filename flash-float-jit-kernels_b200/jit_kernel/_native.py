@@ -20,6 +20,9 @@ K = 2048
 ST_STAGE_TIMEOUT = 1
 ST_INTERNAL = 2
 ST_PEER_TIMEOUT = 4
+ST_CHECK = 16
+
+E_RANGE = -4
 
 #: every symbol include/fftopk.h declares
 EXPORTS = (
@@ -40,6 +43,7 @@ EXPORTS = (
     "fftopk_comm_destroy",
     "fftopk_select2048_cp",
     "fftopk_merge2048_cp",
+    "fftopk_topk2048_cp",
     "fftopk_topk2048_sliced_noalloc",
     "fftopk_host_workspace_bytes",
     "fftopk_select2048_host",
@@ -116,6 +120,10 @@ def lib() -> ctypes.CDLL:
     L.fftopk_merge2048_cp.restype = c.c_int
     L.fftopk_merge2048_cp.argtypes = [c.POINTER(c.c_void_p), c.c_int32, c.c_int32, c.c_int32, c.c_int32, c.c_uint32,
                                       c.c_int32, c.c_void_p, c.c_void_p, c.c_void_p, c.c_void_p]
+    L.fftopk_topk2048_cp.restype = c.c_int
+    L.fftopk_topk2048_cp.argtypes = [c.c_void_p, c.c_int64, c.c_int32, c.c_int64, c.c_void_p, c.c_int32,
+                                     c.POINTER(c.c_void_p), c.c_int32, c.c_int32, c.c_int32, c.c_uint32, c.c_int32,
+                                     c.c_void_p, c.c_void_p, c.c_void_p]
     L.fftopk_topk2048_sliced_noalloc.restype = c.c_int
     L.fftopk_topk2048_sliced_noalloc.argtypes = [c.c_void_p, c.c_int64, c.c_int32, c.c_int64, c.c_void_p, c.c_int32,
                                                  c.c_void_p, c.c_void_p, c.c_void_p]

@@ -96,43 +96,51 @@ def fast_topk_v3_context_parallel(
 class FusedContextParallelTopk:
     """Context-parallel top-2048 without a collective call on the data path.
 
-    Every rank keeps one "comm" buffer that all peers map through CUDA IPC. A call is: local
-    selection straight into the rank's own buffer, a flag release, and ONE merge kernel that waits
-    (bounded, `wait_ms`) for every peer's flag and pulls the peers' candidates over NVLink with
-    plain loads. torch.distributed is used once, at construction, to exchange the IPC handles.
+    Every rank keeps a "comm" buffer that all peers map through CUDA IPC. A call is ONE kernel per
+    rank (fftopk_topk2048_cp): the row's cluster selects the local top 2048, pushes them as
+    self-validating packets into every rank's buffer with plain stores over NVLink, polls (bounded,
+    `wait_ms`) its own buffer for the packets of the row's other slices and merges. Where the
+    launch plan cannot host the merge in the selection kernel (many rows of short slices) the call
+    is two kernels instead: selection that publishes an epoch flag (fftopk_select2048_cp) and a
+    merge kernel that waits for the peers' flags and pulls their candidates (fftopk_merge2048_cp).
+    torch.distributed is used once, at construction, to exchange the IPC handles.
 
-    All ranks of `group` must construct the object and call it the same number of times (the
-    epoch counter advances by one per call on every rank).
+    All ranks of `group` must construct the object and call it the same number of times with the
+    same shapes (the epoch counters advance by one per call on every rank).
     """
 
-    def __init__(self, max_rows: int, group: Optional[dist.ProcessGroup] = None, wait_ms: int = 2000):
-        import ctypes
+    def __init__(self, max_rows: int, group: Optional[dist.ProcessGroup] = None, wait_ms: int = 2000,
+                 single_launch: bool = True):
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         self.b_cap = int(max_rows)
         self.wait_ms = int(wait_ms)
+        self.single_launch = bool(single_launch)
         self.epoch = 0
         self.device = torch.device("cuda", torch.cuda.current_device())
+        # (the single-launch call and the two-call sequence use disjoint regions of the buffers)
+        self._sets = [self._exchange_buffers()]
+        dist.barrier(group=group)  # every buffer is mapped everywhere before the first call
+
+    def _exchange_buffers(self):
+        import ctypes
         lib = _native.lib()
         own = ctypes.c_void_p()
         handle = ctypes.create_string_buffer(64)
         _native.check(lib.fftopk_comm_create(self.b_cap, ctypes.byref(own), handle), "fftopk_comm_create")
-        self._own = own.value
         handles = [None] * self.world
-        dist.all_gather_object(handles, bytes(handle.raw), group=group)
-        self._peers = []
-        ptrs = []
+        dist.all_gather_object(handles, bytes(handle.raw), group=self.group)
+        peers, ptrs = [], []
         for r in range(self.world):
             if r == self.rank:
-                ptrs.append(self._own)
+                ptrs.append(own.value)
                 continue
             p = ctypes.c_void_p()
             _native.check(lib.fftopk_comm_open(handles[r], ctypes.byref(p)), "fftopk_comm_open")
-            self._peers.append(p.value)
+            peers.append(p.value)
             ptrs.append(p.value)
-        self._comms = (ctypes.c_void_p * self.world)(*ptrs)
-        dist.barrier(group=group)  # every buffer is mapped everywhere before the first call
+        return {"own": own.value, "peers": peers, "comms": (ctypes.c_void_p * self.world)(*ptrs)}
 
     def __call__(self, score_shard: torch.Tensor, lengths_global: torch.Tensor, topk: int = TOPK) -> torch.Tensor:
         assert topk == TOPK and score_shard.dim() == 2
@@ -147,7 +155,7 @@ class FusedContextParallelTopk:
         return out
 
     def run_into(self, score_shard: torch.Tensor, local_lens: torch.Tensor, out: torch.Tensor) -> None:
-        """The enqueue-only core (no allocation, no host-side state: the epoch lives on the device),
+        """The enqueue-only core (no allocation, no host-side state: the epochs live on the device),
         so this sequence can be captured in a CUDA graph and replayed - every rank the same number
         of times. `local_lens` = local_lengths(lengths_global, Ls, rank) on the device."""
         B, Ls = score_shard.shape
@@ -156,23 +164,34 @@ class FusedContextParallelTopk:
         status = _status_word(score_shard.device).data_ptr()
         with torch.cuda.device(score_shard.device):
             stream = torch.cuda.current_stream().cuda_stream
+            if self.single_launch:
+                one = self._sets[0]
+                rc = lib.fftopk_topk2048_cp(score_shard.data_ptr(), score_shard.stride(0), B, Ls, local_lens.data_ptr(),
+                                            self.rank * Ls, one["comms"], self.world, self.rank, self.b_cap, 0,
+                                            self.wait_ms, out.data_ptr(), status, stream)
+                if rc != _native.E_RANGE:
+                    _native.check(rc, "fftopk_topk2048_cp")
+                    return
+                # this shape does not fit the single launch (the same answer on every rank)
+            two = self._sets[0]
             rc = lib.fftopk_select2048_cp(score_shard.data_ptr(), score_shard.stride(0), B, Ls, local_lens.data_ptr(),
-                                          self.rank * Ls, self._own, self.b_cap, 0, status, stream)
+                                          self.rank * Ls, two["own"], self.b_cap, 0, status, stream)
             _native.check(rc, "fftopk_select2048_cp")
-            rc = lib.fftopk_merge2048_cp(self._comms, self.world, self.rank, B, self.b_cap, 0, self.wait_ms,
+            rc = lib.fftopk_merge2048_cp(two["comms"], self.world, self.rank, B, self.b_cap, 0, self.wait_ms,
                                          out.data_ptr(), None, status, stream)
             _native.check(rc, "fftopk_merge2048_cp")
 
     def close(self) -> None:
-        """Unmap the peers' buffers and free the own one (all ranks, after a barrier)."""
-        if self._own is None:
+        """Unmap the peers' buffers and free the own ones (all ranks, after a barrier)."""
+        if not self._sets:
             return
         torch.cuda.synchronize()
         dist.barrier(group=self.group)
         lib = _native.lib()
-        for p in self._peers:
-            lib.fftopk_comm_close(p)
+        for s in self._sets:
+            for p in s["peers"]:
+                lib.fftopk_comm_close(p)
         dist.barrier(group=self.group)
-        lib.fftopk_comm_destroy(self._own)
-        self._own = None
-        self._peers = []
+        for s in self._sets:
+            lib.fftopk_comm_destroy(s["own"])
+        self._sets = []

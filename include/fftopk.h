@@ -148,8 +148,9 @@ int fftopk_merge2048(const uint32_t* cand_key, const int32_t* cand_idx, int64_t 
  * No reference counterpart. Every rank owns one "comm" buffer that its peers map through CUDA
  * IPC (NVLink peer access); a call with epoch e (1, 2, 3, ... the same on every rank) works in
  * two enqueue-only steps:
- *   fftopk_select2048_cp  local selection written into the rank's own comm buffer (half e & 1),
- *                         then a one-thread kernel fences and releases the buffer's epoch flag;
+ *   fftopk_select2048_cp  local selection written into the rank's own comm buffer (half e & 1);
+ *                         the last CTA of that kernel to finish fences and releases the buffer's
+ *                         epoch flag;
  *   fftopk_merge2048_cp   ONE kernel per rank that waits - at most wait_ms milliseconds per
  *                         shard - until every shard's flag has reached e, pulls the candidates
  *                         out of the peers' buffers with plain loads and merges them.
@@ -167,7 +168,7 @@ int fftopk_merge2048(const uint32_t* cand_key, const int32_t* cand_idx, int64_t 
  *                (the rank's own pointer for itself, fftopk_comm_open results for the peers)
  *   own          this rank's position in comms
  *   epoch        1, 2, 3, ... chosen by the host, or 0 in BOTH calls for device-side epochs: the
- *                publish kernel then increments the buffer's own flag and the kernels derive the
+ *                selection then increments the buffer's own flag and the kernels derive the
  *                epoch and the buffer half from it, so the select / publish / merge sequence has no
  *                per-call host argument and a captured CUDA graph of it can be replayed
  */
@@ -182,6 +183,31 @@ int fftopk_select2048_cp(const float* score, int64_t row_stride, int32_t B, int6
 int fftopk_merge2048_cp(void* const* comms, int32_t G, int32_t own, int32_t B, int32_t b_cap,
                         uint32_t epoch, int32_t wait_ms, int32_t* out_idx, uint32_t* out_key,
                         uint32_t* status, void* cuda_stream);
+
+/*
+ * The context-parallel call as ONE launch per GPU: local selection, exchange and merge in the same
+ * kernel. No reference counterpart. The cluster that selects a row's local top 2048 pushes them, as
+ * soon as the row is selected, into the comm buffer of every GPU as self-validating packets
+ * {index, epoch, key, epoch} - plain 16-byte stores over NVLink, no flag, no fence; CTA g of the
+ * cluster then polls - in its own GPU's memory, for at most wait_ms - the packets shard g sent for
+ * the row, and the cluster merges the G lists into out_idx. There is no second launch, no
+ * collective library call and no launch-wide synchronisation; a peer that never sends gives -1
+ * rows and FFTOPK_ST_PEER_TIMEOUT, never a hang.
+ *
+ *   score, row_stride, B, L, lengths, idx_offset   this rank's slice, as for fftopk_select2048_cp
+ *   comms, G, own, b_cap, epoch, wait_ms           as for fftopk_merge2048_cp (epoch 0: a counter
+ *                per row in the buffer itself, so a captured graph can be replayed). The call uses
+ *                regions of the comm buffers that the two-call sequence does not touch and keeps
+ *                its own epoch count: both kinds of call may be used on the same buffers
+ *   out_idx      device, int32 [B, 2048]: the global indices of the row's 2048 largest entries
+ * Returns FFTOPK_ERANGE - and enqueues nothing - when the launch plan for (B, L) gives a row fewer
+ * CTAs than there are shards (large batches of short slices); use the two-call sequence then. The
+ * answer depends only on B, L, G and the device, so all ranks of a homogeneous job get the same one.
+ */
+int fftopk_topk2048_cp(const float* score, int64_t row_stride, int32_t B, int64_t L,
+                       const int32_t* lengths, int32_t idx_offset, void* const* comms, int32_t G,
+                       int32_t own, int32_t b_cap, uint32_t epoch, int32_t wait_ms, int32_t* out_idx,
+                       uint32_t* status, void* cuda_stream);
 
 /*
  * Top-2048 by column slices, with no allocation anywhere. (This entry point has no counterpart in

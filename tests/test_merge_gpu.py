@@ -172,3 +172,119 @@ def test_fused_device_side_epochs_and_graph_replay():
     assert int(status.item()) == 0
     for c in comms:
         lib.fftopk_comm_destroy(c)
+
+
+# ----------------------------------------------------------------------------------------------
+# single-launch context-parallel call (fftopk_topk2048_cp) on one device. With one shard (G = 1)
+# the kernel selects, publishes the row's flag, "waits" for its own flag and merges its own list;
+# real peers are covered by test_multi_gpu.py. Nothing here waits on another kernel.
+# ----------------------------------------------------------------------------------------------
+def _single_launch(lib, comms_arr, G, own, b_cap, score_dev, lens_dev, epoch, out, status, stream=None, wait_ms=1000):
+    return lib.fftopk_topk2048_cp(score_dev.data_ptr(), score_dev.stride(0), score_dev.size(0), score_dev.size(1),
+                                  lens_dev.data_ptr(), 0, comms_arr, G, own, b_cap, epoch, wait_ms, out.data_ptr(),
+                                  status.data_ptr(), stream)
+
+
+@pytest.mark.parametrize("case", ["c5", "ragged", "ties", "c2"])
+def test_single_launch_one_shard_matches_oracle(case):
+    import ctypes
+    from jit_kernel import _native
+    lib = _native.lib()
+    dev = torch.device("cuda", 0)
+    if case == "c5":
+        score, lengths = workloads.c5(B=4, L=1 << 19)
+    elif case == "ragged":
+        score, lengths = workloads.c3(B=8, L=70000, min_len=500)
+        lengths[0], lengths[1] = 100, 2048
+    elif case == "ties":
+        score, lengths = workloads.c4(B=3, L=131072)
+    else:
+        score, lengths = workloads.c2(L=40000, B=20)  # 512-thread plan? no: many rows, fewer CTAs per row
+    B = score.size(0)
+    comm = _comm_create(B)
+    arr = (ctypes.c_void_p * 1)(comm)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    out = torch.empty(B, K, dtype=torch.int32, device=dev)
+    sd, ld = score.to(dev), lengths.to(dev)
+    for e in (1, 2, 3):  # both halves, reused
+        out.fill_(-9)
+        assert _single_launch(lib, arr, 1, 0, B, sd, ld, e, out, status) == 0
+        torch.cuda.synchronize()
+        got = out.cpu().numpy()
+        exp = orc.numpy_oracle(score.numpy(), lengths.numpy(), K)
+        for b in range(B):
+            assert np.array_equal(np.sort(got[b]), np.sort(exp[b])), f"{case} epoch {e} row {b}"
+    assert int(status.item()) == 0
+    lib.fftopk_comm_destroy(comm)
+
+
+def test_single_launch_device_side_epochs_and_graph_replay():
+    import ctypes
+    from jit_kernel import _native
+    lib = _native.lib()
+    dev = torch.device("cuda", 0)
+    score, lengths = workloads.c5(B=2, L=1 << 18)
+    comm = _comm_create(2)
+    arr = (ctypes.c_void_p * 1)(comm)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    out = torch.empty(2, K, dtype=torch.int32, device=dev)
+    sd, ld = score.to(dev), lengths.to(dev)
+    for _ in range(2):
+        assert _single_launch(lib, arr, 1, 0, 2, sd, ld, 0, out, status) == 0
+        torch.cuda.synchronize()
+        orc.check_result(score.numpy(), lengths.numpy(), out.cpu().numpy(), what="single launch, device epochs")
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            assert _single_launch(lib, arr, 1, 0, 2, sd, ld, 0, out, status, side.cuda_stream) == 0
+    for _ in range(3):
+        out.fill_(-7)
+        graph.replay()
+        torch.cuda.synchronize()
+        orc.check_result(score.numpy(), lengths.numpy(), out.cpu().numpy(), what="single launch, replay")
+    assert int(status.item()) == 0
+    lib.fftopk_comm_destroy(comm)
+
+
+def test_single_launch_wait_runs_out_without_hanging():
+    """Two shards, but the second buffer is one that nobody ever publishes into: the bounded wait of
+    the CTA that owns that shard gives up, every row is -1, the status says so, the device works."""
+    import ctypes
+    from jit_kernel import _native
+    lib = _native.lib()
+    dev = torch.device("cuda", 0)
+    score, lengths = workloads.c5(B=2, L=1 << 17)
+    own, silent = _comm_create(2), _comm_create(2)
+    arr = (ctypes.c_void_p * 2)(own, silent)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    out = torch.zeros(2, K, dtype=torch.int32, device=dev)
+    assert _single_launch(lib, arr, 2, 0, 2, score.to(dev), lengths.to(dev), 1, out, status, wait_ms=20) == 0
+    torch.cuda.synchronize()
+    assert int(status.item()) & _native.ST_PEER_TIMEOUT
+    assert bool((out == -1).all())
+    s, ln = workloads.c1()
+    from jit_kernel.topk_indexer import fast_topk_v3
+    got = fast_topk_v3(s.to(dev), ln.to(dev), K).cpu().numpy()
+    orc.check_result(s.numpy(), ln.numpy(), got, what="after timeout")
+    for c in (own, silent):
+        lib.fftopk_comm_destroy(c)
+
+
+def test_single_launch_refuses_plans_with_fewer_ctas_than_shards():
+    import ctypes
+    from jit_kernel import _native
+    lib = _native.lib()
+    dev = torch.device("cuda", 0)
+    B = 100  # one CTA per row on a 148-SM device: no room for two shard owners
+    a, b = _comm_create(B), _comm_create(B)
+    arr = (ctypes.c_void_p * 2)(a, b)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    out = torch.zeros(B, K, dtype=torch.int32, device=dev)
+    s = torch.zeros(B, 8192, device=dev)
+    ln = torch.full((B,), 8192, dtype=torch.int32, device=dev)
+    assert _single_launch(lib, arr, 2, 0, B, s, ln, 1, out, status) == _native.E_RANGE
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    for c in (a, b):
+        lib.fftopk_comm_destroy(c)

@@ -4,6 +4,7 @@ in test_merge_gpu.py and the plumbing under gloo in test_distributed_cpu.py."""
 import os
 import sys
 
+import numpy as np
 import pytest
 import torch
 import torch.distributed as dist
@@ -35,13 +36,28 @@ def _worker(rank, world, port, ret):
         out = fast_topk_v3_context_parallel(shard, lengths, K)
         torch.cuda.synchronize()
         orc.check_result(score.numpy(), lengths.numpy(), out.cpu().numpy(), what=f"cp rank {rank}")
-        # the same through the fused path: IPC-mapped peer buffers, no collective on the data path
+        # the same through the fused paths: IPC-mapped peer buffers, no collective on the data path.
+        # `fused` is the single launch per rank (selection, publication, pull and merge in one
+        # kernel), `fused2` the two-kernel sequence (selection with publication, merge that pulls)
         from jit_kernel.distributed import FusedContextParallelTopk
         fused = FusedContextParallelTopk(max_rows=8)
+        fused2 = FusedContextParallelTopk(max_rows=8, single_launch=False)
         for _ in range(3):
             out = fused(shard, lengths)
             torch.cuda.synchronize()
             orc.check_result(score.numpy(), lengths.numpy(), out.cpu().numpy(), what=f"fused cp rank {rank}")
+            out = fused2(shard, lengths)
+            torch.cuda.synchronize()
+            orc.check_result(score.numpy(), lengths.numpy(), out.cpu().numpy(), what=f"two-kernel cp rank {rank}")
+        # ragged global lengths: some slices partly or wholly empty, a row shorter than k
+        rs, rl = workloads.c3(seed=5, B=6, L=world * 20000, min_len=1000)
+        rl[0], rl[1] = 1500, 20000 + 7
+        rshard = rs[:, rank * 20000:(rank + 1) * 20000].contiguous().to(dev)
+        for f in (fused, fused2):
+            out = f(rshard, rl).cpu().numpy()
+            exp = orc.numpy_oracle(rs.numpy(), rl.numpy(), K)
+            for b in range(6):
+                assert np.array_equal(np.sort(out[b]), np.sort(exp[b])), f"ragged cp row {b} rank {rank}"
         # tie stress across shards
         score, lengths = workloads.c4(B=2, L=131072)
         Ls = score.size(1) // world
@@ -55,9 +71,11 @@ def _worker(rank, world, port, ret):
         orc.check_result(score[b0:b1].numpy(), lengths[b0:b1].numpy(), got.cpu().numpy(), what=f"rows rank {rank}")
         s4, l4 = workloads.c4(B=2, L=131072)
         sh4 = s4[:, rank * (131072 // world):(rank + 1) * (131072 // world)].contiguous().to(dev)
-        out = fused(sh4, l4)
-        orc.check_result(s4.numpy(), l4.numpy(), out.cpu().numpy(), what=f"fused ties rank {rank}")
+        for f in (fused, fused2):
+            out = f(sh4, l4)
+            orc.check_result(s4.numpy(), l4.numpy(), out.cpu().numpy(), what=f"fused ties rank {rank}")
         fused.close()
+        fused2.close()
         assert kernel_status(dev) == 0
         ret[rank] = "ok"
     finally:

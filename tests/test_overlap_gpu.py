@@ -42,9 +42,10 @@ def test_host_buffer_entry_with_overlap_on():
     filler = workloads.c3(seed=9, B=64, L=30000)
     fs, fl = filler[0].to(dev), filler[1].to(dev)
     fo = torch.empty(64, K, dtype=torch.int32, device=dev)
-    for s, ln in batches:
+    pinned = [(s.pin_memory(), ln.pin_memory()) for s, ln in batches]  # alive until the stream has drained:
+    for hs, hl in pinned:                                              # the call only enqueues
         fast_topk(fs, fo, fl)  # an overlapped plain call right before the composite one
-        outs.append(fast_topk_v3_host(s.pin_memory(), ln.pin_memory(), K))
+        outs.append(fast_topk_v3_host(hs, hl, K))
         fast_topk(fs, fo, fl)
     torch.cuda.synchronize()
     for (s, ln), out in zip(batches, outs):
