@@ -31,6 +31,8 @@ kept as `cold_start_ms_per_step`.
   latency    p50 microseconds per call at B=1 for the decode sweep L = 64K .. 1M (the other half of
              the headline metric), L2-warm (the reference's own method; also as a fraction of the
              L2 read bandwidth measured with the library's probe) and with rotated buffers
+  decode_loop  B=1, one logit appended per step: us per step cold and with the warm start that carries
+             the previous step's threshold (fast_topk_v3_warm)
   large_batch  one serialised call at B=256 and B=512 of the same ragged distribution: the rate a
              single call reaches when the batch alone fills the device
   context_parallel  (N > 1) config 5 through the three context-parallel variants: first checked
@@ -319,6 +321,50 @@ def latency_sweep(dev, stream, fast_topk, l2_gbs=None):
             res["warm_frac_l2"] = res["warm_gbs"] / l2_gbs
         out[str(L)] = res
         del bufs
+    return out
+
+
+def decode_loop_leg(dev, stream):
+    """A decode loop at B=1: the same row, one logit appended per step (the decode-sweep
+    distribution), selected cold every step (fast_topk_v3's path) and with the warm start that
+    carries the previous step's threshold key (fast_topk_v3_warm). 40 steps per CUDA graph; the
+    graph's first node restores the threshold of the step before the first, so every replay is the
+    same loop. us per step, p50 of 15 replays."""
+    from jit_kernel.topk_indexer import fast_topk, fast_topk_v3_warm
+
+    out = {}
+    steps = 40
+    idx = torch.empty(1, K, dtype=torch.int32, device=dev)
+    for L in (131072, 1048576):
+        score, _ = workloads.c2(L=L + steps)
+        sd = score.to(dev)
+        lens = [torch.full((1,), L + t, dtype=torch.int32, device=dev) for t in range(steps + 1)]
+        thr = torch.zeros(1, dtype=torch.int32, device=dev)
+        with torch.cuda.stream(stream):
+            fast_topk_v3_warm(sd, lens[0], K, thr, out=idx)  # the step before the loop: seeds the threshold
+            for t in range(1, 4):
+                fast_topk(sd, idx, lens[t])
+        stream.synchronize()
+        seed = thr.clone()
+
+        def warm_steps(_):
+            thr.copy_(seed)
+            for t in range(1, steps + 1):
+                fast_topk_v3_warm(sd, lens[t], K, thr, out=idx)
+
+        def cold_steps(_):
+            for t in range(1, steps + 1):
+                fast_topk(sd, idx, lens[t])
+
+        res = {}
+        for name, fn in (("cold", cold_steps), ("warm", warm_steps)):
+            with torch.cuda.stream(stream):
+                fn(0)
+            stream.synchronize()
+            g = capture_steps(fn, 1, stream)
+            ts = sorted(time_graph(g, stream) / steps * 1e6 for _ in range(15))
+            res[name + "_us_per_step"] = ts[len(ts) // 2]
+        out[str(L)] = res
     return out
 
 
@@ -647,6 +693,7 @@ def ours_arm(args, rank: int, local_rank: int, world: int) -> None:
         line["latency"] = latency_sweep(dev, stream, fast_topk, probes.get("l2_4MiB"))
         line["p50_us_B1_L1M"] = line["latency"]["1048576"]["warm"]["p50_us"]
         line["large_batch"] = large_batch_leg(dev, stream, fast_topk, peak)
+        line["decode_loop"] = decode_loop_leg(dev, stream)
         # CPU baseline on this box's host cores, bounded: the 64-row batch a few times (~20 ms each)
         cpu_reps = 10
         cpu_sec = time_cpu(score, lengths, cpu_reps, 2)

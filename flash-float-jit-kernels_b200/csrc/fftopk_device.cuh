@@ -168,6 +168,7 @@ struct Ctrl {
   uint32_t wtot[32];
   uint32_t wmax[32];
   // merge of candidate lists: this CTA's record about its shard, read by the cluster's other CTAs
+  uint32_t thr_key;      // warm start: smallest key among the winners of the finish
   uint32_t merge_count;  // valid candidates
   uint32_t merge_fail;   // the bounded wait for the shard's flag ran out
   uint64_t small[kSmall];
@@ -538,12 +539,15 @@ __device__ __forceinline__ void block_pick(const uint32_t* hist, uint32_t need, 
 // `page`: optional per-row table; the value written is then page[idx] instead of idx + idx_offset
 // (the fused page-table transform of the reference's topk_transform_* kernels, :871-958).
 // ---------------------------------------------------------------------------------------------
-template <int NT, class Src>
+// `known_total`: when not 0, the number of candidates in the source; if it equals `need` they all
+// win and no round is run. kTrackMin: the smallest key among the winners - the key of the
+// need-th largest candidate - is left in ctrl->thr_key (atomic min; the caller presets it).
+template <int NT, class Src, bool kTrackMin = false>
 __device__ void cta_finish(const Src& src, uint32_t need, uint64_t lo, uint64_t cap, uint64_t focus, bool have_hist,
                            int idx_bits, uint32_t* hist /* >= kFinishBins words */, Ctrl* ctrl, int32_t* out_idx,
                            uint32_t* out_key, uint32_t out_base, uint32_t out_slots /* k of the row */,
                            int32_t idx_offset, uint32_t* status,
-                           const int32_t* page = nullptr /* when set: out = page[idx] */) {
+                           const int32_t* page = nullptr /* when set: out = page[idx] */, uint32_t known_total = 0u) {
   const int tid = threadIdx.x;
   const int lane = tid & 31, warp = tid >> 5;
   if (tid == 0) {
@@ -588,7 +592,15 @@ __device__ void cta_finish(const Src& src, uint32_t need, uint64_t lo, uint64_t 
   uint64_t t_lo = 0ull, t_hi = 0ull;
   uint32_t need2 = 0, cnt = 0;
   bool all_bin = false, found = false;
-  for (int round = 0; round < 24; ++round) {
+  if (known_total != 0u && known_total == need && lo <= cap) {
+    // exactly as many candidates as are wanted: all of them win
+    t_lo = lo;
+    t_hi = cap;
+    cnt = need2 = need;
+    all_bin = found = true;
+    __syncthreads();  // (the counters cleared above are used by the pass below)
+  }
+  for (int round = 0; round < 24 && !found; ++round) {
     if ((uint32_t)(lo >> 32) == (uint32_t)(cap >> 32)) {
       // one key left: the inverted indices all start with the same run of ones
       const uint64_t floor_lo = single_key_floor(lo, idx_bits);
@@ -650,6 +662,7 @@ __device__ void cta_finish(const Src& src, uint32_t need, uint64_t lo, uint64_t 
   const unsigned lt = (1u << lane) - 1u;
   // Slots come from one shared counter; the warps' atomics on it serialise (~30 cycles each), so
   // a warp allocates for four candidates per lane with one of them.
+  uint32_t win_min = 0xffffffffu;  // (kTrackMin) smallest key among the winners this thread wrote
   auto pass = [&](auto paged) {
     src.for_each_uniform4([&](uint64_t c0, uint64_t c1, uint64_t c2, uint64_t c3) {
       const uint64_t c[4] = {c0, c1, c2, c3};
@@ -675,6 +688,7 @@ __device__ void cta_finish(const Src& src, uint32_t need, uint64_t lo, uint64_t 
               out_idx[pos] = idx + idx_offset;
             }
             if (out_key) out_key[pos] = (uint32_t)(c[u] >> 32);
+            if constexpr (kTrackMin) win_min = min(win_min, (uint32_t)(c[u] >> 32));
           }
           base += (uint32_t)__popc(b[u]);
         }
@@ -696,6 +710,10 @@ __device__ void cta_finish(const Src& src, uint32_t need, uint64_t lo, uint64_t 
     pass(std::false_type{});
   }
   FFTOPK_MARK(33);
+  if constexpr (kTrackMin) {
+    win_min = __reduce_min_sync(kFull, win_min);
+    if (lane == 0 && win_min != 0xffffffffu) atomicMin(&ctrl->thr_key, win_min);
+  }
 #ifdef FFTOPK_CHECKED
   {
     // every certain winner took exactly one slot, every undecided candidate was set aside
@@ -732,6 +750,7 @@ __device__ void cta_finish(const Src& src, uint32_t need, uint64_t lo, uint64_t 
           out_idx[pos] = page ? __ldg(page + idx) : idx + idx_offset;
           if (out_key) out_key[pos] = (uint32_t)(me >> 32);
         }
+        if constexpr (kTrackMin) atomicMin(&ctrl->thr_key, (uint32_t)(me >> 32));
       }
     }
   }

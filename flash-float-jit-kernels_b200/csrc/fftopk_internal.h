@@ -35,6 +35,10 @@ struct SelectCall {
   int64_t cp_half_words = 0;
   uint32_t* cp_publish = nullptr;  // flag line of the comm buffer: the launch's last CTA releases it
   uint32_t cp_epoch = 0;
+  // warm start (fftopk_select2048_warm): per-row key guesses in, this call's threshold keys out
+  const uint32_t* prev_threshold = nullptr;
+  uint32_t* next_threshold = nullptr;
+  uint32_t warm_margin = 0;
   // false: this launch consumes what a kernel enqueued just before it by the library itself has
   // produced (gathered rows, widened scores, slice lengths), or hands its output to a kernel the
   // library enqueues right after it. Such a launch keeps plain stream order whatever

@@ -90,6 +90,12 @@ struct SelectParams {
   // the value to store, or 0 for "the flag's current value plus one".
   uint32_t* cp_publish;
   uint32_t cp_epoch;
+  // warm start (select2048_kernel<NT, false, true> only): prev_threshold[row] is a key guess of the
+  // row's k-th largest element from an earlier call (0: none), from which warm_margin is
+  // subtracted; next_threshold[row] receives this call's k-th largest key (or a lower bound of it)
+  const uint32_t* prev_threshold;
+  uint32_t* next_threshold;
+  uint32_t warm_margin;
 };
 
 
@@ -702,7 +708,7 @@ __device__ __forceinline__ int refine_from_data(RowCtx<NT>& cx, uint32_t& need, 
 #endif
 // kAnyK = false: k is the constant 2048 of the reference's op (the compiler folds it: one register
 // less in a kernel that sits at its register limit); true: k comes from the parameters.
-template <int NT, bool kAnyK>
+template <int NT, bool kAnyK, bool kWarm = false>
 __device__ __forceinline__ void select_row(const SelectParams& p) {
   RowCtx<NT> cx;
   cg::cluster_group cluster = cg::this_cluster();
@@ -757,6 +763,9 @@ __device__ __forceinline__ void select_row(const SelectParams& p) {
         out_idx[i] = i < len ? (cx.page ? __ldg(cx.page + i) : i + cx.idx_offset) : -1;
         if (out_key) out_key[i] = i < len ? fftopk_key_from_bits(__float_as_uint(__ldg(rowp + i))) : 0u;
       }
+      if constexpr (kWarm) {
+        if (tid == 0 && p.next_threshold) p.next_threshold[row] = 0u;  // nothing to guess for such a row
+      }
     }
     return;  // uniform over the cluster; no shared memory of this CTA is ever read by a peer
   }
@@ -802,6 +811,21 @@ __device__ __forceinline__ void select_row(const SelectParams& p) {
 #endif
   const int ns = min(kRegSlabs, max(1, FFTOPK_SAMPLE_GRANULES / (C * NT)));
 
+  // ---- warm start: a key guess of the row's k-th largest element from an earlier call ----------
+  // With a guess the row skips the sample, its histograms and the cluster-wide search: it is
+  // filtered at once against the guess (minus the caller's margin). The checks after the filter
+  // are the same as for a sampled guess - at least k admitted, no list overflowed - and a guess
+  // that fails them sends the row to the full-histogram path, so the result is exact whatever the
+  // guess was.
+  uint32_t warm_key = 0u;
+  if constexpr (kWarm) {
+    if (p.prev_threshold != nullptr && !p.force_slow) {
+      const uint32_t g = __ldg(p.prev_threshold + row);
+      if (g != 0u) warm_key = g > p.warm_margin ? g - p.warm_margin : 1u;
+    }
+  }
+  const bool warm = kWarm && warm_key != 0u;  // (uniform over the cluster)
+
   // ---- prologue: clear the search totals, both histograms and the control block --------------
   if (tid < kSup) {
     ctrl->tot[0][tid] = 0u;  // (the buffers with index 1 are cleared by the first search)
@@ -810,8 +834,11 @@ __device__ __forceinline__ void select_row(const SelectParams& p) {
   }
   {
     uint4* h4 = reinterpret_cast<uint4*>(cx.hist(0));
-    for (int i = tid; i < 2 * kMaxBins / 4; i += NT) h4[i] = make_uint4(0u, 0u, 0u, 0u);
+    if (!warm) {
+      for (int i = tid; i < 2 * kMaxBins / 4; i += NT) h4[i] = make_uint4(0u, 0u, 0u, 0u);
+    }
     if (tid == 0) {
+      if constexpr (kWarm) ctrl->thr_key = 0xffffffffu;
       ctrl->win_count = 0u;
       ctrl->cand_count = 0u;
       ctrl->pub_flag = 0u;
@@ -837,6 +864,12 @@ __device__ __forceinline__ void select_row(const SelectParams& p) {
     gr[j] = sh.g1;  // "none"
     xr[j] = make_float4(0.f, 0.f, 0.f, 0.f);
   }
+  if (warm) {
+    // Rank 0's counters are cleared: tell the cluster now, check just before the first remote
+    // access - the barrier's latency hides behind the filter pass.
+    __syncthreads();
+    if (C > 1) cluster.barrier_arrive();
+  } else {
   {
     const float4* base4 = reinterpret_cast<const float4*>(sh.gbase);
     if (exact) {
@@ -899,6 +932,7 @@ __device__ __forceinline__ void select_row(const SelectParams& p) {
   if (dual) compute_sup<NT>(cx.hist(1), cx.sup(1), kMaxBins);
   FFTOPK_MARK(2);
   cluster_sync(cluster, C);  // #1: sample histograms complete
+  }  // (!warm)
   FFTOPK_MARK(3);
 
   uint32_t need = K;
@@ -915,8 +949,132 @@ __device__ __forceinline__ void select_row(const SelectParams& p) {
   auto high_end = [](uint32_t key) { return ((uint64_t)key << 32) | 0xffffffffull; };
   int fin_wn = 0, fin_sn = 0;  // ... and, for a lone CTA, this warp's segment length and the spill count
 
+  // Filter the shard against a key guess, gather what passes in rank 0 and check it: fills in what
+  // the finish starts from, or sets mode to kModeFallback. `focus_bin` (lone CTA): a bin of `pbits`
+  // bits the threshold will not lie above, or -1. `after_arrive`: the CTA has arrived at a cluster
+  // barrier that must complete before rank 0's counters are touched.
+  auto filter_gather = [&](const uint32_t gkey, const int focus_bin, const int pbits, const bool after_arrive) {
+    // Lower edge of the guess as a float: key(x) >= gkey  <=>  !(x < edge), NaN included.
+    // Keys outside the range real values map to (below -inf's key / above +inf's) admit
+    // everything instead; that only lengthens the lists.
+    const float edge = __uint_as_float(guess_edge_bits(gkey));
+    // list layout: one segment per warp, then the spill area (an eighth of the list)
+    const uint32_t spill_cap = (uint32_t)p.list_cap / 8u;
+    const uint32_t seg_cap = ((uint32_t)p.list_cap - spill_cap) / NW;
+    uint64_t* seg = list + (size_t)warp * seg_cap;
+    uint64_t* spill = list + (size_t)NW * seg_cap;
+    uint32_t kmax = 0u;
+    // A lone CTA that knows a bin the threshold will not lie above builds the histogram of the
+    // finish's first round while it converts its candidates (they pass through registers there
+    // anyway): the digit rule needs only the guess and that bound.
+    const uint32_t lowkey = guess_low_key(gkey);
+    fin_lo = lowkey;
+    if (C == 1 && focus_bin >= 0) {
+      fin_focus = (((uint32_t)focus_bin + 1u) << (32 - pbits)) - 1u;
+      fin_hist = fin_focus >= lowkey && make_finish_digit(low_end(lowkey), high_end(fin_focus)).key_only();
+    }
+    if (fin_hist) {  // (uniform over the CTA)
+      uint32_t* fh = cx.hist(0);
+      for (int b = tid; b < kFinishBins; b += NT) fh[b] = 0u;
+      __syncthreads();
+    }
+    uint32_t* fh = cx.hist(0);
+    auto round0 = [&](uint32_t key) {
+      if (fin_hist) red_shared_add(&fh[make_finish_digit(low_end(fin_lo), high_end(fin_focus)).of_key(key)], 1u);
+    };
+#ifndef FFTOPK_U512
+#define FFTOPK_U512 8
+#endif
+    constexpr int U = NT >= 1024 ? 4 : FFTOPK_U512;
+    // about 1.5 k candidates per row: up to ~192K elements most trips of the hit loop have work
+    const bool stage = len <= 196608;
+    const uint32_t wcnt = stage ? filter_shard<NT, U, true>(sh, edge, seg, seg_cap, ctrl, spill, spill_cap, kmax, round0)
+                                : filter_shard<NT, U, false>(sh, edge, seg, seg_cap, ctrl, spill, spill_cap, kmax, round0);
+    FFTOPK_MARK(8);
+    if (after_arrive && C > 1) cluster.barrier_wait();  // every CTA's counters are cleared (see the prologue)
+    const uint32_t wown = min(wcnt, seg_cap);
+    fin_wn = (int)wown;
+    kmax = __reduce_max_sync(kFull, kmax);
+    if (lane == 0) {
+      ctrl->wtot[warp] = wown;
+      ctrl->wmax[warp] = kmax;
+    }
+    __syncthreads();
+    FFTOPK_MARK(44);
+    // hand the candidates to rank 0: one remote atomic per CTA allocates the range
+    if (warp == 0) {
+      const uint32_t wmine = lane < NW ? ctrl->wtot[lane] : 0u;
+      uint32_t incl = wmine;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const uint32_t v = __shfl_up_sync(kFull, incl, off);
+        if (lane >= off) incl += v;
+      }
+      const uint32_t cmax = max(__reduce_max_sync(kFull, lane < NW ? ctrl->wmax[lane] : 0u), ctrl->spill_kmax);
+      uint32_t base = 0;
+      if (lane == 31) {
+        const uint32_t spill_n = min(ctrl->lcount, spill_cap);
+        base = atomicAdd(&cx.ctrl0->cand_count, incl + spill_n);
+        atomicMax(&cx.ctrl0->max_key, cmax);
+        if (ctrl->pub_flag) atomicOr(&cx.ctrl0->over_flag, 1u);
+        ctrl->base_c = base + incl;  // where the spill entries go
+      }
+      base = __shfl_sync(kFull, base, 31);
+      if (lane < NW) ctrl->wtot[lane] = base + incl - wmine;
+    }
+    __syncthreads();
+    FFTOPK_MARK(45);
+    fin_sn = (int)min(ctrl->lcount, spill_cap);
+    if (fin_hist) {  // the entries that went to the spill area
+      const uint32_t* sp32 = reinterpret_cast<const uint32_t*>(spill) + 1;
+      const FinishDigit dg = make_finish_digit(low_end(fin_lo), high_end(fin_focus));
+      for (int j = tid; j < fin_sn; j += NT) red_shared_add(&fh[dg.of_key(sp32[2 * j])], 1u);
+    }
+    if (C > 1) {
+      const uint32_t dst = ctrl->wtot[warp];
+      for (uint32_t j = lane; j < wown; j += 32) {
+        if (dst + j < (uint32_t)p.cand_cap) cx.cand0[dst + j] = seg[j];
+      }
+      const uint32_t sbase = ctrl->base_c;
+      for (uint32_t j = tid; j < (uint32_t)fin_sn; j += NT) {
+        if (sbase + j < (uint32_t)p.cand_cap) cx.cand0[sbase + j] = spill[j];
+      }
+    }
+    FFTOPK_MARK(46);
+    cluster_sync(cluster, C);  // #2: every candidate has landed in rank 0
+    FFTOPK_MARK(9);
+    {
+      // every thread reads rank 0's totals itself (no broadcast barrier; for rank 0, whose finish
+      // is the critical path, these are local reads)
+      const Ctrl* c0 = rank == 0 ? ctrl : cx.ctrl0;
+      const uint32_t total = c0->cand_count;
+      const uint32_t over = c0->over_flag;
+      const uint32_t maxkey = c0->max_key;
+      // fewer than k admitted (the guess was too high), a list overflowed, or more than rank 0
+      // can hold: start over with full histograms
+      const uint32_t room = C == 1 ? 0xffffffffu : (uint32_t)p.cand_cap;  // (a lone CTA keeps them in the list)
+      mode = sampled_attempt_ok(over, total, K, room) ? kModeGather : kModeFallback;
+      // every candidate's key lies in [lowkey, maxkey]
+      fin_cap = maxkey;
+      if (fin_hist) {
+        if (fin_cap < fin_focus) fin_cap = fin_focus;  // (a looser bound keeps the digit rule of the histogram)
+      } else {
+        fin_focus = fin_cap;
+      }
+    }
+    need = K;
+    P = 0;
+    r = -1;  // finish first, final barrier afterwards
+    FFTOPK_MARK(10);
+  };
+
   if (p.force_slow) {
     mode = kModeFallback;
+  } else if (warm) {
+    filter_gather(warm_key, -1, 12, true);
+    FFTOPK_MARK(4);
+    // (a miss is worth knowing about: the row is then selected by the full-histogram path)
+    if (mode == kModeFallback && rank == 0 && tid == 0 && p.status) atomicOr(p.status, (uint32_t)FFTOPK_ST_GUESS_MISSED);
   } else if (exact) {
     // ---- the sample is the row: its histogram gives the threshold bin directly -----------------
     cluster_pick<NT>(
@@ -1012,117 +1170,7 @@ __device__ __forceinline__ void select_row(const SelectParams& p) {
       FFTOPK_MARK(11);
     }
     if (smode == kModeGather) {
-      // Lower edge of the guess as a float: key(x) >= gkey  <=>  !(x < edge), NaN included.
-      // Keys outside the range real values map to (below -inf's key / above +inf's) admit
-      // everything instead; that only lengthens the lists.
-      const float edge = __uint_as_float(guess_edge_bits(gkey));
-      // list layout: one segment per warp, then the spill area (an eighth of the list)
-      const uint32_t spill_cap = (uint32_t)p.list_cap / 8u;
-      const uint32_t seg_cap = ((uint32_t)p.list_cap - spill_cap) / NW;
-      uint64_t* seg = list + (size_t)warp * seg_cap;
-      uint64_t* spill = list + (size_t)NW * seg_cap;
-      uint32_t kmax = 0u;
-      // A lone CTA that knows a bin the threshold will not lie above builds the histogram of the
-      // finish's first round while it converts its candidates (they pass through registers there
-      // anyway): the digit rule needs only the guess and that bound.
-      const uint32_t lowkey = guess_low_key(gkey);
-      fin_lo = lowkey;
-      if (C == 1 && dp.focus_bin >= 0) {
-        fin_focus = (((uint32_t)dp.focus_bin + 1u) << (32 - dp.pbits)) - 1u;
-        fin_hist = fin_focus >= lowkey && make_finish_digit(low_end(lowkey), high_end(fin_focus)).key_only();
-      }
-      if (fin_hist) {  // (uniform over the CTA)
-        uint32_t* fh = cx.hist(0);
-        for (int b = tid; b < kFinishBins; b += NT) fh[b] = 0u;
-        __syncthreads();
-      }
-      uint32_t* fh = cx.hist(0);
-      auto round0 = [&](uint32_t key) {
-        if (fin_hist) red_shared_add(&fh[make_finish_digit(low_end(fin_lo), high_end(fin_focus)).of_key(key)], 1u);
-      };
-#ifndef FFTOPK_U512
-#define FFTOPK_U512 8
-#endif
-      constexpr int U = NT >= 1024 ? 4 : FFTOPK_U512;
-      // about 1.5 k candidates per row: up to ~192K elements most trips of the hit loop have work
-      const bool stage = len <= 196608;
-      const uint32_t wcnt = stage ? filter_shard<NT, U, true>(sh, edge, seg, seg_cap, ctrl, spill, spill_cap, kmax, round0)
-                                  : filter_shard<NT, U, false>(sh, edge, seg, seg_cap, ctrl, spill, spill_cap, kmax, round0);
-      FFTOPK_MARK(8);
-      const uint32_t wown = min(wcnt, seg_cap);
-      fin_wn = (int)wown;
-      kmax = __reduce_max_sync(kFull, kmax);
-      if (lane == 0) {
-        ctrl->wtot[warp] = wown;
-        ctrl->wmax[warp] = kmax;
-      }
-      __syncthreads();
-      FFTOPK_MARK(44);
-      // hand the candidates to rank 0: one remote atomic per CTA allocates the range
-      if (warp == 0) {
-        const uint32_t wmine = lane < NW ? ctrl->wtot[lane] : 0u;
-        uint32_t incl = wmine;
-#pragma unroll
-        for (int off = 1; off < 32; off <<= 1) {
-          const uint32_t v = __shfl_up_sync(kFull, incl, off);
-          if (lane >= off) incl += v;
-        }
-        const uint32_t cmax = max(__reduce_max_sync(kFull, lane < NW ? ctrl->wmax[lane] : 0u), ctrl->spill_kmax);
-        uint32_t base = 0;
-        if (lane == 31) {
-          const uint32_t spill_n = min(ctrl->lcount, spill_cap);
-          base = atomicAdd(&cx.ctrl0->cand_count, incl + spill_n);
-          atomicMax(&cx.ctrl0->max_key, cmax);
-          if (ctrl->pub_flag) atomicOr(&cx.ctrl0->over_flag, 1u);
-          ctrl->base_c = base + incl;  // where the spill entries go
-        }
-        base = __shfl_sync(kFull, base, 31);
-        if (lane < NW) ctrl->wtot[lane] = base + incl - wmine;
-      }
-      __syncthreads();
-      FFTOPK_MARK(45);
-      fin_sn = (int)min(ctrl->lcount, spill_cap);
-      if (fin_hist) {  // the entries that went to the spill area
-        const uint32_t* sp32 = reinterpret_cast<const uint32_t*>(spill) + 1;
-        const FinishDigit dg = make_finish_digit(low_end(fin_lo), high_end(fin_focus));
-        for (int j = tid; j < fin_sn; j += NT) red_shared_add(&fh[dg.of_key(sp32[2 * j])], 1u);
-      }
-      if (C > 1) {
-        const uint32_t dst = ctrl->wtot[warp];
-        for (uint32_t j = lane; j < wown; j += 32) {
-          if (dst + j < (uint32_t)p.cand_cap) cx.cand0[dst + j] = seg[j];
-        }
-        const uint32_t sbase = ctrl->base_c;
-        for (uint32_t j = tid; j < (uint32_t)fin_sn; j += NT) {
-          if (sbase + j < (uint32_t)p.cand_cap) cx.cand0[sbase + j] = spill[j];
-        }
-      }
-      FFTOPK_MARK(46);
-      cluster_sync(cluster, C);  // #2: every candidate has landed in rank 0
-      FFTOPK_MARK(9);
-      {
-        // every thread reads rank 0's totals itself (no broadcast barrier; for rank 0, whose finish
-        // is the critical path, these are local reads)
-        const Ctrl* c0 = rank == 0 ? ctrl : cx.ctrl0;
-        const uint32_t total = c0->cand_count;
-        const uint32_t over = c0->over_flag;
-        const uint32_t maxkey = c0->max_key;
-        // fewer than k admitted (the guess was too high), a list overflowed, or more than rank 0
-        // can hold: start over with full histograms
-        const uint32_t room = C == 1 ? 0xffffffffu : (uint32_t)p.cand_cap;  // (a lone CTA keeps them in the list)
-        mode = sampled_attempt_ok(over, total, K, room) ? kModeGather : kModeFallback;
-        // every candidate's key lies in [lowkey, maxkey]
-        fin_cap = maxkey;
-        if (fin_hist) {
-          if (fin_cap < fin_focus) fin_cap = fin_focus;  // (a looser bound keeps the digit rule of the histogram)
-        } else {
-          fin_focus = fin_cap;
-        }
-      }
-      need = K;
-      P = 0;
-      r = -1;  // finish first, final barrier afterwards
-      FFTOPK_MARK(10);
+      filter_gather(gkey, dp.focus_bin, dp.pbits, false);
     } else {
       mode = kModeFallback;
     }
@@ -1145,17 +1193,34 @@ __device__ __forceinline__ void select_row(const SelectParams& p) {
       const uint32_t spill_cap1 = (uint32_t)p.list_cap / 8u;
       const uint32_t seg_cap1 = ((uint32_t)p.list_cap - spill_cap1) / NW;
       const WarpSegCands<NT> src{list + (size_t)warp * seg_cap1, fin_wn, list + (size_t)NW * seg_cap1, fin_sn};
-      cta_finish<NT>(src, need, low_end(fin_lo), high_end(fin_cap), high_end(fin_focus), fin_hist, idx_bits, cx.hist(0),
-                     ctrl, out_idx, out_key,
-                     K - need, K, cx.idx_offset, p.status, cx.page);
+      cta_finish<NT, WarpSegCands<NT>, kWarm>(src, need, low_end(fin_lo), high_end(fin_cap), high_end(fin_focus), fin_hist,
+                                              idx_bits, cx.hist(0), ctrl, out_idx, out_key, K - need, K, cx.idx_offset,
+                                              p.status, cx.page, ctrl->cand_count);
     } else {
       // every candidate shares the key prefix P above bit `sh` of the key (sampled path: range known)
       const int sh = r < 0 ? 0 : round_shift(r);
       const uint64_t lo = r < 0 ? low_end(fin_lo) : ((uint64_t)P << (32 + sh));
       const uint64_t cap = r < 0 ? high_end(fin_cap) : (lo | ((1ull << (32 + sh)) - 1ull));
       const DenseCands<NT> src{cx.cand, (int)min(ctrl->cand_count, (uint32_t)p.cand_cap)};
-      cta_finish<NT>(src, need, lo, cap, cap, false, idx_bits, cx.hist(0), ctrl, out_idx, out_key, K - need, K,
-                     cx.idx_offset, p.status, cx.page);
+      cta_finish<NT, DenseCands<NT>, kWarm>(src, need, lo, cap, cap, false, idx_bits, cx.hist(0), ctrl, out_idx, out_key,
+                                            K - need, K, cx.idx_offset, p.status, cx.page, r < 0 ? (uint32_t)src.n : 0u);
+    }
+  }
+  if constexpr (kWarm) {
+    // This call's threshold for the next one: the smallest key the finish let win (the row's k-th
+    // largest key), or, where no finish ran, the lower edge of the bin the threshold was found in
+    // (a lower bound: the next call then admits a few more candidates and tightens it again).
+    if (rank == 0 && p.next_threshold != nullptr) {
+      __syncthreads();
+      if (tid == 0) {
+        uint32_t thr = 0u;
+        if (mode == kModeGather) {
+          thr = ctrl->thr_key != 0xffffffffu ? ctrl->thr_key : 0u;
+        } else if ((mode == kModeTakeAll || mode == kModeTies) && r >= 0) {
+          thr = P << round_shift(r);
+        }
+        p.next_threshold[row] = thr;
+      }
     }
   }
   FFTOPK_MARK(34);
@@ -1164,9 +1229,9 @@ __device__ __forceinline__ void select_row(const SelectParams& p) {
   if (tid == 0 && p.status && mode == kModeAbort) atomicOr(p.status, (uint32_t)FFTOPK_ST_INTERNAL);
 }
 
-template <int NT, bool kAnyK = false>
+template <int NT, bool kAnyK = false, bool kWarm = false>
 __global__ void __launch_bounds__(NT, (NT == 512 ? FFTOPK_CTAS_512 : 1024 / NT)) select2048_kernel(const SelectParams p) {
-  select_row<NT, kAnyK>(p);
+  select_row<NT, kAnyK, kWarm>(p);
   if (p.cp_publish) {
     // Context-parallel publication folded into the selection: every thread fences its output
     // writes, the CTA arrives, and the last CTA of the grid releases the epoch flag system-wide
@@ -1326,6 +1391,10 @@ int setup_kernel(int smem_optin) {
   e = cudaFuncSetAttribute(select2048_kernel<NT, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
   if (e != cudaSuccess) return cuda_fail(e);
   if constexpr (NT >= 512) {
+    e = cudaFuncSetAttribute(select2048_kernel<NT, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_optin);
+    if (e != cudaSuccess) return cuda_fail(e);
+    e = cudaFuncSetAttribute(select2048_kernel<NT, false, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    if (e != cudaSuccess) return cuda_fail(e);
     e = cudaFuncSetAttribute(select_merge2048_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_optin);
     if (e != cudaSuccess) return cuda_fail(e);
     e = cudaFuncSetAttribute(select_merge2048_kernel<NT>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
@@ -1526,6 +1595,11 @@ int launch_select(const SelectCall& c) {
   p.cp_half_words = c.cp_half_words;
   p.cp_publish = c.cp_publish;
   p.cp_epoch = c.cp_epoch;
+  p.prev_threshold = c.prev_threshold;
+  p.next_threshold = c.next_threshold;
+  p.warm_margin = c.warm_margin;
+  const bool warm = c.prev_threshold != nullptr || c.next_threshold != nullptr;
+  if (warm && (c.k != kK || pl.threads < 512)) return FFTOPK_EINVAL;
   if ((size_t)pl.smem_bytes > (size_t)d->smem_optin) return FFTOPK_ERANGE;
 
   cudaLaunchConfig_t cfg = {};
@@ -1547,7 +1621,10 @@ int launch_select(const SelectCall& c) {
   }
   cudaError_t e;
   const bool any_k = c.k != kK;
-  if (pl.threads == 1024) {
+  if (warm) {
+    e = pl.threads == 1024 ? cudaLaunchKernelEx(&cfg, select2048_kernel<1024, false, true>, p)
+                           : cudaLaunchKernelEx(&cfg, select2048_kernel<512, false, true>, p);
+  } else if (pl.threads == 1024) {
     e = any_k ? cudaLaunchKernelEx(&cfg, select2048_kernel<1024, true>, p) : cudaLaunchKernelEx(&cfg, select2048_kernel<1024>, p);
   } else if (pl.threads == 512) {
     e = any_k ? cudaLaunchKernelEx(&cfg, select2048_kernel<512, true>, p) : cudaLaunchKernelEx(&cfg, select2048_kernel<512>, p);
@@ -1726,6 +1803,17 @@ int fftopk_select_topk(const float* score, int64_t row_stride, int32_t B, int64_
                        uint32_t* status, void* cuda_stream) {
   SelectCall c = basic_call(score, row_stride, B, L, lengths, row_starts, out_idx, out_key, idx_offset, status, cuda_stream);
   c.k = k;
+  return launch_select(c);
+}
+
+int fftopk_select2048_warm(const float* score, int64_t row_stride, int32_t B, int64_t L, const int32_t* lengths,
+                           const int32_t* row_starts, const uint32_t* prev_threshold, uint32_t margin,
+                           uint32_t* next_threshold, int32_t* out_idx, uint32_t* status, void* cuda_stream) {
+  if (B > 0 && !prev_threshold && !next_threshold) return FFTOPK_EINVAL;
+  SelectCall c = basic_call(score, row_stride, B, L, lengths, row_starts, out_idx, nullptr, 0, status, cuda_stream);
+  c.prev_threshold = prev_threshold;
+  c.next_threshold = next_threshold;
+  c.warm_margin = margin;
   return launch_select(c);
 }
 

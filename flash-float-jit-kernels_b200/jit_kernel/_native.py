@@ -20,6 +20,7 @@ K = 2048
 ST_STAGE_TIMEOUT = 1
 ST_INTERNAL = 2
 ST_PEER_TIMEOUT = 4
+ST_GUESS_MISSED = 8
 ST_CHECK = 16
 
 E_RANGE = -4
@@ -31,6 +32,7 @@ EXPORTS = (
     "fftopk_last_cuda_error",
     "fftopk_select2048",
     "fftopk_select_topk",
+    "fftopk_select2048_warm",
     "fftopk_widen_workspace_bytes",
     "fftopk_select_topk_16bit",
     "fftopk_select2048_page_table",
@@ -93,6 +95,9 @@ def lib() -> ctypes.CDLL:
     L.fftopk_select2048.argtypes = [
         c.c_void_p, c.c_int64, c.c_int32, c.c_int64, c.c_void_p, c.c_void_p,
         c.c_void_p, c.c_void_p, c.c_int32, c.c_void_p, c.c_void_p]
+    L.fftopk_select2048_warm.restype = c.c_int
+    L.fftopk_select2048_warm.argtypes = [c.c_void_p, c.c_int64, c.c_int32, c.c_int64, c.c_void_p, c.c_void_p, c.c_void_p,
+                                         c.c_uint32, c.c_void_p, c.c_void_p, c.c_void_p, c.c_void_p]
     L.fftopk_select2048_page_table.restype = c.c_int
     L.fftopk_select2048_page_table.argtypes = [
         c.c_void_p, c.c_int64, c.c_int32, c.c_int64, c.c_void_p, c.c_void_p, c.c_void_p, c.c_void_p, c.c_int64,

@@ -134,6 +134,48 @@ def fast_topk_v3(
     return topk_indices
 
 
+def fast_topk_v3_warm(
+    score: torch.Tensor,
+    lengths: torch.Tensor,
+    topk: int,
+    thresholds: torch.Tensor,
+    row_starts: Optional[torch.Tensor] = None,
+    margin: int = 0,
+    out: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """fast_topk_v3 for a decode loop (no counterpart in the reference; README.md:90-98 discusses
+    the idea): `thresholds`, an int32 CUDA tensor of shape (B) that starts as zeros, carries every
+    row's threshold key from one call to the next and is updated in place. A row with a non-zero
+    entry skips sampling and the threshold search and is filtered at once against that key minus
+    `margin` (key units; 0 is right when rows only grow between calls). The result is always the
+    exact top 2048 - a guess that does not hold only costs time (the row is selected by the
+    full-histogram path and FFTOPK_ST_GUESS_MISSED shows up in kernel_status()).
+    """
+    assert topk == 2048, "fast_topk_v3_warm only supports topk=2048"
+    assert score.dim() == 2
+    _check_inputs(score, lengths, row_starts, out)
+    B = score.size(0)
+    if not thresholds.is_cuda or thresholds.dtype != torch.int32 or thresholds.dim() != 1 or thresholds.size(0) != B \
+            or not thresholds.is_contiguous() or thresholds.device != score.device:
+        raise RuntimeError("thresholds must be a contiguous CUDA int32 tensor of shape (B) on score's device")
+    if not (0 <= int(margin) < (1 << 32)):
+        raise ValueError("margin must fit 32 bits")
+    if out is None:
+        out = torch.empty((B, topk), dtype=torch.int32, device=score.device)
+    if B == 0:
+        return out
+    lib = _native.lib()
+    with torch.cuda.device(score.device):
+        rc = lib.fftopk_select2048_warm(
+            score.data_ptr(), score.stride(0) if B > 1 else max(score.stride(0), 0), B, score.size(1),
+            lengths.data_ptr(), row_starts.data_ptr() if row_starts is not None else None,
+            thresholds.data_ptr(), int(margin), thresholds.data_ptr(), out.data_ptr(),
+            _status_word(score.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
+    _native.check(rc, "fftopk_select2048_warm")
+    _after_launch(score.device, "fftopk_select2048_warm")
+    return out
+
+
 def fast_topk_general(
     score: torch.Tensor,
     lengths: torch.Tensor,

@@ -99,6 +99,34 @@ int fftopk_select_topk(const float* score, int64_t row_stride, int32_t B, int64_
                        uint32_t* out_key, int32_t idx_offset, uint32_t* status, void* cuda_stream);
 
 /*
+ * fftopk_select2048 with a warm start: a decode loop calls the selector once per generated token on
+ * a row that has grown by one logit, so the previous call's threshold - the key of the row's 2048-th
+ * largest element - is an excellent first guess for this one. No counterpart in the reference's code;
+ * its README discusses guess-and-verify selection as a competitor's idea (README.md:90-98).
+ * With a guess a row skips the sample, its histograms and the cluster-wide threshold search: it is
+ * filtered at once against key = prev_threshold[b] - margin, and the checks that protect a sampled
+ * guess protect this one too - at least 2048 elements admitted, no candidate list overflowed. A
+ * guess that fails them (too high, far too low, stale) sends the row to the full-histogram path:
+ * the result is the exact top 2048, ties to the lower index, whatever the guess was, and
+ * FFTOPK_ST_GUESS_MISSED is raised in the status word for information.
+ *
+ *   prev_threshold  device, uint32 [B] or NULL: per-row key guess (the value next_threshold received
+ *                   in an earlier call, or fftopk_key_of(x) of any value x believed to be at or
+ *                   below the row's 2048-th largest); 0 = no guess for that row (cold selection)
+ *   margin          subtracted from every guess, in key units: 0 when the row only grew since the
+ *                   guess was made (its threshold cannot have dropped); for positive fp32 values one
+ *                   key unit is one ulp, so 1 << 20 lowers the guess by 12.5 % of its magnitude at most
+ *   next_threshold  device, uint32 [B] or NULL: receives the key of this call's 2048-th largest
+ *                   element (exact whenever the finishing pass ran; otherwise a lower bound of it;
+ *                   0 for rows of at most 2048 elements). May be the same array as prev_threshold
+ *   everything else as for fftopk_select2048 (no out_key / idx_offset).
+ */
+int fftopk_select2048_warm(const float* score, int64_t row_stride, int32_t B, int64_t L,
+                           const int32_t* lengths, const int32_t* row_starts,
+                           const uint32_t* prev_threshold, uint32_t margin, uint32_t* next_threshold,
+                           int32_t* out_idx, uint32_t* status, void* cuda_stream);
+
+/*
  * Selection fused with the step that follows it in a sparse-attention decode / prefill layer.
  * Replace fast_topk_transform_interface and fast_topk_transform_ragged_interface
  * (topk_indexer_radix.cu:1160-1250) with their three kernels (:871-995), which the reference
