@@ -709,35 +709,59 @@ def ours_arm(args, rank: int, local_rank: int, world: int) -> None:
 
 def profile_case(name: str) -> None:
     """Small fixed cases for profiler captures (`--case`): a few launches, one JSON line.
-    b1: B=1, L=1M decode call, eight rotated 4 MiB inputs. merge: the 8-shard candidate merge of a
-    B=4 batch (shards selected one after the other on this device). tp / serial: the bench's ragged
-    B=64 batch in the throughput plan / the default plan, 12 launches over 8 rotated inputs."""
+    b1: B=1, L=1M decode call, 40 rotated 4 MiB inputs. warm: the same row through the warm start
+    (thresholds carried from call to call). merge: the 8-shard candidate merge of a B=4 batch (shards
+    selected one after the other on this device). tp / serial: the bench's ragged B=64 batch in the
+    throughput plan / the default plan, 12 launches over 8 rotated inputs. f16: the same batch as
+    fp16 scores through the 16-bit instantiation. host: three calls of the host-buffer entry point
+    (gather kernel reading pinned memory, selection). probe: the read-bandwidth probe on a 4 MiB and
+    a 1 GiB buffer."""
+    from jit_kernel import _native
     from jit_kernel.distributed import _cuda_select, local_lengths, merge_candidates
-    from jit_kernel.topk_indexer import fast_topk
+    from jit_kernel.topk_indexer import fast_topk, fast_topk_general, fast_topk_v3_host, fast_topk_v3_warm
 
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
-    if name == "b1":
+    if name in ("b1", "warm"):
         score, lengths = workloads.c2(L=1 << 20)
         bufs = [torch.roll(score, i, 1).contiguous().to(dev) for i in range(40)]  # 160 MiB > L2
         ld = lengths.to(dev)
         out = torch.empty(1, K, dtype=torch.int32, device=dev)
-        for i in range(43):
-            fast_topk(bufs[i % 40], out, ld)
+        if name == "b1":
+            for i in range(43):
+                fast_topk(bufs[i % 40], out, ld)
+        else:  # (rolled copies of one row have the same threshold: every call after the first is warm)
+            thr = torch.zeros(1, dtype=torch.int32, device=dev)
+            for i in range(43):
+                fast_topk_v3_warm(bufs[i % 40], ld, K, thr, out=out)
         torch.cuda.synchronize()
-        print(json.dumps({"case": "b1", "launches": 43, "plan": __import__("jit_kernel._native", fromlist=["x"]).plan(1, 1 << 20)}))
-    elif name in ("tp", "serial"):
-        from jit_kernel import _native
+        print(json.dumps({"case": name, "launches": 43, "plan": _native.plan(1, 1 << 20)}))
+    elif name in ("tp", "serial", "f16"):
         _native.set_overlap(name == "tp")
         score, lengths = workloads.c3()
-        bufs = [torch.roll(score, i, 0).contiguous().to(dev) for i in range(8)]  # 256 MiB > L2
+        dt = torch.float16 if name == "f16" else torch.float32
+        bufs = [torch.roll(score, i, 0).to(dt).contiguous().to(dev) for i in range(8)]  # 256 MiB > L2 (fp16: 128 MiB)
         lens = [torch.roll(lengths, i, 0).contiguous().to(dev) for i in range(8)]
         out = torch.empty(score.size(0), K, dtype=torch.int32, device=dev)
         for i in range(12):
-            fast_topk(bufs[i % 8], out, lens[i % 8])
+            if name == "f16":
+                fast_topk_general(bufs[i % 8], lens[i % 8], K)
+            else:
+                fast_topk(bufs[i % 8], out, lens[i % 8])
         torch.cuda.synchronize()
         print(json.dumps({"case": name, "launches": 12, "plan": _native.plan(score.size(0), score.size(1))}))
         _native.set_overlap(False)
+    elif name == "host":
+        score, lengths = workloads.c3()
+        hs, hl = score.pin_memory(), lengths.pin_memory()
+        ho = torch.empty(score.size(0), K, dtype=torch.int32).pin_memory()
+        for _ in range(3):
+            fast_topk_v3_host(hs, hl, K, out=ho)
+        torch.cuda.synchronize()
+        print(json.dumps({"case": "host", "launches": 3}))
+    elif name == "probe":
+        stream = torch.cuda.Stream(device=dev)
+        print(json.dumps({"case": "probe", "read_gbs": measure_l2_read_gbs(dev, stream)}))
     else:
         score, lengths = workloads.c5()
         G, Ls = 8, score.size(1) // 8
@@ -757,7 +781,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=50)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip the latency sweep and the CPU baseline")
-    ap.add_argument("--case", default=None, choices=["b1", "merge", "tp", "serial"], help="run one small fixed case (for profilers)")
+    ap.add_argument("--case", default=None, choices=["b1", "warm", "merge", "tp", "serial", "f16", "host", "probe"], help="run one small fixed case (for profilers)")
     args = ap.parse_args()
     if args.case:
         profile_case(args.case)

@@ -11,8 +11,6 @@
 //   2. the selection kernel (fftopk_select2048),
 //   3. the device -> host copy of the indices.
 // The device staging area is the caller's: no allocation here.
-#include <cuda_bf16.h>
-#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -68,41 +66,6 @@ __global__ void __launch_bounds__(256) gather_rows_kernel(const float* __restric
     for (int64_t j = (n4 << 2) + t; j < len; j += step) dst[j] = src[j];
   } else {
     for (int64_t j = t; j < len; j += step) dst[j] = src[j];
-  }
-}
-
-// 16-bit scores widened to fp32 (exact, order-preserving, NaN and -0 included): the part of row b
-// that the selector will read, [row_start, row_start + len). grid = (chunks, B).
-template <class T16>
-__global__ void __launch_bounds__(256) widen_rows_kernel(const T16* __restrict__ src16, int64_t s_stride,
-                                                        float* __restrict__ d, int64_t d_stride,
-                                                        const int32_t* __restrict__ lengths,
-                                                        const int32_t* __restrict__ row_starts, int64_t L) {
-  const int b = blockIdx.y;
-  int64_t rs = row_starts ? row_starts[b] : 0;
-  rs = rs < 0 ? 0 : (rs > L ? L : rs);
-  int64_t len = lengths[b];
-  len = len < 0 ? 0 : len;
-  const int64_t end = rs + len > L ? L : rs + len;
-  const T16* src = src16 + (int64_t)b * s_stride;
-  float* dst = d + (int64_t)b * d_stride;
-  const int64_t step = (int64_t)gridDim.x * blockDim.x;
-  const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  const int64_t a0 = (rs + 7) & ~(int64_t)7;  // first 8-element group fully inside, if aligned
-  if ((reinterpret_cast<uintptr_t>(src) & 15u) == 0 && a0 < end) {
-    for (int64_t j = rs + t; j < a0; j += step) dst[j] = (float)src[j];
-    const int64_t n8 = (end - a0) >> 3;
-    const uint4* s8 = reinterpret_cast<const uint4*>(src + a0);
-    float4* d4 = reinterpret_cast<float4*>(dst + a0);
-    for (int64_t i = t; i < n8; i += step) {
-      const uint4 v = s8[i];
-      const T16* h = reinterpret_cast<const T16*>(&v);
-      d4[2 * i] = make_float4((float)h[0], (float)h[1], (float)h[2], (float)h[3]);
-      d4[2 * i + 1] = make_float4((float)h[4], (float)h[5], (float)h[6], (float)h[7]);
-    }
-    for (int64_t j = a0 + (n8 << 3) + t; j < end; j += step) dst[j] = (float)src[j];
-  } else {
-    for (int64_t j = rs + t; j < end; j += step) dst[j] = (float)src[j];
   }
 }
 
@@ -237,37 +200,21 @@ int fftopk_probe_read_bandwidth(const void* d_buf, size_t bytes, size_t bytes_to
 }
 
 size_t fftopk_widen_workspace_bytes(int32_t B, int64_t L) {
-  if (B <= 0 || L < 0) return 0;
-  return align_up((size_t)B * (size_t)((L + 3) & ~(int64_t)3) * 4);
+  (void)B;
+  (void)L;
+  return 0;  // kept for callers of the first form of fftopk_select_topk_16bit, which staged fp32 copies
 }
 
 int fftopk_select_topk_16bit(const void* score16, int32_t dtype, int64_t row_stride, int32_t B, int64_t L,
                              const int32_t* lengths, const int32_t* row_starts, int32_t k, int32_t* out_idx,
                              void* d_workspace, size_t workspace_bytes, uint32_t* status, void* cuda_stream) {
-  if (B < 0 || L < 0 || row_stride < 0 || (dtype != FFTOPK_DTYPE_FP16 && dtype != FFTOPK_DTYPE_BF16)) return FFTOPK_EINVAL;
-  if (B == 0) return FFTOPK_OK;
-  if (!score16 || !lengths || !out_idx || !d_workspace) return FFTOPK_EINVAL;
-  if ((reinterpret_cast<uintptr_t>(score16) & 1u) != 0) return FFTOPK_EINVAL;
-  if (L > (int64_t)0x7fffffff - 8 || B > 65535) return FFTOPK_ERANGE;
-  if (workspace_bytes < fftopk_widen_workspace_bytes(B, L) || (reinterpret_cast<uintptr_t>(d_workspace) & (kAlign - 1)) != 0)
-    return FFTOPK_EINVAL;
-  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
-  float* d_score = static_cast<float*>(d_workspace);
-  const int64_t d_stride = (L + 3) & ~(int64_t)3;
-  const int64_t c = (L + 32767) / 32768;
-  const dim3 grid((unsigned)(c < 1 ? 1 : (c > 64 ? 64 : c)), (unsigned)B);
-  if (dtype == FFTOPK_DTYPE_FP16) {
-    widen_rows_kernel<__half><<<grid, 256, 0, stream>>>(static_cast<const __half*>(score16), row_stride, d_score, d_stride,
-                                                       lengths, row_starts, L);
-  } else {
-    widen_rows_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(score16), row_stride,
-                                                              d_score, d_stride, lengths, row_starts, L);
-  }
-  cudaError_t err = cudaGetLastError();
-  if (err != cudaSuccess) return fftopk::cuda_fail(err);
+  (void)d_workspace;  // not needed any more: the rows are read in their own width
+  (void)workspace_bytes;
+  if (dtype != FFTOPK_DTYPE_FP16 && dtype != FFTOPK_DTYPE_BF16) return FFTOPK_EINVAL;
   fftopk::SelectCall call;
-  call.score = d_score;
-  call.row_stride = d_stride;
+  call.score = score16;
+  call.dtype = dtype == FFTOPK_DTYPE_FP16 ? fftopk::kDtypeF16 : fftopk::kDtypeBF16;
+  call.row_stride = row_stride;
   call.B = B;
   call.L = L;
   call.lengths = lengths;
@@ -276,7 +223,6 @@ int fftopk_select_topk_16bit(const void* score16, int32_t dtype, int64_t row_str
   call.out_idx = out_idx;
   call.status = status;
   call.cuda_stream = cuda_stream;
-  call.may_overlap = false;  // reads the workspace the widening kernel enqueued above has written
   return fftopk::launch_select(call);
 }
 

@@ -11,8 +11,11 @@ namespace fftopk {
 // One selection launch. Every public selection entry point fills one of these and calls
 // launch_select(); the composite entry points (host buffers, 16-bit scores, column slices,
 // context-parallel publication) do the same from their own translation units.
+enum : int { kDtypeF32 = 0, kDtypeF16 = 1, kDtypeBF16 = 2 };
+
 struct SelectCall {
-  const float* score = nullptr;
+  const void* score = nullptr;  // elements of `dtype`
+  int dtype = kDtypeF32;
   int64_t row_stride = 0;
   int32_t B = 0;
   int64_t L = 0;

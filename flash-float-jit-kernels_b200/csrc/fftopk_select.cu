@@ -41,6 +41,8 @@
 //   FFTOPK_KSMALL           undecided candidates ranked by votes (256)
 //   FFTOPK_TRACE            phase timestamps of block 0 (changes no result)
 #include <cooperative_groups.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <string.h>
@@ -57,7 +59,7 @@ namespace fftopk {
 
 
 struct SelectParams {
-  const float* score;
+  const void* score;  // fp32, or fp16 / bf16 for the kernels instantiated on those types
   int64_t row_stride;
   int64_t L;
   const int32_t* lengths;
@@ -105,10 +107,46 @@ constexpr int kRegSlabs = 4;  // granules a thread keeps in registers when the w
 __device__ __forceinline__ int round_width(int r) { return r < 2 ? 12 : 8; }
 __device__ __forceinline__ int round_shift(int r) { return r == 0 ? 20 : (r == 1 ? 8 : 0); }
 
-// Shard of one CTA, in 16-byte granules of the aligned view of the row: granule g covers row
-// elements 4g-a .. 4g-a+3, where a in 0..3 is the row's misalignment in elements.
+// Element types of the score matrix. The kernel works on granules of FOUR elements of the aligned
+// view of the row - 16 bytes of fp32, 8 bytes of fp16 / bf16 - and widens 16-bit elements to fp32
+// (exactly, order-preserving) as it loads them, so that keys, edges and composites are the fp32
+// ones everywhere and a 16-bit row is read once, in its own width.
+template <class T>
+struct Elem;
+template <>
+struct Elem<float> {
+  static __device__ __forceinline__ float4 ld4(const float* gbase, int g) {
+    return __ldg(reinterpret_cast<const float4*>(gbase) + g);
+  }
+  static __device__ __forceinline__ float ld1(const float* p) { return __ldg(p); }
+};
+template <>
+struct Elem<__half> {
+  static __device__ __forceinline__ float4 ld4(const __half* gbase, int g) {
+    const uint2 r = __ldg(reinterpret_cast<const uint2*>(gbase) + g);
+    const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&r.x));
+    const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&r.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+  }
+  static __device__ __forceinline__ float ld1(const __half* p) { return __half2float(__ldg(p)); }
+};
+template <>
+struct Elem<__nv_bfloat16> {
+  static __device__ __forceinline__ float4 ld4(const __nv_bfloat16* gbase, int g) {
+    const uint2 r = __ldg(reinterpret_cast<const uint2*>(gbase) + g);  // bf16 = the upper half of an fp32
+    return make_float4(__uint_as_float(r.x << 16), __uint_as_float(r.x & 0xffff0000u), __uint_as_float(r.y << 16),
+                       __uint_as_float(r.y & 0xffff0000u));
+  }
+  static __device__ __forceinline__ float ld1(const __nv_bfloat16* p) {
+    return __uint_as_float((uint32_t)__bfloat16_as_ushort(__ldg(p)) << 16);
+  }
+};
+
+// Shard of one CTA, in granules of four elements of the aligned view of the row: granule g covers
+// row elements 4g-a .. 4g-a+3, where a in 0..3 is the row's misalignment in elements.
+template <class T>
 struct Shard {
-  const float* gbase;  // 16-byte aligned address of granule 0
+  const T* gbase;      // granule-aligned address of granule 0
   int g0, g1;          // granule range of this CTA
   int i0, i1;          // the part of [g0, g1) whose granules lie completely inside the row
   int a;               // misalignment (elements)
@@ -118,20 +156,22 @@ struct Shard {
 // A granule that straddles the start or the end of the row (at most two per row): scalar loads of
 // the elements that belong to the row, `fill` elsewhere. Kept out of line so that the streaming
 // loops stay small enough to unroll with every load in flight.
-__device__ __noinline__ float4 load_granule_partial(const float* gbase, int a, int len, int g, float fill) {
+template <class T>
+__device__ __noinline__ float4 load_granule_partial(const T* gbase, int a, int len, int g, float fill) {
   const int i0 = 4 * g - a;
   float4 x = make_float4(fill, fill, fill, fill);
-  const float* p = gbase + 4 * (int64_t)g;
-  if ((unsigned)(i0 + 0) < (unsigned)len) x.x = __ldg(p + 0);
-  if ((unsigned)(i0 + 1) < (unsigned)len) x.y = __ldg(p + 1);
-  if ((unsigned)(i0 + 2) < (unsigned)len) x.z = __ldg(p + 2);
-  if ((unsigned)(i0 + 3) < (unsigned)len) x.w = __ldg(p + 3);
+  const T* p = gbase + 4 * (int64_t)g;
+  if ((unsigned)(i0 + 0) < (unsigned)len) x.x = Elem<T>::ld1(p + 0);
+  if ((unsigned)(i0 + 1) < (unsigned)len) x.y = Elem<T>::ld1(p + 1);
+  if ((unsigned)(i0 + 2) < (unsigned)len) x.z = Elem<T>::ld1(p + 2);
+  if ((unsigned)(i0 + 3) < (unsigned)len) x.w = Elem<T>::ld1(p + 3);
   return x;
 }
 
 // One granule from global memory; reads only bytes that belong to the row.
-__device__ __forceinline__ float4 load_granule(const Shard& sh, int g, float fill) {
-  if (g >= sh.i0 && g < sh.i1) return __ldg(reinterpret_cast<const float4*>(sh.gbase) + g);
+template <class T>
+__device__ __forceinline__ float4 load_granule(const Shard<T>& sh, int g, float fill) {
+  if (g >= sh.i0 && g < sh.i1) return Elem<T>::ld4(sh.gbase, g);
   return load_granule_partial(sh.gbase, sh.a, sh.len, g, fill);
 }
 
@@ -174,17 +214,16 @@ __device__ __noinline__ void spill_push(Ctrl* ctrl, uint64_t* spill, uint32_t sp
 // the warp each time). Candidates beyond the segment's capacity go to the shared spill area.
 // Returns the number of candidates the warp found (those beyond seg_cap went to the spill area);
 // kmax is the largest key among the entries this lane converted; post(key) is called for each of them.
-template <int NT, int U, bool kStage, class Post>
-__device__ __forceinline__ uint32_t filter_shard(const Shard& sh, float edge, uint64_t* seg, uint32_t seg_cap, Ctrl* ctrl,
+template <int NT, int U, bool kStage, class T, class Post>
+__device__ __forceinline__ uint32_t filter_shard(const Shard<T>& sh, float edge, uint64_t* seg, uint32_t seg_cap, Ctrl* ctrl,
                                                  uint64_t* spill, uint32_t spill_cap, uint32_t& kmax, Post&& post) {
   const int tid = threadIdx.x;
   const int lane = tid & 31;
   const unsigned lt = (1u << lane) - 1u;
   const float ninf = __uint_as_float(0xff800000u);
-  const float4* base4 = reinterpret_cast<const float4*>(sh.gbase);
+  const T* gbase = sh.gbase;
   const int fa = sh.a, fi1 = sh.i1, len = sh.len;
   uint32_t wcnt = 0;  // candidates of this warp so far (warp-uniform)
-  const uint32_t* base1 = reinterpret_cast<const uint32_t*>(sh.gbase);
   uint32_t* seg32 = reinterpret_cast<uint32_t*>(seg);  // staging: candidate j's row index in word j
   auto keep = [&](bool has, int idx) {  // called by the whole warp
     const unsigned b = __ballot_sync(kFull, has);
@@ -193,7 +232,7 @@ __device__ __forceinline__ uint32_t filter_shard(const Shard& sh, float edge, ui
       if (kStage && pos < seg_cap) {
         seg32[pos] = (uint32_t)idx;
       } else {
-        const uint64_t raw = ((uint64_t)__ldg(base1 + idx + fa) << 32) | (uint64_t)(uint32_t)idx;
+        const uint64_t raw = ((uint64_t)__float_as_uint(Elem<T>::ld1(gbase + idx + fa)) << 32) | (uint64_t)(uint32_t)idx;
         if (pos < seg_cap) {
           seg[pos] = raw;
         } else {
@@ -212,11 +251,11 @@ __device__ __forceinline__ uint32_t filter_shard(const Shard& sh, float edge, ui
     for (int u = 0; u < U; ++u) {
       const int g = gb + u * NT + tid;
       if constexpr (decltype(full)::value) {
-        x[u] = __ldg(base4 + g);
+        x[u] = Elem<T>::ld4(gbase, g);
       } else {
         x[u] = make_float4(ninf, ninf, ninf, ninf);
         if (g < fi1) {
-          x[u] = __ldg(base4 + g);
+          x[u] = Elem<T>::ld4(gbase, g);
         } else {
           vmask &= ~((Mask)0xfu << (4 * u));  // (padding would pass an edge of -inf)
         }
@@ -276,7 +315,7 @@ __device__ __forceinline__ uint32_t filter_shard(const Shard& sh, float edge, ui
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
         if (!FFTOPK_CHECK(7, idx[u], len, ctrl_status(ctrl))) idx[u] = 0u;
-        bits[u] = __ldg(base1 + idx[u] + fa);  // (index 0 is always readable)
+        bits[u] = __float_as_uint(Elem<T>::ld1(gbase + idx[u] + fa));  // (index 0 is always readable)
       }
       __syncwarp();
 #pragma unroll
@@ -303,10 +342,10 @@ __device__ __forceinline__ uint32_t filter_shard(const Shard& sh, float edge, ui
 // Visit every valid element of the shard: op(key, idx). Interior granules are read with
 // unconditional 128-bit loads, four in flight per thread; the at most two granules that straddle
 // the row's ends are visited by one thread each through scalar loads.
-template <int NT, class Op>
-__device__ __forceinline__ void scan_shard(const Shard& sh, Op&& op) {
+template <int NT, class T, class Op>
+__device__ __forceinline__ void scan_shard(const Shard<T>& sh, Op&& op) {
   const int tid = threadIdx.x;
-  const float4* base4 = reinterpret_cast<const float4*>(sh.gbase);
+  const T* gbase = sh.gbase;
   const int a = sh.a, i1 = sh.i1;
   constexpr int U = 4;
   for (int gb = sh.i0; gb < i1; gb += NT * U) {
@@ -315,7 +354,7 @@ __device__ __forceinline__ void scan_shard(const Shard& sh, Op&& op) {
     for (int u = 0; u < U; ++u) {
       const int g = gb + u * NT + tid;
       x[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (g < i1) x[u] = __ldg(base4 + g);
+      if (g < i1) x[u] = Elem<T>::ld4(gbase, g);
     }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
@@ -497,10 +536,10 @@ __device__ __forceinline__ DualPick cluster_pick_dual(cg::cluster_group& cluster
 }
 
 // Everything one CTA needs to know about its row and its shared memory.
-template <int NT>
+template <int NT, class T>
 struct RowCtx {
   int C, rank;
-  Shard sh;
+  Shard<T> sh;
   uint32_t* hist0;  // two histograms of kMaxBins words, back to back
   uint32_t* sup0;   // three super-bin arrays of kSup words, back to back
   // (computed addresses instead of pointer arrays: indexing an array member with the round number
@@ -523,8 +562,8 @@ struct RowCtx {
   uint32_t k;  // elements to select per row (2048 for the reference's op)
 };
 
-template <int NT>
-__device__ __forceinline__ void emit_winner(const RowCtx<NT>& cx, uint32_t base_w, uint32_t key, int idx) {
+template <class Cx>
+__device__ __forceinline__ void emit_winner(const Cx& cx, uint32_t base_w, uint32_t key, int idx) {
   const uint32_t pos = base_w + warp_alloc(&cx.ctrl->wslot);
   if (FFTOPK_CHECK(1, pos, cx.k, cx.status) && pos < cx.k) {
     cx.out_idx[pos] = cx.page ? __ldg(cx.page + idx) : idx + cx.idx_offset;
@@ -538,13 +577,13 @@ __device__ __forceinline__ void emit_winner(const RowCtx<NT>& cx, uint32_t base_
 // would overflow, threshold bins larger than rank 0's buffer, rows of identical values.
 // Returns the final mode; `need`, `P` and `r` describe where it stopped.
 // -----------------------------------------------------------------------------------------
-template <int NT>
-__device__ __forceinline__ int refine_from_data(RowCtx<NT>& cx, uint32_t& need, uint32_t& P, int& r, int& pick_no) {
+template <int NT, class T>
+__device__ __forceinline__ int refine_from_data(RowCtx<NT, T>& cx, uint32_t& need, uint32_t& P, int& r, int& pick_no) {
   cg::cluster_group cluster = cg::this_cluster();
   const int tid = threadIdx.x;
   const int lane = tid & 31, warp = tid >> 5;
   const int C = cx.C, rank = cx.rank;
-  const Shard& sh = cx.sh;
+  const Shard<T>& sh = cx.sh;
   Ctrl* ctrl = cx.ctrl;
   uint32_t* xch = cx.xch;
 
@@ -569,7 +608,7 @@ __device__ __forceinline__ int refine_from_data(RowCtx<NT>& cx, uint32_t& need, 
   __syncthreads();
   {
     uint32_t* h0 = cx.hist(0);
-    scan_shard<NT>(sh, [&](uint32_t key, int) { hist_add(h0, key >> 20, true); });
+    scan_shard<NT, T>(sh, [&](uint32_t key, int) { hist_add(h0, key >> 20, true); });
   }
   __syncthreads();
 
@@ -617,10 +656,10 @@ __device__ __forceinline__ int refine_from_data(RowCtx<NT>& cx, uint32_t& need, 
       const int shift2 = round_shift(r + 1);
       const uint32_t mask2 = (1u << round_width(r + 1)) - 1u;
       uint32_t* h2 = cx.hist((r + 1) & 1);
-      scan_shard<NT>(sh, [&](uint32_t key, int idx) {
+      scan_shard<NT, T>(sh, [&](uint32_t key, int idx) {
         const uint32_t hh = key >> shift;
         if ((hh >> w) == Pold) {
-          if (hh > Pn) emit_winner<NT>(cx, base_w, key, idx);
+          if (hh > Pn) emit_winner(cx, base_w, key, idx);
           hist_add(h2, (key >> shift2) & mask2, hh == Pn);
         }
       });
@@ -628,11 +667,11 @@ __device__ __forceinline__ int refine_from_data(RowCtx<NT>& cx, uint32_t& need, 
       continue;
     }
     if (mode == kModeGather) {
-      scan_shard<NT>(sh, [&](uint32_t key, int idx) {
+      scan_shard<NT, T>(sh, [&](uint32_t key, int idx) {
         const uint32_t hh = key >> shift;
         if ((hh >> w) == Pold) {
           if (hh > Pn) {
-            emit_winner<NT>(cx, base_w, key, idx);
+            emit_winner(cx, base_w, key, idx);
           } else if (hh == Pn) {
             const uint32_t slot = base_c + warp_alloc(&ctrl->cslot);
             if (FFTOPK_CHECK(2, slot, cx.cand_cap, cx.status) && slot < (uint32_t)cx.cand_cap)
@@ -641,15 +680,15 @@ __device__ __forceinline__ int refine_from_data(RowCtx<NT>& cx, uint32_t& need, 
         }
       });
     } else if (mode == kModeTakeAll) {
-      scan_shard<NT>(sh, [&](uint32_t key, int idx) {
+      scan_shard<NT, T>(sh, [&](uint32_t key, int idx) {
         const uint32_t hh = key >> shift;
-        if (((hh >> w) == Pold) && hh >= Pn) emit_winner<NT>(cx, base_w, key, idx);
+        if (((hh >> w) == Pold) && hh >= Pn) emit_winner(cx, base_w, key, idx);
       });
     } else {  // kModeTies: all 32 key bits are fixed; Pn is the threshold key itself
       // (only keys under this round's prefix: larger prefixes were written by the earlier rounds,
       // and the slots reserved here are for this round's winners alone)
-      scan_shard<NT>(sh, [&](uint32_t key, int idx) {
-        if ((key >> w) == Pold && key > Pn) emit_winner<NT>(cx, base_w, key, idx);
+      scan_shard<NT, T>(sh, [&](uint32_t key, int idx) {
+        if ((key >> w) == Pold && key > Pn) emit_winner(cx, base_w, key, idx);
       });
       // Exact duplicates of the threshold key: the first `need` of them in index order win.
       // Shards are contiguous and ordered by rank, so this CTA takes its first `quota`.
@@ -708,9 +747,9 @@ __device__ __forceinline__ int refine_from_data(RowCtx<NT>& cx, uint32_t& need, 
 #endif
 // kAnyK = false: k is the constant 2048 of the reference's op (the compiler folds it: one register
 // less in a kernel that sits at its register limit); true: k comes from the parameters.
-template <int NT, bool kAnyK, bool kWarm = false>
+template <int NT, bool kAnyK, bool kWarm = false, class T = float>
 __device__ __forceinline__ void select_row(const SelectParams& p) {
-  RowCtx<NT> cx;
+  RowCtx<NT, T> cx;
   cg::cluster_group cluster = cg::this_cluster();
   const int C = cx.C = (int)cluster.num_blocks();
   const int rank = cx.rank = (int)cluster.block_rank();
@@ -731,7 +770,7 @@ __device__ __forceinline__ void select_row(const SelectParams& p) {
   len64 = len64 < 0 ? 0 : len64;
   len64 = len64 > p.L - row_start ? p.L - row_start : len64;
   const int len = (int)len64;
-  const float* rowp = p.score + (int64_t)row * p.row_stride + row_start;
+  const T* rowp = static_cast<const T*>(p.score) + (int64_t)row * p.row_stride + row_start;
   const int64_t cp_shift = p.cp_flag ? (int64_t)((__ldcg(p.cp_flag) + 1u) & 1u) * p.cp_half_words : 0;
   const uint32_t K = cx.k = kAnyK ? (uint32_t)p.k : (uint32_t)kK;
   int32_t* out_idx = cx.out_idx = p.out_idx + cp_shift + (int64_t)row * K;
@@ -761,7 +800,7 @@ __device__ __forceinline__ void select_row(const SelectParams& p) {
     if (rank == 0) {
       for (int i = tid; i < (int)K; i += NT) {
         out_idx[i] = i < len ? (cx.page ? __ldg(cx.page + i) : i + cx.idx_offset) : -1;
-        if (out_key) out_key[i] = i < len ? fftopk_key_from_bits(__float_as_uint(__ldg(rowp + i))) : 0u;
+        if (out_key) out_key[i] = i < len ? fftopk_key_from_bits(__float_as_uint(Elem<T>::ld1(rowp + i))) : 0u;
       }
       if constexpr (kWarm) {
         if (tid == 0 && p.next_threshold) p.next_threshold[row] = 0u;  // nothing to guess for such a row
@@ -785,8 +824,8 @@ __device__ __forceinline__ void select_row(const SelectParams& p) {
   uint64_t* list = cx.list;
 
   // ---- shard geometry --------------------------------------------------------------------
-  Shard& sh = cx.sh;
-  sh.a = (int)((reinterpret_cast<uintptr_t>(rowp) >> 2) & 3u);
+  Shard<T>& sh = cx.sh;
+  sh.a = (int)((reinterpret_cast<uintptr_t>(rowp) / sizeof(T)) & 3u);
   sh.len = len;
   sh.gbase = rowp - sh.a;
   const int gn = (sh.a + len + 3) >> 2;
@@ -871,13 +910,12 @@ __device__ __forceinline__ void select_row(const SelectParams& p) {
     if (C > 1) cluster.barrier_arrive();
   } else {
   {
-    const float4* base4 = reinterpret_cast<const float4*>(sh.gbase);
     if (exact) {
 #pragma unroll
       for (int j = 0; j < kRegSlabs; ++j) {
         const int g = sh.g0 + j * NT + tid;
         if (g < sh.g1) gr[j] = g;
-        if (g >= sh.i0 && g < sh.i1) xr[j] = __ldg(base4 + g);
+        if (g >= sh.i0 && g < sh.i1) xr[j] = Elem<T>::ld4(sh.gbase, g);
       }
     } else {
       // ns slabs per warp: small clusters of small CTAs sample more per thread, so that a row
@@ -894,7 +932,7 @@ __device__ __forceinline__ void select_row(const SelectParams& p) {
             g = sh.g0 + j * NT + tid;
           }
           if (g < sh.g1) gr[j] = g;
-          if (g >= sh.i0 && g < sh.i1) xr[j] = __ldg(base4 + g);
+          if (g >= sh.i0 && g < sh.i1) xr[j] = Elem<T>::ld4(sh.gbase, g);
         }
       }
     }
@@ -1099,7 +1137,7 @@ __device__ __forceinline__ void select_row(const SelectParams& p) {
               const uint32_t key = fftopk_key_from_bits(__float_as_uint(xv[e]));
               const uint32_t bin = key >> 20;
               if (bin > t || (take_eq && bin == t)) {
-                emit_winner<NT>(cx, base_w, key, i0 + e);
+                emit_winner(cx, base_w, key, i0 + e);
               } else if (bin == t) {
                 const uint32_t slot = base_c + warp_alloc(&ctrl->cslot);
                 if (FFTOPK_CHECK(2, slot, p.cand_cap, p.status) && slot < (uint32_t)p.cand_cap)
@@ -1176,7 +1214,7 @@ __device__ __forceinline__ void select_row(const SelectParams& p) {
     }
   }
 
-  if (mode == kModeFallback) mode = refine_from_data<NT>(cx, need, P, r, pick_no);
+  if (mode == kModeFallback) mode = refine_from_data<NT, T>(cx, need, P, r, pick_no);
 
   // Candidates that peers pushed into rank 0 are complete after a cluster barrier. The sampled
   // path has had that barrier already (#2) and only needs one more so that rank 0 outlives the
@@ -1229,9 +1267,9 @@ __device__ __forceinline__ void select_row(const SelectParams& p) {
   if (tid == 0 && p.status && mode == kModeAbort) atomicOr(p.status, (uint32_t)FFTOPK_ST_INTERNAL);
 }
 
-template <int NT, bool kAnyK = false, bool kWarm = false>
+template <int NT, bool kAnyK = false, bool kWarm = false, class T = float>
 __global__ void __launch_bounds__(NT, (NT == 512 ? FFTOPK_CTAS_512 : 1024 / NT)) select2048_kernel(const SelectParams p) {
-  select_row<NT, kAnyK, kWarm>(p);
+  select_row<NT, kAnyK, kWarm, T>(p);
   if (p.cp_publish) {
     // Context-parallel publication folded into the selection: every thread fences its output
     // writes, the CTA arrives, and the last CTA of the grid releases the epoch flag system-wide
@@ -1391,6 +1429,15 @@ int setup_kernel(int smem_optin) {
   e = cudaFuncSetAttribute(select2048_kernel<NT, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
   if (e != cudaSuccess) return cuda_fail(e);
   if constexpr (NT >= 512) {
+    e = cudaFuncSetAttribute(select2048_kernel<NT, true, false, __half>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_optin);
+    if (e != cudaSuccess) return cuda_fail(e);
+    e = cudaFuncSetAttribute(select2048_kernel<NT, true, false, __half>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    if (e != cudaSuccess) return cuda_fail(e);
+    e = cudaFuncSetAttribute(select2048_kernel<NT, true, false, __nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             smem_optin);
+    if (e != cudaSuccess) return cuda_fail(e);
+    e = cudaFuncSetAttribute(select2048_kernel<NT, true, false, __nv_bfloat16>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    if (e != cudaSuccess) return cuda_fail(e);
     e = cudaFuncSetAttribute(select2048_kernel<NT, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_optin);
     if (e != cudaSuccess) return cuda_fail(e);
     e = cudaFuncSetAttribute(select2048_kernel<NT, false, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
@@ -1556,7 +1603,8 @@ int launch_select(const SelectCall& c) {
   if (c.B < 0 || c.L < 0 || c.row_stride < 0 || c.k < 1 || c.k > kMaxK) return FFTOPK_EINVAL;
   if (c.B == 0) return FFTOPK_OK;
   if (!c.score || !c.lengths || !c.out_idx) return FFTOPK_EINVAL;
-  if ((reinterpret_cast<uintptr_t>(c.score) & 3u) != 0) return FFTOPK_EINVAL;
+  const bool half_width = c.dtype != kDtypeF32;
+  if ((reinterpret_cast<uintptr_t>(c.score) & (half_width ? 1u : 3u)) != 0) return FFTOPK_EINVAL;
   if (c.L > (int64_t)0x7fffffff - 8 || (int64_t)c.B * kMaxCluster > (int64_t)0x7fffffff) return FFTOPK_ERANGE;
   DeviceInfo* d = nullptr;
   int rc = device_info(&d);
@@ -1564,6 +1612,7 @@ int launch_select(const SelectCall& c) {
   const Tuning tn = tuning_snapshot();
   const bool overlap = tn.overlap != 0 && c.may_overlap;
   Plan pl = make_plan(*d, tn, overlap, c.B, c.L);
+  if (half_width && pl.threads < 512) pl.threads = 512;  // (the 16-bit kernels exist for 512 and 1024 threads)
   if (c.k > kK && pl.cluster == 1 && tn.list_cap <= 0) {
     // more winners than the lone-CTA list was sized for: the long-row list
     pl.list_cap = pl.cand_cap = kOverlapListCap1Long;
@@ -1621,7 +1670,16 @@ int launch_select(const SelectCall& c) {
   }
   cudaError_t e;
   const bool any_k = c.k != kK;
-  if (warm) {
+  if (half_width) {
+    if (warm || c.src_page_table || c.cp_flag || c.cp_publish) return FFTOPK_EINVAL;
+    if (c.dtype == kDtypeF16) {
+      e = pl.threads == 1024 ? cudaLaunchKernelEx(&cfg, select2048_kernel<1024, true, false, __half>, p)
+                             : cudaLaunchKernelEx(&cfg, select2048_kernel<512, true, false, __half>, p);
+    } else {
+      e = pl.threads == 1024 ? cudaLaunchKernelEx(&cfg, select2048_kernel<1024, true, false, __nv_bfloat16>, p)
+                             : cudaLaunchKernelEx(&cfg, select2048_kernel<512, true, false, __nv_bfloat16>, p);
+    }
+  } else if (warm) {
     e = pl.threads == 1024 ? cudaLaunchKernelEx(&cfg, select2048_kernel<1024, false, true>, p)
                            : cudaLaunchKernelEx(&cfg, select2048_kernel<512, false, true>, p);
   } else if (pl.threads == 1024) {

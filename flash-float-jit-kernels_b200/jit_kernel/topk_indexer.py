@@ -205,12 +205,9 @@ def fast_topk_general(
     return out
 
 
-_widen_workspaces = {}
-
-
 def _fast_topk_16bit(score, lengths, topk, row_starts):
-    """fp16 / bf16 scores (fftopk_select_topk_16bit): widened to fp32 in a cached workspace, then
-    the fp32 selector. Functional, not tuned."""
+    """fp16 / bf16 scores (fftopk_select_topk_16bit): the selector instantiated on the 16-bit type;
+    rows are read once in their own width and widened to fp32 in registers."""
     if score.stride(1) != 1 and score.size(0) and score.size(1):
         raise RuntimeError("score must have unit inner stride")
     if lengths.dtype != torch.int32 or not lengths.is_cuda or lengths.numel() != score.size(0) or not lengths.is_contiguous():
@@ -223,19 +220,12 @@ def _fast_topk_16bit(score, lengths, topk, row_starts):
     if B == 0:
         return out
     lib = _native.lib()
-    nbytes = int(lib.fftopk_widen_workspace_bytes(B, L))
-    key = (score.device, B, L)
-    ws = _widen_workspaces.get(key)
-    if ws is None or ws.numel() < nbytes + 256:
-        ws = torch.empty(nbytes + 256, dtype=torch.uint8, device=score.device)
-        _widen_workspaces[key] = ws
-    base = (ws.data_ptr() + 255) & ~255
     with torch.cuda.device(score.device):
         stream = torch.cuda.current_stream(score.device)
         rc = lib.fftopk_select_topk_16bit(score.data_ptr(), 0 if score.dtype == torch.float16 else 1,
                                           score.stride(0) if B > 1 else max(score.stride(0), 0), B, L, lengths.data_ptr(),
                                           None if row_starts is None else row_starts.data_ptr(), topk, out.data_ptr(),
-                                          base, nbytes, _status_word(score.device).data_ptr(), stream.cuda_stream)
+                                          None, 0, _status_word(score.device).data_ptr(), stream.cuda_stream)
     _native.check(rc, "fftopk_select_topk_16bit")
     _after_launch(score.device, "fftopk_select_topk_16bit")
     return out

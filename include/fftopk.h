@@ -267,11 +267,13 @@ int fftopk_topk2048_sliced_noalloc(const float* score, int64_t row_stride, int32
 
 /*
  * fftopk_select_topk for fp16 or bf16 scores (the reference's op takes fp32 only: CHECK of the
- * dtype, topk_indexer_radix.cu:1003-1016). Functional, not tuned: the rows' valid ranges are
- * widened to fp32 - exact and order-preserving - into the caller's workspace
- * (fftopk_widen_workspace_bytes(B, L) bytes of device memory, 256-byte aligned), then the fp32
- * selector runs on it, so a 16-bit row costs about as much HBM traffic as five reads of it.
- * row_stride is in elements. B <= 65535.
+ * dtype, topk_indexer_radix.cu:1003-1016; it sketches a 16-bit key map and leaves it disabled,
+ * :192-195). The same kernel instantiated on the 16-bit type: the row is read ONCE, in its own
+ * width (8-byte granules of four elements), and every element is widened to fp32 - exactly and
+ * order-preserving - in registers, so keys, ties and results are those of the fp32 selector on the
+ * widened values. row_stride is in elements; score16 must be 2-byte aligned.
+ * d_workspace / workspace_bytes are ignored and may be NULL / 0 (an earlier form of this entry
+ * point staged fp32 copies of the rows there; fftopk_widen_workspace_bytes now returns 0).
  */
 #define FFTOPK_DTYPE_FP16 0
 #define FFTOPK_DTYPE_BF16 1

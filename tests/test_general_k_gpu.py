@@ -104,3 +104,52 @@ def test_16bit_scores(dtype, k):
     torch.cuda.synchronize()
     orc.check_result(s1.to(dtype).to(torch.float32).numpy(), l1.numpy(), got.cpu().numpy(), None, k, None, f"{dtype} decode")
     assert kernel_status() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("cluster", [1, 2, 8, 16])
+def test_16bit_every_path(dtype, cluster):
+    """The 16-bit instantiation of the kernel on every path: register-resident and sampled rows,
+    the full-histogram path, exact ties taken in index order, special values, every misalignment
+    of the row start, rows of at most k elements."""
+    dev = torch.device("cuda", 0)
+    _native.set_tuning(cluster_ctas=cluster)
+    try:
+        g = torch.Generator().manual_seed(cluster)
+        s = torch.randn(6, 90001, generator=g)
+        s[0, ::3] = 0.0
+        s[0, 1::5] = -0.0
+        s[0, 11::501] = float("inf")
+        s[0, 13::499] = float("-inf")
+        s[0, 17::1009] = float("nan")
+        s[1] = 2.5  # all equal: the first k indices win
+        s[2, :] = (torch.arange(90001) % 97).to(torch.float32)  # 97 values, thousands of ties at the threshold
+        ln = torch.tensor([90001, 80000, 70001, 2048, 2049, 300], dtype=torch.int32)
+        s16 = s.to(dtype)
+        for k in (2048, 100, 4096):
+            got = fast_topk_general(s16.to(dev), ln.to(dev), k)
+            torch.cuda.synchronize()
+            orc.check_result(s16.to(torch.float32).numpy(), ln.numpy(), got.cpu().numpy(), None, k, None,
+                             f"{dtype} C={cluster} k={k}")
+        # long rows (the sampled path on every cluster size), bf16-/fp16-rounded heavy ties
+        s1, l1 = workloads.c5(B=2, L=500000)
+        got = fast_topk_general(s1.to(dtype).to(dev), l1.to(dev), 2048)
+        orc.check_result(s1.to(dtype).to(torch.float32).numpy(), l1.numpy(), got.cpu().numpy(), None, 2048, None,
+                         f"{dtype} C={cluster} long")
+        # every misalignment of the row start relative to the 8-byte granule
+        wide = torch.randn(2, 30016, generator=g).to(dtype)
+        wd = wide.to(dev)
+        for off in range(8):
+            view = wd[:, off:off + 30000]
+            ln3 = torch.tensor([30000, 29999 - off], dtype=torch.int32)
+            got = fast_topk_general(view, ln3.to(dev), 2048)
+            orc.check_result(wide[:, off:off + 30000].to(torch.float32).contiguous().numpy(), ln3.numpy(),
+                             got.cpu().numpy(), None, 2048, None, f"{dtype} C={cluster} offset {off}")
+        # the full-histogram path
+        _native.set_tuning(cluster_ctas=cluster, force_full_histogram=True)
+        got = fast_topk_general(s16.to(dev), ln.to(dev), 2048)
+        orc.check_result(s16.to(torch.float32).numpy(), ln.numpy(), got.cpu().numpy(), None, 2048, None,
+                         f"{dtype} C={cluster} full histogram")
+        assert kernel_status() == 0
+    finally:
+        _native.set_tuning()

@@ -1,7 +1,7 @@
 """Throughput mode (fftopk_set_overlap(1)) around the entry points that enqueue a producer kernel
-of their own before the selection: host buffers (gather kernel -> select), 16-bit scores (widen
-kernel -> select), column slices without allocation (slice lengths -> selects -> merge) and the
-context-parallel publication (select -> publish -> merge). Their selections must keep plain stream
+of their own before the selection: host buffers (gather kernel -> select), column slices without
+allocation (slice lengths -> selects -> merge) and the context-parallel publication (select ->
+merge); 16-bit scores, which have no producer any more, run overlapped like plain calls. Their selections must keep plain stream
 order whatever the process-wide switch says: a programmatic dependent launch that never waits for
 its predecessor would have no guarantee of seeing the producer's writes. Every path runs several
 calls back to back on DIFFERENT data through the same staging memory, with the switch on, and is
@@ -57,7 +57,7 @@ def test_host_buffer_entry_with_overlap_on():
 def test_16bit_entry_with_overlap_on(dtype):
     dev = torch.device("cuda", 0)
     batches = [(s.to(dtype), ln) for s, ln in _batches(4, 16, 40000, 200)]
-    outs = [fast_topk_general(s.to(dev), ln.to(dev), K) for s, ln in batches]  # one shared workspace
+    outs = [fast_topk_general(s.to(dev), ln.to(dev), K) for s, ln in batches]
     torch.cuda.synchronize()
     for (s, ln), out in zip(batches, outs):
         orc.check_result(s.to(torch.float32).numpy(), ln.numpy(), out.cpu().numpy(), what=f"{dtype}, overlap on")
