@@ -33,6 +33,9 @@ kept as `cold_start_ms_per_step`.
              L2 read bandwidth measured with the library's probe) and with rotated buffers
   decode_loop  B=1, one logit appended per step: us per step cold and with the warm start that carries
              the previous step's threshold (fast_topk_v3_warm)
+  fused_indexer  B=1: indexer logits on the tensor cores fused with the selection
+             (fftopk_indexer_topk2048), us per call with and without a threshold guess, GB/s of
+             key cache read against the HBM peak
   large_batch  one serialised call at B=256 and B=512 of the same ragged distribution: the rate a
              single call reaches when the batch alone fills the device
   context_parallel  (N > 1) config 5 through the three context-parallel variants: first checked
@@ -368,6 +371,61 @@ def decode_loop_leg(dev, stream):
     return out
 
 
+def indexer_leg(dev, stream, peak_gbs):
+    """The step in front of the selector, fused with it (fftopk_indexer_topk2048): B=1 decode rows,
+    bf16 q [64, 128] and key cache [L, 128]. us per call with a standing threshold guess (logits
+    filtered in the tensor-core kernel's epilogue, never written) and without one (logits written,
+    selector on them), beside torch's own einsum + relu + weighted sum for the logits alone. The
+    roofline of the producer is reading the key cache once: 256 B per key."""
+    from jit_kernel.indexer import FusedIndexerTopk, reference_logits
+
+    out = {}
+    for L in (131072, 1048576):
+        g = torch.Generator(device="cpu").manual_seed(L)
+        q = torch.randn(1, 64, 128, generator=g).to(torch.bfloat16).to(dev)
+        nbuf = max(2, (300 << 20) // (L * 256) + 1)  # rotate key caches over more than L2
+        ks = [torch.randn(1, L, 128, generator=g).to(torch.bfloat16).to(dev) for _ in range(nbuf)]
+        w = torch.rand(1, 64, generator=g).to(dev)
+        ln = torch.full((1,), L, dtype=torch.int32, device=dev)
+        fs = [FusedIndexerTopk(1, L, dev) for _ in range(nbuf)]  # one threshold state per cache
+        res = torch.empty(1, K, dtype=torch.int32, device=dev)
+        with torch.cuda.stream(stream):
+            for f, k in zip(fs, ks):
+                f(q, k, w, ln, out=res)  # seeds the thresholds (and sets kernel attributes)
+        stream.synchronize()
+        n = 2 * nbuf
+        r = {"key_cache_bytes": L * 256, "rotated_caches": nbuf}
+        for name in ("warm", "cold"):
+            def call(i):
+                f = fs[i % nbuf]
+                if name == "cold":
+                    f.thresholds.zero_()
+                f(q, ks[i % nbuf], w, ln, out=res)
+            with torch.cuda.stream(stream):
+                call(0)
+            stream.synchronize()
+            gr = capture_steps(call, n, stream)
+            ts = sorted(time_graph(gr, stream) / n * 1e6 for _ in range(9))
+            r[name + "_us_per_call"] = ts[len(ts) // 2]
+            del gr
+            if name == "cold":  # leave the states warm again
+                with torch.cuda.stream(stream):
+                    for f, k in zip(fs, ks):
+                        f(q, k, w, ln, out=res)
+                stream.synchronize()
+        r["warm_gbs"] = L * 256 / r["warm_us_per_call"] / 1e3
+        r["warm_frac_hbm"] = r["warm_gbs"] / peak_gbs
+        with torch.cuda.stream(stream):
+            reference_logits(q, ks[0], w)
+        stream.synchronize()
+        gr = capture_steps(lambda i: reference_logits(q, ks[i % nbuf], w), nbuf, stream)
+        ts = sorted(time_graph(gr, stream) / nbuf * 1e6 for _ in range(5))
+        r["torch_logits_only_us"] = ts[len(ts) // 2]
+        out[str(L)] = r
+        del ks, fs, gr
+    return out
+
+
 def large_batch_leg(dev, stream, fast_topk, peak_gbs):
     """One serialised call (default launch mode, no overlap between calls) on a batch large enough
     to fill the device by itself: B=256 and B=512 rows of the bench's ragged distribution, inputs
@@ -694,6 +752,7 @@ def ours_arm(args, rank: int, local_rank: int, world: int) -> None:
         line["p50_us_B1_L1M"] = line["latency"]["1048576"]["warm"]["p50_us"]
         line["large_batch"] = large_batch_leg(dev, stream, fast_topk, peak)
         line["decode_loop"] = decode_loop_leg(dev, stream)
+        line["fused_indexer"] = indexer_leg(dev, stream, peak)
         # CPU baseline on this box's host cores, bounded: the 64-row batch a few times (~20 ms each)
         cpu_reps = 10
         cpu_sec = time_cpu(score, lengths, cpu_reps, 2)
@@ -715,7 +774,8 @@ def profile_case(name: str) -> None:
     throughput plan / the default plan, 12 launches over 8 rotated inputs. f16: the same batch as
     fp16 scores through the 16-bit instantiation. host: three calls of the host-buffer entry point
     (gather kernel reading pinned memory, selection). probe: the read-bandwidth probe on a 4 MiB and
-    a 1 GiB buffer."""
+    a 1 GiB buffer. indexer: eight calls of the fused indexer at B=1, L=1M over two rotated key
+    caches (the last six with a threshold guess)."""
     from jit_kernel import _native
     from jit_kernel.distributed import _cuda_select, local_lengths, merge_candidates
     from jit_kernel.topk_indexer import fast_topk, fast_topk_general, fast_topk_v3_host, fast_topk_v3_warm
@@ -759,6 +819,19 @@ def profile_case(name: str) -> None:
             fast_topk_v3_host(hs, hl, K, out=ho)
         torch.cuda.synchronize()
         print(json.dumps({"case": "host", "launches": 3}))
+    elif name == "indexer":
+        from jit_kernel.indexer import FusedIndexerTopk
+        L = 1 << 20
+        g = torch.Generator(device="cpu").manual_seed(L)
+        q = torch.randn(1, 64, 128, generator=g).to(torch.bfloat16).to(dev)
+        ks = [torch.randn(1, L, 128, generator=g).to(torch.bfloat16).to(dev) for _ in range(2)]  # 2 x 256 MiB > L2
+        w = torch.rand(1, 64, generator=g).to(dev)
+        ln = torch.full((1,), L, dtype=torch.int32, device=dev)
+        fs = [FusedIndexerTopk(1, L, dev) for _ in range(2)]
+        for i in range(8):  # calls 0 and 1 seed the thresholds, the rest run with a guess
+            fs[i % 2](q, ks[i % 2], w, ln)
+        torch.cuda.synchronize()
+        print(json.dumps({"case": "indexer", "calls": 8, "L": L}))
     elif name == "probe":
         stream = torch.cuda.Stream(device=dev)
         print(json.dumps({"case": "probe", "read_gbs": measure_l2_read_gbs(dev, stream)}))
@@ -781,7 +854,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=50)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip the latency sweep and the CPU baseline")
-    ap.add_argument("--case", default=None, choices=["b1", "warm", "merge", "tp", "serial", "f16", "host", "probe"], help="run one small fixed case (for profilers)")
+    ap.add_argument("--case", default=None, choices=["b1", "warm", "merge", "tp", "serial", "f16", "host", "probe", "indexer"], help="run one small fixed case (for profilers)")
     args = ap.parse_args()
     if args.case:
         profile_case(args.case)

@@ -20,7 +20,7 @@ ROOT = Path(__file__).resolve().parent
 CSRC = ROOT / "csrc"
 LIB_DIR = ROOT / "lib"
 LIB_PATH = LIB_DIR / "libfftopk.so"
-SOURCES = [CSRC / "fftopk_select.cu", CSRC / "fftopk_cp.cu", CSRC / "fftopk_hostio.cu"]
+SOURCES = [CSRC / "fftopk_select.cu", CSRC / "fftopk_cp.cu", CSRC / "fftopk_hostio.cu", CSRC / "fftopk_indexer.cu"]
 HEADERS = [CSRC / "fftopk_device.cuh", CSRC / "fftopk_key.h", CSRC / "fftopk_host.h", CSRC / "fftopk_trace.cuh",
            CSRC / "fftopk_internal.h", CSRC / "fftopk_decide.h", CSRC / "fftopk_merge.cuh", ROOT.parent / "include" / "fftopk.h"]
 

@@ -42,6 +42,7 @@ struct SelectCall {
   const uint32_t* prev_threshold = nullptr;
   uint32_t* next_threshold = nullptr;
   uint32_t warm_margin = 0;
+  const uint32_t* only_rows = nullptr;  // with next_threshold: select only rows whose entry is non-zero
   // false: this launch consumes what a kernel enqueued just before it by the library itself has
   // produced (gathered rows, widened scores, slice lengths), or hands its output to a kernel the
   // library enqueues right after it. Such a launch keeps plain stream order whatever

@@ -88,11 +88,14 @@ struct MergeCtx {
 //               THIS GPU's inbox (the owner pushes them); the CTA polls them until every tag shows
 //               `epoch`
 // A wait that runs out fills the row with -1, raises FFTOPK_ST_PEER_TIMEOUT and returns normally.
-template <int NT>
+// kTrackMin / thr_out: the key of the row's 2048-th largest candidate (or, where the whole threshold
+// bin won without a finish, the bin's lower edge - a lower bound of it) is written to *thr_out.
+template <int NT, bool kTrackMin = false>
 __device__ __forceinline__ void merge_row(cg::cluster_group& cluster, int C, int G, int g, const MergeSmem& sm,
                                           const int32_t* sidx, const uint32_t* skey, const uint32_t* sflag,
                                           const uint4* packets, uint32_t epoch, unsigned long long wait_ns,
-                                          int32_t* __restrict__ out_idx, uint32_t* __restrict__ out_key, uint32_t* status) {
+                                          int32_t* __restrict__ out_idx, uint32_t* __restrict__ out_key, uint32_t* status,
+                                          uint32_t* thr_out = nullptr) {
   const int tid = threadIdx.x;
   const int lane = tid & 31, warp = tid >> 5;
   constexpr int NW = NT / 32;
@@ -123,6 +126,7 @@ __device__ __forceinline__ void merge_row(cg::cluster_group& cluster, int C, int
       ctrl->wslot = 0u;
       ctrl->cslot = 0u;
       ctrl->fslot = 0u;
+      if constexpr (kTrackMin) ctrl->thr_key = 0xffffffffu;
 #ifdef FFTOPK_CHECKED
       ctrl->status_ptr = status;
 #endif
@@ -241,6 +245,7 @@ __device__ __forceinline__ void merge_row(cg::cluster_group& cluster, int C, int
   if (total <= (uint32_t)kK) {
     // no more candidates than k: keep them all, shard after shard, pad with -1
     const uint32_t before = ctrl->tie_prefix;
+    uint32_t kmin = 0xffffffffu;
 #pragma unroll
     for (int u = 0; u < PER; ++u) {
       if (idx[u] >= 0) {
@@ -249,7 +254,12 @@ __device__ __forceinline__ void merge_row(cg::cluster_group& cluster, int C, int
           out_idx[pos] = idx[u];
           if (out_key) out_key[pos] = key[u];
         }
+        kmin = min(kmin, key[u]);
       }
+    }
+    if constexpr (kTrackMin) {  // all candidates win: the smallest key is the threshold
+      kmin = __reduce_min_sync(kFull, kmin);
+      if (lane == 0 && kmin != 0xffffffffu) atomicMin(&cx.ctrl0->thr_key, kmin);
     }
     if (g == 0) {
       for (int i = (int)total + tid; i < kK; i += NT) {
@@ -258,6 +268,9 @@ __device__ __forceinline__ void merge_row(cg::cluster_group& cluster, int C, int
       }
     }
     cluster_sync(cluster, C);
+    if constexpr (kTrackMin) {
+      if (g == 0 && tid == 0 && thr_out != nullptr) *thr_out = total == (uint32_t)kK ? ctrl->thr_key : 0u;
+    }
     return;
   }
   // ---- threshold bin over the shard owners; winners out, the bin itself to the first CTA -------
@@ -298,10 +311,21 @@ __device__ __forceinline__ void merge_row(cg::cluster_group& cluster, int C, int
     const DenseCands<NT> bin_cands{sm.cand, (int)ctrl->cand_count};
     const uint64_t lo = (uint64_t)t << 52;
     const uint64_t cap = lo | ((1ull << 52) - 1ull);
-    cta_finish<NT>(bin_cands, need, lo, cap, cap, false, 31, hist, ctrl, out_idx, out_key, (uint32_t)kK - need, (uint32_t)kK, 0,
-                   status);
+    cta_finish<NT, DenseCands<NT>, kTrackMin>(bin_cands, need, lo, cap, cap, false, 31, hist, ctrl, out_idx, out_key,
+                                              (uint32_t)kK - need, (uint32_t)kK, 0, status);
   } else if (mode != kModeTakeAll) {
     if (tid == 0 && status) atomicOr(status, (uint32_t)FFTOPK_ST_INTERNAL);
+  }
+  if constexpr (kTrackMin) {
+    if (thr_out != nullptr) {
+      __syncthreads();
+      if (tid == 0) {
+        uint32_t thr = 0u;
+        if (mode == kModeGather && ctrl->thr_key != 0xffffffffu) thr = ctrl->thr_key;
+        if (mode == kModeTakeAll) thr = t << 20;  // the whole bin won: its lower edge
+        *thr_out = thr;
+      }
+    }
   }
 }
 

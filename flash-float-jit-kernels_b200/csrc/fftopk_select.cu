@@ -98,6 +98,7 @@ struct SelectParams {
   const uint32_t* prev_threshold;
   uint32_t* next_threshold;
   uint32_t warm_margin;
+  const uint32_t* only_rows;  // (warm-start kernel only) when set: rows with only_rows[row] == 0 are left alone
 };
 
 
@@ -754,6 +755,9 @@ __device__ __forceinline__ void select_row(const SelectParams& p) {
   const int C = cx.C = (int)cluster.num_blocks();
   const int rank = cx.rank = (int)cluster.block_rank();
   const int row = (int)(blockIdx.x / (unsigned)C);
+  if constexpr (kWarm) {
+    if (p.only_rows != nullptr && p.only_rows[row] == 0u) return;  // (uniform over the cluster)
+  }
   const int tid = threadIdx.x;
   const int lane = tid & 31, warp = tid >> 5;
   constexpr int NW = NT / 32;
@@ -1647,6 +1651,7 @@ int launch_select(const SelectCall& c) {
   p.prev_threshold = c.prev_threshold;
   p.next_threshold = c.next_threshold;
   p.warm_margin = c.warm_margin;
+  p.only_rows = c.only_rows;
   const bool warm = c.prev_threshold != nullptr || c.next_threshold != nullptr;
   if (warm && (c.k != kK || pl.threads < 512)) return FFTOPK_EINVAL;
   if ((size_t)pl.smem_bytes > (size_t)d->smem_optin) return FFTOPK_ERANGE;

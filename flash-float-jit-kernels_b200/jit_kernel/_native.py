@@ -49,6 +49,8 @@ EXPORTS = (
     "fftopk_topk2048_sliced_noalloc",
     "fftopk_host_workspace_bytes",
     "fftopk_select2048_host",
+    "fftopk_indexer_workspace_bytes",
+    "fftopk_indexer_topk2048",
     "fftopk_probe_read_bandwidth",
     "fftopk_key_of",
     "fftopk_plan",
@@ -145,6 +147,12 @@ def lib() -> ctypes.CDLL:
     L.fftopk_select2048_host.restype = c.c_int
     L.fftopk_select2048_host.argtypes = [c.c_void_p, c.c_int64, c.c_int32, c.c_int64, c.c_void_p, c.c_void_p,
                                          c.c_void_p, c.c_size_t, c.c_void_p, c.c_void_p]
+    L.fftopk_indexer_workspace_bytes.restype = c.c_size_t
+    L.fftopk_indexer_workspace_bytes.argtypes = [c.c_int32]
+    L.fftopk_indexer_topk2048.restype = c.c_int
+    L.fftopk_indexer_topk2048.argtypes = [c.c_void_p, c.c_void_p, c.c_int64, c.c_void_p, c.c_int32, c.c_int64, c.c_void_p,
+                                          c.c_void_p, c.c_uint32, c.c_void_p, c.c_int64, c.c_void_p, c.c_void_p, c.c_size_t,
+                                          c.c_void_p, c.c_void_p]
     L.fftopk_probe_read_bandwidth.restype = c.c_int
     L.fftopk_probe_read_bandwidth.argtypes = [c.c_void_p, c.c_size_t, c.c_size_t, c.c_void_p, c.POINTER(c.c_size_t),
                                               c.c_void_p]

@@ -304,6 +304,39 @@ int fftopk_select2048_host(const float* h_score, int64_t h_row_stride, int32_t B
                            size_t workspace_bytes, uint32_t* d_status, void* cuda_stream);
 
 /*
+ * The step in FRONT of the selector, fused with it: indexer logits computed on the tensor cores and
+ * selected as they are produced. No counterpart in the reference, which starts from a finished fp32
+ * logit matrix (jit_kernel/topk_indexer.py:42-75; README.md:24 names the step).
+ *   logit[b, t] = sum over 64 heads h of  w[b, h] * relu( q[b, h, :] . k[b, t, :] ),  dimension 128, bf16
+ * One kernel (TMA loads, tcgen05.mma into TMEM, one key per epilogue thread) produces the logits of a
+ * row; for a row with a threshold guess (thresholds[b] != 0: what an earlier call handed back) every
+ * logit is compared with the guess as it leaves the tensor core and only the few that pass are kept
+ * as candidates - the logits are never written to or re-read from memory - and a cluster kernel
+ * selects the exact top 2048 of the candidates. Rows without a guess, and rows whose guess did not
+ * hold (fewer than 2048 admitted, or more than the 16,384-entry candidate list takes; status bit
+ * FFTOPK_ST_GUESS_MISSED), get their logits written to `logits` and go through the selector of
+ * fftopk_select2048. Either way out_idx holds the exact top 2048 OF THE LOGITS THE KERNEL COMPUTED
+ * (fp32 accumulation on the tensor cores; ties to the lower index) and thresholds[b] the key of the
+ * row's 2048-th largest logit for the next call.
+ *   q            device, bf16 [B, 64, 128], 16-byte aligned
+ *   k_cache      device, bf16 [B, k_rows_per_seq, 128] (k_rows_per_seq >= L), 16-byte aligned
+ *   w            device, fp32 [B, 64]
+ *   lengths      device, int32 [B]: valid keys per row (clamped to [0, L])
+ *   thresholds   device, uint32 [B], in and out (start with zeros); margin as for fftopk_select2048_warm
+ *   logits       device, fp32 [B, logits_stride] (logits_stride >= L): scratch for the rows that need it
+ *   out_idx      device, int32 [B, 2048]
+ *   d_workspace  fftopk_indexer_workspace_bytes(B) bytes of device memory, 256-byte aligned
+ * Enqueue-only on `cuda_stream`; the first call on a device sets kernel attributes (make it outside
+ * any stream capture). B <= 65535.
+ */
+size_t fftopk_indexer_workspace_bytes(int32_t B);
+int fftopk_indexer_topk2048(const void* q, const void* k_cache, int64_t k_rows_per_seq, const float* w,
+                            int32_t B, int64_t L, const int32_t* lengths, uint32_t* thresholds,
+                            uint32_t margin, float* logits, int64_t logits_stride, int32_t* out_idx,
+                            void* d_workspace, size_t workspace_bytes, uint32_t* status,
+                            void* cuda_stream);
+
+/*
  * Measurement aid, not part of the selection path (no reference counterpart): a read-only bandwidth
  * probe. One kernel in which every SM reads the buffer with 128-bit loads that bypass L1, wrapping
  * around until about `bytes_to_read` bytes have been read in total; *bytes_read receives the exact

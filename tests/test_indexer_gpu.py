@@ -1,0 +1,148 @@
+"""GPU tests of the fused indexer (fftopk_indexer_topk2048 / FusedIndexerTopk): logits computed on
+the tensor cores and selected as they are produced.
+
+Floating point: the logits are compared with the same formula in torch (fp32 arithmetic on the
+widened bf16 operands) within 2e-5 relative to the row's largest magnitude - the tensor core
+accumulates the 128-long dot products in fp32 in its own order. The selection is integer work and
+must be bit-exact GIVEN the kernel's logits: the index set equals the oracle's on the logits the
+kernel itself wrote, ties to the lower index, whether the row went through the selector (no guess)
+or through the candidate filter in the producer's epilogue (guess from the previous call)."""
+import numpy as np
+import pytest
+import torch
+
+from jit_kernel import _native
+from jit_kernel.indexer import FusedIndexerTopk, reference_logits
+from jit_kernel.topk_indexer import _status_word, kernel_status
+from oracle import topk_oracle as orc
+
+pytestmark = pytest.mark.gpu
+K = 2048
+DEV = torch.device("cuda", 0)
+LOGIT_RTOL = 2e-5
+
+
+@pytest.fixture(autouse=True)
+def _clean_status():
+    _status_word(DEV).zero_()
+    yield
+    _status_word(DEV).zero_()
+
+
+def make(B, L, seed, ties=False):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    q = torch.randn(B, 64, 128, generator=g).to(torch.bfloat16)
+    k = torch.randn(B, L, 128, generator=g).to(torch.bfloat16)
+    if ties:  # repeated keys give exactly equal logits: ties at the threshold are decided by index
+        k[:, L // 2:] = k[:, :L - L // 2]
+    w = torch.rand(B, 64, generator=g)
+    return q.to(DEV), k.to(DEV), w.to(DEV)
+
+
+def kth_keys(logits, lengths):
+    out = []
+    for b in range(logits.shape[0]):
+        n = int(lengths[b])
+        out.append(int(np.sort(orc.keys_of(logits[b, :n]))[-K]) if n > K else 0)
+    return np.array(out, dtype=np.uint32)
+
+
+@pytest.mark.parametrize("B,L", [(1, 4096), (3, 50000), (1, 300000), (8, 20000)])
+def test_logits_match_torch_and_selection_is_exact(B, L):
+    q, k, w = make(B, L, seed=B * 1000 + L)
+    ln = torch.full((B,), L, dtype=torch.int32)
+    if B > 1:
+        ln[1] = L - 777      # a ragged tail inside the last tiles
+        ln[-1] = 1500        # a row of fewer than k keys: -1 padded
+    f = FusedIndexerTopk(B, L)
+    out = f(q, k, w, ln.to(DEV))  # no guess yet: logits are written, the selector runs
+    torch.cuda.synchronize()
+    got = f.logits[:B, :L].cpu()
+    ref = reference_logits(q, k, w).cpu()
+    for b in range(B):
+        n = int(ln[b])
+        scale = float(ref[b, :n].abs().max())
+        assert float((got[b, :n] - ref[b, :n]).abs().max()) <= LOGIT_RTOL * scale, f"row {b}: logits differ from torch"
+    logits_np = got.numpy().copy()
+    orc.check_result(logits_np, ln.numpy(), out.cpu().numpy(), what="cold")
+    want = kth_keys(logits_np, ln.numpy())
+    assert np.array_equal(f.thresholds.cpu().numpy().view(np.uint32)[:B], want)
+    # the same inputs again: every row with more than k keys now has a guess, its logits are
+    # filtered in the producer's epilogue and never written
+    f.logits.fill_(float("nan"))
+    for rep in range(2):
+        out = f(q, k, w, ln.to(DEV))
+        torch.cuda.synchronize()
+        orc.check_result(logits_np, ln.numpy(), out.cpu().numpy(), what=f"warm {rep}")
+        assert np.array_equal(f.thresholds.cpu().numpy().view(np.uint32)[:B], want)
+    written = ~torch.isnan(f.logits[:B, :L]).all(dim=1).cpu()
+    for b in range(B):
+        assert bool(written[b]) == (int(ln[b]) <= K), f"row {b}: logits written although the guess held"
+    assert kernel_status(DEV) == 0
+
+
+def test_decode_loop_grows_the_key_cache():
+    """One key appended per step; thresholds carried along; every step exact on the step's logits."""
+    B, L0, steps = 2, 30000, 6
+    q, k, w = make(B, L0 + steps, seed=7)
+    f = FusedIndexerTopk(B, L0 + steps)
+    ref = reference_logits(q, k, w).cpu().numpy()  # close to the kernel's logits; exactness is checked on its own below
+    for t in range(steps + 1):
+        ln = torch.full((B,), L0 + t, dtype=torch.int32)
+        out = f(q, k, w, ln.to(DEV))
+        torch.cuda.synchronize()
+        got = out.cpu().numpy()
+        for b in range(B):
+            # the k-th and (k+1)-th logits of these rows are far apart compared with the tolerance,
+            # so the torch logits give the same set
+            exp = orc.numpy_oracle(ref[b:b + 1, :L0 + t], np.array([L0 + t]), K)[0]
+            assert np.array_equal(np.sort(got[b]), np.sort(exp)), f"step {t} row {b}"
+    assert kernel_status(DEV) == 0
+
+
+def test_exact_ties_and_guess_misses():
+    B, L = 2, 40000
+    q, k, w = make(B, L, seed=11, ties=True)
+    ln = torch.full((B,), L, dtype=torch.int32)
+    f = FusedIndexerTopk(B, L)
+    out = f(q, k, w, ln.to(DEV))
+    torch.cuda.synchronize()
+    logits_np = f.logits[:B, :L].cpu().numpy().copy()
+    assert np.array_equal(logits_np[:, :L // 2], logits_np[:, L // 2:])  # every logit occurs twice
+    orc.check_result(logits_np, ln.numpy(), out.cpu().numpy(), what="ties cold")
+    out = f(q, k, w, ln.to(DEV))
+    torch.cuda.synchronize()
+    orc.check_result(logits_np, ln.numpy(), out.cpu().numpy(), what="ties warm")
+    assert kernel_status(DEV) == 0
+    want = kth_keys(logits_np, ln.numpy())
+    # guesses that do not hold: too high (fewer than k admitted) and far too low (the list overflows)
+    for bad in (want + np.uint32(1 << 24), np.full(B, orc.keys_of(np.array([-1e30], np.float32))[0], np.uint32)):
+        f.thresholds[:B] = torch.from_numpy(bad.view(np.int32).copy()).to(DEV)
+        out = f(q, k, w, ln.to(DEV))
+        torch.cuda.synchronize()
+        orc.check_result(logits_np, ln.numpy(), out.cpu().numpy(), what="missed guess")
+        assert kernel_status(DEV) & _native.ST_GUESS_MISSED
+        assert np.array_equal(f.thresholds.cpu().numpy().view(np.uint32)[:B], want)
+        _status_word(DEV).zero_()
+
+
+def test_graph_replay():
+    B, L = 2, 60000
+    q, k, w = make(B, L, seed=13)
+    ln = torch.full((B,), L, dtype=torch.int32, device=DEV)
+    f = FusedIndexerTopk(B, L)
+    out = torch.empty(B, K, dtype=torch.int32, device=DEV)
+    f(q, k, w, ln, out=out)  # first call outside the capture (kernel attributes), also seeds the thresholds
+    torch.cuda.synchronize()
+    logits_np = f.logits[:B, :L].cpu().numpy().copy()
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            f(q, k, w, ln, out=out)
+    for _ in range(3):
+        out.fill_(-3)
+        graph.replay()
+        torch.cuda.synchronize()
+        orc.check_result(logits_np, ln.cpu().numpy(), out.cpu().numpy(), what="indexer replay")
+    assert kernel_status(DEV) == 0
