@@ -39,7 +39,7 @@ enum {
 
 /* Bits the kernels may OR into the optional device status word. */
 enum {
-  FFTOPK_ST_STAGE_TIMEOUT = 1, /* reserved                                                  */
+  FFTOPK_ST_STAGE_TIMEOUT = 1, /* fused indexer: a bounded wait on a copy / MMA barrier ran out */
   FFTOPK_ST_INTERNAL = 2,      /* an internal count did not add up (should never be seen)  */
   FFTOPK_ST_PEER_TIMEOUT = 4,  /* merge: a bounded wait on a peer's ready flag ran out      */
   FFTOPK_ST_GUESS_MISSED = 8,  /* warm start: a row's previous threshold was unusable; the row  */
