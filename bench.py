@@ -372,57 +372,64 @@ def decode_loop_leg(dev, stream):
 
 
 def indexer_leg(dev, stream, peak_gbs):
-    """The step in front of the selector, fused with it (fftopk_indexer_topk2048): B=1 decode rows,
-    bf16 q [64, 128] and key cache [L, 128]. us per call with a standing threshold guess (logits
-    filtered in the tensor-core kernel's epilogue, never written) and without one (logits written,
-    selector on them), beside torch's own einsum + relu + weighted sum for the logits alone. The
-    roofline of the producer is reading the key cache once: 256 B per key."""
+    """The step in front of the selector, fused with it (fftopk_indexer_topk2048[_fp8]): B=1 decode
+    rows, q [64, 128] and key cache [L, 128] in bf16 and in fp8 (e4m3, one fp32 scale per key). us
+    per call with a standing threshold guess (logits filtered in the tensor-core kernel's epilogue,
+    never written) and without one (logits written, selector on them), beside torch's own einsum +
+    relu + weighted sum for the logits alone (bf16). The roofline of the producer is reading the key
+    cache once: 256 B per key in bf16, 128 + 4 B in fp8."""
     from jit_kernel.indexer import FusedIndexerTopk, reference_logits
 
     out = {}
-    for L in (131072, 1048576):
-        g = torch.Generator(device="cpu").manual_seed(L)
-        q = torch.randn(1, 64, 128, generator=g).to(torch.bfloat16).to(dev)
-        nbuf = max(2, (300 << 20) // (L * 256) + 1)  # rotate key caches over more than L2
-        ks = [torch.randn(1, L, 128, generator=g).to(torch.bfloat16).to(dev) for _ in range(nbuf)]
-        w = torch.rand(1, 64, generator=g).to(dev)
-        ln = torch.full((1,), L, dtype=torch.int32, device=dev)
-        fs = [FusedIndexerTopk(1, L, dev) for _ in range(nbuf)]  # one threshold state per cache
-        res = torch.empty(1, K, dtype=torch.int32, device=dev)
-        with torch.cuda.stream(stream):
-            for f, k in zip(fs, ks):
-                f(q, k, w, ln, out=res)  # seeds the thresholds (and sets kernel attributes)
-        stream.synchronize()
-        n = 2 * nbuf
-        r = {"key_cache_bytes": L * 256, "rotated_caches": nbuf}
-        for name in ("warm", "cold"):
-            def call(i):
-                f = fs[i % nbuf]
-                if name == "cold":
-                    f.thresholds.zero_()
-                f(q, ks[i % nbuf], w, ln, out=res)
+    for fmt in ("bf16", "fp8"):
+        for L in (131072, 1048576):
+            g = torch.Generator(device="cpu").manual_seed(L)
+            dt = torch.bfloat16 if fmt == "bf16" else torch.float8_e4m3fn
+            key_bytes = L * (256 if fmt == "bf16" else 132)
+            q = (torch.randn(1, 64, 128, generator=g) * 0.5).to(dt).to(dev)
+            nbuf = max(2, (300 << 20) // key_bytes + 1)  # rotate key caches over more than L2
+            ks = [(torch.randn(1, L, 128, generator=g) * 0.5).to(dt).to(dev) for _ in range(nbuf)]
+            scale = (torch.rand(1, L, generator=g) + 0.5).to(dev) if fmt == "fp8" else None
+            w = torch.rand(1, 64, generator=g).to(dev)
+            ln = torch.full((1,), L, dtype=torch.int32, device=dev)
+            fs = [FusedIndexerTopk(1, L, dev) for _ in range(nbuf)]  # one threshold state per cache
+            res = torch.empty(1, K, dtype=torch.int32, device=dev)
             with torch.cuda.stream(stream):
-                call(0)
+                for f, k in zip(fs, ks):
+                    f(q, k, w, ln, out=res, k_scale=scale)  # seeds the thresholds (and sets kernel attributes)
             stream.synchronize()
-            gr = capture_steps(call, n, stream)
-            ts = sorted(time_graph(gr, stream) / n * 1e6 for _ in range(9))
-            r[name + "_us_per_call"] = ts[len(ts) // 2]
-            del gr
-            if name == "cold":  # leave the states warm again
+            n = 2 * nbuf
+            r = {"key_cache_bytes": key_bytes, "rotated_caches": nbuf}
+            for name in ("warm", "cold"):
+                def call(i):
+                    f = fs[i % nbuf]
+                    if name == "cold":
+                        f.thresholds.zero_()
+                    f(q, ks[i % nbuf], w, ln, out=res, k_scale=scale)
                 with torch.cuda.stream(stream):
-                    for f, k in zip(fs, ks):
-                        f(q, k, w, ln, out=res)
+                    call(0)
                 stream.synchronize()
-        r["warm_gbs"] = L * 256 / r["warm_us_per_call"] / 1e3
-        r["warm_frac_hbm"] = r["warm_gbs"] / peak_gbs
-        with torch.cuda.stream(stream):
-            reference_logits(q, ks[0], w)
-        stream.synchronize()
-        gr = capture_steps(lambda i: reference_logits(q, ks[i % nbuf], w), nbuf, stream)
-        ts = sorted(time_graph(gr, stream) / nbuf * 1e6 for _ in range(5))
-        r["torch_logits_only_us"] = ts[len(ts) // 2]
-        out[str(L)] = r
-        del ks, fs, gr
+                gr = capture_steps(call, n, stream)
+                ts = sorted(time_graph(gr, stream) / n * 1e6 for _ in range(9))
+                r[name + "_us_per_call"] = ts[len(ts) // 2]
+                del gr
+                if name == "cold":  # leave the states warm again
+                    with torch.cuda.stream(stream):
+                        for f, k in zip(fs, ks):
+                            f(q, k, w, ln, out=res, k_scale=scale)
+                    stream.synchronize()
+            r["warm_gbs"] = key_bytes / r["warm_us_per_call"] / 1e3
+            r["warm_frac_hbm"] = r["warm_gbs"] / peak_gbs
+            if fmt == "bf16":
+                with torch.cuda.stream(stream):
+                    reference_logits(q, ks[0], w)
+                stream.synchronize()
+                gr = capture_steps(lambda i: reference_logits(q, ks[i % nbuf], w), nbuf, stream)
+                ts = sorted(time_graph(gr, stream) / nbuf * 1e6 for _ in range(5))
+                r["torch_logits_only_us"] = ts[len(ts) // 2]
+                del gr
+            out[f"{fmt}_{L}"] = r
+            del ks, fs
     return out
 
 

@@ -48,8 +48,8 @@ __global__ void __launch_bounds__(NT, 1) merge2048_kernel(const MergeSrc src, in
   extern __shared__ __align__(128) unsigned char smem_raw[];
   MergeSmem sm;
   sm.hist = reinterpret_cast<uint32_t*>(smem_raw);
-  sm.sup = sm.hist + kMaxBins;
-  sm.xch = sm.sup + kSup;
+  sm.sup = sm.hist + 2 * kMaxBins;
+  sm.xch = sm.sup + 2 * kSup;
   sm.ctrl = reinterpret_cast<Ctrl*>(sm.xch + kMaxCluster * kSup);
   sm.cand = reinterpret_cast<uint64_t*>(reinterpret_cast<unsigned char*>(sm.ctrl) + ((sizeof(Ctrl) + 127) & ~127u));
   sm.cand_cap = G * kK;
@@ -133,7 +133,8 @@ int merge_setup() {
 }
 
 size_t merge_smem(int G) {
-  return (size_t)(kMaxBins + kSup + kMaxCluster * kSup) * 4 + ((sizeof(Ctrl) + 127) & ~(size_t)127) + (size_t)G * kK * 8;
+  return (size_t)(2 * kMaxBins + 2 * kSup + kMaxCluster * kSup) * 4 + ((sizeof(Ctrl) + 127) & ~(size_t)127) +
+         (size_t)G * kK * 8;
 }
 
 // One cluster of G CTAs per row.

@@ -228,6 +228,8 @@ struct Picked {
   uint32_t total;     // cluster-wide number of histogrammed elements
   uint32_t any_flag;  // OR of the peers' published flags
   int tf;             // t's position inside its super-bin (index into xch rows)
+  bool fine;          // the search ran on the second, finer histogram (see cluster_pick)
+  uint32_t group;     // ... whose bins all lie under this value of the key's top four bits
 };
 
 // Cluster-wide threshold search on per-CTA histograms `h` (nb bins) with super-bin sums `s`,
@@ -236,18 +238,23 @@ struct Picked {
 // memory; warp 0 picks with shuffle scans. need_of(total) maps the cluster-wide element count
 // to the rank searched for. `post(picked)` runs in warp 0 (all lanes) before the closing
 // barrier; the results it wants every thread to see go through `ctrl`.
+// Optionally a second histogram `hb` / `sb` of the same elements on key bits [27:16] (4096 bins, 16
+// times finer) comes along: it orders the elements only if they all share the key's top four
+// bits, i.e. if one group of four super-bins of `h` holds everything; then the search runs on it
+// (Picked::fine, ::group) and the threshold bin is a 16-bit key prefix. ctrl->totb must be zero.
 // Replaces parallel_reduce_histogram + radix_prefix_sum of the reference
 // (topk_indexer_radix.cu:80-107, 232-279), which reduce to rank 0 and broadcast back with three
 // cluster barriers and eight block barriers per round.
 template <int NT, class NeedFn, class Post>
 __device__ __forceinline__ void cluster_pick(cg::cluster_group& cluster, int C, const uint32_t* h, const uint32_t* s,
                                              uint32_t* xch, Ctrl* ctrl, int& pick_no, int nb, NeedFn&& need_of,
-                                             Post&& post) {
+                                             Post&& post, const uint32_t* hb = nullptr, const uint32_t* sb = nullptr) {
   const int tid = threadIdx.x;
   const int lane = tid & 31, warp = tid >> 5;
   const int fine = nb / kSup;
   uint32_t* tot = ctrl->tot[pick_no & 1];
   uint32_t* tot2 = ctrl->tot2[pick_no & 1];
+  const bool dual = hb != nullptr;
   // (A) cluster-wide super-bin totals: one remote word per thread, summed with shared-memory
   // reductions instead of a serial loop over the ranks. (Pushing the sums into the peers before
   // the cluster barrier instead - remote reductions behind a split arrive / wait barrier - was
@@ -255,6 +262,10 @@ __device__ __forceinline__ void cluster_pick(cg::cluster_group& cluster, int C, 
   for (int i = tid; i < C * kSup; i += NT) {
     const uint32_t* rs = C == 1 ? s : cluster.map_shared_rank(s, i / kSup);
     red_shared_add(&tot[i % kSup], rs[i % kSup]);
+    if (dual) {
+      const uint32_t* rb = C == 1 ? sb : cluster.map_shared_rank(sb, i / kSup);
+      red_shared_add(&ctrl->totb[i % kSup], rb[i % kSup]);
+    }
   }
   __syncthreads();
   FFTOPK_MARK(40);
@@ -262,9 +273,20 @@ __device__ __forceinline__ void cluster_pick(cg::cluster_group& cluster, int C, 
   // saves the two broadcast barriers but was measured slower: 32 warps running the same shuffle
   // scans get in each other's way.)
   if (warp == 0) {
-    const uint32_t lo = tot[2 * lane], hi = tot[2 * lane + 1];
+    uint32_t lo = tot[2 * lane], hi = tot[2 * lane + 1];
     const uint32_t total = warp_sum(lo + hi);
     const uint32_t need = need_of(total);
+    unsigned one = 0u;
+    if (dual) {
+      // four super-bins = 256 bins of `h` = one value of the top four key bits
+      const uint32_t pair = lo + hi;
+      const uint32_t grp = pair + __shfl_xor_sync(kFull, pair, 1);
+      one = __ballot_sync(kFull, fine_histogram_usable(true, total, grp));
+      if (one != 0u) {
+        lo = ctrl->totb[2 * lane];
+        hi = ctrl->totb[2 * lane + 1];
+      }
+    }
     uint32_t above = 0, cnt = 0;
     int ts = -1;
     const bool ok = need > 0 && warp_pick64(lo, hi, need, ts, above, cnt);
@@ -273,11 +295,17 @@ __device__ __forceinline__ void cluster_pick(cg::cluster_group& cluster, int C, 
       ctrl->sup_above = above;
       ctrl->need = need;
       ctrl->run_total = total;
+      ctrl->dual_b = one != 0u ? 1u : 0u;
+      ctrl->dual_g = one != 0u ? (uint32_t)((__ffs(one) - 1) >> 1) : 0u;
     }
   }
   __syncthreads();
   FFTOPK_MARK(41);
   const int ssel = ctrl->sup_sel;
+  if (dual && ctrl->dual_b != 0u) {  // (uniform) the rest of the search runs on the finer histogram
+    h = hb;
+    s = sb;
+  }
   // (B) fine bins of the threshold super-bin: pulled from every peer, kept per rank in xch (the
   // tie path wants them) and summed into tot2
   if (ssel >= 0) {
@@ -308,6 +336,8 @@ __device__ __forceinline__ void cluster_pick(cg::cluster_group& cluster, int C, 
     pk.total = ctrl->run_total;
     pk.any_flag = 0u;
     pk.tf = 0;
+    pk.fine = dual && ctrl->dual_b != 0u;
+    pk.group = ctrl->dual_g;
     if (ssel >= 0) {
       const uint32_t lo = tot2[2 * lane], hi = tot2[2 * lane + 1];
       const uint32_t need = ctrl->need, sup_above = ctrl->sup_above;
@@ -599,6 +629,14 @@ __device__ void cta_finish(const Src& src, uint32_t need, uint64_t lo, uint64_t 
     cnt = need2 = need;
     all_bin = found = true;
     __syncthreads();  // (the counters cleared above are used by the pass below)
+  } else if (known_total != 0u && known_total <= (uint32_t)kSmall && known_total >= need && lo <= cap) {
+    // so few candidates that they are ranked directly: the whole range is the "threshold bin"
+    t_lo = lo;
+    t_hi = cap;
+    cnt = known_total;
+    need2 = need;
+    found = true;
+    __syncthreads();
   }
   for (int round = 0; round < 24 && !found; ++round) {
     if ((uint32_t)(lo >> 32) == (uint32_t)(cap >> 32)) {

@@ -1,20 +1,22 @@
 // Indexer logits fused with the top-2048 selection (sm_100a: TMA + tcgen05 + TMEM).
 //
 // The logit of key t of a row is  sum over 64 heads h of  w[h] * relu(q[h] . k[t])  (q[h], k[t] of
-// dimension 128, bf16). The reference contains no producer of these logits - its selector starts
+// dimension 128; bf16, or fp8 e4m3 with an optional scale per key). The reference contains no producer of these logits - its selector starts
 // from a finished fp32 [B, L] matrix (jit_kernel/topk_indexer.py:42-75) and its README only names
 // the step (README.md:24) - so there is no reference counterpart; this is the step in front of the
 // hot path, fused with it.
 //
-// Producer kernel, one CTA per (row, slice of key tiles), 192 threads in three roles:
+// Producer kernel, one CTA per (row, slice of key tiles), 320 threads in three roles:
 //   warp 0      one thread issues TMA loads (cp.async.bulk.tensor, 128-byte swizzle, no multicast):
 //               the row's q once (64 heads x 128), then key tiles of 128 keys x 128 through a ring
 //               of shared-memory stages guarded by full / empty mbarriers;
-//   warp 1      allocates 128 TMEM columns; one thread issues, per tile, eight tcgen05.mma
-//               (M=128 keys, N=64 heads, K=16) that accumulate D[key][head] in fp32 in one of two
+//   warp 1      allocates 256 TMEM columns; one thread issues, per tile, eight tcgen05.mma of
+//               K=16 (bf16; four of K=32 for fp8), M=128 keys, N=64 heads, that accumulate
+//               D[key][head] in fp32 in one of four
 //               64-column TMEM buffers, and commits to the stage's empty barrier and the buffer's
 //               full barrier;
-//   warps 2-5   epilogue: tcgen05.ld hands every thread the 64 head values of ONE key; relu,
+//   warps 2-9   epilogue, two groups of four warps, one group per TMEM buffer (every second
+//               tile): tcgen05.ld hands every thread the 64 head values of ONE key; relu,
 //               weights and the sum are in-thread - one logit per thread and tile. With a threshold
 //               guess for the row (the previous decode step's, see fftopk_select2048_warm) the
 //               logit is compared with the guess's edge and the few that pass are appended, by
@@ -48,16 +50,32 @@ namespace fftopk {
 constexpr int kIdxHeads = 64;
 constexpr int kIdxDim = 128;
 constexpr int kIdxTile = 128;      // keys per tile = rows of the MMA
-constexpr int kIdxStages = 4;      // key tiles in flight
-constexpr int kIdxThreads = 192;
-constexpr int kIdxChunk = 64;      // bf16 elements per 128-byte swizzle row
-constexpr uint32_t kIdxTileBytes = kIdxTile * kIdxDim * 2;   // 32 KiB: two boxes of 128 rows x 128 B
-constexpr uint32_t kIdxQBytes = kIdxHeads * kIdxDim * 2;     // 16 KiB: two boxes of 64 rows x 128 B
+constexpr int kIdxThreads = 320;    // TMA warp, MMA warp, two groups of four epilogue warps
+// Operand formats: bf16 (two 128-byte swizzle rows per key, MMA K = 16) or fp8 e4m3 (one row per
+// key, MMA K = 32, an optional fp32 scale per key applied in the epilogue).
+template <bool kFp8>
+struct IdxFmt {
+  static constexpr int kElemBytes = kFp8 ? 1 : 2;
+  static constexpr int kChunk = 128 / kElemBytes;                 // elements per 128-byte swizzle row
+  static constexpr int kBoxes = kIdxDim / kChunk;                 // TMA boxes per tile: 2 (bf16), 1 (fp8)
+  static constexpr uint32_t kTileBytes = kIdxTile * kIdxDim * kElemBytes;   // 32 / 16 KiB
+  static constexpr uint32_t kQBytes = kIdxHeads * kIdxDim * kElemBytes;     // 16 / 8 KiB
+  static constexpr int kMmaPerBox = 4;                            // 128 bytes of K per box / 32 bytes per MMA
+  static constexpr int kStages = kFp8 ? 8 : 4;                    // key tiles in flight: 128 KiB either way
+  // instruction descriptor: D fp32; A and B bf16 (format 1) or e4m3 (format 0), both K-major; M = 128, N = 64
+  static constexpr uint32_t kInstrDesc = (1u << 4) | ((kFp8 ? 0u : 1u) << 7) | ((kFp8 ? 0u : 1u) << 10) |
+                                         ((uint32_t)(kIdxHeads >> 3) << 17) | ((uint32_t)(kIdxTile >> 4) << 24);
+};
+constexpr uint32_t kIdxMaxTileBytes = IdxFmt<false>::kTileBytes;
+constexpr uint32_t kIdxMaxQBytes = IdxFmt<false>::kQBytes;
+constexpr int kIdxBufs = 4;         // TMEM accumulators of 64 columns: the MMAs run up to four tiles ahead of the epilogue
 constexpr int kIdxCandShards = 8;  // the candidate list of a row: 8 x 2048 slots, the merge's layout
 constexpr unsigned long long kIdxWaitNs = 200ull * 1000 * 1000;
 
 struct IndexerParams {
   const float* w;            // [B, 64] head weights
+  const float* k_scale;      // fp8 only: [B, k_scale_stride] one scale per key, or nullptr
+  int64_t k_scale_stride;
   const int32_t* lengths;    // [B]
   int64_t k_rows_per_seq;    // rows of the key tensor map per batch row
   int32_t B;
@@ -119,7 +137,7 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
       : "memory");
 }
 // Shared-memory matrix descriptor of a K-major operand in the 128-byte-swizzle layout a TMA box of
-// 64 bf16 x rows produces: rows of 128 bytes, groups of 8 rows 1024 bytes apart.
+// 128 bytes (64 bf16 or 128 fp8) x rows produces: rows of 128 bytes, groups of 8 rows 1024 bytes apart.
 __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
   uint64_t d = 0;
   d |= (uint64_t)((smem_addr >> 4) & 0x3fffu);  // start address, 16-byte units
@@ -129,16 +147,23 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
   d |= (uint64_t)2u << 61;                       // layout type: 128-byte swizzle
   return d;
 }
-// Instruction descriptor: D fp32, A and B bf16, both K-major, M = 128, N = 64.
-constexpr uint32_t kIdxInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kIdxHeads >> 3) << 17) |
-                                   ((uint32_t)(kIdxTile >> 4) << 24);
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
-      "l"(adesc), "l"(bdesc), "r"(kIdxInstrDesc), "r"(accumulate)
-      : "memory");
+template <bool kFp8>
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+  if constexpr (kFp8) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "l"(adesc), "l"(bdesc), "r"(IdxFmt<true>::kInstrDesc), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "l"(adesc), "l"(bdesc), "r"(IdxFmt<false>::kInstrDesc), "r"(accumulate)
+        : "memory");
+  }
 }
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
@@ -157,21 +182,26 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
 }
 
 // ---- producer --------------------------------------------------------------------------------------
+template <bool kFp8>
 __global__ void __launch_bounds__(kIdxThreads, 1)
     indexer_logits_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                           const IndexerParams p) {
+  using F = IdxFmt<kFp8>;
+  constexpr uint32_t kIdxTileBytes = F::kTileBytes;
+  constexpr uint32_t kIdxQBytes = F::kQBytes;
+  constexpr int kIdxStages = F::kStages;
   extern __shared__ unsigned char idx_smem_raw[];
   // 1024-byte alignment for the swizzled tiles
   unsigned char* base = idx_smem_raw + ((1024u - (smem_u32(idx_smem_raw) & 1023u)) & 1023u);
   unsigned char* a_smem = base;                                   // kIdxStages x 32 KiB
-  unsigned char* q_smem = a_smem + (size_t)kIdxStages * kIdxTileBytes;  // 16 KiB
+  unsigned char* q_smem = a_smem + (size_t)kIdxStages * kIdxTileBytes;  // 16 / 8 KiB
   float* w_smem = reinterpret_cast<float*>(q_smem + kIdxQBytes);  // 64 floats
   uint64_t* bars = reinterpret_cast<uint64_t*>(w_smem + kIdxHeads);
   uint64_t* full = bars;                     // [kIdxStages]
   uint64_t* empty = bars + kIdxStages;       // [kIdxStages]
-  uint64_t* tfull = bars + 2 * kIdxStages;   // [2]
-  uint64_t* tempty = tfull + 2;              // [2]
-  uint64_t* qfull = tempty + 2;              // [1]
+  uint64_t* tfull = bars + 2 * kIdxStages;   // [kIdxBufs]
+  uint64_t* tempty = tfull + kIdxBufs;       // [kIdxBufs]
+  uint64_t* qfull = tempty + kIdxBufs;       // [1]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(qfull + 1);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
@@ -194,17 +224,18 @@ __global__ void __launch_bounds__(kIdxThreads, 1)
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
     }
-    mbar_init(&tfull[0], 1);
-    mbar_init(&tfull[1], 1);
-    mbar_init(&tempty[0], 128);
-    mbar_init(&tempty[1], 128);
+    for (int b = 0; b < kIdxBufs; ++b) {
+      mbar_init(&tfull[b], 1);
+      mbar_init(&tempty[b], 128);
+    }
     mbar_init(qfull, 1);
     *abort_flag = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (tid < kIdxHeads) w_smem[tid] = __ldg(p.w + (int64_t)row * kIdxHeads + tid);
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(128u)
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"((uint32_t)(kIdxBufs * kIdxHeads))
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -217,8 +248,9 @@ __global__ void __launch_bounds__(kIdxThreads, 1)
     // ---- TMA producer -----------------------------------------------------------------------
     if (lane == 0) {
       mbar_expect_tx(qfull, kIdxQBytes);
-      tma_load_2d(q_smem, &map_q, 0, row * kIdxHeads, qfull);
-      tma_load_2d(q_smem + kIdxQBytes / 2, &map_q, kIdxChunk, row * kIdxHeads, qfull);
+#pragma unroll
+      for (int bx = 0; bx < F::kBoxes; ++bx)
+        tma_load_2d(q_smem + (size_t)bx * (kIdxQBytes / F::kBoxes), &map_q, bx * F::kChunk, row * kIdxHeads, qfull);
       int it = 0;
       for (int t = blockIdx.x; t < ntiles; t += gridDim.x, ++it) {
         const int s = it % kIdxStages;
@@ -227,8 +259,9 @@ __global__ void __launch_bounds__(kIdxThreads, 1)
         mbar_expect_tx(&full[s], kIdxTileBytes);
         const int y = (int)((int64_t)row * p.k_rows_per_seq + (int64_t)t * kIdxTile);
         unsigned char* dst = a_smem + (size_t)s * kIdxTileBytes;
-        tma_load_2d(dst, &map_k, 0, y, &full[s]);
-        tma_load_2d(dst + kIdxTileBytes / 2, &map_k, kIdxChunk, y, &full[s]);
+#pragma unroll
+        for (int bx = 0; bx < F::kBoxes; ++bx)
+          tma_load_2d(dst + (size_t)bx * (kIdxTileBytes / F::kBoxes), &map_k, bx * F::kChunk, y, &full[s]);
       }
     }
   } else if (warp == 1) {
@@ -239,8 +272,8 @@ __global__ void __launch_bounds__(kIdxThreads, 1)
       for (int t = blockIdx.x; ok && t < ntiles; t += gridDim.x, ++it) {
         const int s = it % kIdxStages;
         const uint32_t ph = (uint32_t)(it / kIdxStages) & 1u;
-        const int buf = it & 1;
-        const uint32_t bph = (uint32_t)(it >> 1) & 1u;
+        const int buf = it % kIdxBufs;
+        const uint32_t bph = (uint32_t)(it / kIdxBufs) & 1u;
         if (!mbar_wait(&tempty[buf], bph ^ 1u, abort_flag)) break;
         if (!mbar_wait(&full[s], ph, abort_flag)) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -248,13 +281,13 @@ __global__ void __launch_bounds__(kIdxThreads, 1)
         const uint32_t b_addr = smem_u32(q_smem);
         const uint32_t d_tmem = tmem_base + (uint32_t)buf * kIdxHeads;
 #pragma unroll
-        for (int kc = 0; kc < 2; ++kc) {
+        for (int kc = 0; kc < F::kBoxes; ++kc) {
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk) {
-            // 16 bf16 = 32 bytes further along K inside the 128-byte swizzle row
-            const uint64_t ad = umma_desc_sw128(a_addr + (uint32_t)kc * (kIdxTileBytes / 2) + (uint32_t)kk * 32u);
-            const uint64_t bd = umma_desc_sw128(b_addr + (uint32_t)kc * (kIdxQBytes / 2) + (uint32_t)kk * 32u);
-            umma_bf16(d_tmem, ad, bd, (kc | kk) != 0 ? 1u : 0u);
+          for (int kk = 0; kk < F::kMmaPerBox; ++kk) {
+            // one MMA consumes 32 bytes of K (16 bf16 or 32 fp8): 32 bytes further inside the swizzle row
+            const uint64_t ad = umma_desc_sw128(a_addr + (uint32_t)kc * (kIdxTileBytes / F::kBoxes) + (uint32_t)kk * 32u);
+            const uint64_t bd = umma_desc_sw128(b_addr + (uint32_t)kc * (kIdxQBytes / F::kBoxes) + (uint32_t)kk * 32u);
+            umma<kFp8>(d_tmem, ad, bd, (kc | kk) != 0 ? 1u : 0u);
           }
         }
         umma_commit(&empty[s]);     // the stage may be refilled once these MMAs have read it
@@ -262,30 +295,50 @@ __global__ void __launch_bounds__(kIdxThreads, 1)
       }
     }
   } else {
-    // ---- epilogue: one key per thread -------------------------------------------------------------
+    // ---- epilogue: one key per thread; group g of four warps serves every second tile. (With two
+    // accumulators and one group the loop MMA -> full barrier -> TMEM loads -> empty barrier -> next
+    // MMA into the same accumulator took ~1.1 us per pair of tiles: as long as the key tiles' copies
+    // take in bf16, twice as long as they take in fp8.) -----------------------------------------
+    const int group = (warp - 2) >> 2;
     const int quarter = warp & 3;                 // the TMEM lanes this warp may read: 32 * (warp % 4)
     const int key_in_tile = quarter * 32 + lane;
     const unsigned lt = (1u << lane) - 1u;
-    int it = 0;
-    for (int t = blockIdx.x; t < ntiles; t += gridDim.x, ++it) {
-      const int buf = it & 1;
-      const uint32_t bph = (uint32_t)(it >> 1) & 1u;
+    const float4* w4 = reinterpret_cast<const float4*>(w_smem);
+    for (int t = blockIdx.x + group * gridDim.x, it = group; t < ntiles; t += 2 * gridDim.x, it += 2) {
+      const int buf = it % kIdxBufs;
+      const uint32_t bph = (uint32_t)(it / kIdxBufs) & 1u;
+      const int key = t * kIdxTile + key_in_tile;
+      const bool valid = key < len;
+      // the key's scale is asked for before the wait: its memory latency hides behind the tile's
+      // copy and MMAs instead of sitting at the end of the epilogue
+      float scale = 1.f;
+      if constexpr (kFp8) {
+        if (p.k_scale != nullptr && valid) scale = __ldg(p.k_scale + (int64_t)row * p.k_scale_stride + key);
+      }
       if (!mbar_wait(&tfull[buf], bph, abort_flag)) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)buf * kIdxHeads;
-      float logit = 0.f;
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t v[32];
-        tmem_ld32(taddr + (uint32_t)half * 32u, v);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-        for (int j = 0; j < 32; ++j) logit = fmaf(w_smem[half * 32 + j], fmaxf(__uint_as_float(v[j]), 0.f), logit);
-      }
+      uint32_t v0[32], v1[32];
+      tmem_ld32(taddr, v0);
+      tmem_ld32(taddr + 32u, v1);
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      mbar_arrive(&tempty[buf]);  // the accumulator buffer may be overwritten
-      const int key = t * kIdxTile + key_in_tile;
-      const bool valid = key < len;
+      mbar_arrive(&tempty[buf]);  // the values are in registers: the accumulator buffer may be overwritten
+      float acc0 = 0.f, acc1 = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float4 wa = w4[j], wb = w4[8 + j];
+        acc0 = fmaf(wa.x, fmaxf(__uint_as_float(v0[4 * j + 0]), 0.f), acc0);
+        acc1 = fmaf(wb.x, fmaxf(__uint_as_float(v1[4 * j + 0]), 0.f), acc1);
+        acc0 = fmaf(wa.y, fmaxf(__uint_as_float(v0[4 * j + 1]), 0.f), acc0);
+        acc1 = fmaf(wb.y, fmaxf(__uint_as_float(v1[4 * j + 1]), 0.f), acc1);
+        acc0 = fmaf(wa.z, fmaxf(__uint_as_float(v0[4 * j + 2]), 0.f), acc0);
+        acc1 = fmaf(wb.z, fmaxf(__uint_as_float(v1[4 * j + 2]), 0.f), acc1);
+        acc0 = fmaf(wa.w, fmaxf(__uint_as_float(v0[4 * j + 3]), 0.f), acc0);
+        acc1 = fmaf(wb.w, fmaxf(__uint_as_float(v1[4 * j + 3]), 0.f), acc1);
+      }
+      // relu(s * x) = s * relu(x) for a positive scale: the key's scale multiplies the finished sum
+      const float logit = (acc0 + acc1) * scale;
       if (filter_mode) {
         const bool hit = valid && !(logit < edge);
         const unsigned b = __ballot_sync(kFull, hit);
@@ -318,7 +371,8 @@ __global__ void __launch_bounds__(kIdxThreads, 1)
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (warp == 1) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(128u) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(kIdxBufs * kIdxHeads))
+                 : "memory");
   }
 }
 
@@ -349,8 +403,8 @@ __global__ void __launch_bounds__(NT, 1)
   }
   MergeSmem sm;
   sm.hist = reinterpret_cast<uint32_t*>(smem_raw);
-  sm.sup = sm.hist + kMaxBins;
-  sm.xch = sm.sup + kSup;
+  sm.sup = sm.hist + 2 * kMaxBins;
+  sm.xch = sm.sup + 2 * kSup;
   sm.ctrl = reinterpret_cast<Ctrl*>(sm.xch + kMaxCluster * kSup);
   sm.cand = reinterpret_cast<uint64_t*>(reinterpret_cast<unsigned char*>(sm.ctrl) + ((sizeof(Ctrl) + 127) & ~127u));
   sm.cand_cap = G * kK;
@@ -375,11 +429,13 @@ DeviceOnce g_indexer_once[kMaxDevices];
 EncodeTiledFn g_encode = nullptr;
 std::mutex g_encode_mu;
 
-constexpr size_t indexer_smem_bytes() {
-  return 1024 + (size_t)kIdxStages * kIdxTileBytes + kIdxQBytes + kIdxHeads * 4 + 16 * 8 + 64;
+constexpr size_t indexer_smem_bytes(bool fp8) {
+  return 1024 +
+         (fp8 ? (size_t)IdxFmt<true>::kStages * IdxFmt<true>::kTileBytes : (size_t)IdxFmt<false>::kStages * IdxFmt<false>::kTileBytes) +
+         (fp8 ? IdxFmt<true>::kQBytes : IdxFmt<false>::kQBytes) + kIdxHeads * 4 + 32 * 8 + 64;
 }
 size_t finish_smem_bytes() {
-  return (size_t)(kMaxBins + kSup + kMaxCluster * kSup) * 4 + ((sizeof(Ctrl) + 127) & ~(size_t)127) +
+  return (size_t)(2 * kMaxBins + 2 * kSup + kMaxCluster * kSup) * 4 + ((sizeof(Ctrl) + 127) & ~(size_t)127) +
          (size_t)kIdxCandShards * kK * 8;
 }
 
@@ -400,8 +456,11 @@ int indexer_setup() {
     }
   }
   return g_indexer_once[dev].run([&] {
-    cudaError_t e2 = cudaFuncSetAttribute(indexer_logits_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          (int)indexer_smem_bytes());
+    cudaError_t e2 = cudaFuncSetAttribute(indexer_logits_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          (int)indexer_smem_bytes(false));
+    if (e2 != cudaSuccess) return cuda_fail(e2);
+    e2 = cudaFuncSetAttribute(indexer_logits_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              (int)indexer_smem_bytes(true));
     if (e2 != cudaSuccess) return cuda_fail(e2);
     e2 = cudaFuncSetAttribute(indexer_finish_kernel<512>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)finish_smem_bytes());
     if (e2 != cudaSuccess) return cuda_fail(e2);
@@ -409,13 +468,15 @@ int indexer_setup() {
   });
 }
 
-// [rows, 128] bf16, row pitch `pitch_elems`, boxes of 64 elements x box_rows rows, 128-byte swizzle
-int make_map(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t pitch_elems, uint32_t box_rows) {
+// [rows, 128] bf16 or fp8 (one byte), row pitch `pitch_elems`, boxes of 128 bytes x box_rows rows,
+// 128-byte swizzle
+int make_map(CUtensorMap* map, const void* ptr, bool fp8, uint64_t rows, uint64_t pitch_elems, uint32_t box_rows) {
   const cuuint64_t gdim[2] = {(cuuint64_t)kIdxDim, (cuuint64_t)rows};
-  const cuuint64_t gstride[1] = {(cuuint64_t)pitch_elems * 2};
-  const cuuint32_t box[2] = {(cuuint32_t)kIdxChunk, box_rows};
+  const cuuint64_t gstride[1] = {(cuuint64_t)pitch_elems * (fp8 ? 1 : 2)};
+  const cuuint32_t box[2] = {(cuuint32_t)(fp8 ? 128 : 64), box_rows};
   const cuuint32_t estr[2] = {1, 1};
-  const CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), gdim, gstride, box, estr,
+  const CUresult r = g_encode(map, fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                              const_cast<void*>(ptr), gdim, gstride, box, estr,
                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : FFTOPK_EINVAL;
@@ -445,11 +506,12 @@ size_t fftopk_indexer_workspace_bytes(int32_t B) {
   return indexer_layout(B).total;
 }
 
-int fftopk_indexer_topk2048(const void* q, const void* k_cache, int64_t k_rows_per_seq, const float* w, int32_t B, int64_t L,
-                            const int32_t* lengths, uint32_t* thresholds, uint32_t margin, float* logits,
-                            int64_t logits_stride, int32_t* out_idx, void* d_workspace, size_t workspace_bytes,
-                            uint32_t* status, void* cuda_stream) {
+static int indexer_topk_impl(bool fp8, const void* q, const void* k_cache, int64_t k_rows_per_seq, const float* k_scale,
+                             int64_t k_scale_stride, const float* w, int32_t B, int64_t L, const int32_t* lengths,
+                             uint32_t* thresholds, uint32_t margin, float* logits, int64_t logits_stride, int32_t* out_idx,
+                             void* d_workspace, size_t workspace_bytes, uint32_t* status, void* cuda_stream) {
   if (B < 0 || L < 0 || k_rows_per_seq < L || logits_stride < L) return FFTOPK_EINVAL;
+  if (k_scale != nullptr && k_scale_stride < L) return FFTOPK_EINVAL;
   if (B == 0) return FFTOPK_OK;
   if (!q || !k_cache || !w || !lengths || !thresholds || !logits || !out_idx || !d_workspace) return FFTOPK_EINVAL;
   if (((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k_cache)) & 15u) != 0) return FFTOPK_EINVAL;
@@ -467,14 +529,16 @@ int fftopk_indexer_topk2048(const void* q, const void* k_cache, int64_t k_rows_p
   char* ws = static_cast<char*>(d_workspace);
 
   CUtensorMap map_q, map_k;
-  rc = make_map(&map_q, q, (uint64_t)B * kIdxHeads, kIdxDim, kIdxHeads);
+  rc = make_map(&map_q, q, fp8, (uint64_t)B * kIdxHeads, kIdxDim, kIdxHeads);
   if (rc) return rc;
-  rc = make_map(&map_k, k_cache, (uint64_t)B * (uint64_t)k_rows_per_seq, kIdxDim, kIdxTile);
+  rc = make_map(&map_k, k_cache, fp8, (uint64_t)B * (uint64_t)k_rows_per_seq, kIdxDim, kIdxTile);
   if (rc) return rc;
 
   IndexerParams p;
   memset(&p, 0, sizeof(p));
   p.w = w;
+  p.k_scale = k_scale;
+  p.k_scale_stride = k_scale_stride;
   p.lengths = lengths;
   p.k_rows_per_seq = k_rows_per_seq;
   p.B = B;
@@ -500,7 +564,11 @@ int fftopk_indexer_topk2048(const void* q, const void* k_cache, int64_t k_rows_p
   if (per_row > ntiles) per_row = (int)ntiles;
   const dim3 grid((unsigned)per_row, (unsigned)B);
   // pass 1: rows with a guess are filtered as their logits are produced; the others get logits
-  indexer_logits_kernel<<<grid, kIdxThreads, indexer_smem_bytes(), stream>>>(map_q, map_k, p);
+  if (fp8) {
+    indexer_logits_kernel<true><<<grid, kIdxThreads, indexer_smem_bytes(true), stream>>>(map_q, map_k, p);
+  } else {
+    indexer_logits_kernel<false><<<grid, kIdxThreads, indexer_smem_bytes(false), stream>>>(map_q, map_k, p);
+  }
   e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e);
   // decide per row; rows whose guess held are finished here
@@ -525,7 +593,11 @@ int fftopk_indexer_topk2048(const void* q, const void* k_cache, int64_t k_rows_p
   // pass 2 (marked rows only): write the logits the first pass did not
   IndexerParams p2 = p;
   p2.only_rows = rewrite_rows;
-  indexer_logits_kernel<<<grid, kIdxThreads, indexer_smem_bytes(), stream>>>(map_q, map_k, p2);
+  if (fp8) {
+    indexer_logits_kernel<true><<<grid, kIdxThreads, indexer_smem_bytes(true), stream>>>(map_q, map_k, p2);
+  } else {
+    indexer_logits_kernel<false><<<grid, kIdxThreads, indexer_smem_bytes(false), stream>>>(map_q, map_k, p2);
+  }
   e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e);
   // the selector on the logits of the rows without a usable guess; it hands back their thresholds
@@ -542,6 +614,23 @@ int fftopk_indexer_topk2048(const void* q, const void* k_cache, int64_t k_rows_p
   c.only_rows = select_rows;
   c.may_overlap = false;
   return launch_select(c);
+}
+
+int fftopk_indexer_topk2048(const void* q, const void* k_cache, int64_t k_rows_per_seq, const float* w, int32_t B, int64_t L,
+                            const int32_t* lengths, uint32_t* thresholds, uint32_t margin, float* logits,
+                            int64_t logits_stride, int32_t* out_idx, void* d_workspace, size_t workspace_bytes,
+                            uint32_t* status, void* cuda_stream) {
+  return indexer_topk_impl(false, q, k_cache, k_rows_per_seq, nullptr, 0, w, B, L, lengths, thresholds, margin, logits,
+                           logits_stride, out_idx, d_workspace, workspace_bytes, status, cuda_stream);
+}
+
+int fftopk_indexer_topk2048_fp8(const void* q, const void* k_cache, int64_t k_rows_per_seq, const float* k_scale,
+                                int64_t k_scale_stride, const float* w, int32_t B, int64_t L, const int32_t* lengths,
+                                uint32_t* thresholds, uint32_t margin, float* logits, int64_t logits_stride,
+                                int32_t* out_idx, void* d_workspace, size_t workspace_bytes, uint32_t* status,
+                                void* cuda_stream) {
+  return indexer_topk_impl(true, q, k_cache, k_rows_per_seq, k_scale, k_scale_stride, w, B, L, lengths, thresholds, margin,
+                           logits, logits_stride, out_idx, d_workspace, workspace_bytes, status, cuda_stream);
 }
 
 }  // extern "C"

@@ -56,8 +56,8 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
 
 // Shared memory a CTA brings to the merge of one row.
 struct MergeSmem {
-  uint32_t* hist;  // kMaxBins words
-  uint32_t* sup;   // kSup words
+  uint32_t* hist;  // 2 * kMaxBins words: the histogram of the top 12 key bits, then the finer one (bits [27:16])
+  uint32_t* sup;   // 2 * kSup words
   uint32_t* xch;   // kMaxCluster * kSup words
   Ctrl* ctrl;
   uint64_t* cand;  // the first CTA's gather area (the same offset in every CTA)
@@ -77,10 +77,13 @@ struct MergeCtx {
 // CTA g waits (fused mode, bounded) for shard g's epoch flag and pulls that shard's 2048
 // (key, global index) candidates of the row into registers - from local memory after an
 // all-gather, from the owner's memory over NVLink in fused mode, G CTAs pulling in parallel - and
-// histograms their top 12 key bits. After ONE cluster barrier every CTA finds the threshold bin
+// histograms their top 12 key bits and, 16 times finer, key bits [27:16] (candidate lists are the
+// upper tail of a row: they nearly always share their top four key bits, and then the finer
+// histogram is the one searched). After ONE cluster barrier every CTA finds the threshold bin
 // from its peers' histograms over distributed shared memory (cluster_pick), writes its own
 // candidates above that bin straight to the output and sends those inside it to the first CTA,
-// which after the second cluster barrier finishes on that one bin with a known key range.
+// which after the second cluster barrier finishes on that one bin with a known key range - by
+// direct ranking when the bin holds at most 256 candidates.
 // Composites carry the inverted global index, so equal values resolve to the lower global index.
 //   sidx, skey  shard g's candidates of this row (ranks >= G: unused)
 //   sflag       shard g's epoch flag, or nullptr for "no wait"
@@ -114,10 +117,11 @@ __device__ __forceinline__ void merge_row(cg::cluster_group& cluster, int C, int
   uint64_t* cand0 = C == 1 ? sm.cand : cluster.map_shared_rank(sm.cand, 0);
   {
     uint4* h4 = reinterpret_cast<uint4*>(hist);
-    for (int i = tid; i < kMaxBins / 4; i += NT) h4[i] = make_uint4(0u, 0u, 0u, 0u);
+    for (int i = tid; i < 2 * kMaxBins / 4; i += NT) h4[i] = make_uint4(0u, 0u, 0u, 0u);
     if (tid < kSup) {
       ctrl->tot[0][tid] = 0u;  // (the buffers with index 1 are cleared by the search)
       ctrl->tot2[0][tid] = 0u;
+      ctrl->totb[tid] = 0u;
     }
     if (tid == 0) {
       ctrl->merge_fail = 0u;
@@ -200,11 +204,13 @@ __device__ __forceinline__ void merge_row(cg::cluster_group& cluster, int C, int
     const bool v = idx[u] >= 0;
     cnt += v ? 1u : 0u;
     hist_add(hist, key[u] >> 20, v);
+    hist_add(hist + kMaxBins, (key[u] >> 16) & 0xfffu, v);
   }
   cnt = __reduce_add_sync(kFull, cnt);
   if (lane == 0) ctrl->wtot[warp] = cnt;
   __syncthreads();
   compute_sup<NT>(hist, sm.sup, kMaxBins);
+  compute_sup<NT>(hist + kMaxBins, sm.sup + kSup, kMaxBins);
   if (warp == 0) {
     const uint32_t c = __reduce_add_sync(kFull, lane < NW ? ctrl->wtot[lane] : 0u);
     if (lane == 0) ctrl->merge_count = c;
@@ -277,17 +283,20 @@ __device__ __forceinline__ void merge_row(cg::cluster_group& cluster, int C, int
   int pick_no = 0;
   cluster_pick<NT>(
       cluster, G, hist, sm.sup, sm.xch, ctrl, pick_no, kMaxBins, [&](uint32_t) { return (uint32_t)kK; },
-      [&](Picked& pk) { decide_and_allocate(cx, pk, kModeAbort, false); });
+      [&](Picked& pk) { decide_and_allocate(cx, pk, kModeAbort, false); }, hist + kMaxBins, sm.sup + kSup);
   FFTOPK_MARK(65);
   const int mode = ctrl->mode;
-  const uint32_t t = (uint32_t)ctrl->t;
+  // the threshold bin as a key prefix: 12 bits, or 16 when the finer histogram was searched
+  const bool fine_bins = ctrl->dual_b != 0u;
+  const int pshift = fine_bins ? 16 : 20;
+  const uint32_t t = fine_bins ? ((ctrl->dual_g << 12) | (uint32_t)ctrl->t) : (uint32_t)ctrl->t;
   if (mode == kModeGather || mode == kModeTakeAll) {
     const uint32_t base_w = ctrl->base_w, base_c = ctrl->base_c;
     const bool take_eq = mode == kModeTakeAll;
 #pragma unroll
     for (int u = 0; u < PER; ++u) {
       if (idx[u] >= 0) {
-        const uint32_t bin = key[u] >> 20;
+        const uint32_t bin = key[u] >> pshift;
         if (bin > t || (take_eq && bin == t)) {
           const uint32_t pos = base_w + warp_alloc(&ctrl->wslot);
           if (FFTOPK_CHECK(12, pos, kK, status) && pos < (uint32_t)kK) {
@@ -309,10 +318,10 @@ __device__ __forceinline__ void merge_row(cg::cluster_group& cluster, int C, int
   if (mode == kModeGather) {
     const uint32_t need = ctrl->above;
     const DenseCands<NT> bin_cands{sm.cand, (int)ctrl->cand_count};
-    const uint64_t lo = (uint64_t)t << 52;
-    const uint64_t cap = lo | ((1ull << 52) - 1ull);
+    const uint64_t lo = (uint64_t)t << (32 + pshift);
+    const uint64_t cap = lo | ((1ull << (32 + pshift)) - 1ull);
     cta_finish<NT, DenseCands<NT>, kTrackMin>(bin_cands, need, lo, cap, cap, false, 31, hist, ctrl, out_idx, out_key,
-                                              (uint32_t)kK - need, (uint32_t)kK, 0, status);
+                                              (uint32_t)kK - need, (uint32_t)kK, 0, status, nullptr, ctrl->cand_count);
   } else if (mode != kModeTakeAll) {
     if (tid == 0 && status) atomicOr(status, (uint32_t)FFTOPK_ST_INTERNAL);
   }
@@ -322,7 +331,7 @@ __device__ __forceinline__ void merge_row(cg::cluster_group& cluster, int C, int
       if (tid == 0) {
         uint32_t thr = 0u;
         if (mode == kModeGather && ctrl->thr_key != 0xffffffffu) thr = ctrl->thr_key;
-        if (mode == kModeTakeAll) thr = t << 20;  // the whole bin won: its lower edge
+        if (mode == kModeTakeAll) thr = t << pshift;  // the whole bin won: its lower edge
         *thr_out = thr;
       }
     }

@@ -1245,7 +1245,7 @@ __device__ __forceinline__ void select_row(const SelectParams& p) {
       const uint64_t cap = r < 0 ? high_end(fin_cap) : (lo | ((1ull << (32 + sh)) - 1ull));
       const DenseCands<NT> src{cx.cand, (int)min(ctrl->cand_count, (uint32_t)p.cand_cap)};
       cta_finish<NT, DenseCands<NT>, kWarm>(src, need, lo, cap, cap, false, idx_bits, cx.hist(0), ctrl, out_idx, out_key,
-                                            K - need, K, cx.idx_offset, p.status, cx.page, r < 0 ? (uint32_t)src.n : 0u);
+                                            K - need, K, cx.idx_offset, p.status, cx.page, (uint32_t)src.n);
     }
   }
   if constexpr (kWarm) {

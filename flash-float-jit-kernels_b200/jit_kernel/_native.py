@@ -51,6 +51,7 @@ EXPORTS = (
     "fftopk_select2048_host",
     "fftopk_indexer_workspace_bytes",
     "fftopk_indexer_topk2048",
+    "fftopk_indexer_topk2048_fp8",
     "fftopk_probe_read_bandwidth",
     "fftopk_key_of",
     "fftopk_plan",
@@ -153,6 +154,10 @@ def lib() -> ctypes.CDLL:
     L.fftopk_indexer_topk2048.argtypes = [c.c_void_p, c.c_void_p, c.c_int64, c.c_void_p, c.c_int32, c.c_int64, c.c_void_p,
                                           c.c_void_p, c.c_uint32, c.c_void_p, c.c_int64, c.c_void_p, c.c_void_p, c.c_size_t,
                                           c.c_void_p, c.c_void_p]
+    L.fftopk_indexer_topk2048_fp8.restype = c.c_int
+    L.fftopk_indexer_topk2048_fp8.argtypes = [c.c_void_p, c.c_void_p, c.c_int64, c.c_void_p, c.c_int64, c.c_void_p, c.c_int32,
+                                              c.c_int64, c.c_void_p, c.c_void_p, c.c_uint32, c.c_void_p, c.c_int64,
+                                              c.c_void_p, c.c_void_p, c.c_size_t, c.c_void_p, c.c_void_p]
     L.fftopk_probe_read_bandwidth.restype = c.c_int
     L.fftopk_probe_read_bandwidth.argtypes = [c.c_void_p, c.c_size_t, c.c_size_t, c.c_void_p, c.POINTER(c.c_size_t),
                                               c.c_void_p]

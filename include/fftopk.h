@@ -330,6 +330,16 @@ int fftopk_select2048_host(const float* h_score, int64_t h_row_stride, int32_t B
  * any stream capture). B <= 65535.
  */
 size_t fftopk_indexer_workspace_bytes(int32_t B);
+/* The same for fp8 (e4m3) operands, the storage format of the key cache this indexer was designed
+ * around: q [B, 64, 128] and k_cache [B, k_rows_per_seq, 128] are one byte per element (half the
+ * HBM traffic of the bf16 form), accumulation is fp32. k_scale, when given, is a device fp32 array
+ * [B, k_scale_stride] (k_scale_stride >= L) with one POSITIVE scale per key, multiplied into the
+ * key's finished logit (relu(s x) = s relu(x)); a scale of q belongs in w. */
+int fftopk_indexer_topk2048_fp8(const void* q, const void* k_cache, int64_t k_rows_per_seq,
+                                const float* k_scale, int64_t k_scale_stride, const float* w, int32_t B,
+                                int64_t L, const int32_t* lengths, uint32_t* thresholds, uint32_t margin,
+                                float* logits, int64_t logits_stride, int32_t* out_idx, void* d_workspace,
+                                size_t workspace_bytes, uint32_t* status, void* cuda_stream);
 int fftopk_indexer_topk2048(const void* q, const void* k_cache, int64_t k_rows_per_seq, const float* w,
                             int32_t B, int64_t L, const int32_t* lengths, uint32_t* thresholds,
                             uint32_t margin, float* logits, int64_t logits_stride, int32_t* out_idx,

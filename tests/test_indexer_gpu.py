@@ -146,3 +146,40 @@ def test_graph_replay():
         torch.cuda.synchronize()
         orc.check_result(logits_np, ln.cpu().numpy(), out.cpu().numpy(), what="indexer replay")
     assert kernel_status(DEV) == 0
+
+
+def make_fp8(B, L, seed):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    q = (torch.randn(B, 64, 128, generator=g) * 0.5).to(torch.float8_e4m3fn)
+    k = (torch.randn(B, L, 128, generator=g) * 0.5).to(torch.float8_e4m3fn)
+    w = torch.rand(B, 64, generator=g)
+    scale = torch.rand(B, L, generator=g) * 1.5 + 0.25  # positive per-key scales
+    return q.to(DEV), k.to(DEV), w.to(DEV), scale.to(DEV)
+
+
+@pytest.mark.parametrize("with_scale", [False, True])
+@pytest.mark.parametrize("B,L", [(1, 4096), (2, 70000), (1, 300000)])
+def test_fp8_operands(B, L, with_scale):
+    """fp8 (e4m3) q and key cache, optional per-key scale: logits against torch on the widened
+    operands, selection exact on the kernel's own logits, cold and with a guess."""
+    q, k, w, scale = make_fp8(B, L, seed=L + B)
+    ks = scale if with_scale else None
+    ln = torch.full((B,), L, dtype=torch.int32)
+    if B > 1:
+        ln[1] = L - 333
+    f = FusedIndexerTopk(B, L)
+    out = f(q, k, w, ln.to(DEV), k_scale=ks)
+    torch.cuda.synchronize()
+    got = f.logits[:B, :L].cpu()
+    ref = reference_logits(q, k, w, ks).cpu()
+    for b in range(B):
+        n = int(ln[b])
+        assert float((got[b, :n] - ref[b, :n]).abs().max()) <= LOGIT_RTOL * float(ref[b, :n].abs().max()), f"row {b}"
+    logits_np = got.numpy().copy()
+    orc.check_result(logits_np, ln.numpy(), out.cpu().numpy(), what="fp8 cold")
+    for rep in range(2):
+        out = f(q, k, w, ln.to(DEV), k_scale=ks)
+        torch.cuda.synchronize()
+        orc.check_result(logits_np, ln.numpy(), out.cpu().numpy(), what=f"fp8 warm {rep}")
+    assert np.array_equal(f.thresholds.cpu().numpy().view(np.uint32)[:B], kth_keys(logits_np, ln.numpy()))
+    assert kernel_status(DEV) == 0
