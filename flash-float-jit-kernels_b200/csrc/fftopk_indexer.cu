@@ -66,8 +66,6 @@ struct IdxFmt {
   static constexpr uint32_t kInstrDesc = (1u << 4) | ((kFp8 ? 0u : 1u) << 7) | ((kFp8 ? 0u : 1u) << 10) |
                                          ((uint32_t)(kIdxHeads >> 3) << 17) | ((uint32_t)(kIdxTile >> 4) << 24);
 };
-constexpr uint32_t kIdxMaxTileBytes = IdxFmt<false>::kTileBytes;
-constexpr uint32_t kIdxMaxQBytes = IdxFmt<false>::kQBytes;
 constexpr int kIdxBufs = 4;         // TMEM accumulators of 64 columns: the MMAs run up to four tiles ahead of the epilogue
 constexpr int kIdxCandShards = 8;  // the candidate list of a row: 8 x 2048 slots, the merge's layout
 constexpr unsigned long long kIdxWaitNs = 200ull * 1000 * 1000;

@@ -27,7 +27,7 @@
 extern "C" {
 #endif
 
-#define FFTOPK_K 2048 /* the only supported k (reference: TopK, topk_indexer_radix.cu:69) */
+#define FFTOPK_K 2048 /* k of the reference's op (TopK, topk_indexer_radix.cu:69); fftopk_select_topk takes others */
 
 enum {
   FFTOPK_OK = 0,
