@@ -47,6 +47,15 @@
 
 namespace fftopk {
 
+// Build-time knobs (optional, for experiments; the defaults are what was measured best):
+//   FFTOPK_IDX_STAGES_FP8   key tiles in flight per CTA for fp8 operands (8 x 16 KiB)
+//   FFTOPK_IDX_CTAS_PER_SM  producer CTAs per SM (1); with 2 the stages must fit twice into shared memory
+#ifndef FFTOPK_IDX_STAGES_FP8
+#define FFTOPK_IDX_STAGES_FP8 8
+#endif
+#ifndef FFTOPK_IDX_CTAS_PER_SM
+#define FFTOPK_IDX_CTAS_PER_SM 1
+#endif
 constexpr int kIdxHeads = 64;
 constexpr int kIdxDim = 128;
 constexpr int kIdxTile = 128;      // keys per tile = rows of the MMA
@@ -61,7 +70,7 @@ struct IdxFmt {
   static constexpr uint32_t kTileBytes = kIdxTile * kIdxDim * kElemBytes;   // 32 / 16 KiB
   static constexpr uint32_t kQBytes = kIdxHeads * kIdxDim * kElemBytes;     // 16 / 8 KiB
   static constexpr int kMmaPerBox = 4;                            // 128 bytes of K per box / 32 bytes per MMA
-  static constexpr int kStages = kFp8 ? 8 : 4;                    // key tiles in flight: 128 KiB either way
+  static constexpr int kStages = kFp8 ? FFTOPK_IDX_STAGES_FP8 : 4 / FFTOPK_IDX_CTAS_PER_SM;  // key tiles in flight: 128 KiB either way
   // instruction descriptor: D fp32; A and B bf16 (format 1) or e4m3 (format 0), both K-major; M = 128, N = 64
   static constexpr uint32_t kInstrDesc = (1u << 4) | ((kFp8 ? 0u : 1u) << 7) | ((kFp8 ? 0u : 1u) << 10) |
                                          ((uint32_t)(kIdxHeads >> 3) << 17) | ((uint32_t)(kIdxTile >> 4) << 24);
@@ -181,7 +190,7 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
 
 // ---- producer --------------------------------------------------------------------------------------
 template <bool kFp8>
-__global__ void __launch_bounds__(kIdxThreads, 1)
+__global__ void __launch_bounds__(kIdxThreads, FFTOPK_IDX_CTAS_PER_SM)
     indexer_logits_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                           const IndexerParams p) {
   using F = IdxFmt<kFp8>;
@@ -558,7 +567,7 @@ static int indexer_topk_impl(bool fp8, const void* q, const void* k_cache, int64
   if (e != cudaSuccess) return cuda_fail(e);
 
   const int64_t ntiles = (L + kIdxTile - 1) / kIdxTile;
-  int per_row = sms / B > 0 ? sms / B : 1;
+  int per_row = sms * FFTOPK_IDX_CTAS_PER_SM / B > 0 ? sms * FFTOPK_IDX_CTAS_PER_SM / B : 1;
   if (per_row > ntiles) per_row = (int)ntiles;
   const dim3 grid((unsigned)per_row, (unsigned)B);
   // pass 1: rows with a guess are filtered as their logits are produced; the others get logits
