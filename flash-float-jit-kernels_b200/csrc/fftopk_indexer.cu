@@ -6,7 +6,7 @@
 // the step (README.md:24) - so there is no reference counterpart; this is the step in front of the
 // hot path, fused with it.
 //
-// Producer kernel, one CTA per (row, slice of key tiles), 320 threads in three roles:
+// Producer kernel, one CTA per (row, slice of key tiles), two CTAs per SM, 320 threads in three roles:
 //   warp 0      one thread issues TMA loads (cp.async.bulk.tensor, 128-byte swizzle, no multicast):
 //               the row's q once (64 heads x 128), then key tiles of 128 keys x 128 through a ring
 //               of shared-memory stages guarded by full / empty mbarriers;
@@ -48,13 +48,16 @@
 namespace fftopk {
 
 // Build-time knobs (optional, for experiments; the defaults are what was measured best):
-//   FFTOPK_IDX_STAGES_FP8   key tiles in flight per CTA for fp8 operands (8 x 16 KiB)
-//   FFTOPK_IDX_CTAS_PER_SM  producer CTAs per SM (1); with 2 the stages must fit twice into shared memory
-#ifndef FFTOPK_IDX_STAGES_FP8
-#define FFTOPK_IDX_STAGES_FP8 8
-#endif
+//   FFTOPK_IDX_CTAS_PER_SM  producer CTAs per SM (2: two independent TMA -> MMA -> epilogue pipelines
+//                           per SM hide each other's per-tile latencies; measured at B=1, L=1M, fp8:
+//                           40.0 us per call against 45.1 with one CTA per SM, bf16: 56.2 / 56.6)
+//   FFTOPK_IDX_STAGES_FP8   key tiles in flight per CTA for fp8 operands (4 x 16 KiB; 12 stages on
+//                           one CTA per SM: 46.7 us, no gain over 8)
 #ifndef FFTOPK_IDX_CTAS_PER_SM
-#define FFTOPK_IDX_CTAS_PER_SM 1
+#define FFTOPK_IDX_CTAS_PER_SM 2
+#endif
+#ifndef FFTOPK_IDX_STAGES_FP8
+#define FFTOPK_IDX_STAGES_FP8 (8 / FFTOPK_IDX_CTAS_PER_SM)
 #endif
 constexpr int kIdxHeads = 64;
 constexpr int kIdxDim = 128;
