@@ -25,11 +25,15 @@
 // Every wait on an mbarrier has a time limit; when one runs out the CTA raises
 // FFTOPK_ST_STAGE_TIMEOUT, lets its copies in flight land, frees its TMEM and returns.
 //
-// Finish kernel (one 8-CTA cluster per row): if the row's guess held - at least 2048 candidates, no
-// more than the list holds - merge_row selects the exact top 2048 of the list (ties to the lower
-// index) and hands back the new threshold; otherwise the row is marked, a second pass of the
-// producer writes its logits and the selector of fftopk_select.cu runs on them (rows that are not
-// marked cost those two launches nothing but an empty CTA).
+// Finish, inside the producer: the CTAs of a row count themselves off as they run out of tiles, and
+// the last one decides. If the row's guess held - at least 2048 candidates, no more than the list
+// holds - it pulls the list into the shared memory its stages no longer need and selects the exact
+// top 2048 (cta_finish: ties to the lower index) and the new threshold; otherwise it marks the row,
+// a second pass of the producer writes the row's logits and the selector of fftopk_select.cu runs on
+// them. Both of those launches follow as programmatic dependents: they are resident, waiting, by the
+// time the first pass ends, and rows that are not marked cost them an empty CTA. The second pass
+// also zeroes the row's counters, so a call leaves the workspace ready for the next one and no
+// launch of a call is a memset.
 #include <cooperative_groups.h>
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -43,7 +47,6 @@
 #include "fftopk_host.h"
 #include "fftopk_internal.h"
 #include "fftopk_key.h"
-#include "fftopk_merge.cuh"
 
 namespace fftopk {
 
@@ -79,7 +82,7 @@ struct IdxFmt {
                                          ((uint32_t)(kIdxHeads >> 3) << 17) | ((uint32_t)(kIdxTile >> 4) << 24);
 };
 constexpr int kIdxBufs = 4;         // TMEM accumulators of 64 columns: the MMAs run up to four tiles ahead of the epilogue
-constexpr int kIdxCandShards = 8;  // the candidate list of a row: 8 x 2048 slots, the merge's layout
+constexpr int kIdxCandCap = 8192;  // slots of a row's candidate list: what the freed stages of a CTA hold (64 KiB of composites)
 constexpr unsigned long long kIdxWaitNs = 200ull * 1000 * 1000;
 
 struct IndexerParams {
@@ -94,9 +97,13 @@ struct IndexerParams {
   int64_t logits_stride;
   const uint32_t* guess;     // [B] threshold key guesses (0: none) or nullptr
   uint32_t margin;
-  int32_t* cand_idx;         // [8, B, 2048] candidate indices (-1: empty), cand_key the same shape
-  uint32_t* cand_key;
-  uint32_t* cand_count;      // [B]
+  uint64_t* cand;            // [B, kIdxCandCap] candidates as (key << 32 | ~index) composites
+  uint32_t* cand_count;      // [B] candidates appended so far (may exceed the capacity: the row then falls back)
+  uint32_t* done_count;      // [B] CTAs of the row that have run out of tiles
+  uint32_t* rewrite_rows;    // [B] out: 1 = the row's logits have to be written by the second pass
+  uint32_t* select_rows;     // [B] out: 1 = the selector has to run on the row's logits
+  int32_t* out_idx;          // [B, 2048]
+  uint32_t* thr_out;         // [B] the row's new threshold key (rows finished here)
   const uint32_t* only_rows; // second pass: rows with only_rows[b] != 0 get their logits written,
                              // the others are skipped; nullptr in the first pass
   uint32_t* status;
@@ -191,12 +198,73 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
       : "memory");
 }
 
+// ---- finish of one row, by the last of its CTAs to run out of tiles ----------------------------------
+// `gkey`: the key guess the row was filtered with (margin already subtracted). `cand_smem` holds
+// kIdxCandCap composites, `hist` kFinishBins words.
+template <int NT>
+__device__ __forceinline__ void indexer_finish_row(const IndexerParams& p, int row, int len, uint32_t gkey,
+                                                   uint64_t* cand_smem, uint32_t* hist, Ctrl* ctrl) {
+  const int tid = threadIdx.x;
+  const int lane = tid & 31, warp = tid >> 5;
+  const uint32_t count = __ldcg(p.cand_count + row);
+  const bool held = len > kK && count >= (uint32_t)kK && count <= (uint32_t)kIdxCandCap;
+  if (!held) {  // (uniform over the CTA)
+    if (tid == 0) {
+      p.rewrite_rows[row] = 1u;  // its logits were not written in the first pass
+      p.select_rows[row] = 1u;
+      if (p.status) atomicOr(p.status, (uint32_t)FFTOPK_ST_GUESS_MISSED);
+    }
+    return;
+  }
+  // the list, out of L2 (other SMs wrote it), eight loads in flight per thread
+  const uint64_t* src = p.cand + (size_t)row * kIdxCandCap;
+  uint32_t kmax = 0u;
+  for (uint32_t i0 = 0; i0 < count; i0 += 8u * NT) {
+    uint64_t c[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const uint32_t i = i0 + (uint32_t)u * NT + tid;
+      c[u] = i < count ? __ldcg(src + i) : 0ull;
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const uint32_t i = i0 + (uint32_t)u * NT + tid;
+      if (i < count) {
+        cand_smem[i] = c[u];
+        kmax = max(kmax, (uint32_t)(c[u] >> 32));
+      }
+    }
+  }
+  kmax = __reduce_max_sync(kFull, kmax);
+  if (lane == 0) ctrl->wmax[warp] = kmax;
+  if (tid == 0) ctrl->thr_key = 0xffffffffu;
+  __syncthreads();
+  kmax = 0u;
+#pragma unroll
+  for (int w = 0; w < NT / 32; ++w) kmax = max(kmax, ctrl->wmax[w]);
+  // every candidate's key lies in [the guess's lowest admitted key, kmax]
+  const uint64_t lo = (uint64_t)guess_low_key(gkey) << 32;
+  const uint64_t cap = ((uint64_t)kmax << 32) | 0xffffffffull;
+  const int idx_bits = 32 - __clz(len - 1);
+  const DenseCands<NT> list{cand_smem, (int)count};
+  cta_finish<NT, DenseCands<NT>, true>(list, (uint32_t)kK, lo, cap, cap, false, idx_bits, hist, ctrl,
+                                       p.out_idx + (int64_t)row * kK, nullptr, 0u, (uint32_t)kK, 0, p.status, nullptr, count);
+  __syncthreads();
+  if (tid == 0) {
+    p.thr_out[row] = ctrl->thr_key != 0xffffffffu ? ctrl->thr_key : 0u;
+    p.rewrite_rows[row] = 0u;
+    p.select_rows[row] = 0u;
+  }
+}
+
 // ---- producer --------------------------------------------------------------------------------------
 template <bool kFp8>
 __global__ void __launch_bounds__(kIdxThreads, FFTOPK_IDX_CTAS_PER_SM)
     indexer_logits_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                           const IndexerParams p) {
   using F = IdxFmt<kFp8>;
+  static_assert((size_t)F::kStages * F::kTileBytes >= (size_t)kIdxCandCap * 8, "the stages hold a row's candidate list");
+  static_assert(F::kQBytes >= (uint32_t)kFinishBins * 4u, "q's place holds the finish's histogram");
   constexpr uint32_t kIdxTileBytes = F::kTileBytes;
   constexpr uint32_t kIdxQBytes = F::kQBytes;
   constexpr int kIdxStages = F::kStages;
@@ -214,11 +282,23 @@ __global__ void __launch_bounds__(kIdxThreads, FFTOPK_IDX_CTAS_PER_SM)
   uint64_t* qfull = tempty + kIdxBufs;       // [1]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(qfull + 1);
   volatile uint32_t* abort_flag = tmem_slot + 1;
+  uint32_t* last_flag = tmem_slot + 2;
+  Ctrl* fin_ctrl = reinterpret_cast<Ctrl*>(reinterpret_cast<unsigned char*>(tmem_slot) + 16);  // (16-byte aligned)
 
   const int row = blockIdx.y;
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
-  if (p.only_rows != nullptr && p.only_rows[row] == 0u) return;  // (uniform over the CTA; nothing allocated yet)
+  // the launches of a call follow one another as programmatic dependents (see the host side)
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (p.only_rows != nullptr) {
+    // second pass: everything the first pass wrote - the marks above all - is visible after this
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (blockIdx.x == 0 && tid == 0) {  // the row's counters, for the next call
+      p.cand_count[row] = 0u;
+      p.done_count[row] = 0u;
+    }
+    if (p.only_rows[row] == 0u) return;  // (uniform over the CTA; nothing allocated yet)
+  }
   int64_t len64 = p.lengths[row];
   len64 = len64 < 0 ? 0 : (len64 > p.L ? p.L : len64);
   const int len = (int)len64;
@@ -227,6 +307,11 @@ __global__ void __launch_bounds__(kIdxThreads, FFTOPK_IDX_CTAS_PER_SM)
   if (guess != 0u) guess = guess > p.margin ? guess - p.margin : 1u;
   const bool filter_mode = guess != 0u;
   const float edge = __uint_as_float(guess_edge_bits(guess));
+  if (p.only_rows == nullptr && blockIdx.x == 0 && tid == 0 && (!filter_mode || ntiles == 0)) {
+    // no guess to test (or no key at all): the selector takes the row from its written logits
+    p.rewrite_rows[row] = 0u;
+    p.select_rows[row] = 1u;
+  }
   if ((int)blockIdx.x >= ntiles) return;  // (uniform)
 
   if (tid == 0) {
@@ -356,11 +441,9 @@ __global__ void __launch_bounds__(kIdxThreads, FFTOPK_IDX_CTAS_PER_SM)
           uint32_t slot = 0;
           if (lane == 0) slot = atomicAdd(p.cand_count + row, (uint32_t)__popc(b));
           slot = __shfl_sync(kFull, slot, 0) + (uint32_t)__popc(b & lt);
-          if (hit && slot < (uint32_t)(kIdxCandShards * kK)) {
-            const size_t at = ((size_t)(slot / kK) * p.B + row) * kK + (slot % kK);
-            p.cand_idx[at] = key;
-            p.cand_key[at] = fftopk_key_from_bits(__float_as_uint(logit));
-          }
+          if (hit && slot < (uint32_t)kIdxCandCap)
+            p.cand[(size_t)row * kIdxCandCap + slot] =
+                ((uint64_t)fftopk_key_from_bits(__float_as_uint(logit)) << 32) | (uint64_t)(~(uint32_t)key);
         }
       } else if (valid) {
         p.logits[(int64_t)row * p.logits_stride + key] = logit;
@@ -384,43 +467,22 @@ __global__ void __launch_bounds__(kIdxThreads, FFTOPK_IDX_CTAS_PER_SM)
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(kIdxBufs * kIdxHeads))
                  : "memory");
   }
-}
-
-// ---- finish: decide whether the guess held; if so, the exact top 2048 of the candidate list ------
-template <int NT>
-__global__ void __launch_bounds__(NT, 1)
-    indexer_finish_kernel(const int32_t* __restrict__ cand_idx, const uint32_t* __restrict__ cand_key,
-                          const uint32_t* __restrict__ cand_count, const uint32_t* __restrict__ guess,
-                          const int32_t* __restrict__ lengths, int B, int32_t* __restrict__ out_idx_all,
-                          uint32_t* __restrict__ thr_out, uint32_t* __restrict__ rewrite_rows,
-                          uint32_t* __restrict__ select_rows, uint32_t* status) {
-  extern __shared__ __align__(128) unsigned char smem_raw[];
-  constexpr int G = kIdxCandShards;
-  cg::cluster_group cluster = cg::this_cluster();
-  const int g = (int)cluster.block_rank();
-  const int row = (int)(blockIdx.x / (unsigned)G);
-  const uint32_t count = cand_count[row];
-  const uint32_t had_guess = guess != nullptr ? guess[row] : 0u;
-  const bool short_row = lengths[row] <= kK;
-  const bool held = had_guess != 0u && !short_row && count >= (uint32_t)kK && count <= (uint32_t)(G * kK);
-  if (!held) {  // (uniform over the cluster)
-    if (g == 0 && threadIdx.x == 0) {
-      rewrite_rows[row] = had_guess != 0u ? 1u : 0u;  // its logits were not written in the first pass
-      select_rows[row] = 1u;
-      if (had_guess != 0u && status) atomicOr(status, (uint32_t)FFTOPK_ST_GUESS_MISSED);
-    }
-    return;
+  if (!filter_mode) return;  // (uniform)
+  // ---- the row's CTAs count themselves off; the last one finishes the row ------------------------
+  __threadfence();  // this thread's candidates, before the CTA's arrival
+  __syncthreads();
+  if (tid == 0) {
+    // a CTA that gave up leaves the list incomplete: a count no list can hold sends the row to the fallback
+    if (*abort_flag) atomicAdd(p.cand_count + row, 0x40000000u);
+    const uint32_t nwork = (uint32_t)min((int)gridDim.x, ntiles);
+    *last_flag = atomicAdd(p.done_count + row, 1u) == nwork - 1u ? 1u : 0u;
   }
-  MergeSmem sm;
-  sm.hist = reinterpret_cast<uint32_t*>(smem_raw);
-  sm.sup = sm.hist + 2 * kMaxBins;
-  sm.xch = sm.sup + 2 * kSup;
-  sm.ctrl = reinterpret_cast<Ctrl*>(sm.xch + kMaxCluster * kSup);
-  sm.cand = reinterpret_cast<uint64_t*>(reinterpret_cast<unsigned char*>(sm.ctrl) + ((sizeof(Ctrl) + 127) & ~127u));
-  sm.cand_cap = G * kK;
-  const int64_t off = ((int64_t)g * B + row) * kK;
-  merge_row<NT, true>(cluster, G, G, g, sm, cand_idx + off, cand_key + off, nullptr, nullptr, 0u, 0ull,
-                      out_idx_all + (int64_t)row * kK, nullptr, status, thr_out + row);
+  __syncthreads();
+  if (*last_flag == 0u) return;  // (uniform)
+  __threadfence();
+  // every copy and MMA of this CTA has completed: the stages hold the list, q's place the histogram
+  indexer_finish_row<kIdxThreads>(p, row, len, guess, reinterpret_cast<uint64_t*>(a_smem), reinterpret_cast<uint32_t*>(q_smem),
+                                  fin_ctrl);
 }
 
 }  // namespace fftopk
@@ -442,11 +504,7 @@ std::mutex g_encode_mu;
 constexpr size_t indexer_smem_bytes(bool fp8) {
   return 1024 +
          (fp8 ? (size_t)IdxFmt<true>::kStages * IdxFmt<true>::kTileBytes : (size_t)IdxFmt<false>::kStages * IdxFmt<false>::kTileBytes) +
-         (fp8 ? IdxFmt<true>::kQBytes : IdxFmt<false>::kQBytes) + kIdxHeads * 4 + 32 * 8 + 64;
-}
-size_t finish_smem_bytes() {
-  return (size_t)(2 * kMaxBins + 2 * kSup + kMaxCluster * kSup) * 4 + ((sizeof(Ctrl) + 127) & ~(size_t)127) +
-         (size_t)kIdxCandShards * kK * 8;
+         (fp8 ? IdxFmt<true>::kQBytes : IdxFmt<false>::kQBytes) + kIdxHeads * 4 + 32 * 8 + 64 + sizeof(Ctrl);
 }
 
 int indexer_setup() {
@@ -472,8 +530,6 @@ int indexer_setup() {
     e2 = cudaFuncSetAttribute(indexer_logits_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                               (int)indexer_smem_bytes(true));
     if (e2 != cudaSuccess) return cuda_fail(e2);
-    e2 = cudaFuncSetAttribute(indexer_finish_kernel<512>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)finish_smem_bytes());
-    if (e2 != cudaSuccess) return cuda_fail(e2);
     return 0;
   });
 }
@@ -492,19 +548,37 @@ int make_map(CUtensorMap* map, const void* ptr, bool fp8, uint64_t rows, uint64_
   return r == CUDA_SUCCESS ? 0 : FFTOPK_EINVAL;
 }
 
+// Workspace: [candidate lists: B x kIdxCandCap composites][candidate counts: B words][arrival
+// counts: B words][rows whose logits the second pass writes: B words][rows the selector takes: B words]
 struct IndexerLayout {
-  size_t idx_off, key_off, count_off, rewrite_off, select_off, total;
+  size_t cand_off, count_off, done_off, rewrite_off, select_off, total;
 };
 IndexerLayout indexer_layout(int32_t B) {
   IndexerLayout l;
-  const size_t plane = (size_t)kIdxCandShards * B * kK * 4;
-  l.idx_off = 0;
-  l.key_off = plane;
-  l.count_off = 2 * plane;
-  l.rewrite_off = l.count_off + (((size_t)B * 4 + 255) & ~(size_t)255);
-  l.select_off = l.rewrite_off + (((size_t)B * 4 + 255) & ~(size_t)255);
-  l.total = l.select_off + (((size_t)B * 4 + 255) & ~(size_t)255);
+  const size_t words = ((size_t)B * 4 + 255) & ~(size_t)255;
+  l.cand_off = 0;
+  l.count_off = (size_t)B * kIdxCandCap * 8;
+  l.done_off = l.count_off + words;
+  l.rewrite_off = l.done_off + words;
+  l.select_off = l.rewrite_off + words;
+  l.total = l.select_off + words;
   return l;
+}
+
+template <bool kFp8>
+cudaError_t launch_producer(dim3 grid, cudaStream_t stream, bool dependent, const CUtensorMap& map_q, const CUtensorMap& map_k,
+                            const IndexerParams& p) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(kIdxThreads, 1, 1);
+  cfg.dynamicSmemBytes = indexer_smem_bytes(kFp8);
+  cfg.stream = stream;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = dependent ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, indexer_logits_kernel<kFp8>, map_q, map_k, p);
 }
 
 }  // namespace
@@ -557,58 +631,28 @@ static int indexer_topk_impl(bool fp8, const void* q, const void* k_cache, int64
   p.logits_stride = logits_stride;
   p.guess = thresholds;
   p.margin = margin;
-  p.cand_idx = reinterpret_cast<int32_t*>(ws + lay.idx_off);
-  p.cand_key = reinterpret_cast<uint32_t*>(ws + lay.key_off);
+  p.cand = reinterpret_cast<uint64_t*>(ws + lay.cand_off);
   p.cand_count = reinterpret_cast<uint32_t*>(ws + lay.count_off);
+  p.done_count = reinterpret_cast<uint32_t*>(ws + lay.done_off);
+  p.rewrite_rows = reinterpret_cast<uint32_t*>(ws + lay.rewrite_off);
+  p.select_rows = reinterpret_cast<uint32_t*>(ws + lay.select_off);
+  p.out_idx = out_idx;
+  p.thr_out = thresholds;
   p.status = status;
-  uint32_t* rewrite_rows = reinterpret_cast<uint32_t*>(ws + lay.rewrite_off);
-  uint32_t* select_rows = reinterpret_cast<uint32_t*>(ws + lay.select_off);
-
-  // empty candidate lists (index -1), counts and marks zero
-  e = cudaMemsetAsync(ws + lay.idx_off, 0xff, lay.key_off, stream);
-  if (e == cudaSuccess) e = cudaMemsetAsync(ws + lay.count_off, 0, lay.total - lay.count_off, stream);
-  if (e != cudaSuccess) return cuda_fail(e);
 
   const int64_t ntiles = (L + kIdxTile - 1) / kIdxTile;
   int per_row = sms * FFTOPK_IDX_CTAS_PER_SM / B > 0 ? sms * FFTOPK_IDX_CTAS_PER_SM / B : 1;
   if (per_row > ntiles) per_row = (int)ntiles;
   const dim3 grid((unsigned)per_row, (unsigned)B);
-  // pass 1: rows with a guess are filtered as their logits are produced; the others get logits
-  if (fp8) {
-    indexer_logits_kernel<true><<<grid, kIdxThreads, indexer_smem_bytes(true), stream>>>(map_q, map_k, p);
-  } else {
-    indexer_logits_kernel<false><<<grid, kIdxThreads, indexer_smem_bytes(false), stream>>>(map_q, map_k, p);
-  }
-  e = cudaGetLastError();
+  // pass 1: rows with a guess are filtered as their logits are produced and finished by their last
+  // CTA; the others get logits. (A plain launch: it orders itself after whatever the stream holds.)
+  e = fp8 ? launch_producer<true>(grid, stream, false, map_q, map_k, p) : launch_producer<false>(grid, stream, false, map_q, map_k, p);
   if (e != cudaSuccess) return cuda_fail(e);
-  // decide per row; rows whose guess held are finished here
-  {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)B * kIdxCandShards, 1, 1);
-    cfg.blockDim = dim3(512, 1, 1);
-    cfg.dynamicSmemBytes = finish_smem_bytes();
-    cfg.stream = stream;
-    cudaLaunchAttribute at[1];
-    at[0].id = cudaLaunchAttributeClusterDimension;
-    at[0].val.clusterDim.x = kIdxCandShards;
-    at[0].val.clusterDim.y = 1;
-    at[0].val.clusterDim.z = 1;
-    cfg.attrs = at;
-    cfg.numAttrs = 1;
-    e = cudaLaunchKernelEx(&cfg, indexer_finish_kernel<512>, (const int32_t*)p.cand_idx, (const uint32_t*)p.cand_key,
-                           (const uint32_t*)p.cand_count, (const uint32_t*)thresholds, lengths, (int)B, out_idx, thresholds,
-                           rewrite_rows, select_rows, status);
-    if (e != cudaSuccess) return cuda_fail(e);
-  }
-  // pass 2 (marked rows only): write the logits the first pass did not
+  // pass 2 (marked rows only): write the logits the first pass did not; zero the counters. A
+  // programmatic dependent of pass 1: its CTAs are resident and waiting when pass 1 ends.
   IndexerParams p2 = p;
-  p2.only_rows = rewrite_rows;
-  if (fp8) {
-    indexer_logits_kernel<true><<<grid, kIdxThreads, indexer_smem_bytes(true), stream>>>(map_q, map_k, p2);
-  } else {
-    indexer_logits_kernel<false><<<grid, kIdxThreads, indexer_smem_bytes(false), stream>>>(map_q, map_k, p2);
-  }
-  e = cudaGetLastError();
+  p2.only_rows = p.rewrite_rows;
+  e = fp8 ? launch_producer<true>(grid, stream, true, map_q, map_k, p2) : launch_producer<false>(grid, stream, true, map_q, map_k, p2);
   if (e != cudaSuccess) return cuda_fail(e);
   // the selector on the logits of the rows without a usable guess; it hands back their thresholds
   SelectCall c;
@@ -621,8 +665,9 @@ static int indexer_topk_impl(bool fp8, const void* q, const void* k_cache, int64
   c.status = status;
   c.cuda_stream = cuda_stream;
   c.next_threshold = thresholds;
-  c.only_rows = select_rows;
+  c.only_rows = p.select_rows;
   c.may_overlap = false;
+  c.wait_prior = true;  // a programmatic dependent of pass 2
   return launch_select(c);
 }
 

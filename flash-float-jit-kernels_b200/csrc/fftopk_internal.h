@@ -49,6 +49,10 @@ struct SelectCall {
   // fftopk_set_overlap says: a programmatic dependent launch that never executes
   // griddepcontrol.wait has no guarantee that its predecessor's writes are visible.
   bool may_overlap = true;
+  // true (warm-start kernel only): launch as a programmatic dependent of the kernel enqueued just
+  // before it; the kernel then waits for that kernel's completion (griddepcontrol.wait) before it
+  // reads anything, so only its launch latency overlaps
+  bool wait_prior = false;
 };
 
 int launch_select(const SelectCall& c);

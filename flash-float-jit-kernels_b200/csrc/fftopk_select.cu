@@ -99,6 +99,7 @@ struct SelectParams {
   uint32_t* next_threshold;
   uint32_t warm_margin;
   const uint32_t* only_rows;  // (warm-start kernel only) when set: rows with only_rows[row] == 0 are left alone
+  int32_t wait_prior;         // (warm-start kernel only) launched as a programmatic dependent: wait for the kernel before it
 };
 
 
@@ -756,6 +757,7 @@ __device__ __forceinline__ void select_row(const SelectParams& p) {
   const int rank = cx.rank = (int)cluster.block_rank();
   const int row = (int)(blockIdx.x / (unsigned)C);
   if constexpr (kWarm) {
+    if (p.wait_prior) asm volatile("griddepcontrol.wait;" ::: "memory");
     if (p.only_rows != nullptr && p.only_rows[row] == 0u) return;  // (uniform over the cluster)
   }
   const int tid = threadIdx.x;
@@ -1652,6 +1654,7 @@ int launch_select(const SelectCall& c) {
   p.next_threshold = c.next_threshold;
   p.warm_margin = c.warm_margin;
   p.only_rows = c.only_rows;
+  p.wait_prior = c.wait_prior ? 1 : 0;
   const bool warm = c.prev_threshold != nullptr || c.next_threshold != nullptr;
   if (warm && (c.k != kK || pl.threads < 512)) return FFTOPK_EINVAL;
   if ((size_t)pl.smem_bytes > (size_t)d->smem_optin) return FFTOPK_ERANGE;
@@ -1668,7 +1671,8 @@ int launch_select(const SelectCall& c) {
   at[0].val.clusterDim.z = 1;
   cfg.attrs = at;
   cfg.numAttrs = 1;
-  if (overlap) {
+  if (c.wait_prior && !warm) return FFTOPK_EINVAL;
+  if (overlap || c.wait_prior) {
     at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     at[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.numAttrs = 2;

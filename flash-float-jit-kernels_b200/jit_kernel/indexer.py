@@ -31,7 +31,7 @@ class FusedIndexerTopk:
         self.b_cap, self.l_cap = int(max_rows), int(max_len)
         lib = _native.lib()
         nbytes = int(lib.fftopk_indexer_workspace_bytes(self.b_cap))
-        self._ws = torch.empty(nbytes + 256, dtype=torch.uint8, device=self.device)
+        self._ws = torch.zeros(nbytes + 256, dtype=torch.uint8, device=self.device)  # (zero-filled once: the C entry's contract)
         self._ws_ptr = (self._ws.data_ptr() + 255) & ~255
         self._ws_bytes = nbytes
         self.thresholds = torch.zeros(self.b_cap, dtype=torch.int32, device=self.device)

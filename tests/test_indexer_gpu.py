@@ -126,6 +126,40 @@ def test_exact_ties_and_guess_misses():
         _status_word(DEV).zero_()
 
 
+def test_mixed_rows_in_one_call():
+    """One call, six kinds of rows: guess holds; guess too high; guess far too low (the candidate list
+    overflows); no guess; fewer than k keys; no key at all. Then the same call again (every row of
+    more than k keys has an exact guess) and once more with a smaller batch on the same workspace."""
+    B, L = 6, 45000
+    q, k, w = make(B, L, seed=21)
+    ln = torch.tensor([L, L - 5, L, L - 129, 1000, 0], dtype=torch.int32)
+    f = FusedIndexerTopk(B, L)
+    out = f(q, k, w, ln.to(DEV))
+    torch.cuda.synchronize()
+    logits_np = f.logits[:B, :L].cpu().numpy().copy()
+    want = kth_keys(logits_np, ln.numpy())
+    orc.check_result(logits_np, ln.numpy(), out.cpu().numpy(), what="cold")
+    guesses = want.copy()
+    guesses[1] = want[1] + np.uint32(1 << 24)
+    guesses[2] = orc.keys_of(np.array([-1e30], np.float32))[0]
+    guesses[3] = 0
+    f.thresholds[:B] = torch.from_numpy(guesses.view(np.int32).copy()).to(DEV)
+    f.logits.fill_(float("nan"))
+    out = f(q, k, w, ln.to(DEV))
+    torch.cuda.synchronize()
+    orc.check_result(logits_np, ln.numpy(), out.cpu().numpy(), what="mixed")
+    assert kernel_status(DEV) == _native.ST_GUESS_MISSED
+    assert np.array_equal(f.thresholds.cpu().numpy().view(np.uint32)[:B], want)
+    written = ~torch.isnan(f.logits[:B, :L]).all(dim=1).cpu()
+    assert [bool(x) for x in written] == [False, True, True, True, True, False]
+    _status_word(DEV).zero_()
+    for nb in (B, 3):
+        out = f(q[:nb], k[:nb], w[:nb], ln[:nb].to(DEV))
+        torch.cuda.synchronize()
+        orc.check_result(logits_np[:nb], ln[:nb].numpy(), out.cpu().numpy(), what=f"again, {nb} rows")
+    assert kernel_status(DEV) == 0
+
+
 def test_graph_replay():
     B, L = 2, 60000
     q, k, w = make(B, L, seed=13)
