@@ -20,20 +20,20 @@
 //               weights and the sum are in-thread - one logit per thread and tile. With a threshold
 //               guess for the row (the previous decode step's, see fftopk_select2048_warm) the
 //               logit is compared with the guess's edge and the few that pass are appended, by
-//               ballot and one atomic per warp, to the row's candidate list; the logit itself is
-//               not written. Without a guess the logits are written for the selector.
+//               ballot and one atomic per warp, to the row's candidate list. The logit is also
+//               written (4 bytes per key beside the 256 or 132 read), but read again only by a row
+//               whose guess fails.
 // Every wait on an mbarrier has a time limit; when one runs out the CTA raises
 // FFTOPK_ST_STAGE_TIMEOUT, lets its copies in flight land, frees its TMEM and returns.
 //
 // Finish, inside the producer: the CTAs of a row count themselves off as they run out of tiles, and
 // the last one decides. If the row's guess held - at least 2048 candidates, no more than the list
 // holds - it pulls the list into the shared memory its stages no longer need and selects the exact
-// top 2048 (cta_finish: ties to the lower index) and the new threshold; otherwise it marks the row,
-// a second pass of the producer writes the row's logits and the selector of fftopk_select.cu runs on
-// them. Both of those launches follow as programmatic dependents: they are resident, waiting, by the
-// time the first pass ends, and rows that are not marked cost them an empty CTA. The second pass
-// also zeroes the row's counters, so a call leaves the workspace ready for the next one and no
-// launch of a call is a memset.
+// top 2048 (cta_finish: ties to the lower index) and the new threshold; otherwise it marks the row
+// and the selector of fftopk_select.cu runs on the row's logits. That launch follows as a
+// programmatic dependent: it is resident, waiting, by the time the producer ends, and rows that are
+// not marked cost it an empty CTA. The last CTA also zeroes the row's counters, so a call leaves the
+// workspace ready for the next one and a call is two launches, none of them a memset.
 #include <cooperative_groups.h>
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -93,19 +93,16 @@ struct IndexerParams {
   int64_t k_rows_per_seq;    // rows of the key tensor map per batch row
   int32_t B;
   int64_t L;
-  float* logits;             // [B, logits_stride]: written for rows without a guess / marked rows
+  float* logits;             // [B, logits_stride]: every valid key's logit
   int64_t logits_stride;
   const uint32_t* guess;     // [B] threshold key guesses (0: none) or nullptr
   uint32_t margin;
   uint64_t* cand;            // [B, kIdxCandCap] candidates as (key << 32 | ~index) composites
   uint32_t* cand_count;      // [B] candidates appended so far (may exceed the capacity: the row then falls back)
   uint32_t* done_count;      // [B] CTAs of the row that have run out of tiles
-  uint32_t* rewrite_rows;    // [B] out: 1 = the row's logits have to be written by the second pass
   uint32_t* select_rows;     // [B] out: 1 = the selector has to run on the row's logits
   int32_t* out_idx;          // [B, 2048]
   uint32_t* thr_out;         // [B] the row's new threshold key (rows finished here)
-  const uint32_t* only_rows; // second pass: rows with only_rows[b] != 0 get their logits written,
-                             // the others are skipped; nullptr in the first pass
   uint32_t* status;
 };
 
@@ -199,18 +196,16 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
 }
 
 // ---- finish of one row, by the last of its CTAs to run out of tiles ----------------------------------
-// `gkey`: the key guess the row was filtered with (margin already subtracted). `cand_smem` holds
-// kIdxCandCap composites, `hist` kFinishBins words.
+// `gkey`: the key guess the row was filtered with (margin already subtracted); `count`: how many
+// candidates were appended. `cand_smem` holds kIdxCandCap composites, `hist` kFinishBins words.
 template <int NT>
-__device__ __forceinline__ void indexer_finish_row(const IndexerParams& p, int row, int len, uint32_t gkey,
+__device__ __forceinline__ void indexer_finish_row(const IndexerParams& p, int row, int len, uint32_t gkey, uint32_t count,
                                                    uint64_t* cand_smem, uint32_t* hist, Ctrl* ctrl) {
   const int tid = threadIdx.x;
   const int lane = tid & 31, warp = tid >> 5;
-  const uint32_t count = __ldcg(p.cand_count + row);
   const bool held = len > kK && count >= (uint32_t)kK && count <= (uint32_t)kIdxCandCap;
   if (!held) {  // (uniform over the CTA)
     if (tid == 0) {
-      p.rewrite_rows[row] = 1u;  // its logits were not written in the first pass
       p.select_rows[row] = 1u;
       if (p.status) atomicOr(p.status, (uint32_t)FFTOPK_ST_GUESS_MISSED);
     }
@@ -252,7 +247,6 @@ __device__ __forceinline__ void indexer_finish_row(const IndexerParams& p, int r
   __syncthreads();
   if (tid == 0) {
     p.thr_out[row] = ctrl->thr_key != 0xffffffffu ? ctrl->thr_key : 0u;
-    p.rewrite_rows[row] = 0u;
     p.select_rows[row] = 0u;
   }
 }
@@ -288,28 +282,18 @@ __global__ void __launch_bounds__(kIdxThreads, FFTOPK_IDX_CTAS_PER_SM)
   const int row = blockIdx.y;
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
-  // the launches of a call follow one another as programmatic dependents (see the host side)
+  // the selector follows as a programmatic dependent (see the host side): let it become resident
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  if (p.only_rows != nullptr) {
-    // second pass: everything the first pass wrote - the marks above all - is visible after this
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    if (blockIdx.x == 0 && tid == 0) {  // the row's counters, for the next call
-      p.cand_count[row] = 0u;
-      p.done_count[row] = 0u;
-    }
-    if (p.only_rows[row] == 0u) return;  // (uniform over the CTA; nothing allocated yet)
-  }
   int64_t len64 = p.lengths[row];
   len64 = len64 < 0 ? 0 : (len64 > p.L ? p.L : len64);
   const int len = (int)len64;
   const int ntiles = (len + kIdxTile - 1) / kIdxTile;
-  uint32_t guess = (p.only_rows == nullptr && p.guess != nullptr) ? p.guess[row] : 0u;
+  uint32_t guess = p.guess != nullptr ? p.guess[row] : 0u;
   if (guess != 0u) guess = guess > p.margin ? guess - p.margin : 1u;
   const bool filter_mode = guess != 0u;
   const float edge = __uint_as_float(guess_edge_bits(guess));
-  if (p.only_rows == nullptr && blockIdx.x == 0 && tid == 0 && (!filter_mode || ntiles == 0)) {
-    // no guess to test (or no key at all): the selector takes the row from its written logits
-    p.rewrite_rows[row] = 0u;
+  if (blockIdx.x == 0 && tid == 0 && (!filter_mode || ntiles == 0)) {
+    // no guess to test (or no key at all): the selector takes the row
     p.select_rows[row] = 1u;
   }
   if ((int)blockIdx.x >= ntiles) return;  // (uniform)
@@ -434,6 +418,7 @@ __global__ void __launch_bounds__(kIdxThreads, FFTOPK_IDX_CTAS_PER_SM)
       }
       // relu(s * x) = s * relu(x) for a positive scale: the key's scale multiplies the finished sum
       const float logit = (acc0 + acc1) * scale;
+      if (valid) p.logits[(int64_t)row * p.logits_stride + key] = logit;
       if (filter_mode) {
         const bool hit = valid && !(logit < edge);
         const unsigned b = __ballot_sync(kFull, hit);
@@ -445,8 +430,6 @@ __global__ void __launch_bounds__(kIdxThreads, FFTOPK_IDX_CTAS_PER_SM)
             p.cand[(size_t)row * kIdxCandCap + slot] =
                 ((uint64_t)fftopk_key_from_bits(__float_as_uint(logit)) << 32) | (uint64_t)(~(uint32_t)key);
         }
-      } else if (valid) {
-        p.logits[(int64_t)row * p.logits_stride + key] = logit;
       }
     }
   }
@@ -475,14 +458,24 @@ __global__ void __launch_bounds__(kIdxThreads, FFTOPK_IDX_CTAS_PER_SM)
     // a CTA that gave up leaves the list incomplete: a count no list can hold sends the row to the fallback
     if (*abort_flag) atomicAdd(p.cand_count + row, 0x40000000u);
     const uint32_t nwork = (uint32_t)min((int)gridDim.x, ntiles);
-    *last_flag = atomicAdd(p.done_count + row, 1u) == nwork - 1u ? 1u : 0u;
+    const bool last = atomicAdd(p.done_count + row, 1u) == nwork - 1u;
+    uint32_t count = 0u;
+    if (last) {
+      // every CTA of the row has arrived: nobody appends any more. Take the count and leave both
+      // counters at zero for the next call.
+      __threadfence();
+      count = atomicExch(p.cand_count + row, 0u);
+      p.done_count[row] = 0u;
+    }
+    last_flag[0] = last ? 1u : 0u;
+    last_flag[1] = count;
   }
   __syncthreads();
-  if (*last_flag == 0u) return;  // (uniform)
+  if (last_flag[0] == 0u) return;  // (uniform)
   __threadfence();
   // every copy and MMA of this CTA has completed: the stages hold the list, q's place the histogram
-  indexer_finish_row<kIdxThreads>(p, row, len, guess, reinterpret_cast<uint64_t*>(a_smem), reinterpret_cast<uint32_t*>(q_smem),
-                                  fin_ctrl);
+  indexer_finish_row<kIdxThreads>(p, row, len, guess, last_flag[1], reinterpret_cast<uint64_t*>(a_smem),
+                                  reinterpret_cast<uint32_t*>(q_smem), fin_ctrl);
 }
 
 }  // namespace fftopk
@@ -549,9 +542,9 @@ int make_map(CUtensorMap* map, const void* ptr, bool fp8, uint64_t rows, uint64_
 }
 
 // Workspace: [candidate lists: B x kIdxCandCap composites][candidate counts: B words][arrival
-// counts: B words][rows whose logits the second pass writes: B words][rows the selector takes: B words]
+// counts: B words][rows the selector takes: B words]
 struct IndexerLayout {
-  size_t cand_off, count_off, done_off, rewrite_off, select_off, total;
+  size_t cand_off, count_off, done_off, select_off, total;
 };
 IndexerLayout indexer_layout(int32_t B) {
   IndexerLayout l;
@@ -559,26 +552,17 @@ IndexerLayout indexer_layout(int32_t B) {
   l.cand_off = 0;
   l.count_off = (size_t)B * kIdxCandCap * 8;
   l.done_off = l.count_off + words;
-  l.rewrite_off = l.done_off + words;
-  l.select_off = l.rewrite_off + words;
+  l.select_off = l.done_off + words;
   l.total = l.select_off + words;
   return l;
 }
 
 template <bool kFp8>
-cudaError_t launch_producer(dim3 grid, cudaStream_t stream, bool dependent, const CUtensorMap& map_q, const CUtensorMap& map_k,
+cudaError_t launch_producer(dim3 grid, cudaStream_t stream, const CUtensorMap& map_q, const CUtensorMap& map_k,
                             const IndexerParams& p) {
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = grid;
-  cfg.blockDim = dim3(kIdxThreads, 1, 1);
-  cfg.dynamicSmemBytes = indexer_smem_bytes(kFp8);
-  cfg.stream = stream;
-  cudaLaunchAttribute at[1];
-  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  at[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = at;
-  cfg.numAttrs = dependent ? 1 : 0;
-  return cudaLaunchKernelEx(&cfg, indexer_logits_kernel<kFp8>, map_q, map_k, p);
+  // (a plain launch: it orders itself after whatever the stream holds)
+  indexer_logits_kernel<kFp8><<<grid, kIdxThreads, indexer_smem_bytes(kFp8), stream>>>(map_q, map_k, p);
+  return cudaGetLastError();
 }
 
 }  // namespace
@@ -634,7 +618,6 @@ static int indexer_topk_impl(bool fp8, const void* q, const void* k_cache, int64
   p.cand = reinterpret_cast<uint64_t*>(ws + lay.cand_off);
   p.cand_count = reinterpret_cast<uint32_t*>(ws + lay.count_off);
   p.done_count = reinterpret_cast<uint32_t*>(ws + lay.done_off);
-  p.rewrite_rows = reinterpret_cast<uint32_t*>(ws + lay.rewrite_off);
   p.select_rows = reinterpret_cast<uint32_t*>(ws + lay.select_off);
   p.out_idx = out_idx;
   p.thr_out = thresholds;
@@ -644,15 +627,9 @@ static int indexer_topk_impl(bool fp8, const void* q, const void* k_cache, int64
   int per_row = sms * FFTOPK_IDX_CTAS_PER_SM / B > 0 ? sms * FFTOPK_IDX_CTAS_PER_SM / B : 1;
   if (per_row > ntiles) per_row = (int)ntiles;
   const dim3 grid((unsigned)per_row, (unsigned)B);
-  // pass 1: rows with a guess are filtered as their logits are produced and finished by their last
-  // CTA; the others get logits. (A plain launch: it orders itself after whatever the stream holds.)
-  e = fp8 ? launch_producer<true>(grid, stream, false, map_q, map_k, p) : launch_producer<false>(grid, stream, false, map_q, map_k, p);
-  if (e != cudaSuccess) return cuda_fail(e);
-  // pass 2 (marked rows only): write the logits the first pass did not; zero the counters. A
-  // programmatic dependent of pass 1: its CTAs are resident and waiting when pass 1 ends.
-  IndexerParams p2 = p;
-  p2.only_rows = p.rewrite_rows;
-  e = fp8 ? launch_producer<true>(grid, stream, true, map_q, map_k, p2) : launch_producer<false>(grid, stream, true, map_q, map_k, p2);
+  // the producer: logits; rows with a guess are filtered as the logits are produced and finished
+  // by their last CTA
+  e = fp8 ? launch_producer<true>(grid, stream, map_q, map_k, p) : launch_producer<false>(grid, stream, map_q, map_k, p);
   if (e != cudaSuccess) return cuda_fail(e);
   // the selector on the logits of the rows without a usable guess; it hands back their thresholds
   SelectCall c;
@@ -667,7 +644,7 @@ static int indexer_topk_impl(bool fp8, const void* q, const void* k_cache, int64
   c.next_threshold = thresholds;
   c.only_rows = p.select_rows;
   c.may_overlap = false;
-  c.wait_prior = true;  // a programmatic dependent of pass 2
+  c.wait_prior = true;  // a programmatic dependent of the producer
   return launch_select(c);
 }
 

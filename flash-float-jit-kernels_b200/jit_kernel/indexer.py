@@ -5,8 +5,8 @@ starts from a finished logit matrix; README.md:24 names the step in front of it)
     64 heads, dimension 128; q and k in bf16, or in fp8 (e4m3) with an optional positive scale per key
 
 ``FusedIndexerTopk`` keeps what the C entry point ``fftopk_indexer_topk2048`` needs between calls of
-a decode loop: the per-row threshold keys, the logit scratch for rows without a usable guess and
-the candidate workspace."""
+a decode loop: the per-row threshold keys, the logit matrix (``.logits``: written by every call,
+read again only for rows without a usable guess) and the candidate workspace."""
 from __future__ import annotations
 
 import torch

@@ -310,13 +310,13 @@ int fftopk_select2048_host(const float* h_score, int64_t h_row_stride, int32_t B
  *   logit[b, t] = sum over 64 heads h of  w[b, h] * relu( q[b, h, :] . k[b, t, :] ),  dimension 128, bf16
  * One kernel (TMA loads, tcgen05.mma into TMEM, one key per epilogue thread) produces the logits of a
  * row; for a row with a threshold guess (thresholds[b] != 0: what an earlier call handed back) every
- * logit is compared with the guess as it leaves the tensor core and only the few that pass are kept
- * as candidates - the logits are never written to or re-read from memory - and the last CTA of the
- * row to finish selects the exact top 2048 of the candidates. Rows without a guess, and rows whose
- * guess did not hold (fewer than 2048 admitted, or more than the 8,192-entry candidate list takes;
- * status bit FFTOPK_ST_GUESS_MISSED), get their logits written to `logits` and go through the
- * selector of fftopk_select2048 (two more launches, enqueued as programmatic dependents, that cost
- * rows in no need of them an empty CTA). Either way out_idx holds the exact top 2048 OF THE LOGITS THE KERNEL COMPUTED
+ * logit is compared with the guess as it leaves the tensor core and the few that pass are kept as
+ * candidates - the logit matrix is written (4 bytes per key beside the 256 read) but not read again -
+ * and the last CTA of the row to finish selects the exact top 2048 of the candidates. Rows without
+ * a guess, and rows whose guess did not hold (fewer than 2048 admitted, or more than the 8,192-entry
+ * candidate list takes; status bit FFTOPK_ST_GUESS_MISSED), go through the selector of
+ * fftopk_select2048 on `logits` (a second launch, enqueued as a programmatic dependent, that costs
+ * rows in no need of it an empty CTA). Either way out_idx holds the exact top 2048 OF THE LOGITS THE KERNEL COMPUTED
  * (fp32 accumulation on the tensor cores; ties to the lower index) and thresholds[b] the key of the
  * row's 2048-th largest logit for the next call.
  *   q            device, bf16 [B, 64, 128], 16-byte aligned
@@ -324,7 +324,7 @@ int fftopk_select2048_host(const float* h_score, int64_t h_row_stride, int32_t B
  *   w            device, fp32 [B, 64]
  *   lengths      device, int32 [B]: valid keys per row (clamped to [0, L])
  *   thresholds   device, uint32 [B], in and out (start with zeros); margin as for fftopk_select2048_warm
- *   logits       device, fp32 [B, logits_stride] (logits_stride >= L): scratch for the rows that need it
+ *   logits       device, fp32 [B, logits_stride] (logits_stride >= L), out: logits[b, t] for t < lengths[b]
  *   out_idx      device, int32 [B, 2048]
  *   d_workspace  fftopk_indexer_workspace_bytes(B) bytes of device memory, 256-byte aligned, ZERO-FILLED
  *                before its first use; every call leaves it ready for the next one (calls with any
