@@ -430,6 +430,44 @@ def indexer_leg(dev, stream, peak_gbs):
                 del gr
             out[f"{fmt}_{L}"] = r
             del ks, fs
+    # a decode batch: B=64 rows of the bench's ragged lengths, every row with its own key cache
+    # (2.1 GB in bf16: nothing stays in L2 from call to call)
+    _, lengths = workloads.c3()  # (only the lengths are wanted)
+    B, L = int(lengths.numel()), 131072
+    ln = lengths.to(dev)
+    n_keys = int(lengths.sum())
+    for fmt in ("bf16", "fp8"):
+        dt = torch.bfloat16 if fmt == "bf16" else torch.float8_e4m3fn
+        g = torch.Generator(device=dev).manual_seed(7)
+        q = (torch.randn(B, 64, 128, generator=g, device=dev) * 0.5).to(dt)
+        k = torch.empty(B, L, 128, dtype=dt, device=dev)
+        for b0 in range(0, B, 8):  # (in slices: the fp32 draw of the whole cache would be 4.3 GB)
+            k[b0:b0 + 8] = (torch.randn(8, L, 128, generator=g, device=dev) * 0.5).to(dt)
+        scale = (torch.rand(B, L, generator=g, device=dev) + 0.5) if fmt == "fp8" else None
+        w = torch.rand(B, 64, generator=g, device=dev)
+        f = FusedIndexerTopk(B, L, dev)
+        res = torch.empty(B, K, dtype=torch.int32, device=dev)
+        with torch.cuda.stream(stream):
+            f(q, k, w, ln, out=res, k_scale=scale)
+        stream.synchronize()
+        gr = capture_steps(lambda i: f(q, k, w, ln, out=res, k_scale=scale), 4, stream)
+        ts = sorted(time_graph(gr, stream) / 4 * 1e6 for _ in range(7))
+        del gr
+        key_bytes = n_keys * (256 if fmt == "bf16" else 132)
+        us = ts[len(ts) // 2]
+        # the selection against torch.topk on the logits the kernel wrote (values: ties may differ in index)
+        lg = f.logits[:B, :L].clone()
+        lg[torch.arange(L, device=dev).unsqueeze(0) >= ln.unsqueeze(1)] = float("-inf")
+        want = torch.topk(lg, K, dim=1).values.sort(dim=1).values
+        got = torch.gather(lg, 1, res.long().clamp_min(0)).sort(dim=1).values
+        long_rows = ln > K
+        same = bool(torch.equal(want[long_rows], got[long_rows]))
+        del lg, want, got
+        out[f"{fmt}_B{B}_ragged"] = {"keys": n_keys, "key_cache_bytes": key_bytes, "warm_us_per_call": us,
+                                     "warm_gbs": key_bytes / us / 1e3, "warm_frac_hbm": key_bytes / us / 1e3 / peak_gbs,
+                                     "rows_per_s": B / us * 1e6,
+                                     "parity": "values bit-exact vs torch.topk on the written logits" if same else "MISMATCH"}
+        del k, f
     return out
 
 
