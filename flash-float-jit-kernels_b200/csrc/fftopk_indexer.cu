@@ -199,7 +199,7 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
 // `gkey`: the key guess the row was filtered with (margin already subtracted); `count`: how many
 // candidates were appended. `cand_smem` holds kIdxCandCap composites, `hist` kFinishBins words.
 template <int NT>
-__device__ __forceinline__ void indexer_finish_row(const IndexerParams& p, int row, int len, uint32_t gkey, uint32_t count,
+__device__ __noinline__ void indexer_finish_row(const IndexerParams& p, int row, int len, uint32_t gkey, uint32_t count,
                                                    uint64_t* cand_smem, uint32_t* hist, Ctrl* ctrl) {
   const int tid = threadIdx.x;
   const int lane = tid & 31, warp = tid >> 5;
@@ -251,11 +251,111 @@ __device__ __forceinline__ void indexer_finish_row(const IndexerParams& p, int r
   }
 }
 
+__device__ __forceinline__ int indexer_row_tiles(const IndexerParams& p, int row, int& len) {
+  int64_t len64 = p.lengths[row];
+  len64 = len64 < 0 ? 0 : (len64 > p.L ? p.L : len64);
+  len = (int)len64;
+  return (len + kIdxTile - 1) / kIdxTile;
+}
+
+// the key guess a row is filtered with: the caller's, less the margin (0: none)
+__device__ __forceinline__ uint32_t indexer_row_guess(const IndexerParams& p, int row) {
+  const uint32_t raw = p.guess != nullptr ? p.guess[row] : 0u;
+  return raw == 0u ? 0u : (raw > p.margin ? raw - p.margin : 1u);
+}
+
+// ---- epilogue of one segment (warps 2-9): one key per thread; group g of four warps serves every
+// second tile. (With two accumulators and one group the loop MMA -> full barrier -> TMEM loads ->
+// empty barrier -> next MMA into the same accumulator took ~1.1 us per pair of tiles: as long as
+// the key tiles' copies take in bf16, twice as long as they take in fp8.) Out of line: the 64
+// accumulator values of a key want the registers the kernel's segment bookkeeping would hold.
+template <bool kFp8>
+__device__ __noinline__ void indexer_epilogue_segment(const IndexerParams& p, int row, int t_lo, int t_step, int n, int it_base,
+                                                      uint32_t tmem_base, uint64_t* tfull, uint64_t* tempty,
+                                                      volatile uint32_t* abort_flag, float* w_smem) {
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5, lane = tid & 31;
+  const int group = (warp - 2) >> 2;
+  const int quarter = warp & 3;                 // the TMEM lanes this warp may read: 32 * (warp % 4)
+  const int key_in_tile = quarter * 32 + lane;
+  const unsigned lt = (1u << lane) - 1u;
+  const float4* w4 = reinterpret_cast<const float4*>(w_smem);
+  // the row's weights, among the epilogue warps only
+  if (tid >= 64 && tid < 64 + kIdxHeads) w_smem[tid - 64] = __ldg(p.w + (int64_t)row * kIdxHeads + (tid - 64));
+  int len;
+  indexer_row_tiles(p, row, len);
+  const uint32_t guess = indexer_row_guess(p, row);
+  const bool filter_mode = guess != 0u;
+  const float edge = __uint_as_float(guess_edge_bits(guess));
+  if (tid == kIdxThreads - 1 && t_lo == 0 && !filter_mode) p.select_rows[row] = 1u;  // no guess to test: the selector takes the row
+  asm volatile("bar.sync 1, 256;" ::: "memory");
+  for (int i = ((it_base & 1) == group) ? 0 : 1; i < n; i += 2) {
+    const int it = it_base + i;
+    const int buf = it % kIdxBufs;
+    const uint32_t bph = (uint32_t)(it / kIdxBufs) & 1u;
+    const int key = (t_lo + i * t_step) * kIdxTile + key_in_tile;
+    const bool valid = key < len;
+    // the key's scale is asked for before the wait: its memory latency hides behind the tile's
+    // copy and MMAs instead of sitting at the end of the epilogue
+    float scale = 1.f;
+    if constexpr (kFp8) {
+      if (p.k_scale != nullptr && valid) scale = __ldg(p.k_scale + (int64_t)row * p.k_scale_stride + key);
+    }
+    if (!mbar_wait(&tfull[buf], bph, abort_flag)) break;
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)buf * kIdxHeads;
+    uint32_t v0[32], v1[32];
+    tmem_ld32(taddr, v0);
+    tmem_ld32(taddr + 32u, v1);
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    mbar_arrive(&tempty[buf]);  // the values are in registers: the accumulator buffer may be overwritten
+    float acc0 = 0.f, acc1 = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float4 wa = w4[j], wb = w4[8 + j];
+      acc0 = fmaf(wa.x, fmaxf(__uint_as_float(v0[4 * j + 0]), 0.f), acc0);
+      acc1 = fmaf(wb.x, fmaxf(__uint_as_float(v1[4 * j + 0]), 0.f), acc1);
+      acc0 = fmaf(wa.y, fmaxf(__uint_as_float(v0[4 * j + 1]), 0.f), acc0);
+      acc1 = fmaf(wb.y, fmaxf(__uint_as_float(v1[4 * j + 1]), 0.f), acc1);
+      acc0 = fmaf(wa.z, fmaxf(__uint_as_float(v0[4 * j + 2]), 0.f), acc0);
+      acc1 = fmaf(wb.z, fmaxf(__uint_as_float(v1[4 * j + 2]), 0.f), acc1);
+      acc0 = fmaf(wa.w, fmaxf(__uint_as_float(v0[4 * j + 3]), 0.f), acc0);
+      acc1 = fmaf(wb.w, fmaxf(__uint_as_float(v1[4 * j + 3]), 0.f), acc1);
+    }
+    // relu(s * x) = s * relu(x) for a positive scale: the key's scale multiplies the finished sum
+    const float logit = (acc0 + acc1) * scale;
+    if (valid) p.logits[(int64_t)row * p.logits_stride + key] = logit;
+    if (filter_mode) {
+      const bool hit = valid && !(logit < edge);
+      const unsigned b = __ballot_sync(kFull, hit);
+      if (b) {
+        uint32_t slot = 0;
+        if (lane == 0) slot = atomicAdd(p.cand_count + row, (uint32_t)__popc(b));
+        slot = __shfl_sync(kFull, slot, 0) + (uint32_t)__popc(b & lt);
+        if (hit && slot < (uint32_t)kIdxCandCap)
+          p.cand[(size_t)row * kIdxCandCap + slot] =
+              ((uint64_t)fftopk_key_from_bits(__float_as_uint(logit)) << 32) | (uint64_t)(~(uint32_t)key);
+      }
+    }
+  }
+}
+
 // ---- producer --------------------------------------------------------------------------------------
+// Work split. The tiles of all rows, row after row, form one sequence; CTA c takes the c-th run of
+// `quota` consecutive tiles of it (quota = tiles / CTAs, rounded up), so every CTA streams the same
+// number of bytes whatever the rows' lengths are, and a run may cover the end of one row, several
+// whole rows and the start of another. The part of a run inside one row is a segment: the CTA
+// loads that row's q and weights, runs its pipeline over the segment's tiles, lets it drain and
+// counts the tiles off at the row's arrival counter. The row -> first-tile table is computed by
+// every CTA for itself (a block scan over the lengths) and kept in shared memory, for batches of up
+// to kIdxBalancedRows rows; larger batches give every row one CTA.
+constexpr int kIdxBalancedRows = 1024;
+
 template <bool kFp8>
 __global__ void __launch_bounds__(kIdxThreads, FFTOPK_IDX_CTAS_PER_SM)
     indexer_logits_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                          const IndexerParams p) {
+                          const __grid_constant__ IndexerParams p) {
   using F = IdxFmt<kFp8>;
   static_assert((size_t)F::kStages * F::kTileBytes >= (size_t)kIdxCandCap * 8, "the stages hold a row's candidate list");
   static_assert(F::kQBytes >= (uint32_t)kFinishBins * 4u, "q's place holds the finish's histogram");
@@ -274,29 +374,18 @@ __global__ void __launch_bounds__(kIdxThreads, FFTOPK_IDX_CTAS_PER_SM)
   uint64_t* tfull = bars + 2 * kIdxStages;   // [kIdxBufs]
   uint64_t* tempty = tfull + kIdxBufs;       // [kIdxBufs]
   uint64_t* qfull = tempty + kIdxBufs;       // [1]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(qfull + 1);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 32);
   volatile uint32_t* abort_flag = tmem_slot + 1;
-  uint32_t* last_flag = tmem_slot + 2;
-  Ctrl* fin_ctrl = reinterpret_cast<Ctrl*>(reinterpret_cast<unsigned char*>(tmem_slot) + 16);  // (16-byte aligned)
+  uint32_t* last_flag = tmem_slot + 2;       // [2]: this CTA finishes the row; the row's candidate count
+  uint32_t* scan_part = tmem_slot + 4;       // [12]: warp totals of the block scan
+  Ctrl* fin_ctrl = reinterpret_cast<Ctrl*>(tmem_slot + 16);
+  uint32_t* first_tile = reinterpret_cast<uint32_t*>(reinterpret_cast<unsigned char*>(fin_ctrl) + ((sizeof(Ctrl) + 15) & ~15u));
+  // first_tile[r], r <= B: tiles of the rows before r (balanced mode only)
 
-  const int row = blockIdx.y;
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
   // the selector follows as a programmatic dependent (see the host side): let it become resident
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  int64_t len64 = p.lengths[row];
-  len64 = len64 < 0 ? 0 : (len64 > p.L ? p.L : len64);
-  const int len = (int)len64;
-  const int ntiles = (len + kIdxTile - 1) / kIdxTile;
-  uint32_t guess = p.guess != nullptr ? p.guess[row] : 0u;
-  if (guess != 0u) guess = guess > p.margin ? guess - p.margin : 1u;
-  const bool filter_mode = guess != 0u;
-  const float edge = __uint_as_float(guess_edge_bits(guess));
-  if (blockIdx.x == 0 && tid == 0 && (!filter_mode || ntiles == 0)) {
-    // no guess to test (or no key at all): the selector takes the row
-    p.select_rows[row] = 1u;
-  }
-  if ((int)blockIdx.x >= ntiles) return;  // (uniform)
 
   if (tid == 0) {
     for (int s = 0; s < kIdxStages; ++s) {
@@ -311,7 +400,6 @@ __global__ void __launch_bounds__(kIdxThreads, FFTOPK_IDX_CTAS_PER_SM)
     *abort_flag = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (tid < kIdxHeads) w_smem[tid] = __ldg(p.w + (int64_t)row * kIdxHeads + tid);
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
                  "r"((uint32_t)(kIdxBufs * kIdxHeads))
@@ -319,124 +407,210 @@ __global__ void __launch_bounds__(kIdxThreads, FFTOPK_IDX_CTAS_PER_SM)
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-  __syncthreads();
+
+  // ---- this CTA's run of tiles [g0, g1) and the row it starts in (the barriers in here also
+  // publish the mbarriers and the TMEM address) ------------------------------------------------------
+  const bool balanced = p.B <= kIdxBalancedRows;
+  uint32_t g0 = 0u, g1 = 0u;
+  int row = 0;
+  if (p.B == 1) {
+    // one row: no table to build (and see below: its tiles go to the CTAs interleaved, not in runs)
+    int len_r;
+    const uint32_t total = (uint32_t)indexer_row_tiles(p, 0, len_r);
+    if (tid == 0) {
+      first_tile[0] = 0u;
+      first_tile[1] = total;
+      if (total == 0u && blockIdx.x == 0) p.select_rows[0] = 1u;
+    }
+    __syncthreads();
+    const uint32_t each = total / gridDim.x, rest = total % gridDim.x;
+    g0 = blockIdx.x * each + min(blockIdx.x, rest);
+    g1 = g0 + each + (blockIdx.x < rest ? 1u : 0u);
+  } else if (balanced) {
+    constexpr int PER = (kIdxBalancedRows + kIdxThreads - 1) / kIdxThreads;
+    uint32_t mine[PER];
+    uint32_t sum = 0u;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      const int r = tid * PER + j;
+      int len_r;
+      mine[j] = r < p.B ? (uint32_t)indexer_row_tiles(p, r, len_r) : 0u;
+      if (r < p.B && mine[j] == 0u && blockIdx.x == 0) p.select_rows[r] = 1u;  // no key at all: the selector pads the row
+      sum += mine[j];
+    }
+    uint32_t incl = sum;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const uint32_t v = __shfl_up_sync(kFull, incl, off);
+      if (lane >= off) incl += v;
+    }
+    if (lane == 31) scan_part[warp] = incl;
+    __syncthreads();
+    uint32_t before = 0u;
+    for (int wv = 0; wv < warp; ++wv) before += scan_part[wv];
+    uint32_t run = before + incl - sum;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      const int r = tid * PER + j;
+      if (r < p.B) first_tile[r] = run;
+      run += mine[j];
+      if (r == p.B - 1) first_tile[p.B] = run;
+    }
+    __syncthreads();
+    // total = each * CTAs + rest: the first `rest` CTAs take one tile more
+    const uint32_t total = first_tile[p.B];
+    const uint32_t each = total / gridDim.x, rest = total % gridDim.x;
+    g0 = blockIdx.x * each + min(blockIdx.x, rest);
+    g1 = g0 + each + (blockIdx.x < rest ? 1u : 0u);
+    // the last row that starts at or before g0
+    int lo = 0, hi = p.B;
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (first_tile[mid] <= g0) lo = mid; else hi = mid;
+    }
+    row = lo;
+  } else {
+    row = (int)blockIdx.x;
+    int len_r;
+    g1 = (uint32_t)indexer_row_tiles(p, row, len_r);
+    if (g1 == 0u && tid == 0) p.select_rows[row] = 1u;
+    __syncthreads();
+  }
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
+  if (g0 >= g1) {  // (uniform) nothing to do
+    if (warp == 1) {
+      asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(kIdxBufs * kIdxHeads))
+                   : "memory");
+    }
+    return;
+  }
 
-  if (warp == 0) {
-    // ---- TMA producer -----------------------------------------------------------------------
-    if (lane == 0) {
-      mbar_expect_tx(qfull, kIdxQBytes);
-#pragma unroll
-      for (int bx = 0; bx < F::kBoxes; ++bx)
-        tma_load_2d(q_smem + (size_t)bx * (kIdxQBytes / F::kBoxes), &map_q, bx * F::kChunk, row * kIdxHeads, qfull);
-      int it = 0;
-      for (int t = blockIdx.x; t < ntiles; t += gridDim.x, ++it) {
-        const int s = it % kIdxStages;
-        const uint32_t ph = (uint32_t)(it / kIdxStages) & 1u;
-        if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag)) break;
-        mbar_expect_tx(&full[s], kIdxTileBytes);
-        const int y = (int)((int64_t)row * p.k_rows_per_seq + (int64_t)t * kIdxTile);
-        unsigned char* dst = a_smem + (size_t)s * kIdxTileBytes;
+  int it_base = 0;   // tiles this CTA has been through: selects stages, accumulators and barrier phases
+  int seg_no = 0;
+  for (uint32_t g = g0; g < g1; ++row) {
+    // ---- the segment of this row -----------------------------------------------------------------
+    // (tile counts out of shared memory: the thread that issues the copies waits for no global load)
+    const uint32_t row_g0 = balanced ? first_tile[row] : 0u;
+    const int ntiles = balanced ? (int)(first_tile[row + 1] - row_g0) : (int)g1;
+    if (row_g0 + (uint32_t)ntiles <= g) continue;  // (a row without tiles)
+    int t_lo = (int)(g - row_g0);
+    const int t_hi = (int)(min(g1, row_g0 + (uint32_t)ntiles) - row_g0);
+    const int n = t_hi - t_lo;
+    g += (uint32_t)n;
+    int t_step = 1;
+    if (p.B == 1) {
+      // One row: CTA x takes tiles x, x + CTAs, ... - as many as its run would hold (the first `rest`
+      // CTAs one more) - so that at any moment the CTAs read one dense window of the key cache
+      // (measured 0.2 us per call faster at 128K keys, 0.7 us at 1M, than a run per CTA).
+      t_lo = (int)blockIdx.x;
+      t_step = (int)gridDim.x;
+    }
+    // (No barrier of the whole CTA here: the barriers at the end of the segment before have ordered
+    // everything this one overwrites. And nothing in front of the role branches that waits for
+    // global memory: the threads that issue the copies and the MMAs start at once; the row's
+    // length and guess are read by the epilogue warps, and by everybody at the segment's end.)
+
+    if (warp == 0) {
+      // ---- TMA producer ---------------------------------------------------------------------------
+      if (lane == 0) {
+        mbar_expect_tx(qfull, kIdxQBytes);
 #pragma unroll
         for (int bx = 0; bx < F::kBoxes; ++bx)
-          tma_load_2d(dst + (size_t)bx * (kIdxTileBytes / F::kBoxes), &map_k, bx * F::kChunk, y, &full[s]);
+          tma_load_2d(q_smem + (size_t)bx * (kIdxQBytes / F::kBoxes), &map_q, bx * F::kChunk, row * kIdxHeads, qfull);
+        for (int i = 0; i < n; ++i) {
+          const int it = it_base + i;
+          const int s = it % kIdxStages;
+          const uint32_t ph = (uint32_t)(it / kIdxStages) & 1u;
+          if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag)) break;
+          mbar_expect_tx(&full[s], kIdxTileBytes);
+          const int y = (int)((int64_t)row * p.k_rows_per_seq + (int64_t)(t_lo + i * t_step) * kIdxTile);
+          unsigned char* dst = a_smem + (size_t)s * kIdxTileBytes;
+#pragma unroll
+          for (int bx = 0; bx < F::kBoxes; ++bx)
+            tma_load_2d(dst + (size_t)bx * (kIdxTileBytes / F::kBoxes), &map_k, bx * F::kChunk, y, &full[s]);
+        }
       }
-    }
-  } else if (warp == 1) {
-    // ---- MMA issuer ---------------------------------------------------------------------------
-    if (lane == 0) {
-      bool ok = mbar_wait(qfull, 0u, abort_flag);
-      int it = 0;
-      for (int t = blockIdx.x; ok && t < ntiles; t += gridDim.x, ++it) {
-        const int s = it % kIdxStages;
-        const uint32_t ph = (uint32_t)(it / kIdxStages) & 1u;
-        const int buf = it % kIdxBufs;
-        const uint32_t bph = (uint32_t)(it / kIdxBufs) & 1u;
-        if (!mbar_wait(&tempty[buf], bph ^ 1u, abort_flag)) break;
-        if (!mbar_wait(&full[s], ph, abort_flag)) break;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t a_addr = smem_u32(a_smem + (size_t)s * kIdxTileBytes);
-        const uint32_t b_addr = smem_u32(q_smem);
-        const uint32_t d_tmem = tmem_base + (uint32_t)buf * kIdxHeads;
+    } else if (warp == 1) {
+      // ---- MMA issuer -----------------------------------------------------------------------------
+      if (lane == 0) {
+        bool ok = mbar_wait(qfull, (uint32_t)seg_no & 1u, abort_flag);
+        for (int i = 0; ok && i < n; ++i) {
+          const int it = it_base + i;
+          const int s = it % kIdxStages;
+          const uint32_t ph = (uint32_t)(it / kIdxStages) & 1u;
+          const int buf = it % kIdxBufs;
+          const uint32_t bph = (uint32_t)(it / kIdxBufs) & 1u;
+          if (!mbar_wait(&tempty[buf], bph ^ 1u, abort_flag)) break;
+          if (!mbar_wait(&full[s], ph, abort_flag)) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t a_addr = smem_u32(a_smem + (size_t)s * kIdxTileBytes);
+          const uint32_t b_addr = smem_u32(q_smem);
+          const uint32_t d_tmem = tmem_base + (uint32_t)buf * kIdxHeads;
 #pragma unroll
-        for (int kc = 0; kc < F::kBoxes; ++kc) {
+          for (int kc = 0; kc < F::kBoxes; ++kc) {
 #pragma unroll
-          for (int kk = 0; kk < F::kMmaPerBox; ++kk) {
-            // one MMA consumes 32 bytes of K (16 bf16 or 32 fp8): 32 bytes further inside the swizzle row
-            const uint64_t ad = umma_desc_sw128(a_addr + (uint32_t)kc * (kIdxTileBytes / F::kBoxes) + (uint32_t)kk * 32u);
-            const uint64_t bd = umma_desc_sw128(b_addr + (uint32_t)kc * (kIdxQBytes / F::kBoxes) + (uint32_t)kk * 32u);
-            umma<kFp8>(d_tmem, ad, bd, (kc | kk) != 0 ? 1u : 0u);
+            for (int kk = 0; kk < F::kMmaPerBox; ++kk) {
+              // one MMA consumes 32 bytes of K (16 bf16 or 32 fp8): 32 bytes further inside the swizzle row
+              const uint64_t ad = umma_desc_sw128(a_addr + (uint32_t)kc * (kIdxTileBytes / F::kBoxes) + (uint32_t)kk * 32u);
+              const uint64_t bd = umma_desc_sw128(b_addr + (uint32_t)kc * (kIdxQBytes / F::kBoxes) + (uint32_t)kk * 32u);
+              umma<kFp8>(d_tmem, ad, bd, (kc | kk) != 0 ? 1u : 0u);
+            }
           }
+          umma_commit(&empty[s]);     // the stage may be refilled once these MMAs have read it
+          umma_commit(&tfull[buf]);   // ... and the accumulator is complete
         }
-        umma_commit(&empty[s]);     // the stage may be refilled once these MMAs have read it
-        umma_commit(&tfull[buf]);   // ... and the accumulator is complete
       }
+    } else {
+      // ---- epilogue ---------------------------------------------------------------------------------
+      indexer_epilogue_segment<kFp8>(p, row, t_lo, t_step, n, it_base, tmem_base, tfull, tempty, abort_flag, w_smem);
     }
-  } else {
-    // ---- epilogue: one key per thread; group g of four warps serves every second tile. (With two
-    // accumulators and one group the loop MMA -> full barrier -> TMEM loads -> empty barrier -> next
-    // MMA into the same accumulator took ~1.1 us per pair of tiles: as long as the key tiles' copies
-    // take in bf16, twice as long as they take in fp8.) -----------------------------------------
-    const int group = (warp - 2) >> 2;
-    const int quarter = warp & 3;                 // the TMEM lanes this warp may read: 32 * (warp % 4)
-    const int key_in_tile = quarter * 32 + lane;
-    const unsigned lt = (1u << lane) - 1u;
-    const float4* w4 = reinterpret_cast<const float4*>(w_smem);
-    for (int t = blockIdx.x + group * gridDim.x, it = group; t < ntiles; t += 2 * gridDim.x, it += 2) {
-      const int buf = it % kIdxBufs;
-      const uint32_t bph = (uint32_t)(it / kIdxBufs) & 1u;
-      const int key = t * kIdxTile + key_in_tile;
-      const bool valid = key < len;
-      // the key's scale is asked for before the wait: its memory latency hides behind the tile's
-      // copy and MMAs instead of sitting at the end of the epilogue
-      float scale = 1.f;
-      if constexpr (kFp8) {
-        if (p.k_scale != nullptr && valid) scale = __ldg(p.k_scale + (int64_t)row * p.k_scale_stride + key);
+    // The idle lanes of the two single-thread warps wait here for their working lane: what follows
+    // (global loads, a fence) would otherwise run ahead on them and hold the warp's issue slot while
+    // the working lane has copies or MMAs to issue (measured: the first tile's MMAs 1.7 us late).
+    if (warp < 2) __syncwarp();
+    it_base += n;
+    ++seg_no;
+    int len;
+    indexer_row_tiles(p, row, len);
+    const uint32_t guess = indexer_row_guess(p, row);
+    const bool filter_mode = guess != 0u;
+    // ---- end of the segment: every tile has been through the epilogue, so every copy and MMA of
+    // the segment has completed; the CTA counts its tiles off and the row's last CTA finishes it ----
+    if (filter_mode) __threadfence();  // this thread's candidates, before the CTA's arrival
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    if (__syncthreads_or((int)*abort_flag)) break;  // (uniform)
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (!filter_mode) continue;  // (uniform)
+    if (tid == 0) {
+      const bool last = atomicAdd(p.done_count + row, (uint32_t)n) + (uint32_t)n == (uint32_t)ntiles;
+      uint32_t count = 0u;
+      if (last) {
+        // every tile of the row has been counted off: nobody appends any more (each CTA's appends
+        // were performed before its arrival). Take the count and leave both counters at zero for
+        // the next call.
+        count = atomicExch(p.cand_count + row, 0u);
+        p.done_count[row] = 0u;
       }
-      if (!mbar_wait(&tfull[buf], bph, abort_flag)) break;
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)buf * kIdxHeads;
-      uint32_t v0[32], v1[32];
-      tmem_ld32(taddr, v0);
-      tmem_ld32(taddr + 32u, v1);
-      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      mbar_arrive(&tempty[buf]);  // the values are in registers: the accumulator buffer may be overwritten
-      float acc0 = 0.f, acc1 = 0.f;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float4 wa = w4[j], wb = w4[8 + j];
-        acc0 = fmaf(wa.x, fmaxf(__uint_as_float(v0[4 * j + 0]), 0.f), acc0);
-        acc1 = fmaf(wb.x, fmaxf(__uint_as_float(v1[4 * j + 0]), 0.f), acc1);
-        acc0 = fmaf(wa.y, fmaxf(__uint_as_float(v0[4 * j + 1]), 0.f), acc0);
-        acc1 = fmaf(wb.y, fmaxf(__uint_as_float(v1[4 * j + 1]), 0.f), acc1);
-        acc0 = fmaf(wa.z, fmaxf(__uint_as_float(v0[4 * j + 2]), 0.f), acc0);
-        acc1 = fmaf(wb.z, fmaxf(__uint_as_float(v1[4 * j + 2]), 0.f), acc1);
-        acc0 = fmaf(wa.w, fmaxf(__uint_as_float(v0[4 * j + 3]), 0.f), acc0);
-        acc1 = fmaf(wb.w, fmaxf(__uint_as_float(v1[4 * j + 3]), 0.f), acc1);
-      }
-      // relu(s * x) = s * relu(x) for a positive scale: the key's scale multiplies the finished sum
-      const float logit = (acc0 + acc1) * scale;
-      if (valid) p.logits[(int64_t)row * p.logits_stride + key] = logit;
-      if (filter_mode) {
-        const bool hit = valid && !(logit < edge);
-        const unsigned b = __ballot_sync(kFull, hit);
-        if (b) {
-          uint32_t slot = 0;
-          if (lane == 0) slot = atomicAdd(p.cand_count + row, (uint32_t)__popc(b));
-          slot = __shfl_sync(kFull, slot, 0) + (uint32_t)__popc(b & lt);
-          if (hit && slot < (uint32_t)kIdxCandCap)
-            p.cand[(size_t)row * kIdxCandCap + slot] =
-                ((uint64_t)fftopk_key_from_bits(__float_as_uint(logit)) << 32) | (uint64_t)(~(uint32_t)key);
-        }
-      }
+      last_flag[0] = last ? 1u : 0u;
+      last_flag[1] = count;
+    }
+    __syncthreads();
+    if (last_flag[0] != 0u) {  // (uniform)
+      __threadfence();
+      // the stages hold the list, q's place the histogram
+      indexer_finish_row<kIdxThreads>(p, row, len, guess, last_flag[1], reinterpret_cast<uint64_t*>(a_smem),
+                                      reinterpret_cast<uint32_t*>(q_smem), fin_ctrl);
+      // the next segment's copies overwrite what the threads wrote there
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncthreads();
     }
   }
   // ---- wind down ---------------------------------------------------------------------------------
   if (*abort_flag) {
     // a wait ran out: give copies that may still be in flight a moment to land before the shared
-    // memory goes away
+    // memory goes away. The rows of this call are not all finished and their counters not all back
+    // at zero: the caller sees the status bit and zero-fills the workspace again.
     unsigned long long t0, t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
     do {
@@ -450,32 +624,6 @@ __global__ void __launch_bounds__(kIdxThreads, FFTOPK_IDX_CTAS_PER_SM)
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(kIdxBufs * kIdxHeads))
                  : "memory");
   }
-  if (!filter_mode) return;  // (uniform)
-  // ---- the row's CTAs count themselves off; the last one finishes the row ------------------------
-  __threadfence();  // this thread's candidates, before the CTA's arrival
-  __syncthreads();
-  if (tid == 0) {
-    // a CTA that gave up leaves the list incomplete: a count no list can hold sends the row to the fallback
-    if (*abort_flag) atomicAdd(p.cand_count + row, 0x40000000u);
-    const uint32_t nwork = (uint32_t)min((int)gridDim.x, ntiles);
-    const bool last = atomicAdd(p.done_count + row, 1u) == nwork - 1u;
-    uint32_t count = 0u;
-    if (last) {
-      // every CTA of the row has arrived: nobody appends any more. Take the count and leave both
-      // counters at zero for the next call.
-      __threadfence();
-      count = atomicExch(p.cand_count + row, 0u);
-      p.done_count[row] = 0u;
-    }
-    last_flag[0] = last ? 1u : 0u;
-    last_flag[1] = count;
-  }
-  __syncthreads();
-  if (last_flag[0] == 0u) return;  // (uniform)
-  __threadfence();
-  // every copy and MMA of this CTA has completed: the stages hold the list, q's place the histogram
-  indexer_finish_row<kIdxThreads>(p, row, len, guess, last_flag[1], reinterpret_cast<uint64_t*>(a_smem),
-                                  reinterpret_cast<uint32_t*>(q_smem), fin_ctrl);
 }
 
 }  // namespace fftopk
@@ -497,7 +645,8 @@ std::mutex g_encode_mu;
 constexpr size_t indexer_smem_bytes(bool fp8) {
   return 1024 +
          (fp8 ? (size_t)IdxFmt<true>::kStages * IdxFmt<true>::kTileBytes : (size_t)IdxFmt<false>::kStages * IdxFmt<false>::kTileBytes) +
-         (fp8 ? IdxFmt<true>::kQBytes : IdxFmt<false>::kQBytes) + kIdxHeads * 4 + 32 * 8 + 64 + sizeof(Ctrl);
+         (fp8 ? IdxFmt<true>::kQBytes : IdxFmt<false>::kQBytes) + kIdxHeads * 4 + 32 * 8 + 64 + ((sizeof(Ctrl) + 15) & ~(size_t)15) +
+         (size_t)(kIdxBalancedRows + 1) * 4 + 16;
 }
 
 int indexer_setup() {
@@ -623,10 +772,16 @@ static int indexer_topk_impl(bool fp8, const void* q, const void* k_cache, int64
   p.thr_out = thresholds;
   p.status = status;
 
+  // batches of up to kIdxBalancedRows rows: as many CTAs as are resident at once, each with an equal
+  // share of all rows' tiles (found on the device); larger batches: one CTA per row
   const int64_t ntiles = (L + kIdxTile - 1) / kIdxTile;
-  int per_row = sms * FFTOPK_IDX_CTAS_PER_SM / B > 0 ? sms * FFTOPK_IDX_CTAS_PER_SM / B : 1;
-  if (per_row > ntiles) per_row = (int)ntiles;
-  const dim3 grid((unsigned)per_row, (unsigned)B);
+  int64_t ctas = B;
+  if (B <= kIdxBalancedRows) {
+    ctas = (int64_t)sms * FFTOPK_IDX_CTAS_PER_SM;
+    if (ctas > (int64_t)B * ntiles) ctas = (int64_t)B * ntiles;
+    if (ctas < 1) ctas = 1;
+  }
+  const dim3 grid((unsigned)ctas, 1u, 1u);
   // the producer: logits; rows with a guess are filtered as the logits are produced and finished
   // by their last CTA
   e = fp8 ? launch_producer<true>(grid, stream, map_q, map_k, p) : launch_producer<false>(grid, stream, map_q, map_k, p);

@@ -47,7 +47,9 @@ def kth_keys(logits, lengths):
     return np.array(out, dtype=np.uint32)
 
 
-@pytest.mark.parametrize("B,L", [(1, 4096), (3, 50000), (1, 300000), (8, 20000)])
+# (1000 rows of 2200 keys: every producer CTA goes through several whole rows and finishes them;
+#  1100 rows: more than the balanced split handles, one CTA per row)
+@pytest.mark.parametrize("B,L", [(1, 4096), (3, 50000), (1, 300000), (8, 20000), (1000, 2200), (1100, 2500)])
 def test_logits_match_torch_and_selection_is_exact(B, L):
     q, k, w = make(B, L, seed=B * 1000 + L)
     ln = torch.full((B,), L, dtype=torch.int32)
@@ -66,7 +68,12 @@ def test_logits_match_torch_and_selection_is_exact(B, L):
     logits_np = got.numpy().copy()
     orc.check_result(logits_np, ln.numpy(), out.cpu().numpy(), what="cold")
     want = kth_keys(logits_np, ln.numpy())
-    assert np.array_equal(f.thresholds.cpu().numpy().view(np.uint32)[:B], want)
+    # what the selector hands back is the row's k-th largest key, or - where it could take a whole
+    # bin without a finish, as in rows of barely more than k keys - a lower bound of it
+    thr = f.thresholds.cpu().numpy().view(np.uint32)[:B]
+    assert np.all(thr <= want) and np.array_equal(thr > 0, want > 0)
+    if L > 4 * K:
+        assert np.array_equal(thr, want)
     # the same inputs again: every row with more than k keys now has a guess and its logits are
     # filtered in the producer's epilogue (they are written all the same, and must be the same bits)
     f.logits.fill_(float("nan"))
