@@ -864,19 +864,22 @@ def profile_case(name: str) -> None:
             fast_topk_v3_host(hs, hl, K, out=ho)
         torch.cuda.synchronize()
         print(json.dumps({"case": "host", "launches": 3}))
-    elif name == "indexer":
+    elif name in ("indexer", "indexer_fp8"):
         from jit_kernel.indexer import FusedIndexerTopk
         L = 1 << 20
+        fp8 = name == "indexer_fp8"
+        dt = torch.float8_e4m3fn if fp8 else torch.bfloat16
         g = torch.Generator(device="cpu").manual_seed(L)
-        q = torch.randn(1, 64, 128, generator=g).to(torch.bfloat16).to(dev)
-        ks = [torch.randn(1, L, 128, generator=g).to(torch.bfloat16).to(dev) for _ in range(2)]  # 2 x 256 MiB > L2
+        q = (torch.randn(1, 64, 128, generator=g) * 0.5).to(dt).to(dev)
+        ks = [(torch.randn(1, L, 128, generator=g) * 0.5).to(dt).to(dev) for _ in range(3 if fp8 else 2)]  # more than L2 together
+        scale = (torch.rand(1, L, generator=g) + 0.5).to(dev) if fp8 else None
         w = torch.rand(1, 64, generator=g).to(dev)
         ln = torch.full((1,), L, dtype=torch.int32, device=dev)
-        fs = [FusedIndexerTopk(1, L, dev) for _ in range(2)]
-        for i in range(8):  # calls 0 and 1 seed the thresholds, the rest run with a guess
-            fs[i % 2](q, ks[i % 2], w, ln)
+        fs = [FusedIndexerTopk(1, L, dev) for _ in ks]
+        for i in range(9):  # the first call on every cache seeds its threshold, the rest run with a guess
+            fs[i % len(ks)](q, ks[i % len(ks)], w, ln, k_scale=scale)
         torch.cuda.synchronize()
-        print(json.dumps({"case": "indexer", "calls": 8, "L": L}))
+        print(json.dumps({"case": name, "calls": 9, "L": L}))
     elif name == "probe":
         stream = torch.cuda.Stream(device=dev)
         print(json.dumps({"case": "probe", "read_gbs": measure_l2_read_gbs(dev, stream)}))
@@ -899,7 +902,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=50)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip the latency sweep and the CPU baseline")
-    ap.add_argument("--case", default=None, choices=["b1", "warm", "merge", "tp", "serial", "f16", "host", "probe", "indexer"], help="run one small fixed case (for profilers)")
+    ap.add_argument("--case", default=None, choices=["b1", "warm", "merge", "tp", "serial", "f16", "host", "probe", "indexer", "indexer_fp8"], help="run one small fixed case (for profilers)")
     args = ap.parse_args()
     if args.case:
         profile_case(args.case)
