@@ -388,6 +388,9 @@ __global__ void __launch_bounds__(kIdxThreads, FFTOPK_IDX_CTAS_PER_SM)
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   if (tid == 0) {
+    // the copies' descriptors, on their way while the tile table is built
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_q)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_k)) : "memory");
     for (int s = 0; s < kIdxStages; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);

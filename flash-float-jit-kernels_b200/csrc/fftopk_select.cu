@@ -1277,11 +1277,12 @@ template <int NT, bool kAnyK = false, bool kWarm = false, class T = float>
 __global__ void __launch_bounds__(NT, (NT == 512 ? FFTOPK_CTAS_512 : 1024 / NT)) select2048_kernel(const SelectParams p) {
   select_row<NT, kAnyK, kWarm, T>(p);
   if (p.cp_publish) {
-    // Context-parallel publication folded into the selection: every thread fences its output
-    // writes, the CTA arrives, and the last CTA of the grid releases the epoch flag system-wide
-    // (peers acquire it in their merge kernel). The counter goes back to zero for the next launch,
-    // which stream order keeps behind this one.
-    __threadfence();
+    // Context-parallel publication folded into the selection: the CTA's barrier orders every
+    // thread's output writes before thread 0's arrival, a release at device scope (one operation
+    // by the arriving thread, as in a grid-wide barrier, instead of a fence per thread); the last
+    // CTA of the grid, which has acquired all the others' arrivals, releases the epoch flag
+    // system-wide (peers acquire it in their merge kernel). The counter goes back to zero for the
+    // next launch, which stream order keeps behind this one.
     __syncthreads();
     if (threadIdx.x == 0) {
       uint32_t* arrive = p.cp_publish + kCommArriveWord;
