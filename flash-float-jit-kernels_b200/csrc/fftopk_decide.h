@@ -130,4 +130,37 @@ FFTOPK_DECIDE_HD uint64_t single_key_floor(uint64_t lo, int idx_bits) {
   return (lo & 0xffffffff00000000ull) | (uint64_t)(~((idx_bits >= 32 ? 0u : (1u << idx_bits)) - 1u));
 }
 
+// ---------------------------------------------------------------------------------------------
+// Work split of the fused indexer's producer. The tiles of all rows, row after row, form one
+// sequence of `total` tiles; first_tile[r] (r <= rows) is the number of tiles of the rows before r.
+// CTA c of `ctas` takes the run [g0, g1): total = each * ctas + rest, and the first `rest` CTAs
+// take one tile more. The part of a run inside one row is a segment.
+// ---------------------------------------------------------------------------------------------
+struct TileRun {
+  uint32_t g0, g1;
+};
+FFTOPK_DECIDE_HD TileRun tile_run(uint32_t total, uint32_t ctas, uint32_t cta) {
+  const uint32_t each = total / ctas, rest = total % ctas;
+  const uint32_t g0 = cta * each + (cta < rest ? cta : rest);
+  return TileRun{g0, g0 + each + (cta < rest ? 1u : 0u)};
+}
+// the last row that starts at or before tile g (rows >= 1)
+FFTOPK_DECIDE_HD int tile_row_at(const uint32_t* first_tile, int rows, uint32_t g) {
+  int lo = 0, hi = rows;
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (first_tile[mid] <= g) lo = mid; else hi = mid;
+  }
+  return lo;
+}
+// Segment of the run [g, g1) inside a row that starts at tile row_g0 and has ntiles tiles: the
+// first row-local tile and the tile count; false if the row has no tile at or behind g.
+FFTOPK_DECIDE_HD bool tile_segment(uint32_t row_g0, uint32_t ntiles, uint32_t g, uint32_t g1, int& t_lo, int& n) {
+  if (row_g0 + ntiles <= g) return false;
+  const uint32_t end = g1 < row_g0 + ntiles ? g1 : row_g0 + ntiles;
+  t_lo = (int)(g - row_g0);
+  n = (int)(end - g);
+  return true;
+}
+
 }  // namespace fftopk

@@ -426,9 +426,9 @@ __global__ void __launch_bounds__(kIdxThreads, FFTOPK_IDX_CTAS_PER_SM)
       if (total == 0u && blockIdx.x == 0) p.select_rows[0] = 1u;
     }
     __syncthreads();
-    const uint32_t each = total / gridDim.x, rest = total % gridDim.x;
-    g0 = blockIdx.x * each + min(blockIdx.x, rest);
-    g1 = g0 + each + (blockIdx.x < rest ? 1u : 0u);
+    const TileRun run = tile_run(total, gridDim.x, blockIdx.x);
+    g0 = run.g0;
+    g1 = run.g1;
   } else if (balanced) {
     constexpr int PER = (kIdxBalancedRows + kIdxThreads - 1) / kIdxThreads;
     uint32_t mine[PER];
@@ -460,18 +460,10 @@ __global__ void __launch_bounds__(kIdxThreads, FFTOPK_IDX_CTAS_PER_SM)
       if (r == p.B - 1) first_tile[p.B] = run;
     }
     __syncthreads();
-    // total = each * CTAs + rest: the first `rest` CTAs take one tile more
-    const uint32_t total = first_tile[p.B];
-    const uint32_t each = total / gridDim.x, rest = total % gridDim.x;
-    g0 = blockIdx.x * each + min(blockIdx.x, rest);
-    g1 = g0 + each + (blockIdx.x < rest ? 1u : 0u);
-    // the last row that starts at or before g0
-    int lo = 0, hi = p.B;
-    while (hi - lo > 1) {
-      const int mid = (lo + hi) >> 1;
-      if (first_tile[mid] <= g0) lo = mid; else hi = mid;
-    }
-    row = lo;
+    const TileRun own = tile_run(first_tile[p.B], gridDim.x, blockIdx.x);
+    g0 = own.g0;
+    g1 = own.g1;
+    row = tile_row_at(first_tile, p.B, g0);
   } else {
     row = (int)blockIdx.x;
     int len_r;
@@ -496,10 +488,8 @@ __global__ void __launch_bounds__(kIdxThreads, FFTOPK_IDX_CTAS_PER_SM)
     // (tile counts out of shared memory: the thread that issues the copies waits for no global load)
     const uint32_t row_g0 = balanced ? first_tile[row] : 0u;
     const int ntiles = balanced ? (int)(first_tile[row + 1] - row_g0) : (int)g1;
-    if (row_g0 + (uint32_t)ntiles <= g) continue;  // (a row without tiles)
-    int t_lo = (int)(g - row_g0);
-    const int t_hi = (int)(min(g1, row_g0 + (uint32_t)ntiles) - row_g0);
-    const int n = t_hi - t_lo;
+    int t_lo, n;
+    if (!tile_segment(row_g0, (uint32_t)ntiles, g, g1, t_lo, n)) continue;  // (a row without tiles)
     g += (uint32_t)n;
     int t_step = 1;
     if (p.B == 1) {

@@ -36,4 +36,37 @@ void dh_finish_bin_range(uint64_t lo, uint64_t focus, uint64_t cap, int t, uint6
 }
 uint64_t dh_single_key_floor(uint64_t lo, int idx_bits) { return single_key_floor(lo, idx_bits); }
 
+
+// Walks every CTA's run of tiles the way the fused indexer's producer does (tile_run, tile_row_at,
+// then tile_segment row after row) and adds, for every (row, row-local tile) the CTAs visit, one to
+// visits[first_tile[row] + tile]. segs_out receives the number of segments each CTA went through.
+// Returns 0, or a negative code when a walk leaves the table.
+int dh_walk_tile_split(const uint32_t* first_tile, int rows, uint32_t ctas, uint32_t* visits, uint32_t* segs_out) {
+  const uint32_t total = first_tile[rows];
+  for (uint32_t c = 0; c < ctas; ++c) {
+    const TileRun run = tile_run(total, ctas, c);
+    if (run.g1 < run.g0 || run.g1 > total) return -1;
+    uint32_t segs = 0;
+    if (run.g0 < run.g1) {
+      int row = tile_row_at(first_tile, rows, run.g0);
+      for (uint32_t g = run.g0; g < run.g1; ++row) {
+        if (row >= rows) return -2;
+        int t_lo, n;
+        if (!tile_segment(first_tile[row], first_tile[row + 1] - first_tile[row], g, run.g1, t_lo, n)) continue;
+        if (n <= 0 || t_lo < 0 || (uint32_t)(t_lo + n) > first_tile[row + 1] - first_tile[row]) return -3;
+        for (int i = 0; i < n; ++i) ++visits[first_tile[row] + (uint32_t)(t_lo + i)];
+        g += (uint32_t)n;
+        ++segs;
+      }
+    }
+    segs_out[c] = segs;
+  }
+  return 0;
+}
+void dh_tile_run(uint32_t total, uint32_t ctas, uint32_t cta, uint32_t* g0, uint32_t* g1) {
+  const TileRun r = tile_run(total, ctas, cta);
+  *g0 = r.g0;
+  *g1 = r.g1;
+}
+
 }  // extern "C"

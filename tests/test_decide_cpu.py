@@ -6,7 +6,9 @@ guess -> float edge -> filter -> keep-or-fall-back) is run end to end on the hos
   * whatever the data and the sample, the attempt is either abandoned or admits a superset of the
     true top k; on i.i.d. rows it is practically never abandoned and admits few extras;
   * finish digits are monotone over the candidate range, stay inside the bin count, agree between
-    the key-only and the full form, and bin ranges tile the range.
+    the key-only and the full form, and bin ranges tile the range;
+  * the fused indexer's work split visits every tile of every row exactly once, whatever the rows'
+    lengths and the number of CTAs, and no CTA gets more than one tile more than another.
 """
 import ctypes
 import subprocess
@@ -41,6 +43,8 @@ def dh(tmp_path_factory):
         "dh_finish_digit": (u32, [u64, u64, u64]), "dh_finish_digit_of_key": (u32, [u64, u64, u32]),
         "dh_finish_bin_range": (None, [u64, u64, u64, i32, ctypes.POINTER(u64), ctypes.POINTER(u64)]),
         "dh_single_key_floor": (u64, [u64, i32]),
+        "dh_walk_tile_split": (i32, [ctypes.c_void_p, i32, u32, ctypes.c_void_p, ctypes.c_void_p]),
+        "dh_tile_run": (None, [u32, u32, u32, ctypes.POINTER(u32), ctypes.POINTER(u32)]),
     }
     for name, (res, args) in sigs.items():
         getattr(lib, name).restype = res
@@ -202,3 +206,38 @@ def test_single_key_floor(dh):
     f = dh.dh_single_key_floor(lo, 17)
     assert f >> 32 == 0x12345678 and (f & 0xFFFFFFFF) == 0xFFFE0000
     assert dh.dh_single_key_floor(lo, 32) == lo
+
+
+# ---- work split of the fused indexer's producer ---------------------------------------------------
+def _walk(dh, tiles_per_row, ctas):
+    first = np.concatenate([[0], np.cumsum(tiles_per_row)]).astype(np.uint32)
+    visits = np.zeros(int(first[-1]) + 1, dtype=np.uint32)
+    segs = np.zeros(ctas, dtype=np.uint32)
+    rc = dh.dh_walk_tile_split(first.ctypes.data, len(tiles_per_row), ctas, visits.ctypes.data, segs.ctypes.data)
+    return rc, first, visits, segs
+
+
+@settings(max_examples=200, deadline=None)
+@given(st.lists(st.integers(0, 2100), min_size=1, max_size=300), st.integers(1, 600))
+def test_tile_split_visits_every_tile_once(dh, tiles_per_row, ctas):
+    rc, first, visits, segs = _walk(dh, tiles_per_row, ctas)
+    assert rc == 0
+    total = int(first[-1])
+    assert np.all(visits[:total] == 1) and visits[total] == 0
+    # a CTA's segments: at most one per row it touches, and none for a CTA without tiles
+    sizes = []
+    for c in range(ctas):
+        g0, g1 = u32(), u32()
+        dh.dh_tile_run(total, ctas, c, ctypes.byref(g0), ctypes.byref(g1))
+        sizes.append(g1.value - g0.value)
+        assert (segs[c] == 0) == (g1.value == g0.value)
+    assert sum(sizes) == total and max(sizes) - min(sizes) <= 1
+
+
+def test_tile_split_edge_cases(dh):
+    # no tile at all; one row; rows without tiles at both ends and in the middle; more CTAs than tiles
+    for tiles, ctas in (([0], 296), ([0, 0, 0], 5), ([8192], 296), ([1], 296), ([0, 5, 0, 0, 7, 0], 3),
+                        ([3] * 1024, 296), ([2048] * 64, 296), ([1, 1, 1], 296)):
+        rc, first, visits, segs = _walk(dh, tiles, ctas)
+        assert rc == 0
+        assert np.all(visits[:int(first[-1])] == 1)
