@@ -164,6 +164,11 @@ def test_mixed_rows_in_one_call():
         n = int(ln[b])
         assert np.array_equal(again[b, :n].view(np.uint32), logits_np[b, :n].view(np.uint32)) and np.isnan(again[b, n:]).all()
     _status_word(DEV).zero_()
+    # every call leaves the rows' candidate and arrival counters at zero (the workspace is zero-filled once):
+    # [B x 8192 composites][candidate counts][arrival counts][selector marks], each array padded to 256 bytes
+    ws = f._ws[f._ws_ptr - f._ws.data_ptr():]
+    count_off, pad = B * 8192 * 8, (B * 4 + 255) // 256 * 256
+    assert int(ws[count_off:count_off + 2 * pad].to(torch.int32).abs().sum()) == 0
     for nb in (B, 3):
         out = f(q[:nb], k[:nb], w[:nb], ln[:nb].to(DEV))
         torch.cuda.synchronize()
