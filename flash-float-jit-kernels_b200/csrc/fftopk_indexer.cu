@@ -82,6 +82,16 @@ struct IdxFmt {
                                          ((uint32_t)(kIdxHeads >> 3) << 17) | ((uint32_t)(kIdxTile >> 4) << 24);
 };
 constexpr int kIdxBufs = 4;         // TMEM accumulators of 64 columns: the MMAs run up to four tiles ahead of the epilogue
+// fp8: the per-key scales of a tile ride along with it as one 512-byte bulk copy onto the same
+// barrier. Their shared-memory slots form a ring of stages + accumulators entries: the copy for
+// tile i reuses the slot of tile i - ring, whose epilogue read its scales before it released its
+// accumulator, which the MMAs of tile i - stages - whose completion frees the stage this copy waits
+// for - had to wait for. (As loads in the epilogue the same 4 MB cost 2 us per call at 1M keys.)
+template <bool kFp8>
+struct IdxScaleRing {
+  static constexpr int kSlots = kFp8 ? IdxFmt<true>::kStages + kIdxBufs : 0;
+};
+constexpr uint32_t kIdxScaleBytes = kIdxTile * 4;
 constexpr int kIdxCandCap = 8192;  // slots of a row's candidate list: what the freed stages of a CTA hold (64 KiB of composites)
 constexpr unsigned long long kIdxWaitNs = 200ull * 1000 * 1000;
 
@@ -89,6 +99,7 @@ struct IndexerParams {
   const float* w;            // [B, 64] head weights
   const float* k_scale;      // fp8 only: [B, k_scale_stride] one scale per key, or nullptr
   int64_t k_scale_stride;
+  int32_t scale_bulk;        // k_scale and its stride are 16-byte aligned: the scales of a tile travel as one bulk copy
   const int32_t* lengths;    // [B]
   int64_t k_rows_per_seq;    // rows of the key tensor map per batch row
   int32_t B;
@@ -149,6 +160,13 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
           smem_u32(smem_dst)),
       "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
       : "memory");
+}
+// 1-D bulk copy global -> shared (16-byte aligned addresses, size a multiple of 16 bytes)
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(smem_dst)),
+               "l"(src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
 }
 // Shared-memory matrix descriptor of a K-major operand in the 128-byte-swizzle layout a TMA box of
 // 128 bytes (64 bf16 or 128 fp8) x rows produces: rows of 128 bytes, groups of 8 rows 1024 bytes apart.
@@ -258,6 +276,16 @@ __device__ __forceinline__ int indexer_row_tiles(const IndexerParams& p, int row
   return (len + kIdxTile - 1) / kIdxTile;
 }
 
+// whether the scales of a row's tile t travel with the tile (a bulk copy of 128 floats): the copy
+// must stay inside the row's scale array
+template <bool kFp8>
+__device__ __forceinline__ bool idx_scales_by_copy(const IndexerParams& p, int t) {
+  if constexpr (kFp8) {
+    return p.k_scale != nullptr && p.scale_bulk != 0 && (int64_t)(t + 1) * kIdxTile <= p.k_scale_stride;
+  } else {
+    return false;
+  }
+}
 // the key guess a row is filtered with: the caller's, less the margin (0: none)
 __device__ __forceinline__ uint32_t indexer_row_guess(const IndexerParams& p, int row) {
   const uint32_t raw = p.guess != nullptr ? p.guess[row] : 0u;
@@ -272,7 +300,7 @@ __device__ __forceinline__ uint32_t indexer_row_guess(const IndexerParams& p, in
 template <bool kFp8>
 __device__ __noinline__ void indexer_epilogue_segment(const IndexerParams& p, int row, int t_lo, int t_step, int n, int it_base,
                                                       uint32_t tmem_base, uint64_t* tfull, uint64_t* tempty,
-                                                      volatile uint32_t* abort_flag, float* w_smem) {
+                                                      volatile uint32_t* abort_flag, float* w_smem, const float* ks_smem) {
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
   const int group = (warp - 2) >> 2;
@@ -293,13 +321,16 @@ __device__ __noinline__ void indexer_epilogue_segment(const IndexerParams& p, in
     const int it = it_base + i;
     const int buf = it % kIdxBufs;
     const uint32_t bph = (uint32_t)(it / kIdxBufs) & 1u;
-    const int key = (t_lo + i * t_step) * kIdxTile + key_in_tile;
+    const int t = t_lo + i * t_step;
+    const int key = t * kIdxTile + key_in_tile;
     const bool valid = key < len;
-    // the key's scale is asked for before the wait: its memory latency hides behind the tile's
-    // copy and MMAs instead of sitting at the end of the epilogue
+    // The key's scale: out of the ring in shared memory where the tile's copy brought it (read below,
+    // before the accumulator is released: see IdxScaleRing), else loaded here, before the wait,
+    // so that its latency hides behind the tile's copy and MMAs.
     float scale = 1.f;
+    const bool scales = idx_scales_by_copy<kFp8>(p, t);
     if constexpr (kFp8) {
-      if (p.k_scale != nullptr && valid) scale = __ldg(p.k_scale + (int64_t)row * p.k_scale_stride + key);
+      if (p.k_scale != nullptr && !scales && valid) scale = __ldg(p.k_scale + (int64_t)row * p.k_scale_stride + key);
     }
     if (!mbar_wait(&tfull[buf], bph, abort_flag)) break;
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -308,6 +339,9 @@ __device__ __noinline__ void indexer_epilogue_segment(const IndexerParams& p, in
     tmem_ld32(taddr, v0);
     tmem_ld32(taddr + 32u, v1);
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+    if constexpr (kFp8) {
+      if (scales) scale = ks_smem[(it % IdxScaleRing<kFp8>::kSlots) * kIdxTile + key_in_tile];
+    }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     mbar_arrive(&tempty[buf]);  // the values are in registers: the accumulator buffer may be overwritten
     float acc0 = 0.f, acc1 = 0.f;
@@ -368,7 +402,8 @@ __global__ void __launch_bounds__(kIdxThreads, FFTOPK_IDX_CTAS_PER_SM)
   unsigned char* a_smem = base;                                   // kIdxStages x 32 KiB
   unsigned char* q_smem = a_smem + (size_t)kIdxStages * kIdxTileBytes;  // 16 / 8 KiB
   float* w_smem = reinterpret_cast<float*>(q_smem + kIdxQBytes);  // 64 floats
-  uint64_t* bars = reinterpret_cast<uint64_t*>(w_smem + kIdxHeads);
+  float* ks_smem = w_smem + kIdxHeads;                            // fp8: ring of per-tile key scales
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ks_smem + IdxScaleRing<kFp8>::kSlots * kIdxTile);
   uint64_t* full = bars;                     // [kIdxStages]
   uint64_t* empty = bars + kIdxStages;       // [kIdxStages]
   uint64_t* tfull = bars + 2 * kIdxStages;   // [kIdxBufs]
@@ -516,12 +551,19 @@ __global__ void __launch_bounds__(kIdxThreads, FFTOPK_IDX_CTAS_PER_SM)
           const int s = it % kIdxStages;
           const uint32_t ph = (uint32_t)(it / kIdxStages) & 1u;
           if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag)) break;
-          mbar_expect_tx(&full[s], kIdxTileBytes);
-          const int y = (int)((int64_t)row * p.k_rows_per_seq + (int64_t)(t_lo + i * t_step) * kIdxTile);
+          const int t = t_lo + i * t_step;
+          const bool scales = idx_scales_by_copy<kFp8>(p, t);
+          mbar_expect_tx(&full[s], kIdxTileBytes + (scales ? kIdxScaleBytes : 0u));
+          const int y = (int)((int64_t)row * p.k_rows_per_seq + (int64_t)t * kIdxTile);
           unsigned char* dst = a_smem + (size_t)s * kIdxTileBytes;
 #pragma unroll
           for (int bx = 0; bx < F::kBoxes; ++bx)
             tma_load_2d(dst + (size_t)bx * (kIdxTileBytes / F::kBoxes), &map_k, bx * F::kChunk, y, &full[s]);
+          if constexpr (kFp8) {
+            if (scales)
+              bulk_load(ks_smem + (it % IdxScaleRing<kFp8>::kSlots) * kIdxTile,
+                        p.k_scale + (int64_t)row * p.k_scale_stride + (int64_t)t * kIdxTile, kIdxScaleBytes, &full[s]);
+          }
         }
       }
     } else if (warp == 1) {
@@ -556,7 +598,7 @@ __global__ void __launch_bounds__(kIdxThreads, FFTOPK_IDX_CTAS_PER_SM)
       }
     } else {
       // ---- epilogue ---------------------------------------------------------------------------------
-      indexer_epilogue_segment<kFp8>(p, row, t_lo, t_step, n, it_base, tmem_base, tfull, tempty, abort_flag, w_smem);
+      indexer_epilogue_segment<kFp8>(p, row, t_lo, t_step, n, it_base, tmem_base, tfull, tempty, abort_flag, w_smem, ks_smem);
     }
     // The idle lanes of the two single-thread warps wait here for their working lane: what follows
     // (global loads, a fence) would otherwise run ahead on them and hold the warp's issue slot while
@@ -641,7 +683,8 @@ std::mutex g_encode_mu;
 constexpr size_t indexer_smem_bytes(bool fp8) {
   return 1024 +
          (fp8 ? (size_t)IdxFmt<true>::kStages * IdxFmt<true>::kTileBytes : (size_t)IdxFmt<false>::kStages * IdxFmt<false>::kTileBytes) +
-         (fp8 ? IdxFmt<true>::kQBytes : IdxFmt<false>::kQBytes) + kIdxHeads * 4 + 32 * 8 + 64 + ((sizeof(Ctrl) + 15) & ~(size_t)15) +
+         (fp8 ? IdxFmt<true>::kQBytes : IdxFmt<false>::kQBytes) + kIdxHeads * 4 + (fp8 ? IdxScaleRing<true>::kSlots * kIdxScaleBytes : 0) +
+         32 * 8 + 64 + ((sizeof(Ctrl) + 15) & ~(size_t)15) +
          (size_t)(kIdxBalancedRows + 1) * 4 + 16;
 }
 
@@ -752,6 +795,7 @@ static int indexer_topk_impl(bool fp8, const void* q, const void* k_cache, int64
   p.w = w;
   p.k_scale = k_scale;
   p.k_scale_stride = k_scale_stride;
+  p.scale_bulk = (k_scale != nullptr && (reinterpret_cast<uintptr_t>(k_scale) & 15u) == 0 && (k_scale_stride & 3) == 0) ? 1 : 0;
   p.lengths = lengths;
   p.k_rows_per_seq = k_rows_per_seq;
   p.B = B;

@@ -208,7 +208,9 @@ def make_fp8(B, L, seed):
 
 
 @pytest.mark.parametrize("with_scale", [False, True])
-@pytest.mark.parametrize("B,L", [(1, 4096), (2, 70000), (1, 300000)])
+# (70001 keys: a scale array whose rows are not 16-byte aligned - the scales are then loaded key by key
+#  instead of travelling with the tiles)
+@pytest.mark.parametrize("B,L", [(1, 4096), (2, 70000), (2, 70001), (1, 300000)])
 def test_fp8_operands(B, L, with_scale):
     """fp8 (e4m3) q and key cache, optional per-key scale: logits against torch on the widened
     operands, selection exact on the kernel's own logits, cold and with a guess."""
