@@ -445,6 +445,11 @@ __global__ void __launch_bounds__(kIdxThreads, FFTOPK_IDX_CTAS_PER_SM)
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  // Everything above touched shared and tensor memory only. From here on the kernel in front of this
+  // one on the stream (the selector of the call before, in a decode loop) has to have completed:
+  // the producer is launched as its programmatic dependent, so its launch and this prologue hide
+  // behind that kernel.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 
   // ---- this CTA's run of tiles [g0, g1) and the row it starts in (the barriers in here also
   // publish the mbarriers and the TMEM address) ------------------------------------------------------
@@ -748,9 +753,19 @@ IndexerLayout indexer_layout(int32_t B) {
 template <bool kFp8>
 cudaError_t launch_producer(dim3 grid, cudaStream_t stream, const CUtensorMap& map_q, const CUtensorMap& map_k,
                             const IndexerParams& p) {
-  // (a plain launch: it orders itself after whatever the stream holds)
-  indexer_logits_kernel<kFp8><<<grid, kIdxThreads, indexer_smem_bytes(kFp8), stream>>>(map_q, map_k, p);
-  return cudaGetLastError();
+  // a programmatic dependent of whatever kernel the stream holds in front of it: the kernel waits
+  // for that one (griddepcontrol.wait) before it touches global memory
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(kIdxThreads, 1, 1);
+  cfg.dynamicSmemBytes = indexer_smem_bytes(kFp8);
+  cfg.stream = stream;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, indexer_logits_kernel<kFp8>, map_q, map_k, p);
 }
 
 }  // namespace
@@ -838,8 +853,7 @@ static int indexer_topk_impl(bool fp8, const void* q, const void* k_cache, int64
   c.cuda_stream = cuda_stream;
   c.next_threshold = thresholds;
   c.only_rows = p.select_rows;
-  c.may_overlap = false;
-  c.wait_prior = true;  // a programmatic dependent of the producer
+  c.may_overlap = false;  // (a programmatic dependent of the producer that waits for it, like every default launch)
   return launch_select(c);
 }
 

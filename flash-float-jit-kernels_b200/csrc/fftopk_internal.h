@@ -44,15 +44,12 @@ struct SelectCall {
   uint32_t warm_margin = 0;
   const uint32_t* only_rows = nullptr;  // with next_threshold: select only rows whose entry is non-zero
   // false: this launch consumes what a kernel enqueued just before it by the library itself has
-  // produced (gathered rows, widened scores, slice lengths), or hands its output to a kernel the
-  // library enqueues right after it. Such a launch keeps plain stream order whatever
-  // fftopk_set_overlap says: a programmatic dependent launch that never executes
-  // griddepcontrol.wait has no guarantee that its predecessor's writes are visible.
+  // produced (gathered rows, widened scores, slice lengths, indexer logits), or hands its output to
+  // a kernel the library enqueues right after it. Such a launch keeps stream order whatever
+  // fftopk_set_overlap says: it executes griddepcontrol.wait like every launch in the default mode
+  // (a programmatic dependent launch that does not has no guarantee that its predecessor's writes
+  // are visible).
   bool may_overlap = true;
-  // true (warm-start kernel only): launch as a programmatic dependent of the kernel enqueued just
-  // before it; the kernel then waits for that kernel's completion (griddepcontrol.wait) before it
-  // reads anything, so only its launch latency overlaps
-  bool wait_prior = false;
 };
 
 int launch_select(const SelectCall& c);

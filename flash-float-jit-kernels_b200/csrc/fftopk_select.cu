@@ -99,7 +99,6 @@ struct SelectParams {
   uint32_t* next_threshold;
   uint32_t warm_margin;
   const uint32_t* only_rows;  // (warm-start kernel only) when set: rows with only_rows[row] == 0 are left alone
-  int32_t wait_prior;         // (warm-start kernel only) launched as a programmatic dependent: wait for the kernel before it
 };
 
 
@@ -756,19 +755,22 @@ __device__ __forceinline__ void select_row(const SelectParams& p) {
   const int C = cx.C = (int)cluster.num_blocks();
   const int rank = cx.rank = (int)cluster.block_rank();
   const int row = (int)(blockIdx.x / (unsigned)C);
+  // Back-to-back kernels on one stream (every launch of this kernel is a programmatic dependent
+  // launch): once every CTA of this grid has passed this point - or exited - the next kernel on
+  // the stream may become resident on whatever the grid leaves free. By default this kernel then
+  // waits, before its first access to global memory, until the kernel in front of it has
+  // completed and its writes are visible - stream order as ever, but the launch latency of a call
+  // hides behind the call before it (2 to 3 us per call in a chain of dependent calls). Only when
+  // the caller has declared consecutive calls independent (fftopk_set_overlap) does it not wait:
+  // the next call then fills the SMs that short rows free early.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (!p.overlap) asm volatile("griddepcontrol.wait;" ::: "memory");
   if constexpr (kWarm) {
-    if (p.wait_prior) asm volatile("griddepcontrol.wait;" ::: "memory");
     if (p.only_rows != nullptr && p.only_rows[row] == 0u) return;  // (uniform over the cluster)
   }
   const int tid = threadIdx.x;
   const int lane = tid & 31, warp = tid >> 5;
   constexpr int NW = NT / 32;
-
-  // Opt-in overlap of back-to-back calls (programmatic dependent launch): once every CTA of this
-  // grid has passed this point - or exited - the next kernel on the stream may start filling the
-  // SMs that short rows free early. This kernel never waits on its predecessor, so it is only
-  // enabled when the caller has declared consecutive calls independent (fftopk_set_overlap).
-  if (p.overlap) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   int64_t row_start = p.row_starts ? (int64_t)p.row_starts[row] : 0;
   row_start = row_start < 0 ? 0 : (row_start > p.L ? p.L : row_start);
@@ -1331,6 +1333,10 @@ __global__ void __launch_bounds__(NT, (NT == 512 ? FFTOPK_CTAS_512 : 1024 / NT))
   const int row = (int)(blockIdx.x / (unsigned)C);
   const int tid = threadIdx.x;
   uint32_t* my_epoch = f.row_epoch + (int64_t)row * kCommRowFlagWords;
+  // launched as a programmatic dependent, like the selection kernel (see select_row): the call in
+  // front of this one has to have completed before the row's epoch counter is read
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   // (the previous call's update of the counter is complete - stream order - and this call's comes
   // at the very end: every CTA of the cluster reads the same value)
   const uint32_t epoch = f.epoch ? f.epoch : __ldcg(my_epoch) + 1u;
@@ -1655,7 +1661,6 @@ int launch_select(const SelectCall& c) {
   p.next_threshold = c.next_threshold;
   p.warm_margin = c.warm_margin;
   p.only_rows = c.only_rows;
-  p.wait_prior = c.wait_prior ? 1 : 0;
   const bool warm = c.prev_threshold != nullptr || c.next_threshold != nullptr;
   if (warm && (c.k != kK || pl.threads < 512)) return FFTOPK_EINVAL;
   if ((size_t)pl.smem_bytes > (size_t)d->smem_optin) return FFTOPK_ERANGE;
@@ -1672,12 +1677,10 @@ int launch_select(const SelectCall& c) {
   at[0].val.clusterDim.z = 1;
   cfg.attrs = at;
   cfg.numAttrs = 1;
-  if (c.wait_prior && !warm) return FFTOPK_EINVAL;
-  if (overlap || c.wait_prior) {
-    at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    at[1].val.programmaticStreamSerializationAllowed = 1;
-    cfg.numAttrs = 2;
-  }
+  // (every launch: see the top of select_row for what the kernel does with it)
+  at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.numAttrs = 2;
   cudaError_t e;
   const bool any_k = c.k != kK;
   if (half_width) {
@@ -1759,13 +1762,15 @@ int launch_select_merge(const SelectCall& c, void* const* comms, int32_t G, int3
   cfg.blockDim = dim3((unsigned)pl.threads, 1, 1);
   cfg.dynamicSmemBytes = (size_t)pl.smem_bytes;
   cfg.stream = static_cast<cudaStream_t>(c.cuda_stream);
-  cudaLaunchAttribute at[1];
+  cudaLaunchAttribute at[2];
   at[0].id = cudaLaunchAttributeClusterDimension;
   at[0].val.clusterDim.x = (unsigned)pl.cluster;
   at[0].val.clusterDim.y = 1;
   at[0].val.clusterDim.z = 1;
+  at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = at;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = 2;
   const cudaError_t e = pl.threads == 1024 ? cudaLaunchKernelEx(&cfg, select_merge2048_kernel<1024>, p, f)
                                            : cudaLaunchKernelEx(&cfg, select_merge2048_kernel<512>, p, f);
   if (e != cudaSuccess) return cuda_fail(e);

@@ -383,11 +383,14 @@ uint32_t fftopk_key_of(float x);
  */
 int fftopk_plan(int32_t B, int64_t L, int32_t plan[6]);
 /*
- * Overlap of back-to-back calls (off by default; process-wide). With enable = 1 every selection
- * launch is a programmatic dependent launch AND signals its own dependents at once, so when two
- * selection kernels follow each other on a stream the second starts filling SMs as soon as CTAs of
- * the first exit (short rows finish early), instead of waiting for the whole grid. The kernel
- * never waits on its predecessor. Enable it only if (1) no kernel that precedes a call on the
+ * Back-to-back calls. Every selection launch is a programmatic dependent launch and lets its own
+ * dependents become resident at once. By default the kernel executes griddepcontrol.wait before
+ * its first access to global memory: plain stream order - the kernel in front of it has completed
+ * and its writes are visible - and only the launch latency of a call hides behind the call in
+ * front of it. Overlap (off by default; process-wide): with enable = 1 the kernel does NOT wait,
+ * so when two selection kernels follow each other on a stream the second starts filling SMs as
+ * soon as CTAs of the first exit (short rows finish early), instead of waiting for the whole
+ * grid. Enable it only if (1) no kernel that precedes a call on the
  * stream hands over unfinished inputs through programmatic launch completion, and (2) calls that
  * may overlap do not share an output buffer. Kernels of other libraries around the calls keep
  * normal stream ordering. No reference counterpart.
