@@ -74,7 +74,7 @@ MIN_REGION_S = 0.05      # a timed region lasts at least this long
 MIN_GRAPH_CALLS = 200    # a captured graph holds at least this many calls
 # dram__bytes_read.sum + dram__bytes_write.sum of one select2048 launch on this workload, from the
 # ncu capture of the throughput plan (profiles/select2048_ragged_b64.md)
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 16774485  # throughput plan, mean of 3 captured launches (16.773888, 16.774912, 16.774656 MB read; 0 written)
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 16775253  # throughput plan, mean of 3 captured launches (16.775424, 16.775168, 16.775168 MB read; 0 written)
 
 
 def bench_config():
