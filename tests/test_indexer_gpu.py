@@ -176,6 +176,43 @@ def test_mixed_rows_in_one_call():
     assert kernel_status(DEV) == 0
 
 
+def test_random_ragged_batches():
+    """Batches of random size and random lengths (empty rows, rows of fewer than k keys, rows that end
+    inside a tile), three calls each - cold, warm, warm with some guesses spoilt - every row exact on
+    the logits the kernel wrote. The producer's CTAs then cross row boundaries at arbitrary places."""
+    rng = np.random.default_rng(5)
+    for trial in range(10):
+        B = int(rng.integers(1, 40))
+        Lmax = int(rng.choice([3000, 9000, 30000]))
+        q, k, w = make(B, Lmax, seed=100 + trial)
+        kinds = rng.integers(0, 10, size=B)
+        ln_np = np.where(kinds == 0, 0, np.where(kinds == 1, rng.integers(1, K + 1, size=B), rng.integers(K + 1, Lmax + 1, size=B)))
+        ln = torch.from_numpy(ln_np.astype(np.int32))
+        f = FusedIndexerTopk(B, Lmax)
+        out = f(q, k, w, ln.to(DEV))
+        torch.cuda.synchronize()
+        logits_np = f.logits[:B, :Lmax].cpu().numpy().copy()
+        orc.check_result(logits_np, ln.numpy(), out.cpu().numpy(), what=f"trial {trial} cold")
+        want = kth_keys(logits_np, ln.numpy())
+        out = f(q, k, w, ln.to(DEV))
+        torch.cuda.synchronize()
+        orc.check_result(logits_np, ln.numpy(), out.cpu().numpy(), what=f"trial {trial} warm")
+        assert np.array_equal(f.thresholds.cpu().numpy().view(np.uint32)[:B], want)
+        assert kernel_status(DEV) == 0
+        spoilt = want.copy()
+        for b in range(B):
+            if want[b] and rng.random() < 0.4:
+                spoilt[b] = want[b] + np.uint32(1 << 22) if rng.random() < 0.5 else np.uint32(1)
+        f.thresholds[:B] = torch.from_numpy(spoilt.view(np.int32).copy()).to(DEV)
+        out = f(q, k, w, ln.to(DEV))
+        torch.cuda.synchronize()
+        orc.check_result(logits_np, ln.numpy(), out.cpu().numpy(), what=f"trial {trial} spoilt guesses")
+        # (rows that went through the selector may hand back a lower bound of their k-th key)
+        thr = f.thresholds.cpu().numpy().view(np.uint32)[:B]
+        assert np.all(thr <= want) and np.array_equal(thr > 0, want > 0)
+        _status_word(DEV).zero_()
+
+
 def test_graph_replay():
     B, L = 2, 60000
     q, k, w = make(B, L, seed=13)
