@@ -471,6 +471,63 @@ def indexer_leg(dev, stream, peak_gbs):
     return out
 
 
+def indexer_drift_leg(dev, stream):
+    """The fused indexer in a decode loop whose QUERY changes from step to step (q_t = q_{t-1} plus
+    noise, at constant norm; bf16, L = 131072 keys plus one per step): how often the threshold carried
+    from the previous step still holds (a miss sends the row through the selector in the same call)
+    and the mean time per step, for three noise levels and three margins. A margin is subtracted
+    from the carried key: 2^18 is about 3 % of the logit's value, 2^20 about 12 %. (One key cache
+    of 33 MB, which stays in L2 from step to step - unlike the rotated caches of indexer_leg.)"""
+    from jit_kernel import _native
+    from jit_kernel.indexer import FusedIndexerTopk
+    from jit_kernel.topk_indexer import _status_word
+
+    L0, steps = 131072, 64
+    g = torch.Generator(device=dev).manual_seed(11)
+    k = (torch.randn(1, L0 + steps, 128, generator=g, device=dev) * 0.5).to(torch.bfloat16)
+    w = torch.rand(1, 64, generator=g, device=dev)
+    lens = [torch.full((1,), L0 + t, dtype=torch.int32, device=dev) for t in range(steps + 1)]
+    res = torch.empty(1, K, dtype=torch.int32, device=dev)
+    status = _status_word(dev)
+    out = {}
+    for noise in (0.0, 0.05, 0.2):
+        q = torch.randn(1, 64, 128, generator=g, device=dev) * 0.5
+        norm = q.norm()
+        qs = [q.to(torch.bfloat16)]
+        for _ in range(steps):
+            q = q + noise * 0.5 * torch.randn(1, 64, 128, generator=g, device=dev)
+            q = q * (norm / q.norm())
+            qs.append(q.to(torch.bfloat16))
+        row = {}
+        for margin in (0, 1 << 18, 1 << 20):
+            f = FusedIndexerTopk(1, L0 + steps, dev)
+            with torch.cuda.stream(stream):
+                f(qs[0], k, w, lens[0], out=res)
+            stream.synchronize()
+            seed = f.thresholds.clone()
+            misses = 0
+            for t in range(1, steps + 1):
+                status.zero_()
+                with torch.cuda.stream(stream):
+                    f(qs[t], k, w, lens[t], margin=margin, out=res)
+                stream.synchronize()
+                misses += 1 if (int(status.item()) & _native.ST_GUESS_MISSED) else 0
+            status.zero_()
+
+            def loop(_):
+                f.thresholds.copy_(seed)
+                for t in range(1, steps + 1):
+                    f(qs[t], k, w, lens[t], margin=margin, out=res)
+
+            gr = capture_steps(loop, 1, stream)
+            ts = sorted(time_graph(gr, stream) / steps * 1e6 for _ in range(7))
+            del gr
+            status.zero_()
+            row[f"margin_{margin}"] = {"miss_rate": misses / steps, "us_per_step": ts[len(ts) // 2]}
+        out[f"noise_{noise}"] = row
+    return out
+
+
 def large_batch_leg(dev, stream, fast_topk, peak_gbs):
     """One serialised call (default launch mode, no overlap between calls) on a batch large enough
     to fill the device by itself: B=256 and B=512 rows of the bench's ragged distribution, inputs
@@ -798,6 +855,7 @@ def ours_arm(args, rank: int, local_rank: int, world: int) -> None:
         line["large_batch"] = large_batch_leg(dev, stream, fast_topk, peak)
         line["decode_loop"] = decode_loop_leg(dev, stream)
         line["fused_indexer"] = indexer_leg(dev, stream, peak)
+        line["fused_indexer_drift"] = indexer_drift_leg(dev, stream)
         # CPU baseline on this box's host cores, bounded: the 64-row batch a few times (~20 ms each)
         cpu_reps = 10
         cpu_sec = time_cpu(score, lengths, cpu_reps, 2)
